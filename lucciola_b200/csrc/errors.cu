@@ -1,0 +1,33 @@
+// Error channel and build identification of the kernel library.
+#include "common.cuh"
+#include <cstring>
+
+namespace lb {
+static thread_local char g_error[1024] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+}  // namespace lb
+
+// Message of the last failed call on this thread.
+LB_EXPORT const char* lb_last_error() { return lb::g_error; }
+
+// Interface version; the Python side refuses a library of another version.
+LB_EXPORT int lb_abi_version() { return 1; }
+
+// Compute capability of the current device as major*10+minor, or a negative
+// CUDA error code.
+LB_EXPORT int lb_device_arch() {
+  int dev = 0, major = 0, minor = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return -(int)e;
+  e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) return -(int)e;
+  e = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+  if (e != cudaSuccess) return -(int)e;
+  return major * 10 + minor;
+}

@@ -1,0 +1,133 @@
+// Per-head RMSNorm of q and k, rotary position encoding, and the write of the
+// new keys and values into their pages: one launch for what lucciola runs as
+// two norms (src/qwen.cc:617-632), two rotations (src/qwen.cc:635-644,
+// src/kernels/rope.cu:28-60) and the cache append
+// (src/kernels/attention_paged.cu:26-44).
+//
+// Order as in the reference: norm over the head (weight [d] shared by all
+// heads), then the rotation of the pairs (i, i + rot/2) by pos * inv_freq[i]
+// ("NeoX" halves), then the write.  v is copied unchanged.  All arithmetic is
+// 32-bit; the angle is one 32-bit product of the position and a host-made
+// table entry, so a plain implementation that uses the same table gets the
+// same angle.
+//
+// Page layout of one cache layer: [page][kv_head][slot][d].
+#include "common.cuh"
+
+namespace lb {
+
+struct RopeKvParams {
+  const void* q_in; const void* k_in; const void* v_in;
+  long long q_stride, k_stride, v_stride;   // elements between token rows
+  void* q_out;                               // [T, nq, d]
+  void* k_out; void* v_out;                  // optional [T, nkv, d] (when no cache is given)
+  void* k_cache; void* v_cache;              // optional pools
+  const int* positions; const int* token_seq; const int* block_table;
+  const float* q_norm_w; const float* k_norm_w; const float* inv_freq;
+  int num_q_heads, num_kv_heads, head_dim, rot_dim, page_size, max_pages;
+  float eps;
+};
+
+template <typename T>
+__global__ void rope_kv_kernel(RopeKvParams p) {
+  extern __shared__ float smem[];
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int d = p.head_dim, half = p.rot_dim >> 1;
+  float* buf = smem + (size_t)warp * d;
+  const int pos = p.positions[t];
+  const int total_heads = p.num_q_heads + 2 * p.num_kv_heads;
+
+  for (int h = warp; h < total_heads; h += nwarps) {
+    const int kind = h < p.num_q_heads ? 0 : (h < p.num_q_heads + p.num_kv_heads ? 1 : 2);
+    const int hh = kind == 0 ? h : (kind == 1 ? h - p.num_q_heads : h - p.num_q_heads - p.num_kv_heads);
+    const T* src = kind == 0 ? (const T*)p.q_in + (size_t)t * p.q_stride + (size_t)hh * d
+                 : kind == 1 ? (const T*)p.k_in + (size_t)t * p.k_stride + (size_t)hh * d
+                             : (const T*)p.v_in + (size_t)t * p.v_stride + (size_t)hh * d;
+    T* dst = nullptr;
+    if (kind == 0) {
+      dst = (T*)p.q_out + ((size_t)t * p.num_q_heads + hh) * d;
+    } else if (p.k_cache) {
+      const int seq = p.token_seq[t];
+      const int page = p.block_table[(size_t)seq * p.max_pages + pos / p.page_size];
+      const int slot = pos % p.page_size;
+      if (page >= 0) {
+        T* pool = (T*)(kind == 1 ? p.k_cache : p.v_cache);
+        dst = pool + (((size_t)page * p.num_kv_heads + hh) * p.page_size + slot) * d;
+      }
+    } else {
+      T* o = (T*)(kind == 1 ? p.k_out : p.v_out);
+      if (o) dst = o + ((size_t)t * p.num_kv_heads + hh) * d;
+    }
+    if (dst == nullptr) continue;  // uniform over the warp
+
+    if (kind == 2) {
+      for (int i = lane; i < d; i += 32) dst[i] = src[i];
+      continue;
+    }
+    const float* w = kind == 0 ? p.q_norm_w : p.k_norm_w;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      const float x = to_f32(src[i]);
+      buf[i] = x;
+      ss += x * x;
+    }
+    __syncwarp();
+    if (w) {
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)d + p.eps);
+      // No rounding between norm and rotation: one rounding at the store.
+      for (int i = lane; i < d; i += 32) buf[i] = buf[i] * inv * w[i];
+      __syncwarp();
+    }
+    if (p.inv_freq) {
+      for (int i = lane; i < half; i += 32) {
+        const float angle = (float)pos * p.inv_freq[i];
+        float s, c;
+        sincosf(angle, &s, &c);
+        const float x = buf[i], y = buf[i + half];
+        dst[i] = from_f32<T>(x * c - y * s);
+        dst[i + half] = from_f32<T>(x * s + y * c);
+      }
+      for (int i = p.rot_dim + lane; i < d; i += 32) dst[i] = from_f32<T>(buf[i]);
+    } else {
+      for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(buf[i]);
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace lb
+
+LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const void* v_in,
+                         long long q_stride, long long k_stride, long long v_stride, void* q_out,
+                         void* k_out, void* v_out, void* k_cache, void* v_cache,
+                         const int* positions, const int* token_seq, const int* block_table,
+                         const float* q_norm_w, const float* k_norm_w, const float* inv_freq,
+                         int num_tokens, int num_q_heads, int num_kv_heads, int head_dim,
+                         int rot_dim, int page_size, int max_pages, float eps,
+                         cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(dtype), "rope_kv: bad dtype %d", dtype);
+  LB_CHECK_ARG(head_dim > 0 && head_dim <= 1024, "rope_kv: head_dim %d not in 1..1024", head_dim);
+  LB_CHECK_ARG(rot_dim >= 0 && rot_dim <= head_dim && rot_dim % 2 == 0,
+               "rope_kv: rotary size %d must be even and at most head_dim %d", rot_dim, head_dim);
+  LB_CHECK_ARG(num_q_heads >= 0 && num_kv_heads >= 0, "rope_kv: bad head counts");
+  LB_CHECK_ARG(k_cache == nullptr || (v_cache && block_table && token_seq && page_size > 0 && max_pages > 0),
+               "rope_kv: a cache needs v pool, block table, token map and page size");
+  if (num_tokens == 0) return 0;
+  lb::RopeKvParams p;
+  p.q_in = q_in; p.k_in = k_in; p.v_in = v_in;
+  p.q_stride = q_stride; p.k_stride = k_stride; p.v_stride = v_stride;
+  p.q_out = q_out; p.k_out = k_out; p.v_out = v_out; p.k_cache = k_cache; p.v_cache = v_cache;
+  p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
+  p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.inv_freq = rot_dim > 0 ? inv_freq : nullptr;
+  p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
+  p.rot_dim = rot_dim; p.page_size = page_size; p.max_pages = max_pages; p.eps = eps;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * head_dim * sizeof(float);
+  LB_DISPATCH_DTYPE(dtype, T, {
+    lb::rope_kv_kernel<T><<<num_tokens, warps * 32, smem, stream>>>(p);
+  })
+  LB_CHECK_LAUNCH("rope_kv");
+  return 0;
+}

@@ -1,0 +1,221 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+A batch may hold portions of prompts beside single decoded tokens, cut anywhere; it runs only
+the tokens it is given and returns float32 logits at the places asked for.  lucciola's
+step_with_paged_attention (src/qwen.cc:801-902) takes all running requests with one token each
+followed by at most one portion of one prompt, computes logits for the last row of every
+request whether wanted or not, and samples inside; here any mix of entries is one batch, logits
+are computed for the wanted rows only, and sampling happens above.
+
+The runner owns the model, the cache manager and the device memory of the caches.  Pages are
+taken here, at the start of a step, for exactly the tokens of the step; whoever builds batches
+(the scheduler, the trace replay) asks `can_run` first and decides what to do when pages are short.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.device_cache import DeviceCache, pages_that_fit
+from ..cache.manager import NO_PAGE, CacheManager, plan_groups
+from ..config.engine_options import EngineOptions
+from ..models.decoder import DecoderModel
+from ..parts.base import Runtime, StepContext
+
+
+class OutOfPages(RuntimeError):
+    """A step needs more pages than are free; nothing was run and nothing was taken."""
+
+
+@dataclass
+class StepEntry:
+    rid: Hashable                    # the request
+    tokens: Sequence[int]            # its next tokens, in order
+    want: Sequence[int] = ()         # places among these tokens whose logits are asked for
+
+
+class _Staging:
+    """Pinned host buffers (a small ring) and one device buffer for the integers of a step."""
+
+    def __init__(self, device: torch.device, capacity: int, ring: int = 4):
+        self.device, self.capacity = device, capacity
+        self.host = [torch.empty(capacity, dtype=torch.int32, pin_memory=True) for _ in range(ring)]
+        self.events: list[Optional[torch.cuda.Event]] = [None] * ring
+        self.dev = torch.empty(capacity, dtype=torch.int32, device=device)
+        self.turn = 0
+
+    def next_host(self) -> tuple[int, torch.Tensor]:
+        i = self.turn
+        self.turn = (self.turn + 1) % len(self.host)
+        if self.events[i] is not None:
+            self.events[i].synchronize()        # the copy that read this buffer has finished
+        return i, self.host[i]
+
+    def upload(self, i: int, n: int) -> None:
+        self.dev[:n].copy_(self.host[i][:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, rt: Runtime, options: EngineOptions, num_pages: Optional[int] = None):
+        options.validate()
+        self.model, self.rt, self.options = model, rt, options
+        self.device = rt.device
+        self.page_size = options.block_size
+        self.max_model_len = options.max_model_len or model.max_positions
+        if self.max_model_len > model.max_positions:
+            raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's {model.max_positions} positions")
+        requests = model.cache_requests()
+        self.groups, self.state_cache_ids = plan_groups(requests)
+        if num_pages is None:
+            num_pages = options.max_blocks
+        if not num_pages:
+            num_pages = pages_that_fit(self.groups, self.page_size, rt.act_dtype, self.device, options.mem_fraction)
+            if num_pages <= 0:
+                raise RuntimeError("no memory left for cache pages")
+        self.num_pages = int(num_pages)
+        self.manager = CacheManager(self.groups, self.page_size, self.num_pages, options.max_num_seqs)
+        self.cache = DeviceCache(requests, self.groups, self.page_size, [self.num_pages] * len(self.groups),
+                                 options.max_num_seqs, rt.act_dtype, self.device)
+        self.max_pages_per_seq = -(-self.max_model_len // self.page_size)
+        self._staging: Optional[_Staging] = None
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ---- what a batch builder may ask ------------------------------------
+    def length(self, rid: Hashable) -> int:
+        return self.manager.length(rid) if self.manager.has_request(rid) else 0
+
+    def can_run(self, entries: Sequence[StepEntry]) -> bool:
+        """True when the free pages and slots suffice for all entries together."""
+        need = [0] * len(self.groups)
+        new_requests = 0
+        for e in entries:
+            if self.manager.has_request(e.rid):
+                n = self.manager.pages_needed(e.rid, self.manager.length(e.rid) + len(e.tokens))
+            else:
+                new_requests += 1
+                n = [-(-len(e.tokens) // self.page_size)] * len(self.groups)
+            need = [a + b for a, b in zip(need, n)]
+        if new_requests > len(self.manager._free_slots):
+            return False
+        return all(self.manager.pools[g].can_allocate(n) for g, n in enumerate(need))
+
+    def finish(self, rid: Hashable) -> None:
+        """The request ended (or is preempted): its pages and its slot go back."""
+        if self.manager.has_request(rid):
+            self.manager.release(rid)
+
+    # ---- the step ----------------------------------------------------------
+    def _staging_for(self, n: int) -> _Staging:
+        if self._staging is None or self._staging.capacity < n:
+            torch.cuda.current_stream(self.device).synchronize()
+            self._staging = _Staging(self.device, max(n, 4096) * 2)
+        return self._staging
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries as one batch.  Returns logits [wanted, vocab] (float32, on the device) in the
+        order of the entries and of their `want`, or None when nothing is wanted."""
+        if not entries:
+            return None
+        vocab = self.model.vocab_size
+        seen: set[Hashable] = set()
+        token_arrays: list[np.ndarray] = []
+        for e in entries:
+            if e.rid in seen:
+                raise ValueError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.rid!r} brings no tokens")
+            if self.length(e.rid) + n > self.max_model_len:
+                raise ValueError(f"request {e.rid!r} would reach {self.length(e.rid) + n} tokens, the limit is {self.max_model_len}")
+            for w in e.want:
+                if not (0 <= w < n):
+                    raise ValueError(f"request {e.rid!r} wants logits at place {w} of {n} tokens")
+            arr = np.asarray(e.tokens, dtype=np.int64)
+            token_arrays.append(arr)
+            if int(arr.min()) < 0 or int(arr.max()) >= vocab:
+                bad = int(arr.min()) if int(arr.min()) < 0 else int(arr.max())
+                raise ValueError(f"request {e.rid!r}: token id {bad} is outside the vocabulary of {vocab}")
+        if not self.can_run(entries):
+            raise OutOfPages(f"the step needs more pages or slots than are free ({[p.num_free for p in self.manager.pools]} pages free)")
+
+        # Take pages; collect the batch on the host.
+        new_slots: list[int] = []
+        starts, q_lens = [], []
+        for e in entries:
+            if not self.manager.has_request(e.rid):
+                new_slots.append(self.manager.admit(e.rid))
+            start = self.manager.length(e.rid)
+            if not self.manager.extend(e.rid, start + len(e.tokens)):
+                raise OutOfPages("pages ran out while a step was being prepared")   # can_run() said yes
+            starts.append(start)
+            q_lens.append(len(e.tokens))
+
+        S, T = len(entries), sum(q_lens)
+        R = sum(len(e.want) for e in entries)
+        G, P = len(self.groups), self.max_pages_per_seq
+        total = 3 * T + (S + 1) + 2 * S + R + G * S * P
+        st = self._staging_for(total)
+        hi, host = st.next_host()
+        h = host.numpy()
+        o = 0
+        def take(n):
+            nonlocal o
+            v = h[o:o + n]
+            o += n
+            return v
+        tok, pos, seq = take(T), take(T), take(T)
+        cu, ctx, slots, rows = take(S + 1), take(S), take(S), take(R)
+        tables = [take(S * P).reshape(S, P) for _ in range(G)]
+        t = r = 0
+        cu[0] = 0
+        for i, e in enumerate(entries):
+            n = q_lens[i]
+            tok[t:t + n] = token_arrays[i]
+            pos[t:t + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
+            seq[t:t + n] = i
+            for w in e.want:
+                rows[r] = t + w
+                r += 1
+            t += n
+            cu[i + 1] = t
+            ctx[i] = starts[i] + n
+            slots[i] = self.manager.slot(e.rid)
+            for g in range(G):
+                bt = self.manager.block_table(e.rid, g)
+                tables[g][i, :len(bt)] = bt
+                tables[g][i, len(bt):] = NO_PAGE
+        st.upload(hi, total)
+
+        d = st.dev
+        o = 0
+        def view(n):
+            nonlocal o
+            v = d[o:o + n]
+            o += n
+            return v
+        d_tok, d_pos, d_seq = view(T), view(T), view(T)
+        d_cu, d_ctx, d_slots, d_rows = view(S + 1), view(S), view(S), view(R)
+        d_tables = [view(S * P).view(S, P) for _ in range(G)]
+
+        step = StepContext(
+            num_tokens=T, num_seqs=S, positions=d_pos, token_seq=d_seq, cu_tokens=d_cu, context_lens=d_ctx,
+            block_tables=d_tables, state_slots=d_slots, q_lens=q_lens, start_positions=starts,
+            max_q_len=max(q_lens), max_context_len=max(s + n for s, n in zip(starts, q_lens)))
+        self.rt.stream = torch.cuda.current_stream(self.device).cuda_stream
+        if new_slots and self.cache.states:
+            self.cache.zero_slots(torch.tensor(new_slots, dtype=torch.long, device=self.device))
+        logits = self.model.forward(d_tok, step, self.cache.views, d_rows if R else None)
+
+        for e in entries:
+            self.manager.release_behind_window(e.rid)
+        self.steps_run += 1
+        self.tokens_run += T
+        return logits

@@ -1,0 +1,200 @@
+"""Tensor-level wrappers of the kernel library.
+
+Each function checks what the kernel cannot check for itself (device, type,
+contiguity), passes raw pointers and the stream to the C interface, and raises
+`KernelError` with the library's message when a call is refused.  There is no
+other implementation behind these functions: without the library they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_uint, c_ulonglong, c_void_p
+
+import torch
+
+from .csrc import KernelLibraryError, library
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dt}")
+
+
+_SIGNATURES = {
+    "lb_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "lb_add_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "lb_rope_kv": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p,
+                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "lb_attention_plain": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "lb_swiglu": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p],
+    "lb_gemm_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
+                      c_longlong, c_void_p],
+    "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+}
+
+_fn_cache: dict[str, object] = {}
+
+
+def _fn(name: str):
+    f = _fn_cache.get(name)
+    if f is None:
+        lib = library()
+        try:
+            f = getattr(lib, name)
+        except AttributeError as e:
+            raise KernelLibraryError(f"the kernel library lacks {name}") from e
+        f.argtypes = _SIGNATURES[name]
+        f.restype = c_int
+        _fn_cache[name] = f
+    return f
+
+
+def _call(name: str, *args) -> None:
+    rc = _fn(name)(*args)
+    if rc != 0:
+        raise KernelError(library().lb_last_error().decode())
+
+
+def hash_uniform(key: int, counter: int, i: int) -> float:
+    """The sampler's uniform number for (request key, generated index, vocabulary index), on the host."""
+    lib = library()
+    f = lib.lb_hash_uniform
+    f.argtypes = [c_ulonglong, c_uint, c_uint]
+    f.restype = c_float
+    return float(f(key, counter, i))
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _check(t: torch.Tensor, what: str, dtype: torch.dtype | None = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what} must be on the GPU")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, is {t.dtype}")
+
+
+def current_stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def embedding(out: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, stream: int) -> None:
+    """out[t, :] = table[ids[t], :] as float32."""
+    _check(out, "embedding output", torch.float32); _check(ids, "token ids", torch.int32); _check(table, "embedding table")
+    T, H = out.shape
+    _call("lb_embedding", out.data_ptr(), ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), T, H,
+          table.shape[0], stream)
+
+
+def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
+                eps: float, stream: int, rows: torch.Tensor | None = None) -> None:
+    """residual += delta (when rows is None); out = rmsnorm(residual [+ delta]) * weight, on `rows` if given."""
+    _check(out, "norm output"); _check(residual, "residual", torch.float32); _check(weight, "norm weight", torch.float32)
+    n = out.shape[0]
+    H = out.shape[-1]
+    if delta is not None:
+        _check(delta, "delta")
+    if rows is not None:
+        _check(rows, "row index", torch.int32)
+    _call("lb_add_rmsnorm", out.data_ptr(), dtype_code(out.dtype), residual.data_ptr(), _ptr(delta),
+          dtype_code(delta.dtype) if delta is not None else F32, weight.data_ptr(), _ptr(rows), n, H, eps, stream)
+
+
+def rope_kv(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, q_out: torch.Tensor,
+            positions: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, eps: float, stream: int,
+            q_norm_w: torch.Tensor | None = None, k_norm_w: torch.Tensor | None = None,
+            inv_freq: torch.Tensor | None = None, rot_dim: int = 0,
+            k_cache: torch.Tensor | None = None, v_cache: torch.Tensor | None = None,
+            token_seq: torch.Tensor | None = None, block_table: torch.Tensor | None = None, page_size: int = 0,
+            k_out: torch.Tensor | None = None, v_out: torch.Tensor | None = None) -> None:
+    """Per-head norm of q and k, rotation, and the write of k and v into pages (or into k_out, v_out).
+
+    q_in, k_in and v_in are 2-d views whose rows may be column ranges of one wider matrix."""
+    T = q_in.shape[0]
+    dt = q_in.dtype
+    for t, w in ((q_in, "q"), (k_in, "k"), (v_in, "v")):
+        if not t.is_cuda or t.dtype != dt or t.stride(-1) != 1:
+            raise KernelError(f"{w} must be on the GPU, of one type, with unit stride in its last dimension")
+    _check(q_out, "q output", dt); _check(positions, "positions", torch.int32)
+    max_pages = 0
+    if k_cache is not None:
+        _check(k_cache, "k pool", dt); _check(v_cache, "v pool", dt)
+        _check(token_seq, "token map", torch.int32); _check(block_table, "block table", torch.int32)
+        max_pages = block_table.shape[1]
+    _call("lb_rope_kv", dtype_code(dt), q_in.data_ptr(), k_in.data_ptr(), v_in.data_ptr(), q_in.stride(0),
+          k_in.stride(0), v_in.stride(0), q_out.data_ptr(), _ptr(k_out), _ptr(v_out), _ptr(k_cache), _ptr(v_cache),
+          positions.data_ptr(), _ptr(token_seq), _ptr(block_table), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
+          T, num_q_heads, num_kv_heads, head_dim, rot_dim, page_size, max_pages, eps, stream)
+
+
+def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    positions: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor,
+                    num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+                    stream: int) -> None:
+    dt = q.dtype
+    _check(q, "q"); _check(out, "attention output", dt); _check(k_cache, "k pool", dt); _check(v_cache, "v pool", dt)
+    _check(positions, "positions", torch.int32); _check(token_seq, "token map", torch.int32)
+    _check(block_table, "block table", torch.int32)
+    _call("lb_attention_plain", dtype_code(dt), q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+          positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), q.shape[0], num_q_heads, num_kv_heads,
+          head_dim, page_size, block_table.shape[1], window, scale, stream)
+
+
+def swiglu(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, stream: int) -> None:
+    """out = silu(gate) * up; gate and up are 2-d views with the same row stride."""
+    if gate.stride(0) != up.stride(0) or gate.stride(1) != 1 or up.stride(1) != 1:
+        raise KernelError("gate and up need the same row stride and unit column stride")
+    _check(out, "swiglu output", gate.dtype)
+    T, inter = out.shape
+    _call("lb_swiglu", dtype_code(out.dtype), out.data_ptr(), gate.data_ptr(), up.data_ptr(), gate.stride(0), T, inter, stream)
+
+
+def gemm_plain(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int) -> None:
+    """y[M, N] = x[M, K] . w[N, K]^T on the 32-bit pipes; x and y may be row-strided views."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(y.shape) != (M, N):
+        raise KernelError(f"gemm shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    if x.stride(1) != 1 or y.stride(1) != 1 or not w.is_contiguous() or not (x.is_cuda and w.is_cuda and y.is_cuda):
+        raise KernelError("gemm operands must be on the GPU with unit column stride; w contiguous")
+    _call("lb_gemm_plain", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), dtype_code(x.dtype), w.data_ptr(),
+          dtype_code(w.dtype), M, N, K, x.stride(0) if M > 1 else K, y.stride(0) if M > 1 else N, stream)
+
+
+def sample(tokens: torch.Tensor, logits: torch.Tensor, stream: int, temperature: torch.Tensor | None = None,
+           keys: torch.Tensor | None = None, counters: torch.Tensor | None = None) -> None:
+    """tokens[r] = greedy or temperature sample of logits[r, :]; see sampling/sampler.py for the key."""
+    _check(tokens, "token output", torch.int32); _check(logits, "logits", torch.float32)
+    if temperature is not None:
+        _check(temperature, "temperature", torch.float32); _check(keys, "keys", torch.int64)
+        _check(counters, "counters", torch.int32)
+    R, V = logits.shape
+    _call("lb_sample", tokens.data_ptr(), logits.data_ptr(), _ptr(temperature), _ptr(keys), _ptr(counters), R, V, stream)
+
+
+def linear(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, fast: bool) -> None:
+    """y = x . w^T.  `fast` allows the tensor-core kernel where its conditions hold; the 32-bit
+    path never sets it."""
+    gemm_plain(y, x, w, stream)
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
+              num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+              stream: int, fast: bool) -> None:
+    """Causal attention of this step's queries over the pages of their requests."""
+    attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
+                    num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)

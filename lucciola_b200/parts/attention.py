@@ -1,0 +1,95 @@
+"""Grouped-query attention over paged keys and values, with per-head RMSNorm of q and k.
+
+Order of operations as in lucciola's decoder layer (src/qwen.cc:592-742): q, k, v projections
+without bias; RMSNorm over each head of q and of k with a weight [head_dim] shared by the heads,
+before the rotation; rotary position encoding of q and k; k and v written to the cache at the
+token's position; causal attention of every query head h over the keys of kv head
+h / (nq / nkv) with scale 1/sqrt(head_dim) unless another scale is given; output projection.
+A window W, which lucciola does not have, limits a query at position p to keys p-W+1 .. p.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Optional
+
+import torch
+
+from .. import ops
+from .base import KVCacheView, KVPages, Mixer, ParamSpec, Part, PositionEncoding, Runtime, StepContext
+from .linear import Linear
+
+
+class GQAttention(Mixer):
+    def __init__(self, rt: Runtime, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position_encoding: Optional[PositionEncoding], qk_norm_eps: Optional[float], window: int = 0,
+                 scale: Optional[float] = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
+        self.rt, self.prefix = rt, prefix
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
+        self.position_encoding = position_encoding
+        self.qk_norm_eps = qk_norm_eps              # None: no q/k norm
+        self.window = int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.q_size, self.kv_size = num_heads * head_dim, num_kv_heads * head_dim
+        self.qkv = Linear(rt, [f"{prefix}.q_proj.weight", f"{prefix}.k_proj.weight", f"{prefix}.v_proj.weight"],
+                          hidden_size, [self.q_size, self.kv_size, self.kv_size])
+        self.o = Linear(rt, f"{prefix}.o_proj.weight", self.q_size, hidden_size)
+        self.q_norm_w: torch.Tensor | None = None
+        self.k_norm_w: torch.Tensor | None = None
+
+    def children(self) -> list[Part]:
+        return [self.qkv, self.o]
+
+    def param_specs(self) -> list[ParamSpec]:
+        if self.qk_norm_eps is None:
+            return []
+        return [ParamSpec(f"{self.prefix}.q_norm.weight", (self.head_dim,), "norm"),
+                ParamSpec(f"{self.prefix}.k_norm.weight", (self.head_dim,), "norm")]
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        if self.qk_norm_eps is not None:
+            self.q_norm_w = get(f"{self.prefix}.q_norm.weight").to(torch.float32).contiguous()
+            self.k_norm_w = get(f"{self.prefix}.k_norm.weight").to(torch.float32).contiguous()
+
+    def cache_request(self) -> KVPages:
+        return KVPages(self.num_kv_heads, self.head_dim, self.window)
+
+    def forward(self, h: torch.Tensor, step: StepContext, cache: KVCacheView, write_cache: bool = True) -> torch.Tensor:
+        rt = self.rt
+        T = h.shape[0]
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        table = cache_table = step.block_tables[cache.group]
+        eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
+        q = rt.empty((T, nq, d))
+        if write_cache:
+            qkv = self.qkv.forward(h)
+            q_in, k_in, v_in = qkv[:, :self.q_size], qkv[:, self.q_size:self.q_size + self.kv_size], qkv[:, self.q_size + self.kv_size:]
+            n_kv = nkv
+        else:
+            # This call reads a cache another call has written: only q is needed.
+            q_in = k_in = v_in = self.qkv.forward(h, rows=self.q_size)
+            n_kv = 0
+        rotary = self.position_encoding.rotary_table() if self.position_encoding is not None else None
+        if self.position_encoding is None or rotary is not None:
+            inv_freq, rot = rotary if rotary is not None else (None, 0)
+            ops.rope_kv(q_in, k_in, v_in, q, step.positions, nq, n_kv, d, eps, rt.stream,
+                        q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, inv_freq=inv_freq, rot_dim=rot,
+                        k_cache=cache.k, v_cache=cache.v, token_seq=step.token_seq, block_table=cache_table,
+                        page_size=cache.page_size)
+        else:
+            # A position encoding the fused kernel does not know: norm first, then the part's own
+            # apply(), then the write.
+            k_tmp, v_tmp = rt.empty((T, max(n_kv, 1), d)), rt.empty((T, max(n_kv, 1), d))
+            ops.rope_kv(q_in, k_in, v_in, q, step.positions, nq, n_kv, d, eps, rt.stream,
+                        q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, k_out=k_tmp, v_out=v_tmp)
+            self.position_encoding.apply(q, k_tmp, step.positions)
+            if n_kv:
+                k2, v2 = k_tmp.view(T, n_kv * d), v_tmp.view(T, n_kv * d)
+                ops.rope_kv(k2, k2, v2, q, step.positions, 0, n_kv, d, 0.0, rt.stream,
+                            k_cache=cache.k, v_cache=cache.v, token_seq=step.token_seq, block_table=cache_table,
+                            page_size=cache.page_size)
+        out = rt.empty((T, nq, d))
+        ops.attention(q, out, cache.k, cache.v, step, cache.group, nq, nkv, d, cache.page_size, self.window,
+                      self.scale, rt.stream, fast=rt.fast_kernels)
+        return self.o.forward(out.view(T, self.q_size))

@@ -1,0 +1,167 @@
+"""Interfaces of the parts a decoder is put together from.
+
+A model is a list of blocks and a list of calls that says in which order the
+blocks run and which cache each call uses.  A block arranges a mixer, a
+feed-forward and norms; a mixer may use a position encoding.  Every part takes
+its sizes and constants as constructor arguments, names the tensors it wants
+from the checkpoint, and knows nothing of the model it sits in.
+
+What a part must provide:
+
+Part (all)        param_specs() -> [ParamSpec]    tensors wanted, by full name
+                  bind(get)                        take them: get(name) -> tensor on the device
+Norm              forward(x, out_dtype)            -> normed copy
+                  add_forward(residual, delta, out_dtype, rows=None)
+                                                   residual += delta; -> norm(residual) [on rows]
+PositionEncoding  rotary_table() / apply(q, k, positions)
+Mixer             cache_request() -> KVPages | StateSlot | None
+                  forward(h, step, cache) -> [T, hidden] in the activation type
+FeedForward       forward(h, step) -> [T, hidden]
+Block             mixer, forward(residual, delta, step, cache) -> (residual, delta)
+
+`step` is the StepContext: what a part may know about the batch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Optional, Sequence
+
+import torch
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    name: str                       # full tensor name in the checkpoint
+    shape: tuple[int, ...]
+    init: str = "linear"            # "linear" | "embedding" | "norm": how random weights are drawn
+    integer: bool = False           # integer tables are kept as int32
+
+
+@dataclass(frozen=True)
+class KVPages:
+    """A mixer that keeps keys and values of past tokens in pages."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0                 # 0: all keys; W: the last W keys (the query's own included)
+
+
+@dataclass(frozen=True)
+class StateSlot:
+    """A mixer that keeps a state of fixed size for each request."""
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Runtime:
+    """What parts share at run time: device, activation type, the stream of the current step."""
+
+    def __init__(self, device: torch.device | str, act_dtype: torch.dtype):
+        self.device = torch.device(device)
+        self.act_dtype = act_dtype
+        self.stream: int = 0        # raw handle, set by the step function before parts run
+        self.fast_kernels = act_dtype == torch.bfloat16
+
+    def empty(self, shape: Sequence[int], dtype: torch.dtype | None = None) -> torch.Tensor:
+        return torch.empty(tuple(shape), dtype=dtype or self.act_dtype, device=self.device)
+
+
+@dataclass
+class KVCacheView:
+    """One cache layer of paged keys and values, as a mixer sees it."""
+    k: torch.Tensor                 # [pages, kv_heads, page_size, head_dim]
+    v: torch.Tensor
+    group: int                      # index into StepContext.block_tables
+    page_size: int
+
+
+@dataclass
+class StateCacheView:
+    """One cache layer of per-request state: row `slot` belongs to the request in that slot."""
+    state: torch.Tensor             # [slots, *shape]
+
+
+@dataclass
+class StepContext:
+    """The batch of one step, as parts see it.  Device tensors are int32.
+
+    Tokens of one request are contiguous and in order; `token_seq[t]` is the
+    index of token t's request among the S requests of this step."""
+    num_tokens: int
+    num_seqs: int
+    positions: torch.Tensor                     # [T] absolute position of each token
+    token_seq: torch.Tensor                     # [T]
+    cu_tokens: torch.Tensor                     # [S+1] first token of each request
+    context_lens: torch.Tensor                  # [S] length after this step
+    block_tables: list[torch.Tensor]            # per cache group: [S, max_pages], -1 where no page
+    state_slots: torch.Tensor                   # [S] slot of each request's fixed-size state
+    # Host copies for planning (lists of ints).
+    q_lens: list[int] = field(default_factory=list)
+    start_positions: list[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_context_len: int = 0
+    # Per step scratch that parts of the same kind may share (plans of the attention kernels).
+    plans: dict = field(default_factory=dict)
+    # Per cache group plan tensors prepared by the step function (see engine/step.py).
+    attn_meta: dict = field(default_factory=dict)
+
+
+class Part:
+    def param_specs(self) -> list[ParamSpec]:
+        return []
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        pass
+
+    def children(self) -> list["Part"]:
+        return []
+
+    def all_param_specs(self) -> list[ParamSpec]:
+        specs = list(self.param_specs())
+        for c in self.children():
+            specs += c.all_param_specs()
+        return specs
+
+    def bind_all(self, get: Callable[[str], torch.Tensor]) -> None:
+        self.bind(get)
+        for c in self.children():
+            c.bind_all(get)
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
+                    rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary_table(self) -> Optional[tuple[torch.Tensor, int]]:
+        """(inv_freq [rot/2] float32 on the device, rot) if this is a half-rotation encoding the fused kernel can apply."""
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        """Encode positions into q [T, nq, d] and k [T, nkv, d] in place (used when rotary_table() is None)."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_request(self) -> KVPages | StateSlot | None:
+        return None
+
+    def forward(self, h: torch.Tensor, step: StepContext, cache, write_cache: bool = True) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, step: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    mixer: Mixer
+
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], step: StepContext, cache,
+                write_cache: bool = True) -> tuple[torch.Tensor, Optional[torch.Tensor]]:
+        raise NotImplementedError

@@ -1,0 +1,53 @@
+"""Linear maps without bias: y = x . W^T with W [out, in] as the checkpoint stores it.
+
+A Linear may be made of several checkpoint tensors stacked along the output
+dimension (q|k|v, gate|up): one product instead of several.  lucciola keeps
+them apart and runs one product each (src/qwen.cc:592-615, 762-777).
+"""
+from __future__ import annotations
+
+from typing import Callable, Sequence
+
+import torch
+
+from .. import ops
+from .base import ParamSpec, Part, Runtime
+
+
+class Linear(Part):
+    def __init__(self, rt: Runtime, names: str | Sequence[str], in_features: int, out_features: int | Sequence[int],
+                 init: str = "linear"):
+        self.rt = rt
+        self.names = [names] if isinstance(names, str) else list(names)
+        self.out_sizes = [out_features] if isinstance(out_features, int) else list(out_features)
+        if len(self.names) != len(self.out_sizes):
+            raise ValueError("one output size for each tensor name")
+        self.in_features = in_features
+        self.out_features = sum(self.out_sizes)
+        self.init = init
+        self.weight: torch.Tensor | None = None
+
+    def param_specs(self) -> list[ParamSpec]:
+        return [ParamSpec(n, (o, self.in_features), self.init) for n, o in zip(self.names, self.out_sizes)]
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        ws = [get(n) for n in self.names]
+        if len(ws) == 1:
+            self.weight = ws[0].contiguous()
+        else:
+            dt = ws[0].dtype
+            if any(w.dtype != dt for w in ws):
+                raise ValueError(f"tensors {self.names} are stacked into one product and must share a type")
+            self.weight = torch.cat(ws, dim=0).contiguous()
+
+    def bind_tensor(self, weight: torch.Tensor) -> None:
+        """Use a tensor another part owns (a tied output head)."""
+        self.weight = weight
+
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, rows: int | None = None) -> torch.Tensor:
+        """y = x . W^T; with `rows`, only the first `rows` output features."""
+        M = x.shape[0]
+        w = self.weight if rows is None else self.weight[:rows]
+        y = self.rt.empty((M, w.shape[0]), out_dtype or self.rt.act_dtype)
+        ops.linear(y, x, w, self.rt.stream, fast=self.rt.fast_kernels)
+        return y
