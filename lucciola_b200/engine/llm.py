@@ -1,0 +1,162 @@
+"""The Python entry points, in the manner of lucciola's AsyncEngine (include/async_engine.h:22-35):
+
+    engine = AsyncEngine(model_path, max_blocks=0, block_size=16)
+    req_id = engine.generate_async(prompt, max_new_tokens, callback)    # callback(token, is_finished)
+    engine.stop()
+
+lucciola's prompt is text and its callback receives text; tokenisation is outside this engine, so
+here a prompt is a list of token ids and the callback receives token ids.  `Engine` is the same
+loop without the thread: `generate(prompts, params)` returns when every request has finished.
+"""
+from __future__ import annotations
+
+import threading
+from pathlib import Path
+from typing import Any, Callable, Mapping, Optional, Sequence
+
+import torch
+
+from ..config.engine_options import EngineOptions
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .load import build_runner, build_runner_random
+from .request import Request
+from .scheduler import Scheduled, Scheduler
+from .step import ModelRunner, StepEntry
+
+
+class Engine:
+    """Synchronous engine: scheduler above the step function, sampler after it."""
+
+    def __init__(self, model_path: Optional[str | Path] = None, max_blocks: int = 0, block_size: int = 16,
+                 options: Optional[EngineOptions] = None, runner: Optional[ModelRunner] = None, **kw: Any):
+        if runner is None:
+            options = options or EngineOptions(max_blocks=max_blocks, block_size=block_size, **kw)
+            if model_path is None:
+                raise ValueError("give a model folder (or a runner)")
+            runner = build_runner(model_path, options)
+        self.runner = runner
+        self.options = runner.options
+        self.scheduler = Scheduler(runner.manager, self.options.max_tokens_per_step, self.options.max_num_seqs,
+                                   runner.max_model_len, self.options.prefill_chunk, runner.model.eos_token_ids)
+        self.sampler = Sampler(runner.device)
+        self._next_id = 1
+
+    @classmethod
+    def from_random(cls, config_dict: Mapping[str, Any], seed: int, options: Optional[EngineOptions] = None,
+                    std: float = 0.02, norm_std: float = 0.0) -> "Engine":
+        return cls(runner=build_runner_random(config_dict, seed, options, std, norm_std))
+
+    # ---- requests ----------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    callback: Optional[Callable[[int, bool], None]] = None) -> Request:
+        req = Request(self._next_id, [int(t) for t in prompt], params or SamplingParams(), callback)
+        vocab = self.runner.model.vocab_size
+        bad = [t for t in req.prompt if not (0 <= t < vocab)]
+        if bad:
+            raise ValueError(f"token id {bad[0]} is outside the vocabulary of {vocab}")
+        self.scheduler.add_request(req)
+        self._next_id += 1
+        return req
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    # ---- one step: schedule, run, sample, update ----------------------------------
+    def step(self) -> list[tuple[Request, int, bool]]:
+        plan = self.scheduler.schedule()
+        if not plan:
+            return []
+        entries = []
+        for s in plan:
+            toks = s.request.tokens[s.start:s.start + s.num_tokens]
+            entries.append(StepEntry(s.request.rid, toks, (s.num_tokens - 1,) if s.sample else ()))
+        logits = self.runner.step(entries)
+        sampled: list[int] = []
+        if logits is not None:
+            who = [s.request for s in plan if s.sample]
+            sampled = self.sampler.sample(logits, [r.params for r in who], [len(r.output) for r in who])
+        events = self.scheduler.update(plan, sampled)
+        for req, tok, done in events:
+            if req.callback is not None:
+                req.callback(tok, done)
+        return events
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams] | None = None
+                 ) -> list[list[int]]:
+        """Generate for all prompts together; returns the new tokens of each."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        reqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while self.scheduler.has_unfinished():
+            self.step()
+        return [r.output for r in reqs]
+
+    def stats(self) -> dict[str, int]:
+        sch = self.scheduler
+        return {"steps": sch.num_steps, "scheduled_tokens": sch.num_scheduled_tokens, "preemptions": sch.num_preemptions,
+                "page_high_water": max(p.high_water for p in self.runner.manager.pools) if self.runner.manager.pools else 0}
+
+
+class AsyncEngine:
+    """A background thread runs the engine loop; requests are added from any thread
+    (src/async_engine.cc:38-168 of lucciola: queue under a mutex, condition variable, per-token callback
+    on the engine thread, stop() joins the thread after the work is done)."""
+
+    def __init__(self, model_path: Optional[str | Path] = None, max_blocks: int = 0, block_size: int = 16,
+                 engine: Optional[Engine] = None, **kw: Any):
+        self.engine = engine or Engine(model_path, max_blocks, block_size, **kw)
+        self._cv = threading.Condition()
+        self._pending: list[tuple[int, list[int], SamplingParams, Optional[Callable[[int, bool], None]]]] = []
+        self._stop = False
+        self._next_id = 1
+        self._error: Optional[BaseException] = None
+        self._thread = threading.Thread(target=self._loop, name="lucciola-engine", daemon=True)
+        self._thread.start()
+
+    def generate_async(self, prompt: Sequence[int], max_new_tokens: int,
+                       callback: Optional[Callable[[int, bool], None]] = None, temperature: float = 0.0,
+                       seed: int = 0, ignore_eos: bool = False) -> int:
+        params = SamplingParams(max_new_tokens=max_new_tokens, temperature=temperature, seed=seed, ignore_eos=ignore_eos)
+        params.validate()
+        with self._cv:
+            if self._stop:
+                raise RuntimeError("the engine is stopped")
+            rid = self._next_id
+            self._next_id += 1
+            self._pending.append((rid, [int(t) for t in prompt], params, callback))
+            self._cv.notify()
+        return rid
+
+    def stop(self) -> None:
+        """Finish what was submitted, then end the thread."""
+        with self._cv:
+            if self._stop:
+                return
+            self._stop = True
+            self._cv.notify_all()
+        self._thread.join()
+        if self._error is not None:
+            raise self._error
+
+    def _loop(self) -> None:
+        eng = self.engine
+        torch.cuda.set_device(eng.runner.device)
+        try:
+            while True:
+                with self._cv:
+                    self._cv.wait_for(lambda: self._stop or self._pending or eng.has_unfinished())
+                    if self._stop and not self._pending and not eng.has_unfinished():
+                        return
+                    batch, self._pending = self._pending, []
+                for rid, prompt, params, cb in batch:
+                    try:
+                        req = eng.add_request(prompt, params, cb)
+                        req.user_id = rid
+                    except ValueError:
+                        if cb is not None:
+                            cb(-1, True)             # refused: finished without a token
+                if eng.has_unfinished():
+                    eng.step()
+        except BaseException as e:                       # surfaces in stop()
+            self._error = e

@@ -169,7 +169,7 @@ def forward(cfg, weights, ids, dtype=torch.float64, calls=None):
 # ---- sampling ------------------------------------------------------------------------------
 def greedy(logits_row) -> int:
     """Index of the largest logit, the lowest index among equals (src/kernels/argmax.cu:8-59 leaves ties open)."""
-    return int(torch.argmax(logits_row))          # torch returns the first maximal index
+    return int(np.argmax(np.asarray(logits_row)))          # numpy returns the first maximal index
 
 
 _M64 = (1 << 64) - 1

@@ -1,0 +1,153 @@
+"""The engine against the plain implementation under every way of cutting the work (GPU)."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import replay_util as ru
+from conftest import ROOT, TINY, tokens_for
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+def make_runner(folder, name, dtype, num_pages, **kw):
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.load import build_runner
+
+    page = TINY[name][4]
+    return build_runner(folder, EngineOptions(dtype=dtype, block_size=page, max_blocks=num_pages, max_num_seqs=8,
+                                              use_cuda_graph=False, **kw), num_pages=num_pages)
+
+
+def requests_for(name):
+    """Four requests per configuration (the prompt lengths of the tiny workloads among them), up to the
+    configuration's longest sequence."""
+    top = TINY[name][0]["max_position_embeddings"]
+    lengths = {"A": [5, 17, 33, 128], "B": [1, 9, 40, 100, 256], "C": [3, 64, 200, 333]}[name]
+    assert max(lengths) <= top
+    return {f"{name}{n}": tokens_for(name, n) for n in lengths}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(TINY))
+@pytest.mark.parametrize("cut", ["whole", "tail_decoded", "portions"])
+def test_each_request_alone(tiny_models, name, dtype, cut):
+    reqs = requests_for(name)
+    steps = getattr(ru, cut)(reqs)
+    page = TINY[name][4]
+    runner = make_runner(tiny_models[name], name, dtype, ru.max_live_tokens(steps) // page)
+    got = ru.replay(runner, steps)
+    ru.compare(got, tiny_models[name], reqs, dtype)
+    assert all(p.num_free == p.num_pages for p in runner.manager.pools)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(TINY))
+@pytest.mark.parametrize("seed", [0, 1])
+def test_mixed_batches_with_reused_pages(tiny_models, name, dtype, seed):
+    top = TINY[name][0]["max_position_embeddings"]
+    lengths = [n for n in (70, 9, 120, 33, 101, 2, 64, 47, 90) if n <= top]
+    reqs = {f"m{i}": tokens_for(name, n, salt=seed + 1) for i, n in enumerate(lengths)}
+    steps = ru.mixed(reqs, seed=seed)
+    page = TINY[name][4]
+    pages = ru.max_live_tokens(steps) // page
+    assert pages * page < sum(ru.ceil64(len(v)) for v in reqs.values()), "the trace must force pages to be used again"
+    runner = make_runner(tiny_models[name], name, dtype, pages)
+    got = ru.replay(runner, steps, poison=True)
+    ru.compare(got, tiny_models[name], reqs, dtype)
+    assert max(len(s["entries"]) for s in steps) >= 3
+    assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"]) and any(len(e["tokens"]) > 1 for s in steps for e in s["entries"])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cutting_does_not_change_float32_results_at_all(tiny_models, dtype):
+    """In 32-bit every kernel visits a sum's terms in an order that does not depend on the batch, so
+    whole, portions and mixed agree to the last bit; in bfloat16 they agree within rounding."""
+    name = "B"
+    reqs = requests_for(name)
+    runs = []
+    for steps in (ru.whole(reqs), ru.portions(reqs), ru.mixed(reqs, seed=3)):
+        runner = make_runner(tiny_models[name], name, dtype, 200)
+        runs.append(ru.replay(runner, steps))
+    common = set(runs[0]) & set(runs[1]) & set(runs[2])
+    assert len(common) > 50
+    for key in common:
+        for other in runs[1:]:
+            if dtype == "float32":
+                assert torch.equal(runs[0][key], other[key]), key
+            else:
+                assert (runs[0][key] - other[key]).abs().max() <= 2 * ru.TOL[dtype] * runs[0][key].abs().max(), key
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(tiny_models, dtype):
+    """One prompt token, then every token decoded one by one up to the longest sequence of the configuration."""
+    name = "C"
+    ids = tokens_for(name, 400, salt=9)
+    steps = ru.tail_decoded({"long": ids}, tail=399)
+    runner = make_runner(tiny_models[name], name, dtype, ru.max_live_tokens(steps) // 16)
+    got = ru.replay(runner, steps)
+    assert len(got) == 400
+    ru.compare(got, tiny_models[name], {"long": ids}, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(TINY))
+def test_first_tokens_of_a_sequence(tiny_models, name, dtype):
+    """Positions 0, 1, 2: a single key, a page that holds one token, a one-token prompt."""
+    for n in (1, 2, 3):
+        ids = tokens_for(name, n, salt=n)
+        for steps in (ru.whole({"f": ids}), ru.tail_decoded({"f": ids}, tail=n - 1) if n > 1 else ru.whole({"f": ids})):
+            runner = make_runner(tiny_models[name], name, dtype, 8)
+            ru.compare(ru.replay(runner, steps), tiny_models[name], {"f": ids}, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(tiny_models, tmp_path, dtype):
+    """The program itself, as a user runs it: steps on standard input, <step>.f32 files out."""
+    name = "A"
+    reqs = {"a": tokens_for(name, 70), "b": tokens_for(name, 33, salt=1), "c": tokens_for(name, 90, salt=2)}
+    steps = ru.mixed(reqs, seed=5, max_live=2)
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(tiny_models[name]), "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", str(ru.max_live_tokens(steps))],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    vocab = TINY[name][0]["vocab_size"]
+    got, held = {}, {}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        f = out / f"{s['step']}.f32"
+        assert f.exists() == (wanted > 0)
+        rows = np.fromfile(f, dtype="<f4").reshape(wanted, vocab) if wanted else None
+        r = 0
+        for e in s["entries"]:
+            start = held.get(e["id"], 0)
+            for w in e["want"]:
+                got[(e["id"], start + w)] = torch.from_numpy(rows[r].astype(np.float64)); r += 1
+            held[e["id"]] = start + len(e["tokens"])
+    ru.compare(got, tiny_models[name], reqs, dtype)
+
+
+def test_step_refuses_bad_input(tiny_models):
+    from lucciola_b200.engine.step import OutOfPages, StepEntry
+    runner = make_runner(tiny_models["A"], "A", "float32", 4)
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        runner.step([StepEntry("x", [1, 256], [0])])
+    with pytest.raises(ValueError, match="twice"):
+        runner.step([StepEntry("x", [1], []), StepEntry("x", [2], [])])
+    with pytest.raises(ValueError, match="place 3"):
+        runner.step([StepEntry("x", [1, 2], [3])])
+    with pytest.raises(ValueError, match="limit is 128"):
+        runner.step([StepEntry("x", [1] * 129, [])])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry("x", [1] * 65, [])])
+    assert runner.manager.num_requests() == 0 and runner.manager.pools[0].num_free == 4     # nothing was taken
+    assert runner.step([StepEntry("x", [1] * 64, [])]) is None

@@ -1,0 +1,232 @@
+"""The scheduler's decisions, with the cache manager but without a GPU.
+
+A stand-in for the step function takes pages exactly as the real one does (admit, extend, release
+behind the window) and "samples" a token that is a fixed function of all tokens of the request so
+far, so that a recomputed request must reproduce its earlier output."""
+import random
+
+import pytest
+
+from lucciola_b200.cache import CacheGroup, CacheManager
+from lucciola_b200.engine.request import Request, Status
+from lucciola_b200.engine.scheduler import Scheduler
+from lucciola_b200.sampling import SamplingParams
+
+VOCAB = 97
+
+
+def next_token(tokens):
+    h = 17
+    for t in tokens:
+        h = (h * 31 + t + 1) % 1000003
+    return h % VOCAB
+
+
+def make(pages=64, page=4, budget=16, seqs=8, max_len=256, chunk=0, eos=(), window=0):
+    groups = [CacheGroup(2, 16, 0, (0,))] + ([CacheGroup(2, 16, window, (1,))] if window else [])
+    m = CacheManager(groups, page, pages, seqs)
+    return m, Scheduler(m, budget, seqs, max_len, chunk, eos)
+
+
+def run_step(m, s, log=None):
+    plan = s.schedule()
+    sampled = []
+    for e in plan:
+        r = e.request
+        if not m.has_request(r.rid):
+            m.admit(r.rid)
+        assert m.length(r.rid) == e.start == r.num_computed
+        assert m.extend(r.rid, e.start + e.num_tokens), "the scheduler planned more than the pool has"
+        if e.sample:
+            sampled.append(next_token(r.tokens[:e.start + e.num_tokens]))
+    for e in plan:
+        m.release_behind_window(e.request.rid)
+    if log is not None:
+        log.append([(e.request.rid, e.start, e.num_tokens, e.sample) for e in plan])
+    events = s.update(plan, sampled)
+    m.check_invariants()
+    return plan, events
+
+
+def req(rid, n, new=8, **kw):
+    rng = random.Random(rid)
+    return Request(rid, [rng.randrange(VOCAB) for _ in range(n)], SamplingParams(max_new_tokens=new, **kw))
+
+
+def expected_output(r):
+    toks, out = list(r.prompt), []
+    for _ in range(r.params.max_new_tokens):
+        t = next_token(toks); out.append(t); toks.append(t)
+    return out
+
+
+def test_prompt_is_cut_under_the_budget_then_decoded():
+    m, s = make(budget=16)
+    r = req(1, 40, new=3)
+    s.add_request(r)
+    log = []
+    while s.has_unfinished():
+        run_step(m, s, log)
+    assert log[:3] == [[(1, 0, 16, False)], [(1, 16, 16, False)], [(1, 32, 8, True)]]
+    assert log[3:] == [[(1, 40, 1, True)], [(1, 41, 1, True)]]
+    assert r.output == expected_output(r) and r.finish_reason == "length" and r.status is Status.FINISHED
+    assert m.pools[0].num_free == 64 and m.num_requests() == 0
+
+
+def test_decodes_go_first_and_the_rest_of_the_budget_goes_to_prompts():
+    m, s = make(budget=10)
+    a, b, c = req(1, 6, new=20), req(2, 7, new=20), req(3, 30, new=2)
+    s.add_request(a); s.add_request(b)
+    log = []
+    run_step(m, s, log)                       # a whole (6) and the first 4 of b
+    assert log[-1] == [(1, 0, 6, True), (2, 0, 4, False)]
+    s.add_request(c)
+    run_step(m, s, log)                       # a decodes; b's rest (3); c gets what is left (6)
+    assert log[-1] == [(1, 6, 1, True), (2, 4, 3, True), (3, 0, 6, False)]
+    run_step(m, s, log)                       # a and b decode first, then c continues with 8
+    assert log[-1] == [(1, 7, 1, True), (2, 7, 1, True), (3, 6, 8, False)]
+
+
+def test_prefill_chunk_option_and_several_prompts_in_one_step():
+    m, s = make(budget=32, chunk=5)
+    s.add_request(req(1, 12)); s.add_request(req(2, 3)); s.add_request(req(3, 9))
+    log = []
+    run_step(m, s, log)
+    assert log[-1] == [(1, 0, 5, False), (2, 0, 3, True), (3, 0, 5, False)]
+
+
+def test_stops_on_eos_max_new_tokens_and_model_length():
+    m, s = make(eos=(next_token([5, 6, 7]),))
+    r = Request(1, [5, 6, 7], SamplingParams(max_new_tokens=9))
+    s.add_request(r)
+    while s.has_unfinished():
+        run_step(m, s)
+    assert len(r.output) == 1 and r.finish_reason == "stop"
+    r2 = Request(2, [5, 6, 7], SamplingParams(max_new_tokens=4, ignore_eos=True))
+    s.add_request(r2)
+    while s.has_unfinished():
+        run_step(m, s)
+    assert len(r2.output) == 4 and r2.finish_reason == "length"
+    m, s = make(max_len=12)
+    r3 = req(3, 9, new=50)
+    s.add_request(r3)
+    while s.has_unfinished():
+        run_step(m, s)
+    assert r3.length == 12 and r3.finish_reason == "length"
+
+
+def test_refuses_what_can_never_run():
+    m, s = make(pages=4, page=4, max_len=64)
+    with pytest.raises(ValueError, match="at least one prompt token"):
+        s.add_request(Request(1, [], SamplingParams()))
+    with pytest.raises(ValueError, match="pages"):
+        s.add_request(req(2, 10, new=10))               # 20 tokens = 5 pages > 4
+    with pytest.raises(ValueError, match="nothing could be generated"):
+        s.add_request(req(3, 64, new=1))
+    with pytest.raises(ValueError, match="max_new_tokens"):
+        s.add_request(Request(4, [1], SamplingParams(max_new_tokens=0)))
+    s.add_request(req(5, 10, new=6))                    # 16 tokens = 4 pages: fits alone
+
+
+def test_admission_waits_for_the_pages_of_the_whole_prompt():
+    m, s = make(pages=5, page=4, budget=64)
+    a = req(1, 12, new=4)
+    s.add_request(a)
+    run_step(m, s)                                      # a holds 3 pages
+    b = req(2, 12, new=2)
+    s.add_request(b)
+    log = []
+    run_step(m, s, log)                                 # a decodes into a 4th page; b needs 3, one is free
+    assert log[-1] == [(1, 12, 1, True)] and list(s.waiting) == [b]
+    while a.status is not Status.FINISHED:
+        run_step(m, s, log)
+    run_step(m, s, log)
+    assert log[-1] == [(2, 0, 12, True)]
+
+
+def test_later_portion_shrinks_to_the_free_pages():
+    m, s = make(pages=6, page=4, budget=9)
+    a, b = req(1, 4, new=12), req(2, 16, new=2)
+    s.add_request(a); s.add_request(b)
+    log = []
+    run_step(m, s, log)                                 # a whole (1 page), b's first 5 (2 pages); b was admitted with 4 free
+    assert log[-1] == [(1, 0, 4, True), (2, 0, 5, False)]
+    run_step(m, s, log)                                 # a takes a page; b's next 8 fit the 2 pages left only up to 16
+    assert log[-1] == [(1, 4, 1, True), (2, 5, 8, False)]
+    run_step(m, s, log)                                 # no page left for position 16.. wait: 13..15 are in b's 4th page
+    assert log[-1] == [(1, 5, 1, True), (2, 13, 3, True)]
+
+
+def test_out_of_pages_preempts_the_latest_and_recomputes_it():
+    m, s = make(pages=6, page=4, budget=64)
+    a, b = req(1, 8, new=12), req(2, 8, new=12)          # each grows to 20 tokens = 5 pages; the pool has 6
+    s.add_request(a); s.add_request(b)
+    log = []
+    while s.has_unfinished():
+        run_step(m, s, log)
+        assert len(log) < 200
+    assert s.num_preemptions >= 1 and b.preemptions >= 1 and a.preemptions == 0    # the one admitted last gives way
+    assert a.output == expected_output(a) and b.output == expected_output(b)
+    # The recomputation runs prompt + output so far as one prompt and samples only at its end.
+    recompute = [e for step in log for e in step if e[0] == 2 and e[1] == 0 and e[2] > 8]
+    assert len(recompute) == 1 and recompute[0][3] is True and b.preemptions == 1
+    assert m.pools[0].num_free == 6
+
+
+def test_preempted_request_returns_to_the_front_of_the_queue():
+    m, s = make(pages=6, page=4, budget=64)
+    a, b, c = req(1, 8, new=12), req(2, 8, new=12), req(3, 4, new=2)
+    s.add_request(a); s.add_request(b)
+    for _ in range(3):
+        run_step(m, s)
+    s.add_request(c)
+    while b.preemptions == 0:
+        run_step(m, s)
+    assert list(s.waiting)[0] is b and b.num_computed == 0 and b.status is Status.WAITING
+
+
+def test_all_prompts_stuck_frees_the_latest():
+    m, s = make(pages=6, page=4, budget=8, chunk=4)       # both are admitted early and are mid-prompt when the pool is empty
+    a, b = req(1, 16, new=2), req(2, 16, new=2)
+    s.add_request(a); s.add_request(b)
+    n = 0
+    while s.has_unfinished():
+        run_step(m, s); n += 1
+        assert n < 100
+    assert a.output == expected_output(a) and b.output == expected_output(b) and s.num_preemptions >= 1
+
+
+def test_abort():
+    m, s = make()
+    a, b = req(1, 8), req(2, 8)
+    s.add_request(a); run_step(m, s); s.add_request(b)
+    assert s.abort(1) and s.abort(2) and not s.abort(3)
+    assert a.finish_reason == b.finish_reason == "abort" and not s.has_unfinished() and m.pools[0].num_free == 64
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_arrivals_under_pressure_finish_with_the_unpressured_output(seed):
+    rng = random.Random(seed)
+    page = rng.choice([2, 4, 8])
+    window = rng.choice([0, 0, 6])
+    m, s = make(pages=rng.randint(12, 24), page=page, budget=rng.choice([8, 16, 48]), seqs=rng.choice([2, 3, 6]),
+                max_len=200, chunk=rng.choice([0, 5]), window=window)
+    cap = m.pools[0].num_pages * page
+    reqs, pending = [], []
+    for i in range(12):
+        n = rng.randint(1, cap // 2)
+        pending.append(req(i + 1, n, new=rng.randint(1, min(16, cap - n))))
+    steps = 0
+    while pending or s.has_unfinished():
+        while pending and rng.random() < 0.4:
+            r = pending.pop(0); s.add_request(r); reqs.append(r)
+        if s.has_unfinished():
+            plan, _ = run_step(m, s)
+            assert plan, "work is waiting but nothing was scheduled"
+            assert sum(e.num_tokens for e in plan if e.num_tokens > 1) <= s.max_tokens_per_step
+            assert len(s.running) <= s.max_num_seqs
+        steps += 1
+        assert steps < 5000
+    for r in reqs:
+        assert r.status is Status.FINISHED and r.output == expected_output(r), (r.rid, r.preemptions)
+    assert all(p.num_free == p.num_pages for p in m.pools) and m.num_requests() == 0
