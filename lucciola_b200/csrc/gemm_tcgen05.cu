@@ -1,0 +1,449 @@
+// Matrix product on the 5th-generation tensor cores: Y[M,N] = X[M,K] . W[N,K]^T, bfloat16 in,
+// 32-bit accumulation in tensor memory, bfloat16 or 32-bit out.  This is the product behind every
+// linear map of the bfloat16 path (q|k|v, o, gate|up, down, the output head); lucciola computes
+// the same contraction with one thread per output element (src/kernels/linear.cu:24-55).
+//
+// Orientation.  Weight rows go on the 128 lanes of the accumulator (the M side of tcgen05.mma),
+// tokens on its columns (the N side, 16..256).  One kernel therefore serves decode (a handful of
+// tokens: a 128 x 16 tile, the weights stream through once) and prefill (128 x 256 tiles).
+//
+// Pipeline of one CTA (192 threads):
+//   warp 0      producer: one thread issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle)
+//               of a 128 x 64 weight tile and a BT x 64 token tile per stage into a ring of stages
+//   warp 1      one thread issues tcgen05.mma (kind::f16, M=128, N=BT, K=16) four times per stage on
+//               shared-memory descriptors; tcgen05.commit frees the stage, and at the end signals
+//               the epilogue; this warp also allocates and frees tensor memory
+//   warps 2..5  epilogue: tcgen05.ld (32 lanes x 32 bit) of the accumulator, conversion, stores
+// K may be split over gridDim.z: each split writes 32-bit partials to a workspace; the CTA that
+// finishes last for a tile adds the partials in the order of the splits (so the result does not
+// depend on timing) and writes the output.
+//
+// Every wait on an mbarrier is bounded: when a wait gives up the CTA records a code in a device
+// flag, stops, waits (bounded) for its loads in flight, frees its tensor memory and returns.
+// K must be a multiple of 8 and X, W 16-byte aligned (TMA strides); M, N, K tails are handled by
+// TMA's zero fill on loads and by bounds checks on stores.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace lb {
+
+// ---- device error flag (shared by kernels with bounded waits) ---------------------------------
+__device__ int g_device_error = 0;
+
+constexpr int BM = 128;          // weight rows of a tile (lanes of the accumulator)
+constexpr int BK = 64;           // k extent of a stage: 64 bfloat16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr unsigned long long WAIT_CYCLES = 4000000000ull;   // about two seconds
+
+enum : int { ERR_FULL_WAIT = 101, ERR_EMPTY_WAIT = 102, ERR_ACCUM_WAIT = 103 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the limit passed or another role of the CTA gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (unsigned it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if ((unsigned long long)(clock64() - t0) > WAIT_CYCLES) {
+        *abort_flag = code;
+        atomicCAS(&g_device_error, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, groups
+// of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
+struct GemmParams {
+  void* y;              // [M, N] output, row stride ldy
+  float* workspace;     // [splits, M, N] partials (split-K only)
+  int* counters;        // one per output tile, zero between launches (split-K only)
+  int M, N, K;
+  long long ldy;
+  int out_dtype;        // LB_F32 or LB_BF16
+};
+
+template <int BT>
+__host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
+
+template <int BT, int STAGES>
+struct SmemLayout {
+  static constexpr int W_BYTES = BM * BK * 2;
+  static constexpr int X_BYTES = BT * BK * 2;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16;
+};
+
+template <int BT, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+  using L = SmemLayout<BT, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // The swizzled tiles need 1024-byte alignment.
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  const uint32_t accum_bar = bar_base + 8u * (2 * STAGES);
+  uint32_t* tmem_slot = (uint32_t*)(smem + L::BAR_OFFSET + (2 * STAGES + 1) * 8);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* last_flag = (int*)(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BT;
+  const int splits = gridDim.z, split = blockIdx.z;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_begin = (int)((long long)kb_total * split / splits);
+  const int kb_end = (int)((long long)kb_total * (split + 1) / splits);
+  const int num_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols<BT>()) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- producer --------------------------------------------------------------------------
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t parity = ((i / STAGES) & 1) ^ 1;          // a fresh barrier passes a wait on parity 1
+        if (!mbar_wait(empty_bar(s), parity, abort_flag, ERR_EMPTY_WAIT)) break;
+        mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+        const uint32_t dst = smem_base + s * L::STAGE_BYTES;
+        const int k = (kb_begin + i) * BK;
+        tma_load_2d(dst, &map_w, k, n0, full_bar(s));
+        tma_load_2d(dst + L::W_BYTES, &map_x, k, m0, full_bar(s));
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        // Give the loads in flight time to land before this CTA's shared memory is given away.
+        for (int i = max(0, issued - STAGES); i < issued; ++i) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(full_bar(i % STAGES), (i / STAGES) & 1) &&
+                 (unsigned long long)(clock64() - t0) < WAIT_CYCLES / 8) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- tensor-core issue ---------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BT);
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % STAGES;
+        ok = mbar_wait(full_bar(s), (i / STAGES) & 1, abort_flag, ERR_FULL_WAIT);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
+        const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + L::W_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // 16 bfloat16 = 32 bytes further along k inside the swizzled row: +2 in the address field
+          umma_f16(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (i | k) != 0);
+        }
+        umma_commit(empty_bar(s));
+      }
+      if (ok) umma_commit(accum_bar);
+    }
+  } else {
+    // ---- epilogue: warps 2..5, lanes (warp % 4) * 32 .. + 31 of the accumulator ----------------
+    const int quarter = warp & 3;
+    const int n = n0 + quarter * 32 + lane;
+    mbar_wait(accum_bar, 0, abort_flag, ERR_ACCUM_WAIT);
+    // All four epilogue warps take the same path: agree on the outcome before any of them goes on.
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = (*abort_flag == 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+      const bool direct = splits == 1;
+      float* part = direct ? nullptr : p.workspace + (size_t)split * p.M * p.N;
+#pragma unroll 1
+      for (int c = 0; c < BT; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c + j;
+            if (m < p.M) {
+              const float v = __uint_as_float(r[j]);
+              if (!direct) part[(size_t)m * p.N + n] = v;
+              else if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + n] = v;
+              else ((bf16*)p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+      if (!direct) {
+        // The CTA that arrives last for this tile adds the partials in the order of the splits.
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        if (threadIdx.x == 64) {
+          const int prev = atomicAdd(&p.counters[tile], 1);
+          *last_flag = (prev == splits - 1);
+          if (prev == splits - 1) p.counters[tile] = 0;           // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          if (n < p.N) {
+            for (int m = m0; m < min(m0 + BT, p.M); ++m) {
+              float acc = 0.f;
+              for (int z = 0; z < splits; ++z) acc += __ldcg(p.workspace + ((size_t)z * p.M + m) * p.N + n);
+              if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + n] = acc;
+              else ((bf16*)p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(acc);
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols<BT>()) : "memory");
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+// A [rows, K] bfloat16 matrix, row stride ld elements, read in boxes of box_rows x 64.
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct MapKey {
+  const void* base; long long rows, K, ld; int box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.base);
+    h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.K;
+    h = h * 1000003u ^ (size_t)k.ld; h = h * 1000003u ^ (size_t)k.box_rows;
+    return h;
+  }
+};
+
+static bool cached_map(CUtensorMap* out, const void* base, long long rows, long long K, long long ld, int box_rows) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{base, rows, K, ld, box_rows};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  if (cache.size() > 8192) cache.clear();
+  if (!make_map(out, base, rows, K, ld, box_rows)) return false;
+  cache.emplace(key, *out);
+  return true;
+}
+
+template <int BT, int STAGES>
+int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, int splits, cudaStream_t stream) {
+  using L = SmemLayout<BT, STAGES>;
+  const int smem = L::TOTAL + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) { set_error("gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e)); return 2; }
+    configured = true;
+  }
+  dim3 grid((p.N + BM - 1) / BM, (p.M + BT - 1) / BT, splits);
+  gemm_tcgen05_kernel<BT, STAGES><<<grid, 192, smem, stream>>>(mw, mx, p);
+  return 0;
+}
+
+}  // namespace lb
+
+// Which (token tile, splits) the launcher would choose; exposed so that callers can size the workspace
+// and tests can force a choice.  Returns splits; *bt receives the token tile.
+LB_EXPORT int lb_gemm_tcgen05_plan(int M, int N, int K, int* bt) {
+  int t = 16;
+  if (M > 128) {
+    t = (((M + 255) / 256) * 256 <= ((M + 127) / 128) * 128) ? 256 : 128;
+    if (t == 256 && ((N + lb::BM - 1) / lb::BM) * ((M + 255) / 256) < 148) t = 128;   // more, smaller tiles to fill the SMs
+  }
+  else if (M > 64) t = 128;
+  else if (M > 32) t = 64;
+  else if (M > 16) t = 32;
+  if (bt) *bt = t;
+  const int tiles = ((N + lb::BM - 1) / lb::BM) * ((M + t - 1) / t);
+  const int kb = (K + lb::BK - 1) / lb::BK;
+  int splits = 1;
+  if (tiles < 148 && M <= 256) {       // splitting pays only while the weights are what is streamed
+    splits = (296 + tiles - 1) / tiles;
+    if (splits > kb / 4) splits = kb / 4;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+  }
+  return splits;
+}
+
+// y[M,N] = x[M,K] . w[N,K]^T.  x: bfloat16, row stride ldx; w: bfloat16, contiguous; y: bfloat16 or float32,
+// row stride ldy.  workspace (float32, workspace_elems elements) and counters (int32, zero, counters_len
+// entries) are needed when K is split; with too little of either the product runs unsplit.
+// force_bt / force_splits (0: choose) are for tests.
+LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
+                              long long ldy, float* workspace, long long workspace_elems, int* counters,
+                              int counters_len, int force_bt, int force_splits, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(y_dtype), "gemm_tcgen05: bad output dtype %d", y_dtype);
+  LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && ldx >= K && ldy >= N, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+  LB_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0, "gemm_tcgen05: K=%d and the row stride %lld must be multiples of 8 (TMA strides are multiples of 16 bytes)", K, ldx);
+  LB_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
+  if (M == 0) return 0;
+  int bt = 16;
+  int splits = lb_gemm_tcgen05_plan(M, N, K, &bt);
+  if (force_bt) {
+    LB_CHECK_ARG(force_bt == 16 || force_bt == 32 || force_bt == 64 || force_bt == 128 || force_bt == 256,
+                 "gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", force_bt);
+    bt = force_bt;
+  }
+  if (force_splits) splits = force_splits;
+  const int kb = (K + lb::BK - 1) / lb::BK;
+  if (splits > kb) splits = kb;
+  const long long tiles = (long long)((N + lb::BM - 1) / lb::BM) * ((M + bt - 1) / bt);
+  if (splits > 1 && (workspace == nullptr || counters == nullptr || (long long)splits * M * N > workspace_elems ||
+                     tiles > counters_len))
+    splits = 1;
+  LB_CHECK_ARG((M + bt - 1) / bt <= 65535 && splits <= 65535, "gemm_tcgen05: grid too large");
+
+  CUtensorMap mw, mx;
+  if (!lb::cached_map(&mw, w, N, K, K, lb::BM) || !lb::cached_map(&mx, x, M, K, ldx, bt)) {
+    lb::set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);
+    return 3;
+  }
+  lb::GemmParams p;
+  p.y = y; p.workspace = workspace; p.counters = counters; p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.out_dtype = y_dtype;
+  int rc = 0;
+  switch (bt) {
+    case 16: rc = lb::launch_tc<16, 6>(mw, mx, p, splits, stream); break;
+    case 32: rc = lb::launch_tc<32, 6>(mw, mx, p, splits, stream); break;
+    case 64: rc = lb::launch_tc<64, 6>(mw, mx, p, splits, stream); break;
+    case 128: rc = lb::launch_tc<128, 6>(mw, mx, p, splits, stream); break;
+    default: rc = lb::launch_tc<256, 4>(mw, mx, p, splits, stream); break;
+  }
+  if (rc) return rc;
+  LB_CHECK_LAUNCH("gemm_tcgen05");
+  return 0;
+}
+
+// Reads and clears the device error flag that kernels with bounded waits set when a wait gave up.
+// Synchronises the device.  0: no error.
+LB_EXPORT int lb_device_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, lb::g_device_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(lb::g_device_error, &zero, sizeof(int));
+  return v;
+}

@@ -40,6 +40,8 @@ _SIGNATURES = {
     "lb_swiglu": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p],
     "lb_gemm_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
                       c_longlong, c_void_p],
+    "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
+                        c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -186,10 +188,59 @@ def sample(tokens: torch.Tensor, logits: torch.Tensor, stream: int, temperature:
     _call("lb_sample", tokens.data_ptr(), logits.data_ptr(), _ptr(temperature), _ptr(keys), _ptr(counters), R, V, stream)
 
 
+_WORKSPACE_ELEMS = 16 * 1024 * 1024      # float32 partials of split products (64 MB)
+_COUNTERS = 4096
+_scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _gemm_scratch(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per device: the workspace for partial sums of split products and the tile counters (zero between launches)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    s = _scratch.get(key)
+    if s is None:
+        s = (torch.empty(_WORKSPACE_ELEMS, dtype=torch.float32, device=device),
+             torch.zeros(_COUNTERS, dtype=torch.int32, device=device))
+        _scratch[key] = s
+    return s
+
+
+def gemm_tcgen05_ok(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
+    """The conditions of the tensor-core kernel: bfloat16 operands, K a multiple of 8, 16-byte alignment."""
+    K = x.shape[1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and y.dtype in (torch.bfloat16, torch.float32)
+            and K % 8 == 0 and (x.shape[0] == 1 or x.stride(0) % 8 == 0) and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and w.is_contiguous() and x.stride(1) == 1 and y.stride(1) == 1)
+
+
+def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, force_bt: int = 0,
+                 force_splits: int = 0) -> None:
+    """y[M, N] = x[M, K] . w[N, K]^T on the tensor cores (tcgen05, accumulators in tensor memory)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(y.shape) != (M, N):
+        raise KernelError(f"gemm shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    if not gemm_tcgen05_ok(y, x, w):
+        raise KernelError("gemm_tcgen05 takes bfloat16 operands with K a multiple of 8, 16-byte aligned, unit column stride")
+    ws, counters = _gemm_scratch(x.device)
+    _call("lb_gemm_tcgen05", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), w.data_ptr(), M, N, K,
+          x.stride(0) if M > 1 else K, y.stride(0) if M > 1 else N, ws.data_ptr(), ws.numel(), counters.data_ptr(),
+          counters.numel(), force_bt, force_splits, stream)
+
+
+def device_error() -> int:
+    """Code that a kernel left when one of its bounded waits gave up (0: none).  Synchronises the device."""
+    lib = library()
+    lib.lb_device_error.restype = c_int
+    return int(lib.lb_device_error())
+
+
 def linear(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, fast: bool) -> None:
-    """y = x . w^T.  `fast` allows the tensor-core kernel where its conditions hold; the 32-bit
-    path never sets it."""
-    gemm_plain(y, x, w, stream)
+    """y = x . w^T.  `fast` allows the tensor-core kernel where its conditions hold (otherwise, and
+    always on the 32-bit path, the product runs on the ordinary pipes)."""
+    if fast and gemm_tcgen05_ok(y, x, w):
+        gemm_tcgen05(y, x, w, stream)
+    else:
+        gemm_plain(y, x, w, stream)
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
