@@ -1,0 +1,379 @@
+// Causal grouped-query attention over paged keys and values on the tensor cores (bfloat16),
+// for portions of prompts and for decoded tokens alike.
+//
+// A work item ("tile") is a run of up to 64/G consecutive tokens of one request (G = query heads per
+// kv head) and one kv head: its G*tokens query rows are stacked into a 64-row tile, so that the keys
+// and values of a kv head are read once for all query heads that share them.  A decoded token is a
+// tile with one token.  The keys a tile sees may be cut into `splits` ranges (grid z): each range
+// produces an unnormalised partial (m, l, o) in 32-bit, and a second kernel combines the partials in
+// the order of the ranges.  That is what keeps all SMs busy when few tokens attend to long contexts.
+//
+// Per CTA (4 warps, 16 query rows each): keys and values stream through a ring of shared-memory
+// stages of 64 keys, fetched with 16-byte cp.async copies through the block table (any page size);
+// scores S = Q K^T and the product P V run on mma.sync.m16n8k16 with ldmatrix-fed fragments; the
+// softmax is the online form of src/kernels/flash_attention.cu:246-298 of lucciola (m, l, o per row,
+// 32-bit), with P rounded to bfloat16 for the second product.  Keys outside a row's range (after its
+// position, before its window, past the end) are masked, and their rows in shared memory are zeros,
+// so whatever a reused page still holds cannot reach a sum (lucciola zero-fills the tail of the last
+// page for the same reason, src/kernels/flash_attention.cu:142-154).
+//
+// Head sizes: any multiple of 8 up to 128 (padded with zeros to 64 or 128 in shared memory).
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int FA_ROWS = 64;      // query rows of a tile
+constexpr int FA_KEYS = 64;      // keys of a stage
+constexpr int FA_STAGES = 3;
+constexpr int FA_THREADS = 128;
+
+struct FlashParams {
+  const bf16* q; bf16* out;                 // [T, nq, d]
+  const bf16* k_cache; const bf16* v_cache; // [pages, nkv, page_size, d]
+  const int* positions;                     // [T]
+  const int* block_table; int max_pages;    // [S, max_pages]
+  const int4* tiles;                        // {first token, tokens, request index, unused}
+  float* part_o;                            // [tiles, nkv, splits, part_rows, d]
+  float* part_ml;                           // [tiles, nkv, splits, part_rows, 2]
+  int part_rows;                            // most query rows of any tile
+  int num_q_heads, num_kv_heads, head_dim, group, page_size, window, splits;
+  float scale_log2;                         // scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;             // 0: the 16 bytes are filled with zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold DP bfloat16.
+// Chunks are permuted by the row's low bits so that ldmatrix reads hit all banks.
+template <int DP>
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+  return (uint32_t)(row * (DP * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+template <int DP>
+__global__ void __launch_bounds__(FA_THREADS)
+flash_attention_kernel(FlashParams p) {
+  constexpr int CHUNKS = DP / 8;                  // 16-byte chunks of a row
+  constexpr int TILE_BYTES = FA_KEYS * DP * 2;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t q_smem = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t k_smem = q_smem + FA_ROWS * DP * 2;
+  const uint32_t v_smem = k_smem + FA_STAGES * TILE_BYTES;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int4 tile = p.tiles[blockIdx.x];
+  const int t0 = tile.x, ntok = tile.y, seq = tile.z;
+  const int kvh = blockIdx.y, split = blockIdx.z;
+  const int G = p.group, d = p.head_dim;
+  const int rows = ntok * G;
+  const int pos0 = p.positions[t0];
+  const int pos_last = pos0 + ntok - 1;
+  const int* bt = p.block_table + (size_t)seq * p.max_pages;
+
+  // Keys this tile can see, and the part of them this split handles (multiples of a stage).
+  const int lo_tile = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int span = pos_last - lo_tile + 1;
+  const int per_split = ((span + p.splits - 1) / p.splits + FA_KEYS - 1) / FA_KEYS * FA_KEYS;
+  const int kbeg = lo_tile + split * per_split;
+  const int kend = min(pos_last + 1, kbeg + per_split);      // exclusive
+  const int num_stages = kend > kbeg ? (kend - kbeg + FA_KEYS - 1) / FA_KEYS : 0;
+
+  // ---- Q: global -> shared (zero padded), then into A fragments ------------------------------
+  for (int idx = tid; idx < FA_ROWS * CHUNKS; idx += FA_THREADS) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool valid = r < rows && c * 8 < d;
+    const bf16* src = p.q;
+    if (valid) src = p.q + ((size_t)(t0 + r / G) * p.num_q_heads + kvh * G + r % G) * d + c * 8;
+    cp_async16(q_smem + tile_offset<DP>(r, c), src, valid);
+  }
+  cp_async_commit();
+
+  auto load_stage = [&](int stage_idx) {
+    const int buf = stage_idx % FA_STAGES;
+    const int kbase = kbeg + stage_idx * FA_KEYS;
+    for (int idx = tid; idx < FA_KEYS * CHUNKS; idx += FA_THREADS) {
+      const int r = idx / CHUNKS, c = idx % CHUNKS;
+      const int j = kbase + r;
+      bool valid = j < kend && c * 8 < d;
+      size_t off = 0;
+      if (valid) {
+        const int page = bt[j / p.page_size];
+        valid = page >= 0;
+        off = (((size_t)(valid ? page : 0) * p.num_kv_heads + kvh) * p.page_size + (j % p.page_size)) * d + c * 8;
+      }
+      const uint32_t so = buf * TILE_BYTES + tile_offset<DP>(r, c);
+      cp_async16(k_smem + so, p.k_cache + off, valid);
+      cp_async16(v_smem + so, p.v_cache + off, valid);
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < FA_STAGES - 1; ++s) {
+    if (s < num_stages) load_stage(s);
+    cp_async_commit();
+  }
+
+  // Rows of this thread: r0 = warp*16 + lane/4 and r0 + 8.
+  const int r0 = warp * 16 + (lane >> 2);
+  int row_pos[2], row_lo[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = r0 + 8 * h;
+    row_pos[h] = r < rows ? pos0 + r / G : -1;                  // -1: no key passes the mask
+    row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+  }
+  const bool warp_active = warp * 16 < rows;
+
+  cp_async_wait<FA_STAGES - 1>();     // Q has landed (the stage loads may still be in flight)
+  __syncthreads();
+  uint32_t qf[DP / 16][4];
+  if (warp_active) {
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk) {
+      const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int c = kk * 2 + (lane >> 4);
+      ldmatrix_x4(q_smem + tile_offset<DP>(r, c), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+    }
+  }
+
+  float o[DP / 8][4];
+#pragma unroll
+  for (int i = 0; i < DP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  for (int st = 0; st < num_stages; ++st) {
+    cp_async_wait<FA_STAGES - 2>();
+    __syncthreads();                   // stage st is visible; the buffer of stage st-1 is free
+    if (st + FA_STAGES - 1 < num_stages) load_stage(st + FA_STAGES - 1);
+    cp_async_commit();
+    if (!warp_active) continue;
+
+    const int buf = st % FA_STAGES;
+    const uint32_t kb = k_smem + buf * TILE_BYTES, vb = v_smem + buf * TILE_BYTES;
+    const int kbase = kbeg + st * FA_KEYS;
+
+    // ---- S = Q K^T: 16 rows x 64 keys per warp ------------------------------------------------
+    float s[FA_KEYS / 8][4];
+#pragma unroll
+    for (int i = 0; i < FA_KEYS / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk) {
+#pragma unroll
+      for (int nb = 0; nb < FA_KEYS / 8; nb += 2) {
+        // matrices: (keys nb, dims lo), (keys nb, dims hi), (keys nb+1, dims lo), (keys nb+1, dims hi)
+        const int key = nb * 8 + (lane & 7) + (lane >> 4) * 8;
+        const int c = kk * 2 + ((lane >> 3) & 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(kb + tile_offset<DP>(key, c), b0, b1, b2, b3);
+        mma_bf16(s[nb], qf[kk], b0, b1);
+        mma_bf16(s[nb + 1], qf[kk], b2, b3);
+      }
+    }
+
+    // ---- mask, online softmax ----------------------------------------------------------------
+    const bool need_mask = (kbase + FA_KEYS - 1 > pos0) || (p.window > 0) || (kbase + FA_KEYS > kend) || (rows < FA_ROWS);
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int nb = 0; nb < FA_KEYS / 8; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        if (need_mask) {
+          const int j = kbase + nb * 8 + (lane & 3) * 2 + (e & 1);
+          if (j > row_pos[h] || j < row_lo[h] || j >= kend) s[nb][e] = -INFINITY;
+        }
+        m_new[h] = fmaxf(m_new[h], s[nb][e]);
+      }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+      m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+      m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h] * p.scale_log2;
+      alpha[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] * p.scale_log2 - m_use[h]);
+      m_run[h] = m_new[h];
+    }
+    float row_sum[2] = {0.f, 0.f};
+    uint32_t pf[FA_KEYS / 16][4];
+#pragma unroll
+    for (int nb = 0; nb < FA_KEYS / 8; ++nb) {
+      float pv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        pv[e] = exp2f(s[nb][e] * p.scale_log2 - m_use[h]);       // exp2(-inf) = 0 for masked keys
+        row_sum[h] += pv[e];
+      }
+      // C fragments of two key blocks become one A fragment of 16 keys
+      pf[nb >> 1][(nb & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);
+      pf[nb >> 1][(nb & 1) * 2 + 1] = pack_bf16(pv[2], pv[3]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * alpha[h] + row_sum[h];
+#pragma unroll
+    for (int i = 0; i < DP / 8; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+
+    // ---- O += P V ----------------------------------------------------------------------------------
+#pragma unroll
+    for (int ks = 0; ks < FA_KEYS / 16; ++ks) {
+#pragma unroll
+      for (int db = 0; db < DP / 8; db += 2) {
+        // matrices (transposed on load): (keys lo, dims db), (keys hi, dims db), (keys lo, dims db+1), (keys hi, dims db+1)
+        const int key = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = db + (lane >> 4);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(vb + tile_offset<DP>(key, c), b0, b1, b2, b3);
+        mma_bf16(o[db], pf[ks], b0, b1);
+        mma_bf16(o[db + 1], pf[ks], b2, b3);
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // ---- write: the row sums live in four lanes each ------------------------------------------------
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  if (!warp_active) return;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = r0 + 8 * h;
+    if (r >= rows) continue;
+    const int token = t0 + r / G, head = kvh * G + r % G;
+    if (p.splits == 1) {
+      const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+      bf16* dst = p.out + ((size_t)token * p.num_q_heads + head) * d;
+#pragma unroll
+      for (int i = 0; i < DP / 8; ++i) {
+        const int dim = i * 8 + (lane & 3) * 2;
+        if (dim < d) *reinterpret_cast<__nv_bfloat162*>(dst + dim) = __floats2bfloat162_rn(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      }
+    } else {
+      const size_t slot = (((size_t)blockIdx.x * p.num_kv_heads + kvh) * p.splits + split) * p.part_rows + r;
+      float* dst = p.part_o + slot * d;
+#pragma unroll
+      for (int i = 0; i < DP / 8; ++i) {
+        const int dim = i * 8 + (lane & 3) * 2;
+        if (dim < d) *reinterpret_cast<float2*>(dst + dim) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+      }
+      if ((lane & 3) == 0) {
+        p.part_ml[slot * 2 + 0] = m_run[h] == -INFINITY ? -INFINITY : m_run[h] * p.scale_log2;
+        p.part_ml[slot * 2 + 1] = l_run[h];
+      }
+    }
+  }
+}
+
+// Combines the partials of the splits, in their order: out = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M).
+__global__ void flash_combine_kernel(FlashParams p) {
+  const int4 tile = p.tiles[blockIdx.x];
+  const int kvh = blockIdx.y;
+  const int rows = tile.y * p.group, d = p.head_dim;
+  for (int r = threadIdx.y; r < rows; r += blockDim.y) {
+    const size_t base = ((size_t)blockIdx.x * p.num_kv_heads + kvh) * p.splits;
+    float M = -INFINITY;
+    for (int z = 0; z < p.splits; ++z) M = fmaxf(M, p.part_ml[((base + z) * p.part_rows + r) * 2]);
+    float L = 0.f;
+    for (int z = 0; z < p.splits; ++z) {
+      const float mz = p.part_ml[((base + z) * p.part_rows + r) * 2];
+      if (mz != -INFINITY) L += p.part_ml[((base + z) * p.part_rows + r) * 2 + 1] * exp2f(mz - M);
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const int token = tile.x + r / p.group, head = kvh * p.group + r % p.group;
+    bf16* dst = p.out + ((size_t)token * p.num_q_heads + head) * d;
+    for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
+      float acc = 0.f;
+      for (int z = 0; z < p.splits; ++z) {
+        const float mz = p.part_ml[((base + z) * p.part_rows + r) * 2];
+        if (mz != -INFINITY) acc += p.part_o[((base + z) * p.part_rows + r) * d + dim] * exp2f(mz - M);
+      }
+      dst[dim] = __float2bfloat16_rn(acc * inv);
+    }
+  }
+}
+
+}  // namespace lb
+
+// Floats of workspace a launch with these sizes needs (partials of o, then of m and l).
+LB_EXPORT long long lb_attention_flash_workspace(int num_tiles, int num_kv_heads, int splits, int part_rows, int head_dim) {
+  if (splits <= 1) return 0;
+  return (long long)num_tiles * num_kv_heads * splits * part_rows * (head_dim + 2);
+}
+
+// q, out: [T, nq, d] bfloat16.  tiles: [num_tiles] of {first token, tokens, request index, 0} with
+// tokens * (nq / nkv) <= part_rows <= 64.  workspace: float32, needed when splits > 1.
+LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                 const int* positions, const int* block_table, const void* tiles, int num_tiles,
+                                 int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
+                                 int window, float scale, int splits, int part_rows, float* workspace,
+                                 long long workspace_elems, cudaStream_t stream) {
+  LB_CHECK_ARG(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
+               "attention_flash: %d query heads are not a multiple of %d kv heads", num_q_heads, num_kv_heads);
+  const int group = num_q_heads / num_kv_heads;
+  LB_CHECK_ARG(group <= lb::FA_ROWS, "attention_flash: %d query heads per kv head, at most %d", group, lb::FA_ROWS);
+  LB_CHECK_ARG(head_dim >= 8 && head_dim <= 128 && head_dim % 8 == 0,
+               "attention_flash: head_dim %d must be a multiple of 8 between 8 and 128", head_dim);
+  LB_CHECK_ARG(page_size > 0 && max_pages > 0 && window >= 0 && splits >= 1 && splits <= 65535, "attention_flash: bad sizes");
+  LB_CHECK_ARG(num_kv_heads <= 65535, "attention_flash: too many kv heads");
+  LB_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) &&
+               ((uintptr_t)out % 4 == 0), "attention_flash: operands must be 16-byte aligned");
+  if (num_tiles == 0) return 0;
+  LB_CHECK_ARG(part_rows >= group && part_rows <= lb::FA_ROWS, "attention_flash: rows of a tile must be in %d..%d, got %d", group, lb::FA_ROWS, part_rows);
+  LB_CHECK_ARG(splits == 1 || (workspace && workspace_elems >= lb_attention_flash_workspace(num_tiles, num_kv_heads, splits, part_rows, head_dim)),
+               "attention_flash: the workspace is too small for %d splits", splits);
+  lb::FlashParams p;
+  p.q = (const lb::bf16*)q; p.out = (lb::bf16*)out; p.k_cache = (const lb::bf16*)k_cache; p.v_cache = (const lb::bf16*)v_cache;
+  p.positions = positions; p.block_table = block_table; p.max_pages = max_pages; p.tiles = (const int4*)tiles;
+  p.part_o = workspace;
+  p.part_ml = workspace ? workspace + (long long)num_tiles * num_kv_heads * splits * part_rows * head_dim : nullptr;
+  p.part_rows = part_rows;
+  p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim; p.group = group;
+  p.page_size = page_size; p.window = window; p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(num_tiles, num_kv_heads, splits);
+  const int dp = head_dim <= 64 ? 64 : 128;
+  const int smem = (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2;
+  if (dp == 64) {
+    static bool cfg = false;
+    if (!cfg) { cudaFuncSetAttribute(lb::flash_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
+    lb::flash_attention_kernel<64><<<grid, lb::FA_THREADS, smem, stream>>>(p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { cudaFuncSetAttribute(lb::flash_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
+    lb::flash_attention_kernel<128><<<grid, lb::FA_THREADS, smem, stream>>>(p);
+  }
+  LB_CHECK_LAUNCH("attention_flash");
+  if (splits > 1) {
+    dim3 cgrid(num_tiles, num_kv_heads), cblock(32, 4);
+    lb::flash_combine_kernel<<<cgrid, cblock, 0, stream>>>(p);
+    LB_CHECK_LAUNCH("attention_flash combine");
+  }
+  return 0;
+}

@@ -83,6 +83,9 @@ class ModelRunner:
         self.cache = DeviceCache(requests, self.groups, self.page_size, [self.num_pages] * len(self.groups),
                                  options.max_num_seqs, rt.act_dtype, self.device)
         self.max_pages_per_seq = -(-self.max_model_len // self.page_size)
+        # Group sizes for which a step carries tiles of the tensor-core attention kernel.
+        self.tile_groups = sorted({g for b in model.blocks if (g := b.mixer.query_group_size()) and g <= 64}) \
+            if rt.fast_kernels else []
         self._staging: Optional[_Staging] = None
         self.steps_run = 0
         self.tokens_run = 0
@@ -117,6 +120,17 @@ class ModelRunner:
             torch.cuda.current_stream(self.device).synchronize()
             self._staging = _Staging(self.device, max(n, 4096) * 2)
         return self._staging
+
+    @staticmethod
+    def _tiles(q_lens: Sequence[int], group: int) -> list[tuple[int, int, int, int]]:
+        """Runs of up to 64 // group consecutive tokens of one request: (first token, tokens, request, 0)."""
+        per = 64 // group
+        tiles, t = [], 0
+        for i, n in enumerate(q_lens):
+            for off in range(0, n, per):
+                tiles.append((t + off, min(per, n - off), i, 0))
+            t += n
+        return tiles
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run the entries as one batch.  Returns logits [wanted, vocab] (float32, on the device) in the
@@ -161,7 +175,8 @@ class ModelRunner:
         S, T = len(entries), sum(q_lens)
         R = sum(len(e.want) for e in entries)
         G, P = len(self.groups), self.max_pages_per_seq
-        total = 3 * T + (S + 1) + 2 * S + R + G * S * P
+        tile_lists = {g: self._tiles(q_lens, g) for g in self.tile_groups}
+        total = 3 * T + (S + 1) + 2 * S + R + G * S * P + sum(4 * len(t) + 3 for t in tile_lists.values())
         st = self._staging_for(total)
         hi, host = st.next_host()
         h = host.numpy()
@@ -174,6 +189,9 @@ class ModelRunner:
         tok, pos, seq = take(T), take(T), take(T)
         cu, ctx, slots, rows = take(S + 1), take(S), take(S), take(R)
         tables = [take(S * P).reshape(S, P) for _ in range(G)]
+        for g, tl in tile_lists.items():
+            o = (o + 3) & ~3                      # the kernel reads a tile as one 16-byte word
+            take(4 * len(tl))[:] = np.asarray(tl, dtype=np.int32).reshape(-1)
         t = r = 0
         cu[0] = 0
         for i, e in enumerate(entries):
@@ -204,11 +222,15 @@ class ModelRunner:
         d_tok, d_pos, d_seq = view(T), view(T), view(T)
         d_cu, d_ctx, d_slots, d_rows = view(S + 1), view(S), view(S), view(R)
         d_tables = [view(S * P).view(S, P) for _ in range(G)]
+        attn_meta = {}
+        for g, tl in tile_lists.items():
+            o = (o + 3) & ~3
+            attn_meta[g] = (view(4 * len(tl)).view(len(tl), 4), min(64, max(n for _, n, _, _ in tl) * g))
 
         step = StepContext(
             num_tokens=T, num_seqs=S, positions=d_pos, token_seq=d_seq, cu_tokens=d_cu, context_lens=d_ctx,
             block_tables=d_tables, state_slots=d_slots, q_lens=q_lens, start_positions=starts,
-            max_q_len=max(q_lens), max_context_len=max(s + n for s, n in zip(starts, q_lens)))
+            max_q_len=max(q_lens), max_context_len=max(s + n for s, n in zip(starts, q_lens)), attn_meta=attn_meta)
         self.rt.stream = torch.cuda.current_stream(self.device).cuda_stream
         if new_slots and self.cache.states:
             self.cache.zero_slots(torch.tensor(new_slots, dtype=torch.long, device=self.device))

@@ -42,6 +42,8 @@ _SIGNATURES = {
                       c_longlong, c_void_p],
     "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
                         c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -243,9 +245,66 @@ def linear(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, fast:
         gemm_plain(y, x, w, stream)
 
 
+_attn_ws: dict[int, torch.Tensor] = {}
+
+
+def _attention_workspace(device: torch.device, elems: int) -> torch.Tensor:
+    """Per device: float32 scratch for the partial results of split attention; grows on demand."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _attn_ws.get(key)
+    if ws is None or ws.numel() < elems:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the attention workspace cannot grow while a CUDA graph is captured; run the step once before")
+        ws = torch.empty(max(elems, 1 << 20), dtype=torch.float32, device=device)
+        _attn_ws[key] = ws
+    return ws
+
+
+def attention_flash_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """The conditions of the tensor-core attention kernel."""
+    return (q.dtype == torch.bfloat16 and head_dim % 8 == 0 and 8 <= head_dim <= 128
+            and num_q_heads % num_kv_heads == 0 and num_q_heads // num_kv_heads <= 64)
+
+
+def attention_splits(num_tiles: int, num_kv_heads: int, max_span: int) -> int:
+    """Into how many key ranges a launch is cut: enough CTAs for twice the SMs, ranges of 256 keys at least."""
+    base = max(num_tiles * num_kv_heads, 1)
+    return max(1, min(-(-296 // base), max_span // 256, 64))
+
+
+def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, max_rows: int,
+                    num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+                    splits: int, stream: int) -> None:
+    """Tensor-core attention over pages.  tiles: int32 [n, 4] of (first token, tokens, request index, 0)."""
+    _check(q, "q", torch.bfloat16); _check(out, "attention output", torch.bfloat16)
+    _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
+    _check(positions, "positions", torch.int32); _check(block_table, "block table", torch.int32)
+    _check(tiles, "tiles", torch.int32)
+    n = tiles.shape[0]
+    ws, ws_elems = None, 0
+    if splits > 1:
+        ws_elems = n * num_kv_heads * splits * max_rows * (head_dim + 2)
+        ws = _attention_workspace(q.device, ws_elems)
+        ws_elems = ws.numel()
+    _call("lb_attention_flash", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+          positions.data_ptr(), block_table.data_ptr(), tiles.data_ptr(), n, num_q_heads, num_kv_heads, head_dim,
+          page_size, block_table.shape[1], window, scale, splits, max_rows, _ptr(ws), ws_elems, stream)
+
+
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
               num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
               stream: int, fast: bool) -> None:
-    """Causal attention of this step's queries over the pages of their requests."""
-    attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
-                    num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
+    """Causal attention of this step's queries over the pages of their requests.  `fast` allows the
+    tensor-core kernel where its conditions hold and the step carries tiles for this group size."""
+    G = num_q_heads // num_kv_heads
+    meta = step.attn_meta.get(G) if fast else None
+    if meta is not None and attention_flash_ok(q, num_q_heads, num_kv_heads, head_dim):
+        tiles, max_rows = meta
+        span = min(step.max_context_len, window + step.max_q_len) if window > 0 else step.max_context_len
+        splits = step.plans.get("attention_splits") or attention_splits(tiles.shape[0], num_kv_heads, span)
+        attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, max_rows,
+                        num_q_heads, num_kv_heads, head_dim, page_size, window, scale, splits, stream)
+    else:
+        attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
+                        num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)

@@ -52,6 +52,9 @@ class GQAttention(Mixer):
             self.q_norm_w = get(f"{self.prefix}.q_norm.weight").to(torch.float32).contiguous()
             self.k_norm_w = get(f"{self.prefix}.k_norm.weight").to(torch.float32).contiguous()
 
+    def query_group_size(self) -> int:
+        return self.num_heads // self.num_kv_heads
+
     def cache_request(self) -> KVPages:
         return KVPages(self.num_kv_heads, self.head_dim, self.window)
 

@@ -101,7 +101,8 @@ class StepContext:
     max_context_len: int = 0
     # Per step scratch that parts of the same kind may share (plans of the attention kernels).
     plans: dict = field(default_factory=dict)
-    # Per cache group plan tensors prepared by the step function (see engine/step.py).
+    # Work items of the tensor-core attention kernel, by query-group size G: (tiles int32 [n, 4] of
+    # (first token, tokens, request index, 0) on the device, most query rows of a tile).
     attn_meta: dict = field(default_factory=dict)
 
 
@@ -148,6 +149,10 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     def cache_request(self) -> KVPages | StateSlot | None:
+        return None
+
+    def query_group_size(self) -> Optional[int]:
+        """Query heads per kv head, if this mixer wants the step to carry attention tiles for it."""
         return None
 
     def forward(self, h: torch.Tensor, step: StepContext, cache, write_cache: bool = True) -> torch.Tensor:
