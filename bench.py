@@ -1,0 +1,295 @@
+"""Decode and prefill throughput of the engine on one B200, with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default workload: the layer sizes of the Qwen3-8B shape (36 layers, hidden 4096, 32 query heads,
+8 kv heads, head size 128, intermediate 12288, vocabulary 151936), bfloat16, random weights, a
+batch of 8 requests that decode at a context of 8192 tokens, pages of 16 tokens.  A step is one
+decode step of the whole batch.  The line printed at the end is one JSON object:
+
+  value       decoded tokens a second over K steps, timed on the device (CUDA events): the step
+              function plus the sampler, token ids fed from the host, nothing read back
+  e2e         the same through the public entry point (Engine.step: scheduler, step, sampler), with
+              the step's inputs copied from pinned host memory and the sampled tokens read back
+  prefill     one step over a prompt of 2048 tokens: tokens a second, and its FLOPs / time / peak
+  roofline    bytes a decode step must read (every weight once, the cache of the live requests)
+              / time, against the measured copy bandwidth
+  points      decode at batch 1 and 64, same context
+
+Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
+fallback figures 6650 GB/s and 1590 TFLOP/s.  The timed work reads far more than the 126 MB of L2
+per step (weights alone are 16 GB), so no explicit L2 flush is made.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False, "max_position_embeddings": 40960, "hidden_act": "silu", "attention_bias": False,
+    "torch_dtype": "bfloat16",
+}
+FULL_LAYERS = 36
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if p.is_file():
+        try:
+            d = json.loads(p.read_text())
+            if d.get("hbm_gbs"):
+                out["hbm_gbs"] = float(d["hbm_gbs"])
+            if d.get("bf16_tflops"):
+                out["bf16_tflops"] = float(d["bf16_tflops"])
+            out["source"] = "measured"
+        except (ValueError, OSError):
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.samples: list[list[str]] = []
+        self.proc = None
+        self.index = index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()          # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        mhz = [int(s[0]) for s in self.samples if s[0].isdigit()]
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def model_bytes_and_flops(cfg: dict, layers: int):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nq + 2 * nkv) * d * H + H * nq * d + 2 * I * H + H * I          # linear weights
+    norms = 2 * H + 2 * d
+    weight_bytes = layers * (per_layer * 2 + norms * 4) + V * H * 2 + H * 4        # every weight a decode step reads once
+    kv_bytes_per_token = layers * 2 * nkv * d * 2
+    return per_layer, weight_bytes, kv_bytes_per_token
+
+
+def prefill_flops(cfg: dict, layers: int, T: int) -> float:
+    per_layer, _, _ = model_bytes_and_flops(cfg, layers)
+    nq, d, V, H = cfg["num_attention_heads"], cfg["head_dim"], cfg["vocab_size"], cfg["hidden_size"]
+    linear = 2.0 * T * per_layer * layers
+    attention = layers * nq * 4.0 * d * (T * (T + 1) / 2)                          # causal: QK^T and PV over i+1 keys
+    return linear + attention + 2.0 * V * H                                        # the output head on one row
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192, help="context length the decode steps end at")
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps from CUDA graphs")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "JunkuiZhang/lucciola has no Python package or install target (CMake project whose configure step "
+                          "fetches dependencies from the network and needs <print>, absent from g++ 13.3): pip install of the reference fails offline"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    from lucciola_b200 import ops
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.llm import Engine
+    from lucciola_b200.engine.step import StepEntry
+    from lucciola_b200.sampling.params import SamplingParams
+
+    pk = peaks()
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    K, W, ctx = args.steps, args.warmup, args.context
+    batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
+    page = 16
+    max_b = max(batches)
+    pages = max_b * (-(-ctx // page)) + 64
+    options = EngineOptions(dtype="bfloat16", block_size=page, max_blocks=pages, max_num_seqs=max(64, max_b),
+                            max_tokens_per_step=max(args.prefill_tokens, 2048) + max_b, max_model_len=max(ctx, args.prefill_tokens),
+                            use_cuda_graph=not args.no_graph)
+    t_build = time.time()
+    engine = Engine.from_random(cfg, seed=0, options=options)
+    runner = engine.runner
+    torch.cuda.synchronize()
+    build_s = time.time() - t_build
+    rng = np.random.default_rng(0)
+    V = cfg["vocab_size"]
+    _, weight_bytes, kv_per_token = model_bytes_and_flops(cfg, args.layers)
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    # ---- prefill: one step over a prompt of --prefill-tokens tokens -----------------------------------
+    T = args.prefill_tokens
+    times = []
+    for i in range(3 + 5):
+        ids = rng.integers(0, V, size=T).tolist()
+        a, b = ev(), ev()
+        torch.cuda.synchronize()
+        a.record()
+        logits = runner.step([StepEntry(("prefill", i), ids, [T - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        runner.finish(("prefill", i))
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+    prefill_ms = statistics.median(times)
+    flops = prefill_flops(cfg, args.layers, T)
+    prefill = {"value": round(T / prefill_ms * 1e3, 1), "tokens": T, "ms": round(prefill_ms, 3),
+               "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode ------------------------------------------------------------------------------------------------------
+    def decode_point(B: int, with_e2e: bool):
+        """B requests brought to a context just short of `ctx`, then 2 x (W + K) decode steps."""
+        total_steps = (2 if with_e2e else 1) * (W + K) + 2
+        # requests whose prompt is done decode while the prompts behind them are still read: leave room
+        ctx0 = ctx - total_steps - (B - 1) * -(-ctx // options.max_tokens_per_step) - 1
+        params = SamplingParams(max_new_tokens=total_steps + 8, temperature=0.0, ignore_eos=True)
+        reqs = [engine.add_request(rng.integers(0, V, size=ctx0).tolist(), params) for _ in range(B)]
+        while any(r.remaining > 1 or not r.output for r in reqs):       # prompts, in portions under the budget
+            engine.step()
+        torch.cuda.synchronize()
+        out = {}
+        if with_e2e:
+            h2d0 = runner.h2d_bytes
+            for _ in range(W):
+                engine.step()
+            with ClockSampler() as clocks_e2e:
+                a, b = ev(), ev()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                a.record()
+                h2d1 = runner.h2d_bytes
+                for _ in range(K):
+                    engine.step()
+                b.record()
+                torch.cuda.synchronize()
+                wall = time.perf_counter() - t0
+            ms = max(a.elapsed_time(b), wall * 1e3)
+            out["e2e"] = {"value": round(B * K / ms * 1e3, 2), "unit": "tokens/s", "ms_per_step": round(ms / K, 4),
+                          "h2d_bytes_per_step": int((runner.h2d_bytes - h2d1) / K), "d2h_bytes_per_step": 4 * B}
+        # device-timed: the step function and the sampler; token ids come from the host, nothing is read back
+        rids = [r.rid for r in reqs]
+        feed = [[int(x) for x in rng.integers(0, V, size=W + K)] for _ in range(B)]
+        tokens = torch.empty(B, dtype=torch.int32, device=runner.device)
+
+        def one(i):
+            logits = runner.step([StepEntry(rid, [feed[j][i]], [0]) for j, rid in enumerate(rids)])
+            ops.sample(tokens, logits, torch.cuda.current_stream().cuda_stream)
+
+        for i in range(W):
+            one(i)
+        launches0 = runner.kernel_launches()
+        with ClockSampler() as clocks:
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            for i in range(W, W + K):
+                one(i)
+            b.record()
+            torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        launches = runner.kernel_launches() - launches0
+        final_ctx = max(runner.length(r) for r in rids)
+        cached_tokens = sum(runner.length(r) for r in rids) - B * K / 2         # mean over the timed steps
+        step_bytes = weight_bytes + cached_tokens * kv_per_token
+        out.update({"value": B * K / ms * 1e3, "ms_per_step": ms / K, "launches": launches, "clocks": clocks.summary(),
+                    "bytes": step_bytes, "gbs": step_bytes / (ms / K * 1e-3) / 1e9, "final_context": final_ctx})
+        for r in reqs:
+            engine.scheduler.abort(r.rid)
+        return out
+
+    results = {}
+    for B in sorted(batches, reverse=True):
+        results[B] = decode_point(B, with_e2e=(B == args.batch))
+    main_r = results[args.batch]
+    err = ops.device_error()
+
+    line = {
+        "metric": "decode tokens/s (Qwen3-8B shape, bf16, batch %d, context %d)" % (args.batch, ctx),
+        "value": round(main_r["value"], 2), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(main_r["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0, 0.02)", "impl": "ours",
+        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_configuration": FULL_LAYERS,
+                   "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+                   "intermediate_size": 12288, "vocab_size": 151936, "global_batch": args.batch, "seq_len": ctx,
+                   "context_len": main_r["final_context"], "page_size": page, "parallelism": "single GPU",
+                   "cuda_graph": bool(options.use_cuda_graph), "l2": "inputs larger than L2 (16 GB of weights a step)",
+                   "prefill_tokens": T, "peaks": pk["source"]},
+        "e2e": main_r.get("e2e"),
+        "gpu_launches": int(main_r["launches"]),
+        "clocks": main_r["clocks"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(main_r["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(main_r["gbs"] / pk["hbm_gbs"], 4)},
+        "points": {f"decode_b{B}": round(r["value"], 2) for B, r in results.items() if B != args.batch},
+        "points_roofline_frac": {f"decode_b{B}": round(r["gbs"] / pk["hbm_gbs"], 4) for B, r in results.items()},
+        "device_error": err, "build_s": round(build_s, 1),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -23,6 +23,7 @@ namespace lb {
 typedef __nv_bfloat16 bf16;
 
 void set_error(const char* fmt, ...);
+void count_launch();   // every kernel launch of the library is counted (lb_launch_count)
 
 #define LB_CHECK_ARG(cond, ...)          \
   do {                                   \
@@ -40,6 +41,7 @@ void set_error(const char* fmt, ...);
       lb::set_error("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
       return 2;                                                            \
     }                                                                      \
+    lb::count_launch();                                                    \
   } while (0)
 
 __device__ __forceinline__ float to_f32(float x) { return x; }

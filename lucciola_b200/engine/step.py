@@ -26,6 +26,10 @@ from ..models.decoder import DecoderModel
 from ..parts.base import Runtime, StepContext
 
 
+# Batch sizes for which decode-only steps are recorded as CUDA graphs; a batch is padded to the next one.
+_GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
 class OutOfPages(RuntimeError):
     """A step needs more pages than are free; nothing was run and nothing was taken."""
 
@@ -54,8 +58,8 @@ class _Staging:
             self.events[i].synchronize()        # the copy that read this buffer has finished
         return i, self.host[i]
 
-    def upload(self, i: int, n: int) -> None:
-        self.dev[:n].copy_(self.host[i][:n], non_blocking=True)
+    def upload(self, i: int, n: int, dev: Optional[torch.Tensor] = None) -> None:
+        (self.dev if dev is None else dev)[:n].copy_(self.host[i][:n], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
@@ -89,6 +93,10 @@ class ModelRunner:
         self._staging: Optional[_Staging] = None
         self.steps_run = 0
         self.tokens_run = 0
+        self.h2d_bytes = 0                 # bytes of step inputs copied from pinned host memory so far
+        self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._graph_inputs: dict[tuple[int, int], torch.Tensor] = {}
+        self._graph_launches = 0           # kernels replayed from CUDA graphs so far
 
     # ---- what a batch builder may ask ------------------------------------
     def length(self, rid: Hashable) -> int:
@@ -109,6 +117,11 @@ class ModelRunner:
             return False
         return all(self.manager.pools[g].can_allocate(n) for g, n in enumerate(need))
 
+    def kernel_launches(self) -> int:
+        """Kernels of the library launched so far (replays of CUDA graphs counted by their kernel nodes)."""
+        from .. import ops
+        return ops.launch_count() + self._graph_launches
+
     def finish(self, rid: Hashable) -> None:
         """The request ended (or is preempted): its pages and its slot go back."""
         if self.manager.has_request(rid):
@@ -120,6 +133,29 @@ class ModelRunner:
             torch.cuda.current_stream(self.device).synchronize()
             self._staging = _Staging(self.device, max(n, 4096) * 2)
         return self._staging
+
+    def _run_graph(self, key: tuple[int, int], d_tok: torch.Tensor, step: StepContext, d_rows: torch.Tensor) -> torch.Tensor:
+        """Decode-only step of a fixed batch size: the first time it runs as usual and is then recorded
+        (launches into a capturing stream are not executed); later steps replay the recording.  The
+        result lives in the graph's memory and is valid until the next step."""
+        from .. import ops
+        hit = self._graphs.get(key)
+        if hit is not None:
+            graph, logits, kernels = hit
+            graph.replay()
+            self._graph_launches += kernels
+            return logits
+        logits = self.model.forward(d_tok, step, self.cache.views, d_rows)      # also warms every lazy set-up
+        torch.cuda.current_stream(self.device).synchronize()
+        before = ops.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        outer = self.rt.stream
+        with torch.cuda.graph(graph):
+            self.rt.stream = torch.cuda.current_stream(self.device).cuda_stream
+            static_logits = self.model.forward(d_tok, step, self.cache.views, d_rows)
+        self.rt.stream = outer
+        self._graphs[key] = (graph, static_logits, ops.launch_count() - before)
+        return logits
 
     @staticmethod
     def _tiles(q_lens: Sequence[int], group: int) -> list[tuple[int, int, int, int]]:
@@ -172,8 +208,20 @@ class ModelRunner:
             starts.append(start)
             q_lens.append(len(e.tokens))
 
-        S, T = len(entries), sum(q_lens)
-        R = sum(len(e.want) for e in entries)
+        S_real = len(entries)
+        max_ctx = max(s + n for s, n in zip(starts, q_lens))
+        # Decode-only steps replay a CUDA graph: the batch is padded to a bucket with entries that
+        # own no page (their keys and values are written nowhere and they attend to nothing).
+        graph_key = None
+        if (self.options.use_cuda_graph and self.rt.fast_kernels and not self.cache.states and max(q_lens) == 1
+                and S_real <= _GRAPH_BUCKETS[-1]):
+            S = next(b for b in _GRAPH_BUCKETS if b >= S_real)
+            span_hint = max(256, 1 << (max_ctx - 1).bit_length())
+            graph_key = (S, span_hint)
+            q_lens = q_lens + [1] * (S - S_real)
+            starts = starts + [0] * (S - S_real)
+        S, T = len(q_lens), sum(q_lens)
+        R = T if graph_key else sum(len(e.want) for e in entries)
         G, P = len(self.groups), self.max_pages_per_seq
         tile_lists = {g: self._tiles(q_lens, g) for g in self.tile_groups}
         total = 3 * T + (S + 1) + 2 * S + R + G * S * P + sum(4 * len(t) + 3 for t in tile_lists.values())
@@ -194,25 +242,39 @@ class ModelRunner:
             take(4 * len(tl))[:] = np.asarray(tl, dtype=np.int32).reshape(-1)
         t = r = 0
         cu[0] = 0
-        for i, e in enumerate(entries):
+        wanted_rows: list[int] = []
+        for i in range(S):
             n = q_lens[i]
-            tok[t:t + n] = token_arrays[i]
+            if i < S_real:
+                e = entries[i]
+                tok[t:t + n] = token_arrays[i]
+                slots[i] = self.manager.slot(e.rid)
+                for g in range(G):
+                    bt = self.manager.block_table(e.rid, g)
+                    tables[g][i, :len(bt)] = bt
+                    tables[g][i, len(bt):] = NO_PAGE
+                wanted_rows += [t + w for w in e.want]
+            else:
+                tok[t] = 0
+                slots[i] = 0
+                for g in range(G):
+                    tables[g][i, :] = NO_PAGE
             pos[t:t + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
             seq[t:t + n] = i
-            for w in e.want:
-                rows[r] = t + w
-                r += 1
             t += n
             cu[i + 1] = t
             ctx[i] = starts[i] + n
-            slots[i] = self.manager.slot(e.rid)
-            for g in range(G):
-                bt = self.manager.block_table(e.rid, g)
-                tables[g][i, :len(bt)] = bt
-                tables[g][i, len(bt):] = NO_PAGE
-        st.upload(hi, total)
+        if graph_key:
+            rows[:] = np.arange(T, dtype=np.int32)
+        else:
+            rows[:] = np.asarray(wanted_rows, dtype=np.int32)
+        dev = self._graph_inputs.get(graph_key) if graph_key else None
+        if graph_key and dev is None:
+            dev = self._graph_inputs[graph_key] = torch.empty(total, dtype=torch.int32, device=self.device)
+        st.upload(hi, total, dev)
+        self.h2d_bytes += 4 * total
 
-        d = st.dev
+        d = st.dev if dev is None else dev
         o = 0
         def view(n):
             nonlocal o
@@ -230,11 +292,21 @@ class ModelRunner:
         step = StepContext(
             num_tokens=T, num_seqs=S, positions=d_pos, token_seq=d_seq, cu_tokens=d_cu, context_lens=d_ctx,
             block_tables=d_tables, state_slots=d_slots, q_lens=q_lens, start_positions=starts,
-            max_q_len=max(q_lens), max_context_len=max(s + n for s, n in zip(starts, q_lens)), attn_meta=attn_meta)
+            max_q_len=max(q_lens), max_context_len=max_ctx, attn_meta=attn_meta)
         self.rt.stream = torch.cuda.current_stream(self.device).cuda_stream
         if new_slots and self.cache.states:
             self.cache.zero_slots(torch.tensor(new_slots, dtype=torch.long, device=self.device))
-        logits = self.model.forward(d_tok, step, self.cache.views, d_rows if R else None)
+        if graph_key is None:
+            logits = self.model.forward(d_tok, step, self.cache.views, d_rows if R else None)
+        else:
+            step.plans["span_hint"] = graph_key[1]
+            logits = self._run_graph(graph_key, d_tok, step, d_rows)
+            if not wanted_rows:
+                logits = None
+            elif wanted_rows == list(range(len(wanted_rows))):
+                logits = logits[:len(wanted_rows)]
+            else:
+                logits = logits.index_select(0, torch.tensor(wanted_rows, dtype=torch.long, device=self.device))
 
         for e in entries:
             self.manager.release_behind_window(e.rid)

@@ -229,6 +229,13 @@ def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int,
           counters.numel(), force_bt, force_splits, stream)
 
 
+def launch_count() -> int:
+    """Kernels the library has launched so far in this process."""
+    lib = library()
+    lib.lb_launch_count.restype = c_ulonglong
+    return int(lib.lb_launch_count())
+
+
 def device_error() -> int:
     """Code that a kernel left when one of its bounded waits gave up (0: none).  Synchronises the device."""
     lib = library()
@@ -301,8 +308,9 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     meta = step.attn_meta.get(G) if fast else None
     if meta is not None and attention_flash_ok(q, num_q_heads, num_kv_heads, head_dim):
         tiles, max_rows = meta
-        span = min(step.max_context_len, window + step.max_q_len) if window > 0 else step.max_context_len
-        splits = step.plans.get("attention_splits") or attention_splits(tiles.shape[0], num_kv_heads, span)
+        longest = step.plans.get("span_hint", step.max_context_len)      # a recorded step plans for a bucket of lengths
+        span = min(longest, window + step.max_q_len) if window > 0 else longest
+        splits = attention_splits(tiles.shape[0], num_kv_heads, span)
         attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, max_rows,
                         num_q_heads, num_kv_heads, head_dim, page_size, window, scale, splits, stream)
     else:
