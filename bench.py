@@ -136,6 +136,8 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps from CUDA graphs")
+    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                    help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -179,6 +181,31 @@ def main() -> int:
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
+
+    if args.profile:
+        options.use_cuda_graph = False
+        B, T = args.batch, args.prefill_tokens
+        if args.profile == "prefill":
+            entries = lambda i: [StepEntry(("p", i), rng.integers(0, V, size=T).tolist(), [T - 1])]
+        else:
+            for j in range(B):                                        # bring B requests to the context, untimed
+                left = ctx - 8
+                while left > 0:
+                    n = min(left, 2048)
+                    runner.step([StepEntry(("d", j), rng.integers(0, V, size=n).tolist(), [])])
+                    left -= n
+            entries = lambda i: [StepEntry(("d", j), [int(rng.integers(0, V))], [0]) for j in range(B)]
+        for i in range(3):
+            runner.step(entries(i))
+            if args.profile == "prefill":
+                runner.finish(("p", i))
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        runner.step(entries(3))
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": args.profile, "layers": args.layers, "batch": B, "context": ctx, "tokens": T}))
+        return 0
 
     # ---- prefill: one step over a prompt of --prefill-tokens tokens -----------------------------------
     T = args.prefill_tokens

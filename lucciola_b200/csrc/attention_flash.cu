@@ -17,6 +17,11 @@
 // so whatever a reused page still holds cannot reach a sum (lucciola zero-fills the tail of the last
 // page for the same reason, src/kernels/flash_attention.cu:142-154).
 //
+// Two arrangements of the four warps.  When tiles have more than 16 query rows (portions of prompts)
+// each warp owns 16 rows and visits all 64 keys of a stage.  When no tile has more than 16 rows
+// (decoded tokens) all warps share the rows and each visits 16 of the 64 keys, keeping its own
+// (m, l, o); the four are merged through shared memory, in the order of the warps, at the end.
+//
 // Head sizes: any multiple of 8 up to 128 (padded with zeros to 64 or 128 in shared memory).
 #include "common.cuh"
 
@@ -36,7 +41,7 @@ struct FlashParams {
   float* part_o;                            // [tiles, nkv, splits, part_rows, d]
   float* part_ml;                           // [tiles, nkv, splits, part_rows, 2]
   int part_rows;                            // most query rows of any tile
-  int num_q_heads, num_kv_heads, head_dim, group, page_size, window, splits;
+  int num_q_heads, num_kv_heads, head_dim, group, page_size, page_shift, window, splits;   // page_shift: log2(page_size) or -1
   float scale_log2;                         // scale * log2(e)
 };
 
@@ -72,10 +77,13 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
   return (uint32_t)(row * (DP * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int DP>
+template <int DP, bool KEYSPLIT>
 __global__ void __launch_bounds__(FA_THREADS)
 flash_attention_kernel(FlashParams p) {
   constexpr int CHUNKS = DP / 8;                  // 16-byte chunks of a row
+  constexpr int NB = KEYSPLIT ? 2 : FA_KEYS / 8;  // blocks of 8 keys a warp visits in a stage
+  constexpr int LOADS = FA_KEYS * CHUNKS / FA_THREADS;      // 16-byte copies a thread makes per stage and matrix
+  constexpr int ROW_STEP = FA_THREADS / CHUNKS;             // rows between two copies of one thread
   constexpr int TILE_BYTES = FA_KEYS * DP * 2;
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t q_smem = (uint32_t)__cvta_generic_to_shared(smem);
@@ -110,20 +118,29 @@ flash_attention_kernel(FlashParams p) {
   }
   cp_async_commit();
 
+  // A thread copies the same 16-byte column of rows ld_row, ld_row + ROW_STEP, ...: the swizzled
+  // column is the same for all of them because ROW_STEP is a multiple of 8.
+  const int ld_row = tid / CHUNKS, ld_chunk = tid % CHUNKS;
+  const bool ld_col_valid = ld_chunk * 8 < d;
+  const uint32_t ld_smem = tile_offset<DP>(ld_row, ld_chunk);
+  const size_t head_off = (size_t)kvh * p.page_size * d + ld_chunk * 8;
+  const size_t page_stride = (size_t)p.num_kv_heads * p.page_size * d;
   auto load_stage = [&](int stage_idx) {
     const int buf = stage_idx % FA_STAGES;
-    const int kbase = kbeg + stage_idx * FA_KEYS;
-    for (int idx = tid; idx < FA_KEYS * CHUNKS; idx += FA_THREADS) {
-      const int r = idx / CHUNKS, c = idx % CHUNKS;
-      const int j = kbase + r;
-      bool valid = j < kend && c * 8 < d;
-      size_t off = 0;
-      if (valid) {
-        const int page = bt[j / p.page_size];
-        valid = page >= 0;
-        off = (((size_t)(valid ? page : 0) * p.num_kv_heads + kvh) * p.page_size + (j % p.page_size)) * d + c * 8;
-      }
-      const uint32_t so = buf * TILE_BYTES + tile_offset<DP>(r, c);
+    const int kbase = kbeg + stage_idx * FA_KEYS + ld_row;
+    int page[LOADS], slot[LOADS];
+#pragma unroll
+    for (int i = 0; i < LOADS; ++i) {           // all page lookups first: they are independent loads
+      const int j = kbase + i * ROW_STEP;
+      const int pi = p.page_shift >= 0 ? (j >> p.page_shift) : (j / p.page_size);
+      slot[i] = j - pi * p.page_size;
+      page[i] = (j < kend && ld_col_valid) ? bt[pi] : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < LOADS; ++i) {
+      const bool valid = page[i] >= 0;
+      const size_t off = valid ? (size_t)page[i] * page_stride + head_off + (size_t)slot[i] * d : 0;
+      const uint32_t so = buf * TILE_BYTES + ld_smem + i * ROW_STEP * (DP * 2);
       cp_async16(k_smem + so, p.k_cache + off, valid);
       cp_async16(v_smem + so, p.v_cache + off, valid);
     }
@@ -135,8 +152,9 @@ flash_attention_kernel(FlashParams p) {
     cp_async_commit();
   }
 
-  // Rows of this thread: r0 = warp*16 + lane/4 and r0 + 8.
-  const int r0 = warp * 16 + (lane >> 2);
+  // Rows of this thread: r0 = (first row of the warp) + lane/4 and r0 + 8.
+  const int warp_row0 = KEYSPLIT ? 0 : warp * 16;
+  const int r0 = warp_row0 + (lane >> 2);
   int row_pos[2], row_lo[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -144,7 +162,7 @@ flash_attention_kernel(FlashParams p) {
     row_pos[h] = r < rows ? pos0 + r / G : -1;                  // -1: no key passes the mask
     row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
   }
-  const bool warp_active = warp * 16 < rows;
+  const bool warp_active = warp_row0 < rows;
 
   cp_async_wait<FA_STAGES - 1>();     // Q has landed (the stage loads may still be in flight)
   __syncthreads();
@@ -152,7 +170,7 @@ flash_attention_kernel(FlashParams p) {
   if (warp_active) {
 #pragma unroll
     for (int kk = 0; kk < DP / 16; ++kk) {
-      const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int r = warp_row0 + (lane & 7) + ((lane >> 3) & 1) * 8;
       const int c = kk * 2 + (lane >> 4);
       ldmatrix_x4(q_smem + tile_offset<DP>(r, c), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
     }
@@ -174,16 +192,17 @@ flash_attention_kernel(FlashParams p) {
     const uint32_t kb = k_smem + buf * TILE_BYTES, vb = v_smem + buf * TILE_BYTES;
     const int kbase = kbeg + st * FA_KEYS;
 
-    // ---- S = Q K^T: 16 rows x 64 keys per warp ------------------------------------------------
-    float s[FA_KEYS / 8][4];
+    // ---- S = Q K^T: 16 rows x (64 or, with shared rows, this warp's 16) keys -----------------------
+    const int key0 = KEYSPLIT ? warp * 16 : 0;       // first key of the stage this warp visits
+    float s[NB][4];
 #pragma unroll
-    for (int i = 0; i < FA_KEYS / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+    for (int i = 0; i < NB; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll
     for (int kk = 0; kk < DP / 16; ++kk) {
 #pragma unroll
-      for (int nb = 0; nb < FA_KEYS / 8; nb += 2) {
+      for (int nb = 0; nb < NB; nb += 2) {
         // matrices: (keys nb, dims lo), (keys nb, dims hi), (keys nb+1, dims lo), (keys nb+1, dims hi)
-        const int key = nb * 8 + (lane & 7) + (lane >> 4) * 8;
+        const int key = key0 + nb * 8 + (lane & 7) + (lane >> 4) * 8;
         const int c = kk * 2 + ((lane >> 3) & 1);
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4(kb + tile_offset<DP>(key, c), b0, b1, b2, b3);
@@ -196,12 +215,12 @@ flash_attention_kernel(FlashParams p) {
     const bool need_mask = (kbase + FA_KEYS - 1 > pos0) || (p.window > 0) || (kbase + FA_KEYS > kend) || (rows < FA_ROWS);
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
-    for (int nb = 0; nb < FA_KEYS / 8; ++nb) {
+    for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
         if (need_mask) {
-          const int j = kbase + nb * 8 + (lane & 3) * 2 + (e & 1);
+          const int j = kbase + key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
           if (j > row_pos[h] || j < row_lo[h] || j >= kend) s[nb][e] = -INFINITY;
         }
         m_new[h] = fmaxf(m_new[h], s[nb][e]);
@@ -217,9 +236,9 @@ flash_attention_kernel(FlashParams p) {
       m_run[h] = m_new[h];
     }
     float row_sum[2] = {0.f, 0.f};
-    uint32_t pf[FA_KEYS / 16][4];
+    uint32_t pf[NB / 2][4];
 #pragma unroll
-    for (int nb = 0; nb < FA_KEYS / 8; ++nb) {
+    for (int nb = 0; nb < NB; ++nb) {
       float pv[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -240,11 +259,11 @@ flash_attention_kernel(FlashParams p) {
 
     // ---- O += P V ----------------------------------------------------------------------------------
 #pragma unroll
-    for (int ks = 0; ks < FA_KEYS / 16; ++ks) {
+    for (int ks = 0; ks < NB / 2; ++ks) {
 #pragma unroll
       for (int db = 0; db < DP / 8; db += 2) {
         // matrices (transposed on load): (keys lo, dims db), (keys hi, dims db), (keys lo, dims db+1), (keys hi, dims db+1)
-        const int key = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int key = key0 + ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         const int c = db + (lane >> 4);
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4_trans(vb + tile_offset<DP>(key, c), b0, b1, b2, b3);
@@ -260,6 +279,52 @@ flash_attention_kernel(FlashParams p) {
   for (int h = 0; h < 2; ++h) {
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  if (KEYSPLIT) {
+    // Merge the four warps' (m, l, o) through shared memory (the stages are no longer needed).
+    __syncthreads();
+    float* mo = reinterpret_cast<float*>(smem + FA_ROWS * DP * 2);          // [4][16][DP]
+    float* mml = mo + 4 * 16 * DP;                                           // [4][16][2]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = (lane >> 2) + 8 * h;
+#pragma unroll
+      for (int i = 0; i < DP / 8; ++i) {
+        const int dim = i * 8 + (lane & 3) * 2;
+        *reinterpret_cast<float2*>(mo + ((warp * 16 + r) * DP + dim)) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+      }
+      if ((lane & 3) == 0) {
+        mml[(warp * 16 + r) * 2 + 0] = m_run[h] == -INFINITY ? -INFINITY : m_run[h] * p.scale_log2;
+        mml[(warp * 16 + r) * 2 + 1] = l_run[h];
+      }
+    }
+    __syncthreads();
+    for (int r = 0; r < rows; ++r) {
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
+      float L = 0.f, wgt[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = mml[(w * 16 + r) * 2];
+        wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - M);
+        L += mml[(w * 16 + r) * 2 + 1] * wgt[w];
+      }
+      const int token = t0 + r / G, head = kvh * G + r % G;
+      for (int dim = tid; dim < d; dim += FA_THREADS) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += mo[(w * 16 + r) * DP + dim] * wgt[w];
+        if (p.splits == 1) {
+          p.out[((size_t)token * p.num_q_heads + head) * d + dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+          const size_t slot = (((size_t)blockIdx.x * p.num_kv_heads + kvh) * p.splits + split) * p.part_rows + r;
+          p.part_o[slot * d + dim] = acc;
+          if (dim == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
+        }
+      }
+    }
+    return;
   }
   if (!warp_active) return;
 #pragma unroll
@@ -356,19 +421,25 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   p.part_rows = part_rows;
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim; p.group = group;
   p.page_size = page_size; p.window = window; p.splits = splits;
+  p.page_shift = -1;
+  for (int b = 0; b < 31; ++b) if ((1 << b) == page_size) p.page_shift = b;
   p.scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(num_tiles, num_kv_heads, splits);
   const int dp = head_dim <= 64 ? 64 : 128;
   const int smem = (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2;
-  if (dp == 64) {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(lb::flash_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
-    lb::flash_attention_kernel<64><<<grid, lb::FA_THREADS, smem, stream>>>(p);
-  } else {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(lb::flash_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
-    lb::flash_attention_kernel<128><<<grid, lb::FA_THREADS, smem, stream>>>(p);
-  }
+  const bool keysplit = part_rows <= 16;      // no tile has more than 16 query rows: the warps share them
+#define LB_FLASH_LAUNCH(DP, KS)                                                                                 \
+  do {                                                                                                          \
+    static bool cfg = false;                                                                                    \
+    if (!cfg) {                                                                                                 \
+      cudaFuncSetAttribute(lb::flash_attention_kernel<DP, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+      cfg = true;                                                                                               \
+    }                                                                                                           \
+    lb::flash_attention_kernel<DP, KS><<<grid, lb::FA_THREADS, smem, stream>>>(p);                              \
+  } while (0)
+  if (dp == 64) { if (keysplit) LB_FLASH_LAUNCH(64, true); else LB_FLASH_LAUNCH(64, false); }
+  else { if (keysplit) LB_FLASH_LAUNCH(128, true); else LB_FLASH_LAUNCH(128, false); }
+#undef LB_FLASH_LAUNCH
   LB_CHECK_LAUNCH("attention_flash");
   if (splits > 1) {
     dim3 cgrid(num_tiles, num_kv_heads), cblock(32, 4);

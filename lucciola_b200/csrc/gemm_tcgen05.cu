@@ -383,7 +383,7 @@ LB_EXPORT int lb_gemm_tcgen05_plan(int M, int N, int K, int* bt) {
   const int kb = (K + lb::BK - 1) / lb::BK;
   int splits = 1;
   if (tiles < 148 && M <= 256) {       // splitting pays only while the weights are what is streamed
-    splits = (296 + tiles - 1) / tiles;
+    splits = 296 / tiles;                // all CTAs in one wave of two per SM
     if (splits > kb / 4) splits = kb / 4;
     if (splits > 16) splits = 16;
     if (splits < 1) splits = 1;

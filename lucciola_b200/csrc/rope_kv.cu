@@ -38,7 +38,8 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   const int pos = p.positions[t];
   const int total_heads = p.num_q_heads + 2 * p.num_kv_heads;
 
-  for (int h = warp; h < total_heads; h += nwarps) {
+  // One head per warp: the grid's second dimension covers the heads.
+  for (int h = blockIdx.y * nwarps + warp; h < total_heads; h += gridDim.y * nwarps) {
     const int kind = h < p.num_q_heads ? 0 : (h < p.num_q_heads + p.num_kv_heads ? 1 : 2);
     const int hh = kind == 0 ? h : (kind == 1 ? h - p.num_q_heads : h - p.num_q_heads - p.num_kv_heads);
     const T* src = kind == 0 ? (const T*)p.q_in + (size_t)t * p.q_stride + (size_t)hh * d
@@ -126,7 +127,11 @@ LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const vo
   const int warps = 4;
   const size_t smem = (size_t)warps * head_dim * sizeof(float);
   LB_DISPATCH_DTYPE(dtype, T, {
-    lb::rope_kv_kernel<T><<<num_tokens, warps * 32, smem, stream>>>(p);
+    const int total_heads = num_q_heads + 2 * num_kv_heads;
+    int head_blocks = (total_heads + warps - 1) / warps;
+    if (head_blocks > 65535) head_blocks = 65535;
+    if (head_blocks < 1) head_blocks = 1;
+    lb::rope_kv_kernel<T><<<dim3(num_tokens, head_blocks), warps * 32, smem, stream>>>(p);
   })
   LB_CHECK_LAUNCH("rope_kv");
   return 0;

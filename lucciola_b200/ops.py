@@ -273,10 +273,21 @@ def attention_flash_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, hea
             and num_q_heads % num_kv_heads == 0 and num_q_heads // num_kv_heads <= 64)
 
 
-def attention_splits(num_tiles: int, num_kv_heads: int, max_span: int) -> int:
-    """Into how many key ranges a launch is cut: enough CTAs for twice the SMs, ranges of 256 keys at least."""
+def attention_splits(num_tiles: int, num_kv_heads: int, max_span: int, slots: int = 296) -> int:
+    """Into how many key ranges a launch is cut.  `slots` is how many CTAs run at a time (two on each
+    of the 148 SMs).  Fewer CTAs than slots: as many ranges as still fit one wave.  More: the count
+    (up to 8) whose last wave is fullest.  A range has 256 keys at least."""
     base = max(num_tiles * num_kv_heads, 1)
-    return max(1, min(-(-296 // base), max_span // 256, 64))
+    cap = max(1, min(max_span // 256, 64))
+    if base <= slots:
+        return max(1, min(slots // base, cap))
+    best, best_fill = 1, 0.0
+    for s in range(1, min(cap, 8) + 1):
+        waves = base * s / slots
+        fill = waves / -(-base * s // slots)
+        if fill > best_fill + 0.02:
+            best, best_fill = s, fill
+    return best
 
 
 def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -1,0 +1,356 @@
+"""Each kernel alone against a plain PyTorch float32 statement of the same operation, at sizes other
+than the engine's tiny models use (GPU)."""
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env():
+    from lucciola_b200 import ops
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    return ops, dev, torch.cuda.current_stream().cuda_stream
+
+
+def rel(a, b):
+    return ((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30)).item()
+
+
+# ---- embedding ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [6, 100, 1030])
+def test_embedding(env, dtype, hidden):
+    ops, dev, st = env
+    table = torch.randn(77, hidden, device=dev).to(dtype)
+    ids = torch.tensor([0, 76, 5, 5, 33], dtype=torch.int32, device=dev)
+    out = torch.empty(5, hidden, device=dev)
+    ops.embedding(out, ids, table, st)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+# ---- residual add + RMSNorm ------------------------------------------------------------------------------
+@pytest.mark.parametrize("hidden,eps", [(7, 1e-5), (100, 1e-6), (4100, 3e-3)])
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(env, hidden, eps, act):
+    ops, dev, st = env
+    T = 9
+    res = torch.randn(T, hidden, device=dev) * 3
+    delta = (torch.randn(T, hidden, device=dev)).to(act)
+    w = 1 + 0.3 * torch.randn(hidden, device=dev)
+    want_res = res + delta.float()
+    want = plain.rms_norm(want_res.double(), w.double(), eps)
+    r = res.clone()
+    out = torch.empty(T, hidden, device=dev, dtype=act)
+    ops.add_rmsnorm(out, r, delta, w, eps, st)
+    assert torch.equal(r, want_res)                                   # the residual stream is updated in 32-bit
+    assert rel(out, want) < (1e-6 if act == torch.float32 else 5e-3)
+    # without a delta the residual stays and the norm is of the residual
+    r2 = res.clone()
+    ops.add_rmsnorm(out, r2, None, w, eps, st)
+    assert torch.equal(r2, res) and rel(out, plain.rms_norm(res.double(), w.double(), eps)) < (1e-6 if act == torch.float32 else 5e-3)
+    # on chosen rows: nothing is written back, the sum is formed on the fly
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=dev)
+    r3 = res.clone()
+    out3 = torch.empty(3, hidden, device=dev, dtype=act)
+    ops.add_rmsnorm(out3, r3, delta, w, eps, st, rows=rows)
+    assert torch.equal(r3, res) and rel(out3, want[rows.long()]) < (1e-6 if act == torch.float32 else 5e-3)
+
+
+# ---- q/k norm + rotation + cache write ---------------------------------------------------------------------
+def paged_setup(dev, seqs, nkv, d, ps, dtype, seed=0, fill=float("nan")):
+    """seqs: (cached tokens, new tokens) per request.  Returns pools filled with `fill`, a shuffled block
+    table, positions and the request index of each new token."""
+    rnd = random.Random(seed)
+    S = len(seqs)
+    maxlen = max(s + n for s, n in seqs)
+    P = -(-maxlen // ps) + 1
+    npages = sum(-(-(s + n) // ps) for s, n in seqs) + 2
+    perm = list(range(npages)); rnd.shuffle(perm)
+    bt = torch.full((S, P), -1, dtype=torch.int32)
+    pi = 0
+    pos, seq = [], []
+    for i, (s0, n) in enumerate(seqs):
+        for j in range(-(-(s0 + n) // ps)):
+            bt[i, j] = perm[pi]; pi += 1
+        pos += list(range(s0, s0 + n)); seq += [i] * n
+    kc = torch.full((npages, nkv, ps, d), fill, device=dev, dtype=dtype)
+    vc = kc.clone()
+    return kc, vc, bt.to(dev), torch.tensor(pos, dtype=torch.int32, device=dev), torch.tensor(seq, dtype=torch.int32, device=dev)
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,ps,theta", [(3, 1, 24, 4, 1e4), (8, 2, 64, 16, 5e5), (2, 2, 144, 32, 1e6)])
+def test_rope_kv(env, act, nq, nkv, d, ps, theta):
+    ops, dev, st = env
+    seqs = [(0, 7), (37, 1), (1021, 3)]
+    kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, act)
+    T = pos.shape[0]
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, device=dev).to(act)
+    qw, kw = 1 + 0.2 * torch.randn(d, device=dev), 1 + 0.2 * torch.randn(d, device=dev)
+    eps = 1e-5
+    inv = (1.0 / torch.pow(torch.tensor(theta), torch.arange(0, d, 2, dtype=torch.float32) / d)).to(dev)
+    q_out = torch.empty(T, nq, d, device=dev, dtype=act)
+    a, b = nq * d, (nq + nkv) * d
+    ops.rope_kv(qkv[:, :a], qkv[:, a:b], qkv[:, b:], q_out, pos, nq, nkv, d, eps, st, q_norm_w=qw, k_norm_w=kw,
+                inv_freq=inv, rot_dim=d, k_cache=kc, v_cache=vc, token_seq=seq, block_table=bt, page_size=ps)
+    x = qkv.double().cpu()
+    p = pos.cpu().tolist()
+    q_ref = plain.rope(plain.rms_norm(x[:, :a].reshape(T, nq, d), qw.double().cpu(), eps), p, theta)
+    k_ref = plain.rope(plain.rms_norm(x[:, a:b].reshape(T, nkv, d), kw.double().cpu(), eps), p, theta)
+    v_ref = x[:, b:].reshape(T, nkv, d)
+    tol = 2e-6 if act == torch.float32 else 6e-3
+    assert rel(q_out.cpu(), q_ref) < tol
+    btc, seqc = bt.cpu(), seq.cpu().tolist()
+    written = torch.zeros(kc.shape[0], ps, dtype=torch.bool)
+    for t in range(T):
+        page, slot = int(btc[seqc[t], p[t] // ps]), p[t] % ps
+        written[page, slot] = True
+        assert rel(kc[page, :, slot].cpu(), k_ref[t]) < tol
+        assert torch.equal(vc[page, :, slot].cpu().double(), v_ref[t])          # values are copied unchanged
+    untouched = kc.cpu().float().permute(0, 2, 1, 3)[~written]
+    assert torch.isnan(untouched).all()                                         # no other slot was written
+
+
+# ---- attention ------------------------------------------------------------------------------------------------
+def attention_reference(q, kc, vc, bt, pos, seq, nq, nkv, ps, window, scale):
+    """Plain float64 attention of each query over the keys its request holds in the pages."""
+    T, _, d = q.shape
+    out = torch.zeros(T, nq, d, dtype=torch.float64)
+    kcd, vcd, btc = kc.double().cpu(), vc.double().cpu(), bt.cpu()
+    qd = q.double().cpu()
+    for t in range(T):
+        s, p = int(seq[t]), int(pos[t])
+        lo = max(0, p - window + 1) if window else 0
+        idx = list(range(lo, p + 1))
+        k = torch.stack([kcd[int(btc[s, j // ps]), :, j % ps] for j in idx])        # [n, nkv, d]
+        v = torch.stack([vcd[int(btc[s, j // ps]), :, j % ps] for j in idx])
+        out[t] = plain.attention(qd[t:t + 1], k, v, [p], idx, scale, window)[0]
+    return out
+
+
+def fill_pages(kc, vc, bt, seqs, ps, seed=0, k_scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    nkv, d = kc.shape[1], kc.shape[3]
+    for i, (s0, n) in enumerate(seqs):
+        L = s0 + n
+        k = torch.randn(L, nkv, d, generator=g) * k_scale
+        v = torch.randn(L, nkv, d, generator=g)
+        for j in range(L):
+            kc[int(bt[i, j // ps]), :, j % ps] = k[j].to(kc.dtype).to(kc.device)
+            vc[int(bt[i, j // ps]), :, j % ps] = v[j].to(vc.dtype).to(vc.device)
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,ps,window,seqs", [
+    (6, 2, 24, 4, 0, [(0, 9), (30, 1), (5, 6)]),
+    (4, 4, 72, 16, 11, [(0, 40), (100, 2)]),
+    (8, 1, 160, 32, 0, [(63, 1), (64, 1), (0, 65)]),
+])
+def test_attention_plain(env, act, nq, nkv, d, ps, window, seqs):
+    ops, dev, st = env
+    kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, act)
+    fill_pages(kc, vc, bt.cpu(), seqs, ps)
+    q = torch.randn(pos.shape[0], nq, d, device=dev).to(act)
+    out = torch.empty_like(q)
+    ops.attention_plain(q, out, kc, vc, pos, seq, bt, nq, nkv, d, ps, window, 0.2, st)
+    ref = attention_reference(q, kc, vc, bt, pos.cpu(), seq.cpu(), nq, nkv, ps, window, 0.2)
+    assert torch.isfinite(out).all()                              # unused slots hold NaN and must not be read
+    assert rel(out.cpu(), ref) < (3e-6 if act == torch.float32 else 6e-3)
+
+
+def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=None, k_scale=1.0, q=None, hook=None):
+    kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, torch.bfloat16)
+    fill_pages(kc, vc, bt.cpu(), seqs, ps, k_scale=k_scale)
+    if hook:
+        hook(kc, vc, bt.cpu())
+    T = pos.shape[0]
+    q = torch.randn(T, nq, d, device=dev).bfloat16() if q is None else q
+    G, per = nq // nkv, 64 // (nq // nkv)
+    tiles, t = [], 0
+    for i, (_, n) in enumerate(seqs):
+        for off in range(0, n, per):
+            tiles.append((t + off, min(per, n - off), i, 0))
+        t += n
+    tl = torch.tensor(tiles, dtype=torch.int32, device=dev)
+    scale = scale if scale is not None else 1 / math.sqrt(d)
+    out = torch.full_like(q, float("nan"))
+    sp = splits or ops.attention_splits(len(tiles), nkv, max(s + n for s, n in seqs))
+    ops.attention_flash(q, out, kc, vc, pos, bt, tl, min(64, max(n for _, n, _, _ in tiles) * G), nq, nkv, d, ps, window,
+                        scale, sp, st)
+    ref = attention_reference(q, kc, vc, bt, pos.cpu(), seq.cpu(), nq, nkv, ps, window, scale)
+    return out, ref
+
+
+@pytest.mark.parametrize("nq,nkv,d,ps,window,seqs,splits", [
+    (4, 2, 64, 16, 0, [(0, 5)], None),
+    (8, 2, 128, 16, 0, [(0, 130), (37, 1), (0, 3)], None),
+    (32, 8, 128, 16, 0, [(1000, 1), (17, 1), (2047, 1)], 8),
+    (6, 2, 48, 8, 0, [(5, 40), (63, 2)], None),
+    (8, 1, 32, 8, 0, [(0, 100), (99, 1)], 2),
+    (5, 5, 16, 16, 24, [(0, 33), (200, 7)], None),
+    (4, 4, 80, 32, 64, [(300, 50)], 3),
+    (3, 1, 104, 64, 0, [(0, 64), (64, 64), (127, 1)], None),
+    (64, 1, 64, 16, 0, [(10, 3)], None),
+])
+def test_attention_flash(env, nq, nkv, d, ps, window, seqs, splits):
+    ops, dev, st = env
+    out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits)
+    assert torch.isfinite(out).all()
+    assert rel(out.cpu(), ref) < 8e-3
+
+
+def test_attention_flash_finds_a_far_key_among_hundreds(env):
+    """Random keys make every score alike, so a key that is skipped changes little.  Here one key far back
+    (at a page's first slot, in another split than the query) is made to carry nearly all the weight."""
+    ops, dev, st = env
+    nq, nkv, d, ps = 8, 2, 128, 16
+    L, far = 900, 16 * 13                                      # first slot of page 13
+    q = torch.randn(1, nq, d, device=dev).bfloat16()
+    marks = {}
+
+    def hook(kc, vc, bt):
+        page, slot = int(bt[0, far // ps]), far % ps
+        for kvh in range(nkv):
+            kc[page, kvh, slot] = (q[0, kvh * 4].float() * 3).bfloat16()     # aligned with query head kvh*4
+            vc[page, kvh, slot] = 7.0
+        marks["v"] = vc[page, :, slot].clone()
+
+    for splits in (1, 4, 7):
+        out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, 0, [(L - 1, 1)], splits, k_scale=0.05, q=q, hook=hook)
+        assert rel(out.cpu(), ref) < 8e-3
+        assert (out[0, 0].float() - 7.0).abs().max() < 0.1 and (out[0, 4].float() - 7.0).abs().max() < 0.1
+
+
+@pytest.mark.parametrize("window", [1, 16, 17, 63, 64, 65])
+def test_attention_flash_window_edge(env, window):
+    """The key just outside the window carries a huge value: if the edge is off by one it shows."""
+    ops, dev, st = env
+    nq, nkv, d, ps = 2, 1, 64, 16
+    pos_q = 200
+
+    def hook(kc, vc, bt):
+        j = pos_q - window                                       # the last key that must NOT be seen
+        vc[int(bt[0, j // ps]), :, j % ps] = 1000.0
+        j = pos_q - window + 1                                   # the first key that must be seen
+        vc[int(bt[0, j // ps]), :, j % ps] = -5.0
+
+    out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, window, [(pos_q, 1)], 1, hook=hook)
+    assert out.float().abs().max() < 50 and rel(out.cpu(), ref) < 8e-3
+    out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, window, [(pos_q - 30, 31)], 1, hook=hook)
+    assert rel(out.cpu(), ref) < 8e-3
+
+
+# ---- SwiGLU ------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("act,inter", [(torch.float32, 37), (torch.bfloat16, 37), (torch.bfloat16, 1000)])
+def test_swiglu(env, act, inter):
+    ops, dev, st = env
+    gu = (torch.randn(5, 2 * inter, device=dev) * 3).to(act)
+    out = torch.empty(5, inter, device=dev, dtype=act)
+    ops.swiglu(out, gu[:, :inter], gu[:, inter:], st)
+    want = plain.swiglu(gu[:, :inter].double(), gu[:, inter:].double())
+    assert rel(out, want) < (1e-6 if act == torch.float32 else 5e-3)
+
+
+# ---- matrix products --------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (3, 70, 33), (65, 129, 100), (200, 64, 17)])
+@pytest.mark.parametrize("tx,tw,ty", [(torch.float32,) * 3, (torch.bfloat16,) * 3, (torch.bfloat16, torch.float32, torch.float32)])
+def test_gemm_plain(env, M, N, K, tx, tw, ty):
+    ops, dev, st = env
+    x, w = torch.randn(M, K, device=dev).to(tx), torch.randn(N, K, device=dev).to(tw)
+    y = torch.empty(M, N, device=dev, dtype=ty)
+    ops.gemm_plain(y, x, w, st)
+    assert rel(y, x.double() @ w.double().t()) < (2e-6 if ty == torch.float32 else 5e-3)
+
+
+def test_gemm_plain_is_true_32_bit(env):
+    """No reduced-precision matrix mode: a product that needs all 24 bits of the inputs comes out right."""
+    ops, dev, st = env
+    x = torch.full((4, 8), 1.0 + 2.0 ** -20, device=dev)
+    w = torch.full((4, 8), 1.0 + 2.0 ** -19, device=dev)
+    y = torch.empty(4, 4, device=dev)
+    ops.gemm_plain(y, x, w, st)
+    exact = 8 * (1 + 2.0 ** -20) * (1 + 2.0 ** -19)
+    assert abs(y[0, 0].item() - exact) < 2e-6 and abs(y[0, 0].item() - 8.0) > 1e-5     # tf32 would give 8.0
+
+
+@pytest.mark.parametrize("M,N,K,bt,splits", [
+    (16, 128, 64, 16, 1), (5, 100, 96, 0, 0), (1, 503, 96, 0, 0), (16, 128, 1024, 16, 4), (33, 384, 520, 64, 3),
+    (128, 256, 512, 128, 1), (300, 1000, 776, 0, 0), (256, 384, 1024, 256, 1), (7, 1536, 2048, 0, 0), (70, 200, 4096, 0, 0),
+])
+@pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
+    ops, dev, st = env
+    x, w = torch.randn(M, K, device=dev).bfloat16(), torch.randn(N, K, device=dev).bfloat16()
+    y = torch.full((M, N), float("nan"), device=dev, dtype=ty)
+    ops.gemm_tcgen05(y, x, w, st, bt, splits)
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
+    assert rel(y, x.double() @ w.double().t()) < (2e-6 if ty == torch.float32 else 5e-3)
+    # a row-strided view of a wider matrix as input, as the q|k|v product's consumers use it
+    wide = torch.randn(M, K + 64, device=dev).bfloat16()
+    ops.gemm_tcgen05(y, wide[:, 32:32 + K] if (32 * 2) % 16 == 0 else wide[:, :K], w, st, bt, splits)
+    assert rel(y, wide[:, 32:32 + K].double() @ w.double().t()) < (2e-6 if ty == torch.float32 else 5e-3)
+
+
+def test_gemm_tcgen05_refuses_what_it_cannot_do(env):
+    ops, dev, st = env
+    from lucciola_b200.ops import KernelError
+    x, w = torch.randn(4, 100, device=dev).bfloat16(), torch.randn(8, 100, device=dev).bfloat16()
+    y = torch.empty(4, 8, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        ops.gemm_tcgen05(y, x, w, st)
+    ops.linear(y, x, w, st, fast=True)                          # the dispatcher takes the plain kernel instead
+    assert rel(y, x.double() @ w.double().t()) < 5e-3
+    with pytest.raises(KernelError, match="do not fit"):
+        ops.gemm_tcgen05(y, x, torch.randn(8, 96, device=dev).bfloat16(), st)
+
+
+# ---- samplers ------------------------------------------------------------------------------------------------------
+def test_greedy_takes_the_lowest_index_among_equals(env):
+    ops, dev, st = env
+    logits = torch.zeros(3, 70001, device=dev)
+    logits[0, [5, 69999]] = 2.0
+    logits[1, 70000] = 1.0
+    logits[2] = -1.0
+    tokens = torch.empty(3, dtype=torch.int32, device=dev)
+    ops.sample(tokens, logits, st)
+    assert tokens.tolist() == [5, 70000, 0]
+
+
+def test_temperature_sampler_equals_its_plain_restatement(env):
+    ops, dev, st = env
+    from lucciola_b200.sampling.sampler import sampling_key
+    V, R = 503, 24
+    logits = torch.randn(R, V, device=dev) * 2
+    temps = torch.tensor([0.8] * 12 + [0.0] * 4 + [1.7] * 8, device=dev)
+    seeds = [7] * 12 + [1] * 4 + [123456789] * 8
+    keys = torch.from_numpy(np.array([sampling_key(s) for s in seeds], dtype=np.uint64).view(np.int64)).to(dev)
+    counters = torch.arange(R, dtype=torch.int32, device=dev)
+    tokens = torch.empty(R, dtype=torch.int32, device=dev)
+    ops.sample(tokens, logits, st, temps, keys, counters)
+    rows = logits.cpu().numpy()
+    for r in range(R):
+        want = plain.temperature_sample(rows[r], float(temps[r]), sampling_key(seeds[r]), r)
+        assert int(tokens[r]) == want, r
+    # the draw depends on the request's key and counter only: the same row alone gives the same token
+    one = torch.empty(1, dtype=torch.int32, device=dev)
+    ops.sample(one, logits[5:6].contiguous(), st, temps[5:6].contiguous(), keys[5:6].contiguous(), counters[5:6].contiguous())
+    assert int(one[0]) == int(tokens[5])
+    # and it follows the softmax
+    l4 = torch.tensor([[2.0, 1.0, 0.0, -1.0]], device=dev).repeat(4000, 1)
+    t4 = torch.full((4000,), 0.8, device=dev)
+    k4 = keys[:1].repeat(4000)
+    c4 = torch.arange(4000, dtype=torch.int32, device=dev)
+    o4 = torch.empty(4000, dtype=torch.int32, device=dev)
+    ops.sample(o4, l4, st, t4, k4, c4)
+    p = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]) / 0.8, 0)
+    freq = torch.bincount(o4.cpu().long(), minlength=4).float() / 4000
+    assert (freq - p).abs().max() < 0.03
