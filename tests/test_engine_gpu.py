@@ -1,0 +1,185 @@
+"""Generation through the entry points: greedy and temperature sampling against the plain
+implementation, page pressure, CUDA graphs, the asynchronous engine and the command line (GPU)."""
+import subprocess
+import sys
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import ROOT, TINY, tokens_for
+
+pytestmark = pytest.mark.gpu
+
+
+def make_engine(folder, name, dtype, **kw):
+    from lucciola_b200 import Engine, EngineOptions
+    opts = dict(dtype=dtype, block_size=TINY[name][4], max_blocks=64, max_tokens_per_step=48, max_num_seqs=8)
+    opts.update(kw)
+    return Engine(folder, options=EngineOptions(**opts))
+
+
+def check_against_plain(folder, prompt, output, temperature, key, slack):
+    """Every generated token must be the plain implementation's choice given the same prefix, or lose to it
+    by no more than `slack` in the sampler's score (a near-tie that rounding may flip)."""
+    cfg, w = plain.read_model(folder)
+    ids = list(prompt)
+    for n, tok in enumerate(output):
+        row = plain.forward(cfg, w, ids)[-1].float().numpy()
+        if temperature > 0:
+            u = np.array([plain.hash_uniform(key, n, i) for i in range(row.shape[0])], dtype=np.float32)
+            score = row / np.float32(temperature) - np.log(-np.log(u))
+        else:
+            score = row
+        assert score.max() - score[tok] <= slack, f"token {n}: chose {tok} (score {score[tok]:.5f}), plain chooses {int(score.argmax())} ({score.max():.5f})"
+        ids.append(tok)
+
+
+@pytest.mark.parametrize("dtype,slack", [("float32", 1e-5), ("bfloat16", 0.05)])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_the_entry_point(tiny_models, name, dtype, slack):
+    from lucciola_b200 import SamplingParams
+    eng = make_engine(tiny_models[name], name, dtype)
+    lengths = {"A": [5, 17, 33], "B": [1, 9, 40, 100], "C": [3, 30, 70]}[name]
+    prompts = [tokens_for(name, n, salt=2) for n in lengths]
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=8, ignore_eos=True))
+    assert all(len(o) == 8 for o in outs)
+    for p, o in zip(prompts, outs):
+        check_against_plain(tiny_models[name], p, o, 0.0, 0, slack)
+    if dtype == "float32":
+        cfg, w = plain.read_model(tiny_models[name])
+        assert outs[0] == plain.generate(cfg, w, prompts[0], 8)
+    assert eng.runner.manager.num_requests() == 0 and all(p.num_free == p.num_pages for p in eng.runner.manager.pools)
+
+
+@pytest.mark.parametrize("dtype,slack", [("float32", 1e-4), ("bfloat16", 0.08)])
+def test_temperature_sampling_through_the_entry_point(tiny_models, dtype, slack):
+    """Tiny workload B: temperature 0.8, seed 7; then the same prompts greedily."""
+    from lucciola_b200 import SamplingParams
+    from lucciola_b200.sampling.sampler import sampling_key
+    name = "B"
+    eng = make_engine(tiny_models[name], name, dtype, prefill_chunk=7)
+    prompts = [tokens_for(name, n, salt=3) for n in (1, 9, 40, 100)]
+    params = SamplingParams(max_new_tokens=6, temperature=0.8, seed=7, ignore_eos=True)
+    outs = eng.generate(prompts, params)
+    for p, o in zip(prompts, outs):
+        check_against_plain(tiny_models[name], p, o, 0.8, sampling_key(7), slack)
+    # the draw does not depend on the batch: one prompt alone gives the same tokens
+    alone = eng.generate([prompts[2]], params)[0]
+    assert alone == outs[2]
+    other_seed = eng.generate([prompts[2]], SamplingParams(max_new_tokens=6, temperature=0.8, seed=8, ignore_eos=True))[0]
+    assert other_seed != outs[2]
+    greedy = eng.generate(prompts, SamplingParams(max_new_tokens=6, ignore_eos=True))
+    for p, o in zip(prompts, greedy):
+        check_against_plain(tiny_models[name], p, o, 0.0, 0, slack)
+
+
+def test_eos_stops_generation(tiny_models):
+    from lucciola_b200 import SamplingParams
+    name = "A"
+    eng = make_engine(tiny_models[name], name, "float32")
+    prompt = tokens_for(name, 12, salt=5)
+    free_run = eng.generate([prompt], SamplingParams(max_new_tokens=10, ignore_eos=True))[0]
+    eng.scheduler.eos_token_ids = frozenset({free_run[3]})
+    stopped = eng.generate([prompt], SamplingParams(max_new_tokens=10))[0]
+    assert stopped == free_run[:free_run.index(free_run[3]) + 1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_page_pressure_preempts_and_still_gives_the_same_tokens(tiny_models, dtype):
+    from lucciola_b200 import SamplingParams
+    name = "C"
+    prompts = [tokens_for(name, n, salt=6) for n in (40, 55, 33, 61, 20, 48)]
+    params = SamplingParams(max_new_tokens=40, ignore_eos=True)
+    roomy = make_engine(tiny_models[name], name, dtype, max_blocks=64)
+    want = roomy.generate(prompts, params)
+    assert roomy.stats()["preemptions"] == 0
+    tight = make_engine(tiny_models[name], name, dtype, max_blocks=14)          # 224 tokens for 6 requests of up to 101
+    got = tight.generate(prompts, params)
+    assert tight.stats()["preemptions"] > 0
+    if dtype == "float32":
+        assert got == want
+    else:   # a recomputed request runs as a prompt, not token by token: bfloat16 may round differently at a near-tie
+        for p, o in zip(prompts, got):
+            check_against_plain(tiny_models[name], p, o[:12], 0.0, 0, 0.05)
+    tight.runner.manager.check_invariants()
+    assert all(p.num_free == p.num_pages for p in tight.runner.manager.pools)
+
+
+def test_cuda_graph_decode_equals_eager_decode(tiny_models):
+    """Decode-only steps replayed from a recorded graph (batch padded to a bucket) give the logits of the
+    same steps run kernel by kernel."""
+    from lucciola_b200.engine.step import StepEntry
+    name = "B"
+    engines = [make_engine(tiny_models[name], name, "bfloat16", use_cuda_graph=g) for g in (False, True)]
+    prompts = {f"r{i}": tokens_for(name, n, salt=8) for i, n in enumerate((9, 30, 17))}
+    feeds = {rid: tokens_for(name, 20, salt=9 + i) for i, rid in enumerate(prompts)}
+    results = []
+    for eng in engines:
+        r = eng.runner
+        rows = []
+        for rid, p in prompts.items():
+            r.step([StepEntry(rid, p, [])])
+        for t in range(20):
+            live = list(prompts) if t < 12 else list(prompts)[:2]          # the batch shrinks: another bucket
+            if t == 12:
+                r.finish("r2")
+            want = [rid for rid in live if not (t % 5 == 0 and rid == "r1")]   # a step where one request wants nothing
+            logits = r.step([StepEntry(rid, [feeds[rid][t]], [0] if rid in want else []) for rid in live])
+            rows.append(logits.float().cpu().clone())
+        results.append(torch.cat(rows))
+        assert (len(r._graphs) > 0) == eng.options.use_cuda_graph
+    assert torch.equal(results[0], results[1])
+
+
+def test_async_engine_streams_tokens_and_stops(tiny_models):
+    from lucciola_b200 import AsyncEngine, EngineOptions
+    name = "A"
+    folder = tiny_models[name]
+    eng = AsyncEngine(folder, max_blocks=32, block_size=16, dtype="float32", max_tokens_per_step=24)
+    got: dict[int, list[int]] = {}
+    done = {i: threading.Event() for i in range(3)}
+    prompts = [tokens_for(name, n, salt=11) for n in (5, 17, 33)]
+
+    def cb(i):
+        def f(token, finished):
+            got.setdefault(i, []).append(token)
+            if finished:
+                done[i].set()
+        return f
+
+    ids = [eng.generate_async(p, 8, cb(i), ignore_eos=True) for i, p in enumerate(prompts)]
+    assert len(set(ids)) == 3
+    for e in done.values():
+        assert e.wait(120)
+    refused = threading.Event()
+    eng.generate_async(list(range(200)), 4, lambda t, f: refused.set() if (t, f) == (-1, True) else None)   # longer than the model allows
+    assert refused.wait(60)
+    eng.stop()
+    cfg, w = plain.read_model(folder)
+    for i, p in enumerate(prompts):
+        assert got[i] == plain.generate(cfg, w, p, 8)
+    with pytest.raises(RuntimeError, match="stopped"):
+        eng.generate_async([1], 1)
+
+
+def test_command_line(tiny_models):
+    name = "A"
+    prompt = tokens_for(name, 9, salt=12)
+    cmd = [sys.executable, str(ROOT / "bin" / "lucciola_chat"), "--model", str(tiny_models[name]), "--dtype", "float32",
+           "--max-blocks", "16", "--max-new-tokens", "5", "--ignore-eos"]
+    p = subprocess.run(cmd, input=" ".join(map(str, prompt)) + "\n" + ",".join(map(str, prompt[:4])) + "\nexit\n",
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [l for l in p.stdout.splitlines() if l.strip()]
+    cfg, w = plain.read_model(tiny_models[name])
+    assert [int(x) for x in lines[0].split()] == plain.generate(cfg, w, prompt, 5)
+    assert [int(x) for x in lines[1].split()] == plain.generate(cfg, w, prompt[:4], 5)
+
+
+def test_smoke_entry():
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as g
+    g.smoke()

@@ -1,0 +1,294 @@
+"""Each part alone against the plain implementation's function for it, the order of layers as data,
+and a toy mixer with state of its own that is registered, built and stepped without a change to
+the framework's files (GPU)."""
+import json
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import TINY, tokens_for
+
+pytestmark = pytest.mark.gpu
+ACTS = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 3e-6, torch.bfloat16: 1.5e-2}
+
+
+def rel(a, b):
+    return ((a.double().cpu() - b.double().cpu()).abs().max() / b.double().abs().max().clamp_min(1e-30)).item()
+
+
+def make_rt(act):
+    from lucciola_b200.parts import Runtime
+    torch.cuda.set_device(0)
+    rt = Runtime("cuda:0", act)
+    rt.stream = torch.cuda.current_stream().cuda_stream
+    return rt
+
+
+def bind_random(part, act, seed=0, std=0.1, norm_std=0.2):
+    """Give a part random tensors; returns them as float64 on the CPU, rounded as the part holds them."""
+    from lucciola_b200.weights.random_init import random_tensor
+    held = {}
+
+    def get(name):
+        spec = {s.name: s for s in part.all_param_specs()}[name]
+        t = random_tensor(spec, seed, std, norm_std, torch.bfloat16)
+        held[name] = t.double()
+        return t.to("cuda:0", dtype=torch.float32 if act == torch.float32 else torch.bfloat16)
+
+    part.bind_all(get)
+    return held
+
+
+def one_request_step(rt, T, page, nkv, d, start=0, window=0, group=None):
+    """A StepContext and a cache for one request that brings T tokens after `start` cached ones."""
+    from lucciola_b200.parts import KVCacheView, StepContext
+    dev = rt.device
+    L = start + T
+    P = -(-L // page) + 1
+    bt = torch.full((1, P), -1, dtype=torch.int32)
+    bt[0, :-(-L // page)] = torch.randperm(-(-L // page) + 2)[:-(-L // page)].int()
+    pool = torch.full((2, P + 2, nkv, page, d), float("nan"), dtype=rt.act_dtype, device=dev)
+    pos = torch.arange(start, L, dtype=torch.int32, device=dev)
+    meta = {}
+    if group and rt.fast_kernels:
+        per = 64 // group
+        tiles = [(o, min(per, T - o), 0, 0) for o in range(0, T, per)]
+        meta[group] = (torch.tensor(tiles, dtype=torch.int32, device=dev), min(64, max(t[1] for t in tiles) * group))
+    step = StepContext(num_tokens=T, num_seqs=1, positions=pos, token_seq=torch.zeros(T, dtype=torch.int32, device=dev),
+                       cu_tokens=torch.tensor([0, T], dtype=torch.int32, device=dev),
+                       context_lens=torch.tensor([L], dtype=torch.int32, device=dev), block_tables=[bt.to(dev)],
+                       state_slots=torch.zeros(1, dtype=torch.int32, device=dev), q_lens=[T], start_positions=[start],
+                       max_q_len=T, max_context_len=L, attn_meta=meta)
+    return step, KVCacheView(pool[0], pool[1], 0, page)
+
+
+@pytest.mark.parametrize("act", ACTS)
+def test_rmsnorm_part(act):
+    from lucciola_b200.parts import RMSNorm
+    rt = make_rt(act)
+    n = RMSNorm(rt, "n.weight", 200, 2e-5)
+    w = bind_random(n, act)["n.weight"]
+    x = torch.randn(6, 200, device="cuda:0")
+    want = plain.rms_norm(x.double().cpu(), w, 2e-5)
+    assert rel(n.forward(x, act), want) < TOL[act]
+    delta = torch.randn(6, 200, device="cuda:0").to(act)
+    r = x.clone()
+    out = n.add_forward(r, delta, act)
+    assert torch.equal(r, x + delta.float()) and rel(out, plain.rms_norm((x + delta.float()).double().cpu(), w, 2e-5)) < TOL[act]
+
+
+@pytest.mark.parametrize("act", ACTS)
+def test_linear_and_stacked_linear(act):
+    from lucciola_b200.parts import Linear
+    rt = make_rt(act)
+    lin = Linear(rt, ["a.weight", "b.weight"], 72, [40, 24])
+    w = bind_random(lin, act)
+    x = torch.randn(5, 72, device="cuda:0").to(act)
+    y = lin.forward(x)
+    want = torch.cat([plain.linear(x.double().cpu(), w["a.weight"]), plain.linear(x.double().cpu(), w["b.weight"])], dim=1)
+    assert y.shape == (5, 64) and rel(y, want) < TOL[act]
+    assert rel(lin.forward(x, rows=40), want[:, :40]) < TOL[act]
+
+
+@pytest.mark.parametrize("act", ACTS)
+def test_feed_forward_part(act):
+    from lucciola_b200.parts import SwiGLUFeedForward
+    rt = make_rt(act)
+    ffn = SwiGLUFeedForward(rt, "mlp", 72, 200)
+    w = bind_random(ffn, act)
+    x = torch.randn(7, 72, device="cuda:0").to(act)
+    assert rel(ffn.forward(x, None), plain.feed_forward(x.double().cpu(), w, "mlp")) < TOL[act]
+
+
+@pytest.mark.parametrize("act", ACTS)
+def test_embedding_and_head_parts(act):
+    from lucciola_b200.parts import OutputHead, TokenEmbedding
+    rt = make_rt(act)
+    emb = TokenEmbedding(rt, "e.weight", 90, 40)
+    w = bind_random(emb, act)["e.weight"]
+    ids = torch.tensor([3, 89, 0, 3], dtype=torch.int32, device="cuda:0")
+    assert torch.equal(emb.forward(ids).double().cpu(), plain.embed(ids.cpu().tolist(), w))
+    tied = OutputHead(rt, "h.weight", 90, 40, emb)
+    tied.bind_all(lambda name: (_ for _ in ()).throw(AssertionError("a tied head asks for no tensor")))
+    x = torch.randn(3, 40, device="cuda:0").to(act)
+    logits = tied.forward(x)
+    assert logits.dtype == torch.float32 and rel(logits, plain.linear(x.double().cpu(), w)) < TOL[act]
+    own = OutputHead(rt, "h.weight", 90, 40, None)
+    wh = bind_random(own, act, seed=5)["h.weight"]
+    assert rel(own.forward(x), plain.linear(x.double().cpu(), wh)) < TOL[act]
+
+
+@pytest.mark.parametrize("act", ACTS)
+@pytest.mark.parametrize("nq,nkv,d,window,start,T", [(6, 2, 24, 0, 0, 21), (4, 4, 64, 9, 0, 40), (8, 2, 128, 0, 0, 70)])
+def test_attention_part(act, nq, nkv, d, window, start, T):
+    """Norm of q and k per head, rotation, cache write, attention and output projection, whole and then
+    continued from the cache in a second step."""
+    from lucciola_b200.parts import GQAttention, RotaryEmbedding
+    rt = make_rt(act)
+    hidden, theta, eps, page = 56, 7e4, 3e-6, 8
+    att = GQAttention(rt, "self_attn", hidden, nq, nkv, d, RotaryEmbedding(rt, d, theta), qk_norm_eps=eps, window=window)
+    w = bind_random(att, act, std=0.15)
+    cfg = {"num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": d, "hidden_size": hidden,
+           "rms_norm_eps": eps, "rope_theta": theta}
+    x = torch.randn(T, hidden, device="cuda:0").to(act)
+    want, _ = plain.attention_block(x.double().cpu(), w, "self_attn", cfg, list(range(T)), window)
+    step, cache = one_request_step(rt, T, page, nkv, d, group=nq // nkv)
+    assert rel(att.forward(x, step, cache), want) < TOL[act]
+    # the same tokens in two steps: the second reads what the first left in the pages
+    cut = T // 2 + 1
+    step1, cache = one_request_step(rt, cut, page, nkv, d, group=nq // nkv)
+    step2, _ = one_request_step(rt, T - cut, page, nkv, d, start=cut, group=nq // nkv)
+    need = -(-T // page)
+    bt = torch.full((1, need + 1), -1, dtype=torch.int32)
+    bt[0, :need] = torch.arange(need, dtype=torch.int32)
+    step1.block_tables = [bt.cuda()]; step2.block_tables = [bt.cuda()]
+    pool = torch.full((2, need + 1, nkv, page, d), float("nan"), dtype=act, device="cuda:0")
+    from lucciola_b200.parts import KVCacheView
+    cache = KVCacheView(pool[0], pool[1], 0, page)
+    a = att.forward(x[:cut].contiguous(), step1, cache)
+    b = att.forward(x[cut:].contiguous(), step2, cache)
+    assert rel(torch.cat([a, b]), want) < TOL[act]
+
+
+def test_another_position_encoding_goes_through_apply():
+    """A position encoding the fused kernel does not know: the mixer norms, calls the part's apply(), then writes."""
+    from lucciola_b200.parts import GQAttention, PositionEncoding
+    rt = make_rt(torch.float32)
+
+    class SignFlip(PositionEncoding):            # toy: negate q and k at odd positions
+        def apply(self, q, k, positions):
+            s = (1 - 2 * (positions % 2)).to(q.dtype)[:, None, None]
+            q.mul_(s); k.mul_(s)
+
+    nq, nkv, d, hidden, T = 4, 2, 16, 32, 13
+    att = GQAttention(rt, "a", hidden, nq, nkv, d, SignFlip(), qk_norm_eps=None)
+    w = bind_random(att, torch.float32)
+    x = torch.randn(T, hidden, device="cuda:0")
+    step, cache = one_request_step(rt, T, 4, nkv, d)
+    got = att.forward(x, step, cache)
+    xd = x.double().cpu()
+    sign = (1 - 2 * (torch.arange(T) % 2)).double()[:, None, None]
+    q = plain.linear(xd, w["a.q_proj.weight"]).reshape(T, nq, d) * sign
+    k = plain.linear(xd, w["a.k_proj.weight"]).reshape(T, nkv, d) * sign
+    v = plain.linear(xd, w["a.v_proj.weight"]).reshape(T, nkv, d)
+    o = plain.attention(q, k, v, list(range(T)), list(range(T)), 1 / math.sqrt(d))
+    assert rel(got, plain.linear(o.reshape(T, nq * d), w["a.o_proj.weight"])) < 3e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_order_of_layers_is_data(tiny_models, dtype):
+    """A layer named twice (two caches) and a layer that reads another layer's cache, against the plain
+    implementation run with the same list of calls; whole and cut into portions."""
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.load import build_runner
+    from lucciola_b200.engine.step import ModelRunner, StepEntry
+    from lucciola_b200.models import LayerCall
+    import replay_util as ru
+
+    folder = tiny_models["A"]
+    pc, pw = plain.read_model(folder)
+    ids = tokens_for("A", 50, salt=4)
+    for calls in ([(0, 0, True), (0, 1, True), (1, 2, True)], [(0, 0, True), (1, 0, False), (1, 1, True)]):
+        base = build_runner(folder, EngineOptions(dtype=dtype, block_size=16, max_blocks=16, max_num_seqs=2, use_cuda_graph=False))
+        model = base.model
+        model.calls = [LayerCall(*c) for c in calls]
+        model._check_calls()
+        runner = ModelRunner(model, base.rt, base.options, 16)
+        want = plain.forward(pc, pw, ids, calls=calls)
+        got = runner.step([StepEntry("w", ids, list(range(50)))]).double().cpu()
+        scale = want.abs().max()
+        assert ((got - want).abs().max() / scale).item() < ru.TOL[dtype]
+        runner.finish("w")
+        parts = [runner.step([StepEntry("p", ids[a:b], list(range(b - a)))]) for a, b in ((0, 17), (17, 19), (19, 50))]
+        got2 = torch.cat(parts).double().cpu()
+        assert ((got2 - want).abs().max() / scale).item() < ru.TOL[dtype]
+
+
+def test_toy_mixer_with_state_of_its_own(tmp_path):
+    """A mixer defined here, with a fixed-size state per request (a running mean of what it has seen),
+    inside an architecture defined here: registered, built from a config.json, loaded from safetensors
+    and stepped by the framework's runner, whole and in portions, mixed with a second request."""
+    from lucciola_b200.config import EngineOptions, register_architecture
+    from lucciola_b200.engine.load import build_runner
+    from lucciola_b200.engine.step import StepEntry
+    from lucciola_b200.models import DecoderModel, LayerCall
+    from lucciola_b200.parts import (Linear, Mixer, OutputHead, PreNormBlock, RMSNorm, StateSlot, SwiGLUFeedForward,
+                                     TokenEmbedding)
+    from lucciola_b200.weights import write_safetensors
+    from lucciola_b200.weights.random_init import RandomWeights
+
+    class RunningMean(Mixer):
+        """out_t = W . mean(h_0 .. h_t).  State per request: the sum so far and the count."""
+        def __init__(self, rt, prefix, hidden):
+            self.rt, self.hidden = rt, hidden
+            self.proj = Linear(rt, f"{prefix}.proj.weight", hidden, hidden)
+
+        def children(self):
+            return [self.proj]
+
+        def cache_request(self):
+            return StateSlot((self.hidden + 1,), torch.float32)
+
+        def forward(self, h, step, cache, write_cache=True):
+            out = torch.empty_like(h)
+            for i in range(step.num_seqs):
+                a, b = sum(step.q_lens[:i]), sum(step.q_lens[:i + 1])
+                slot = int(step.state_slots[i])
+                st = cache.state[slot]
+                sums = st[:-1] + torch.cumsum(h[a:b].float(), dim=0)
+                counts = st[-1] + torch.arange(1, b - a + 1, device=h.device, dtype=torch.float32)
+                out[a:b] = (sums / counts[:, None]).to(h.dtype)
+                st[:-1] = sums[-1]; st[-1] = counts[-1]
+            return self.proj.forward(out)
+
+    def config_from_dict(d):
+        return dict(d)
+
+    def build(cfg, rt):
+        H, V = cfg["hidden_size"], cfg["vocab_size"]
+        emb = TokenEmbedding(rt, "emb.weight", V, H)
+        blocks = [PreNormBlock(RunningMean(rt, f"l{i}.mix", H), SwiGLUFeedForward(rt, f"l{i}.mlp", H, cfg["inner"]),
+                               RMSNorm(rt, f"l{i}.n1.weight", H, cfg["eps"]), RMSNorm(rt, f"l{i}.n2.weight", H, cfg["eps"]),
+                               rt.act_dtype) for i in range(cfg["layers"])]
+        return DecoderModel(rt, emb, blocks, [LayerCall(i, i) for i in range(cfg["layers"])],
+                            RMSNorm(rt, "norm.weight", H, cfg["eps"]), OutputHead(rt, "head.weight", V, H, None), V, cfg["max_len"])
+
+    register_architecture("ToyRunningMeanLM", config_from_dict, build, replace=True)
+    cfg = {"architectures": ["ToyRunningMeanLM"], "hidden_size": 40, "vocab_size": 61, "inner": 72, "layers": 2,
+           "eps": 1e-5, "max_len": 64}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    from lucciola_b200.parts import Runtime
+    specs = build(cfg, Runtime("cpu", torch.float32)).all_param_specs()
+    src = RandomWeights(specs, 3, std=0.2, norm_std=0.1)
+    weights = {n: src.get(n) for n in src.names()}
+    write_safetensors(tmp_path / "model.safetensors", weights)
+
+    def plain_forward(ids):
+        w = {k: v.double() for k, v in weights.items()}
+        x = w["emb.weight"][torch.tensor(ids)]
+        for i in range(cfg["layers"]):
+            h = plain.rms_norm(x, w[f"l{i}.n1.weight"], cfg["eps"])
+            mean = torch.cumsum(h, 0) / torch.arange(1, len(ids) + 1, dtype=torch.float64)[:, None]
+            x = x + plain.linear(mean, w[f"l{i}.mix.proj.weight"])
+            h = plain.rms_norm(x, w[f"l{i}.n2.weight"], cfg["eps"])
+            x = x + plain.feed_forward(h, {k.replace(f"l{i}.mlp.", "m."): v for k, v in w.items()}, "m")
+        return plain.linear(plain.rms_norm(x, w["norm.weight"], cfg["eps"]), w["head.weight"])
+
+    runner = build_runner(tmp_path, EngineOptions(dtype="float32", block_size=16, max_blocks=4, max_num_seqs=3, use_cuda_graph=False))
+    assert runner.groups == [] and list(runner.cache.states) == [0, 1]          # no pages, two state caches
+    a, b = [5, 9, 60, 0, 33, 7, 7, 18, 2, 41, 3], [11, 12, 13, 14, 15, 16]
+    wa, wb = plain_forward(a), plain_forward(b)
+    got = runner.step([StepEntry("a", a, list(range(len(a))))]).double().cpu()
+    assert ((got - wa).abs().max() / wa.abs().max()) < 1e-5
+    runner.finish("a")
+    # portions, with another request in between; "a" is a new request again: its slot must have been cleared
+    g1 = runner.step([StepEntry("a", a[:4], [0, 1, 2, 3]), StepEntry("b", b[:1], [0])]).double().cpu()
+    g2 = runner.step([StepEntry("b", b[1:], list(range(5))), StepEntry("a", a[4:6], [0, 1])]).double().cpu()
+    g3 = runner.step([StepEntry("a", a[6:], list(range(5)))]).double().cpu()
+    got_a = torch.cat([g1[:4], g2[5:], g3]); got_b = torch.cat([g1[4:], g2[:5]])
+    assert ((got_a - wa).abs().max() / wa.abs().max()) < 1e-5 and ((got_b - wb).abs().max() / wb.abs().max()) < 1e-5
+    runner.finish("a"); runner.finish("b")
+    runner.manager.check_invariants()
