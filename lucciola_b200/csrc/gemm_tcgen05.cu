@@ -447,3 +447,89 @@ LB_EXPORT int lb_device_error() {
   if (v != 0) cudaMemcpyToSymbol(lb::g_device_error, &zero, sizeof(int));
   return v;
 }
+
+// ---- the same product for callers that cannot allocate (see no_alloc.h) ---------------------------------
+#include "no_alloc.h"
+
+namespace lb {
+
+// Scratch of the static-scratch entry point: tile counters first, then the float32 partial sums.
+// One copy per device, held from the moment the library's code is loaded there until the process ends.
+static __device__ __align__(256) unsigned char g_static_scratch[LB_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on each device, resolved at the first call there.
+constexpr int MAX_DEVICES = 64;
+static unsigned char* g_static_scratch_addr[MAX_DEVICES] = {};
+static std::mutex g_static_scratch_mu;
+
+// In host code `g_static_scratch` names a host-side handle; a kernel given that would read the wrong
+// memory.  The runtime translates it for the device that is current.
+static int static_scratch_address(unsigned char** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { set_error("gemm_tcgen05_static_scratch: cudaGetDevice failed: %s", cudaGetErrorString(e)); return 4; }
+  if (dev < 0 || dev >= MAX_DEVICES) { set_error("gemm_tcgen05_static_scratch: device %d is beyond the %d this table holds", dev, MAX_DEVICES); return 4; }
+  std::lock_guard<std::mutex> g(g_static_scratch_mu);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("gemm_tcgen05_static_scratch: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return 4;
+    }
+    g_static_scratch_addr[dev] = (unsigned char*)p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace lb
+
+LB_EXPORT int lb_gemm_tcgen05_static_scratch(void* y, int y_dtype, const void* x, const void* w, int M, int N, int K,
+                                             long long ldx, long long ldy, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(y_dtype), "gemm_tcgen05_static_scratch: bad output dtype %d", y_dtype);
+  LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && ldx >= K && ldy >= N, "gemm_tcgen05_static_scratch: bad sizes M=%d N=%d K=%d", M, N, K);
+  LB_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0, "gemm_tcgen05_static_scratch: K=%d and the row stride %lld must be multiples of 8", K, ldx);
+  LB_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05_static_scratch: operands must be 16-byte aligned");
+  if (M == 0) return 0;
+  int bt = 16;
+  int splits = lb_gemm_tcgen05_plan(M, N, K, &bt);
+  const int kb = (K + lb::BK - 1) / lb::BK;
+  if (splits > kb) splits = kb;
+  const long long tiles = (long long)((N + lb::BM - 1) / lb::BM) * ((M + bt - 1) / bt);
+  LB_CHECK_ARG((M + bt - 1) / bt <= 65535, "gemm_tcgen05_static_scratch: too many rows (%d)", M);
+  float* partials = nullptr;
+  int* counters = nullptr;
+  if (splits > 1) {
+    const long long need = (long long)splits * M * N;
+    LB_CHECK_ARG(need <= LB_STATIC_SCRATCH_PARTIALS && tiles <= LB_STATIC_SCRATCH_COUNTERS,
+                 "gemm_tcgen05_static_scratch: M=%d N=%d K=%d is split %d ways and needs %lld partial sums and %lld tile "
+                 "counters; the built-in scratch holds %d and %d",
+                 M, N, K, splits, need, tiles, LB_STATIC_SCRATCH_PARTIALS, LB_STATIC_SCRATCH_COUNTERS);
+    unsigned char* base = nullptr;
+    if (int rc = lb::static_scratch_address(&base)) return rc;
+    counters = (int*)base;
+    partials = (float*)(base + LB_STATIC_SCRATCH_COUNTERS * 4);
+    // The counters must start at zero whatever an earlier call left behind.
+    cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)tiles * sizeof(int), stream);
+    if (e != cudaSuccess) { lb::set_error("gemm_tcgen05_static_scratch: clearing the counters failed: %s", cudaGetErrorString(e)); return 4; }
+  }
+  CUtensorMap mw, mx;                      // built for this call, on the stack
+  if (!lb::make_map(&mw, w, N, K, K, lb::BM) || !lb::make_map(&mx, x, M, K, ldx, bt)) {
+    lb::set_error("gemm_tcgen05_static_scratch: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);
+    return 3;
+  }
+  lb::GemmParams p;
+  p.y = y; p.workspace = partials; p.counters = counters; p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.out_dtype = y_dtype;
+  int rc = 0;
+  switch (bt) {
+    case 16: rc = lb::launch_tc<16, 6>(mw, mx, p, splits, stream); break;
+    case 32: rc = lb::launch_tc<32, 6>(mw, mx, p, splits, stream); break;
+    case 64: rc = lb::launch_tc<64, 6>(mw, mx, p, splits, stream); break;
+    case 128: rc = lb::launch_tc<128, 6>(mw, mx, p, splits, stream); break;
+    default: rc = lb::launch_tc<256, 4>(mw, mx, p, splits, stream); break;
+  }
+  if (rc) return rc;
+  LB_CHECK_LAUNCH("gemm_tcgen05_static_scratch");
+  return 0;
+}
