@@ -90,6 +90,8 @@ flash_attention_kernel(FlashParams p) {
   const uint32_t k_smem = q_smem + FA_ROWS * DP * 2;
   const uint32_t v_smem = k_smem + FA_STAGES * TILE_BYTES;
 
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int4 tile = p.tiles[blockIdx.x];
   const int t0 = tile.x, ntok = tile.y, seq = tile.z;
@@ -358,6 +360,8 @@ flash_attention_kernel(FlashParams p) {
 
 // Combines the partials of the splits, in their order: out = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M).
 __global__ void flash_combine_kernel(FlashParams p) {
+  pdl_trigger();
+  pdl_wait();
   const int4 tile = p.tiles[blockIdx.x];
   const int kvh = blockIdx.y;
   const int rows = tile.y * p.group, d = p.head_dim;
@@ -435,7 +439,7 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
       cudaFuncSetAttribute(lb::flash_attention_kernel<DP, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
       cfg = true;                                                                                               \
     }                                                                                                           \
-    lb::flash_attention_kernel<DP, KS><<<grid, lb::FA_THREADS, smem, stream>>>(p);                              \
+    lb::launch(lb::flash_attention_kernel<DP, KS>, grid, dim3(lb::FA_THREADS), smem, stream, p);                \
   } while (0)
   if (dp == 64) { if (keysplit) LB_FLASH_LAUNCH(64, true); else LB_FLASH_LAUNCH(64, false); }
   else { if (keysplit) LB_FLASH_LAUNCH(128, true); else LB_FLASH_LAUNCH(128, false); }
@@ -443,7 +447,7 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   LB_CHECK_LAUNCH("attention_flash");
   if (splits > 1) {
     dim3 cgrid(num_tiles, num_kv_heads), cblock(32, 4);
-    lb::flash_combine_kernel<<<cgrid, cblock, 0, stream>>>(p);
+    lb::launch(lb::flash_combine_kernel, cgrid, cblock, 0, stream, p);
     LB_CHECK_LAUNCH("attention_flash combine");
   }
   return 0;

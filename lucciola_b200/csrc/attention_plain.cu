@@ -25,6 +25,8 @@ struct PlainAttnParams {
 template <typename T, int DPL>
 __global__ void plain_attention_kernel(PlainAttnParams p) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int t = blockIdx.y;
   const int h = blockIdx.x * nwarps + warp;
@@ -97,11 +99,11 @@ int launch_plain(const PlainAttnParams& p, int num_tokens, cudaStream_t stream) 
   dim3 grid((p.num_q_heads + warps - 1) / warps, num_tokens);
   const size_t smem = (size_t)warps * p.head_dim * sizeof(float);
   const int dpl = (p.head_dim + 31) / 32;
-  if (dpl <= 1) plain_attention_kernel<T, 1><<<grid, warps * 32, smem, stream>>>(p);
-  else if (dpl <= 2) plain_attention_kernel<T, 2><<<grid, warps * 32, smem, stream>>>(p);
-  else if (dpl <= 4) plain_attention_kernel<T, 4><<<grid, warps * 32, smem, stream>>>(p);
-  else if (dpl <= 8) plain_attention_kernel<T, 8><<<grid, warps * 32, smem, stream>>>(p);
-  else plain_attention_kernel<T, 16><<<grid, warps * 32, smem, stream>>>(p);
+  if (dpl <= 1) launch(plain_attention_kernel<T, 1>, grid, dim3(warps * 32), smem, stream, p);
+  else if (dpl <= 2) launch(plain_attention_kernel<T, 2>, grid, dim3(warps * 32), smem, stream, p);
+  else if (dpl <= 4) launch(plain_attention_kernel<T, 4>, grid, dim3(warps * 32), smem, stream, p);
+  else if (dpl <= 8) launch(plain_attention_kernel<T, 8>, grid, dim3(warps * 32), smem, stream, p);
+  else launch(plain_attention_kernel<T, 16>, grid, dim3(warps * 32), smem, stream, p);
   return 0;
 }
 

@@ -44,6 +44,30 @@ void count_launch();   // every kernel launch of the library is counted (lb_laun
     lb::count_launch();                                                    \
   } while (0)
 
+// Programmatic dependent launch.  Every kernel of the library is launched with the attribute that
+// lets it start while the kernel before it on the stream is still running, calls pdl_trigger() at its
+// start (so that its own successor may be scheduled early) and pdl_wait() before it reads anything
+// another kernel wrote or writes anything at all.  pdl_wait() returns when the kernel before has
+// completed and its writes are visible; in a kernel launched without the attribute both are no-ops.
+// lb_set_pdl(0) switches the attribute off for all later launches.
+extern int g_pdl_enabled;
+
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl_enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
 

@@ -10,6 +10,8 @@ namespace lb {
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const int* __restrict__ ids,
                                  const TW* __restrict__ table, int hidden, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -28,7 +30,7 @@ LB_EXPORT int lb_embedding(float* out, const int* ids, const void* table, int ta
   if (num_tokens == 0) return 0;
   int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
   LB_DISPATCH_DTYPE(table_dtype, TW, {
-    lb::embedding_kernel<TW><<<num_tokens, threads, 0, stream>>>(out, ids, (const TW*)table, hidden, vocab);
+    lb::launch(lb::embedding_kernel<TW>, dim3(num_tokens), dim3(threads), 0, stream, out, ids, (const TW*)table, hidden, vocab);
   })
   LB_CHECK_LAUNCH("embedding");
   return 0;

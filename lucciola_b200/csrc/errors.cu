@@ -11,6 +11,7 @@ void set_error(const char* fmt, ...) {
   vsnprintf(g_error, sizeof(g_error), fmt, ap);
   va_end(ap);
 }
+int g_pdl_enabled = 1;
 static unsigned long long g_launches = 0;
 void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
 }  // namespace lb
@@ -18,6 +19,9 @@ void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
 // Kernels this library has launched so far in this process (launches recorded into a CUDA graph
 // count once, when they are recorded).
 LB_EXPORT unsigned long long lb_launch_count() { return __atomic_load_n(&lb::g_launches, __ATOMIC_RELAXED); }
+
+// Switches programmatic dependent launch on (default) or off for all later launches.
+LB_EXPORT void lb_set_pdl(int on) { lb::g_pdl_enabled = on ? 1 : 0; }
 
 // Message of the last failed call on this thread.
 LB_EXPORT const char* lb_last_error() { return lb::g_error; }

@@ -20,6 +20,8 @@ gemm_plain_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __rest
                   int K, long long ldx, long long ldy) {
   __shared__ float xs[PG_BK][PG_BM + 4];
   __shared__ float ws[PG_BK][PG_BN + 4];
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * PG_BM, n0 = blockIdx.x * PG_BN;
   const int tr = tid / 16, tc = tid % 16;  // thread owns rows tr*4.., cols tc*4..
@@ -69,8 +71,7 @@ template <typename TX, typename TW, typename TY>
 void launch_gemm_plain(void* y, const void* x, const void* w, int M, int N, int K, long long ldx,
                        long long ldy, cudaStream_t stream) {
   dim3 grid((N + PG_BN - 1) / PG_BN, (M + PG_BM - 1) / PG_BM);
-  gemm_plain_kernel<TX, TW, TY><<<grid, 256, 0, stream>>>((TY*)y, (const TX*)x, (const TW*)w, M, N, K,
-                                                           ldx, ldy);
+  launch(gemm_plain_kernel<TX, TW, TY>, grid, dim3(256), 0, stream, (TY*)y, (const TX*)x, (const TW*)w, M, N, K, ldx, ldy);
 }
 
 }  // namespace lb

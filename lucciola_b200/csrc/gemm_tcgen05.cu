@@ -14,9 +14,12 @@
 //               shared-memory descriptors; tcgen05.commit frees the stage, and at the end signals
 //               the epilogue; this warp also allocates and frees tensor memory
 //   warps 2..5  epilogue: tcgen05.ld (32 lanes x 32 bit) of the accumulator, conversion, stores
-// K may be split over gridDim.z: each split writes 32-bit partials to a workspace; the CTA that
-// finishes last for a tile adds the partials in the order of the splits (so the result does not
-// depend on timing) and writes the output.
+// K may be split over gridDim.z.  With up to 8 splits the CTAs of a tile form a thread-block cluster:
+// each leaves its 32-bit partial tile in its own shared memory, and after a cluster barrier every CTA
+// adds, for its share of the tile's columns, the partials of all CTAs in the order of the splits,
+// reading its peers' shared memory directly (ld.shared::cluster).  With more splits (or when asked
+// to) the partials go through a workspace in global memory and the CTA that finishes last for a
+// tile adds them, again in the order of the splits.  Either way the result does not depend on timing.
 //
 // Every wait on an mbarrier is bounded: when a wait gives up the CTA records a code in a device
 // flag, stops, waits (bounded) for its loads in flight, frees its tensor memory and returns.
@@ -121,6 +124,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
       : "r"(taddr));
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 struct GemmParams {
   void* y;              // [M, N] output, row stride ldy
   float* workspace;     // [splits, M, N] partials (split-K only)
@@ -128,6 +142,8 @@ struct GemmParams {
   int M, N, K;
   long long ldy;
   int out_dtype;        // LB_F32 or LB_BF16
+  int cluster;          // > 0: the splits of a tile form a thread-block cluster of this size and add
+                        // their partials through distributed shared memory (no workspace, no counters)
 };
 
 template <int BT>
@@ -166,12 +182,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int kb_end = (int)((long long)kb_total * (split + 1) / splits);
   const int num_kb = kb_end - kb_begin;
 
+  pdl_trigger();
+  const int early = num_kb < STAGES ? num_kb : STAGES;
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // This thread is also the producer.  The weights do not depend on the kernel before this one:
+    // the first ring of weight tiles is requested at once, before the rest of the CTA is even set up.
+    for (int i = 0; i < early; ++i) {
+      mbar_expect_tx(full_bar(i), L::STAGE_BYTES);
+      tma_load_2d(smem_base + i * L::STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, full_bar(i));
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols<BT>()) : "memory");
@@ -186,9 +212,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---- producer --------------------------------------------------------------------------
     if (lane == 0) {
       int issued = 0;
-      for (int i = 0; i < num_kb; ++i) {
+      // The token tiles follow the early weight tiles when the kernel before this one has completed.
+      pdl_wait();
+      for (int i = 0; i < early; ++i)
+        tma_load_2d(smem_base + i * L::STAGE_BYTES + L::W_BYTES, &map_x, (kb_begin + i) * BK, m0, full_bar(i));
+      issued = early;
+      for (int i = early; i < num_kb; ++i) {
         const int s = i % STAGES;
-        const uint32_t parity = ((i / STAGES) & 1) ^ 1;          // a fresh barrier passes a wait on parity 1
+        const uint32_t parity = ((i / STAGES) & 1) ^ 1;          // the stage's earlier use has been consumed
         if (!mbar_wait(empty_bar(s), parity, abort_flag, ERR_EMPTY_WAIT)) break;
         mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
         const uint32_t dst = smem_base + s * L::STAGE_BYTES;
@@ -239,13 +270,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (ok) {
       const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
       const bool direct = splits == 1;
-      float* part = direct ? nullptr : p.workspace + (size_t)split * p.M * p.N;
+      const bool via_cluster = !direct && p.cluster > 0;
+      float* part = (direct || via_cluster) ? nullptr : p.workspace + (size_t)split * p.M * p.N;
+      float* part_smem = reinterpret_cast<float*>(smem);          // [BT][128]; the stages are drained by now
 #pragma unroll 1
       for (int c = 0; c < BT; c += 16) {
         uint32_t r[16];
         tmem_ld16(taddr + c, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (n < p.N) {
+        if (via_cluster) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) part_smem[(c + j) * BM + quarter * 32 + lane] = __uint_as_float(r[j]);
+        } else if (n < p.N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = m0 + c + j;
@@ -258,7 +294,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           }
         }
       }
-      if (!direct) {
+      if (!direct && !via_cluster) {
         // The CTA that arrives last for this tile adds the partials in the order of the splits.
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -272,11 +308,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (*last_flag) {
           __threadfence();
           if (n < p.N) {
-            for (int m = m0; m < min(m0 + BT, p.M); ++m) {
-              float acc = 0.f;
-              for (int z = 0; z < splits; ++z) acc += __ldcg(p.workspace + ((size_t)z * p.M + m) * p.N + n);
-              if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + n] = acc;
-              else ((bf16*)p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(acc);
+            // All partials of a few rows are requested before any is added (the loads are independent;
+            // the additions keep the order of the splits).
+            const int m_end = min(m0 + BT, p.M);
+            const size_t zstride = (size_t)p.M * p.N;
+            for (int m = m0; m < m_end; m += 4) {
+              float v[4][16];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float* src = p.workspace + (size_t)min(m + i, m_end - 1) * p.N + n;
+#pragma unroll
+                for (int z = 0; z < 16; ++z) v[i][z] = z < splits ? __ldcg(src + z * zstride) : 0.f;
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                if (m + i >= m_end) break;
+                float acc = 0.f;
+#pragma unroll
+                for (int z = 0; z < 16; ++z) acc += v[i][z];
+                if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)(m + i) * p.ldy + n] = acc;
+                else ((bf16*)p.y)[(size_t)(m + i) * p.ldy + n] = __float2bfloat16_rn(acc);
+              }
             }
           }
         }
@@ -285,6 +337,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (p.cluster > 0 && splits > 1) {
+    // Every thread of every CTA of the cluster passes both barriers, whatever happened before.
+    cluster_sync_all();                               // all partial tiles are in place
+    if (warp >= 2 && *abort_flag == 0) {
+      const int quarter = warp & 3;
+      const int nl = quarter * 32 + lane;
+      const int n = n0 + nl;
+      const int per = BT / p.cluster;                 // columns (tokens) of the tile this CTA adds up
+      const uint32_t base = smem_base + (uint32_t)nl * 4u;
+      if (n < p.N) {
+        for (int j = split * per; j < (split + 1) * per; ++j) {
+          const int m = m0 + j;
+          if (m >= p.M) break;
+          float acc = 0.f;
+          for (int z = 0; z < splits; ++z) acc += ld_cluster_f32(base + (uint32_t)j * (BM * 4u), (uint32_t)z);
+          if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + n] = acc;
+          else ((bf16*)p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(acc);
+        }
+      }
+    }
+    cluster_sync_all();                               // no CTA leaves while a peer still reads its memory
+  }
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols<BT>()) : "memory");
@@ -361,8 +435,34 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
     configured = true;
   }
   dim3 grid((p.N + BM - 1) / BM, (p.M + BT - 1) / BT, splits);
-  gemm_tcgen05_kernel<BT, STAGES><<<grid, 192, smem, stream>>>(mw, mx, p);
+  if (p.cluster > 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl_enabled ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BT, STAGES>, mw, mx, p);
+  } else {
+    launch(gemm_tcgen05_kernel<BT, STAGES>, grid, dim3(192), smem, stream, mw, mx, p);
+  }
   return 0;
+}
+
+// Stages per token tile: up to 128 tokens the ring is sized so that two CTAs share an SM (about 100 KB
+// each): the product is bound by memory there and a second CTA hides the first one's start and end.
+static int launch_for_tile(int bt, const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, int splits,
+                           cudaStream_t stream) {
+  switch (bt) {
+    case 16: return launch_tc<16, 6>(mw, mx, p, splits, stream);
+    case 32: return launch_tc<32, 5>(mw, mx, p, splits, stream);
+    case 64: return launch_tc<64, 4>(mw, mx, p, splits, stream);
+    case 128: return launch_tc<128, 3>(mw, mx, p, splits, stream);
+    default: return launch_tc<256, 4>(mw, mx, p, splits, stream);
+  }
 }
 
 }  // namespace lb
@@ -385,8 +485,8 @@ LB_EXPORT int lb_gemm_tcgen05_plan(int M, int N, int K, int* bt) {
   if (tiles < 148 && M <= 256) {       // splitting pays only while the weights are what is streamed
     splits = 296 / tiles;                // all CTAs in one wave of two per SM
     if (splits > kb / 4) splits = kb / 4;
-    if (splits > 16) splits = 16;
-    if (splits < 1) splits = 1;
+    // A power of two up to 8: the splits of a tile then form a cluster and add up through shared memory.
+    splits = splits >= 8 ? 8 : splits >= 4 ? 4 : splits >= 2 ? 2 : 1;
   }
   return splits;
 }
@@ -410,12 +510,15 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
                  "gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", force_bt);
     bt = force_bt;
   }
-  if (force_splits) splits = force_splits;
+  const bool workspace_path = force_splits < 0;
+  if (force_splits) splits = force_splits < 0 ? -force_splits : force_splits;
   const int kb = (K + lb::BK - 1) / lb::BK;
   if (splits > kb) splits = kb;
+  if (splits > 16) splits = 16;            // the reduction holds at most 16 partials of an element at a time
   const long long tiles = (long long)((N + lb::BM - 1) / lb::BM) * ((M + bt - 1) / bt);
-  if (splits > 1 && (workspace == nullptr || counters == nullptr || (long long)splits * M * N > workspace_elems ||
-                     tiles > counters_len))
+  const bool cluster_ok = !workspace_path && splits <= 8 && (splits & (splits - 1)) == 0 && bt % splits == 0;
+  if (splits > 1 && !cluster_ok && (workspace == nullptr || counters == nullptr || (long long)splits * M * N > workspace_elems ||
+                                    tiles > counters_len))
     splits = 1;
   LB_CHECK_ARG((M + bt - 1) / bt <= 65535 && splits <= 65535, "gemm_tcgen05: grid too large");
 
@@ -426,15 +529,10 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   }
   lb::GemmParams p;
   p.y = y; p.workspace = workspace; p.counters = counters; p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.out_dtype = y_dtype;
-  int rc = 0;
-  switch (bt) {
-    case 16: rc = lb::launch_tc<16, 6>(mw, mx, p, splits, stream); break;
-    case 32: rc = lb::launch_tc<32, 6>(mw, mx, p, splits, stream); break;
-    case 64: rc = lb::launch_tc<64, 6>(mw, mx, p, splits, stream); break;
-    case 128: rc = lb::launch_tc<128, 6>(mw, mx, p, splits, stream); break;
-    default: rc = lb::launch_tc<256, 4>(mw, mx, p, splits, stream); break;
-  }
-  if (rc) return rc;
+  // Clusters when the split count allows it and the caller did not ask for the workspace path
+  // (force_splits < 0 asks for -force_splits splits through the workspace).
+  p.cluster = (!workspace_path && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && bt % splits == 0) ? splits : 0;
+  if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
   LB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
 }
@@ -521,15 +619,8 @@ LB_EXPORT int lb_gemm_tcgen05_static_scratch(void* y, int y_dtype, const void* x
   }
   lb::GemmParams p;
   p.y = y; p.workspace = partials; p.counters = counters; p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.out_dtype = y_dtype;
-  int rc = 0;
-  switch (bt) {
-    case 16: rc = lb::launch_tc<16, 6>(mw, mx, p, splits, stream); break;
-    case 32: rc = lb::launch_tc<32, 6>(mw, mx, p, splits, stream); break;
-    case 64: rc = lb::launch_tc<64, 6>(mw, mx, p, splits, stream); break;
-    case 128: rc = lb::launch_tc<128, 6>(mw, mx, p, splits, stream); break;
-    default: rc = lb::launch_tc<256, 4>(mw, mx, p, splits, stream); break;
-  }
-  if (rc) return rc;
+  p.cluster = 0;                           // this entry point is the workspace path, with the workspace built in
+  if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
   LB_CHECK_LAUNCH("gemm_tcgen05_static_scratch");
   return 0;
 }

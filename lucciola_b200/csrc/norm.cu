@@ -19,6 +19,8 @@ __global__ void add_rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ res
                                    const TD* __restrict__ delta, const float* __restrict__ weight,
                                    const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   const int src = rows ? rows[i] : i;
   float* r = residual + (size_t)src * hidden;
@@ -70,11 +72,11 @@ LB_EXPORT int lb_add_rmsnorm(void* out, int out_dtype, float* residual, const vo
   LB_DISPATCH_DTYPE(delta_dtype, TD, {
     LB_DISPATCH_DTYPE(out_dtype, TO, {
       if (vec4)
-        lb::add_rmsnorm_kernel<TD, TO, 4><<<num_rows, threads, 0, stream>>>(
-            (TO*)out, residual, (const TD*)delta, weight, rows, hidden, eps);
+        lb::launch(lb::add_rmsnorm_kernel<TD, TO, 4>, dim3(num_rows), dim3(threads), 0, stream,
+                   (TO*)out, residual, (const TD*)delta, weight, rows, hidden, eps);
       else
-        lb::add_rmsnorm_kernel<TD, TO, 1><<<num_rows, threads, 0, stream>>>(
-            (TO*)out, residual, (const TD*)delta, weight, rows, hidden, eps);
+        lb::launch(lb::add_rmsnorm_kernel<TD, TO, 1>, dim3(num_rows), dim3(threads), 0, stream,
+                   (TO*)out, residual, (const TD*)delta, weight, rows, hidden, eps);
     })
   })
   LB_CHECK_LAUNCH("add_rmsnorm");

@@ -31,6 +31,8 @@ struct RopeKvParams {
 template <typename T>
 __global__ void rope_kv_kernel(RopeKvParams p) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int d = p.head_dim, half = p.rot_dim >> 1;
@@ -131,7 +133,7 @@ LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const vo
     int head_blocks = (total_heads + warps - 1) / warps;
     if (head_blocks > 65535) head_blocks = 65535;
     if (head_blocks < 1) head_blocks = 1;
-    lb::rope_kv_kernel<T><<<dim3(num_tokens, head_blocks), warps * 32, smem, stream>>>(p);
+    lb::launch(lb::rope_kv_kernel<T>, dim3(num_tokens, head_blocks), dim3(warps * 32), smem, stream, p);
   })
   LB_CHECK_LAUNCH("rope_kv");
   return 0;

@@ -32,6 +32,8 @@ __global__ void sample_kernel(int* __restrict__ tokens, const float* __restrict_
                               const int* __restrict__ counters, int vocab) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * vocab;
   const float temp = temperature ? temperature[r] : 0.f;
@@ -80,7 +82,7 @@ LB_EXPORT int lb_sample(int* tokens, const float* logits, const float* temperatu
   LB_CHECK_ARG(num_rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", num_rows, vocab);
   if (num_rows == 0) return 0;
   const int threads = vocab >= 8192 ? 1024 : (vocab >= 1024 ? 256 : 64);
-  lb::sample_kernel<<<num_rows, threads, 0, stream>>>(tokens, logits, temperature, keys, counters, vocab);
+  lb::launch(lb::sample_kernel, dim3(num_rows), dim3(threads), 0, stream, tokens, logits, temperature, keys, counters, vocab);
   LB_CHECK_LAUNCH("sample");
   return 0;
 }

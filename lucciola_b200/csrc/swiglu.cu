@@ -10,6 +10,8 @@ template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gate,
                               const T* __restrict__ up, long long in_stride, int inter,
                               long long total) {
+  pdl_trigger();
+  pdl_wait();
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long t = idx / inter;
@@ -24,6 +26,8 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gate,
 __global__ void swiglu_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gate,
                                      const bf16* __restrict__ up, long long in_stride, int inter,
                                      long long total8) {
+  pdl_trigger();
+  pdl_wait();
   const int per_row = inter >> 3;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
        idx += (long long)gridDim.x * blockDim.x) {
@@ -58,13 +62,13 @@ LB_EXPORT int lb_swiglu(int dtype, void* out, const void* gate, const void* up, 
   if (vec) {
     const long long total8 = total >> 3;
     const int blocks = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
-    lb::swiglu_bf16x8_kernel<<<blocks, 256, 0, stream>>>((lb::bf16*)out, (const lb::bf16*)gate,
-                                                         (const lb::bf16*)up, in_stride, inter, total8);
+    lb::launch(lb::swiglu_bf16x8_kernel, dim3(blocks), dim3(256), 0, stream, (lb::bf16*)out, (const lb::bf16*)gate,
+               (const lb::bf16*)up, in_stride, inter, total8);
   } else {
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     LB_DISPATCH_DTYPE(dtype, T, {
-      lb::swiglu_kernel<T><<<blocks, 256, 0, stream>>>((T*)out, (const T*)gate, (const T*)up, in_stride,
-                                                      inter, total);
+      lb::launch(lb::swiglu_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)out, (const T*)gate, (const T*)up,
+                 in_stride, inter, total);
     })
   }
   LB_CHECK_LAUNCH("swiglu");

@@ -284,6 +284,9 @@ def test_gemm_plain_is_true_32_bit(env):
 @pytest.mark.parametrize("M,N,K,bt,splits", [
     (16, 128, 64, 16, 1), (5, 100, 96, 0, 0), (1, 503, 96, 0, 0), (16, 128, 1024, 16, 4), (33, 384, 520, 64, 3),
     (128, 256, 512, 128, 1), (300, 1000, 776, 0, 0), (256, 384, 1024, 256, 1), (7, 1536, 2048, 0, 0), (70, 200, 4096, 0, 0),
+    # splits > 0: through a cluster when the count is a power of two up to 8; < 0: through the workspace
+    (16, 128, 1024, 16, -4), (9, 300, 2048, 16, 8), (40, 520, 1024, 64, 2), (100, 256, 4096, 128, 8), (64, 4096, 512, 64, -2),
+    (200, 384, 2048, 256, 4), (3, 130, 8192, 16, 16),
 ])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
