@@ -49,6 +49,7 @@ class _RequestCache:
     slot: int
     tables: list[list[int]]          # per group: page of each logical page index, NO_PAGE once released
     length: int = 0                  # tokens whose keys are (or are about to be) in the cache
+    version: int = 0                 # new, manager-wide unique number whenever a table changes (lets callers cache a converted copy)
 
 
 class CacheManager:
@@ -60,6 +61,7 @@ class CacheManager:
         self.num_slots = num_slots
         self._free_slots = list(range(num_slots - 1, -1, -1))
         self._requests: dict[Hashable, _RequestCache] = {}
+        self._versions = 0
 
     # ---- requests ------------------------------------------------------
     def has_request(self, rid: Hashable) -> bool:
@@ -75,7 +77,8 @@ class CacheManager:
         if not self._free_slots:
             raise PagePoolError("no free state slot")
         slot = self._free_slots.pop()
-        self._requests[rid] = _RequestCache(slot, [[] for _ in self.groups])
+        self._versions += 1
+        self._requests[rid] = _RequestCache(slot, [[] for _ in self.groups], version=self._versions)
         return slot
 
     def release(self, rid: Hashable) -> None:
@@ -113,6 +116,9 @@ class CacheManager:
         for g, n in enumerate(need):
             for _ in range(n):
                 rc.tables[g].append(self.pools[g].allocate())
+        if any(need):
+            self._versions += 1
+            rc.version = self._versions
         rc.length = new_length
         return True
 
@@ -137,6 +143,9 @@ class CacheManager:
                     self.pools[g].free(table[i])
                     table[i] = NO_PAGE
                     freed += 1
+        if freed:
+            self._versions += 1
+            rc.version = self._versions
         return freed
 
     # ---- views ---------------------------------------------------------
@@ -148,6 +157,9 @@ class CacheManager:
 
     def block_table(self, rid: Hashable, group: int) -> list[int]:
         return self._requests[rid].tables[group]
+
+    def version(self, rid: Hashable) -> int:
+        return self._requests[rid].version
 
     def num_requests(self) -> int:
         return len(self._requests)

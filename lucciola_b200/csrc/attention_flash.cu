@@ -41,6 +41,7 @@ struct FlashParams {
   float* part_o;                            // [tiles, nkv, splits, part_rows, d]
   float* part_ml;                           // [tiles, nkv, splits, part_rows, 2]
   int part_rows;                            // most query rows of any tile
+  int cluster;                              // > 0: the splits of a tile form a cluster of this size and combine through shared memory
   int num_q_heads, num_kv_heads, head_dim, group, page_size, page_shift, window, splits;   // page_shift: log2(page_size) or -1
   float scale_log2;                         // scale * log2(e)
 };
@@ -68,6 +69,17 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void fa_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float fa_ld_cluster(const float* local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }
 
 // Byte offset of 16-byte chunk `chunk` of row `row` in a tile whose rows hold DP bfloat16.
@@ -301,6 +313,10 @@ flash_attention_kernel(FlashParams p) {
       }
     }
     __syncthreads();
+    // With a cluster the merged (M, L, O) of this CTA stay in shared memory (in the value stages, free by
+    // now) for the combination across the cluster; otherwise they go straight out.
+    float* fin_o = reinterpret_cast<float*>(smem + FA_ROWS * DP * 2 + FA_STAGES * TILE_BYTES);    // [16][DP]
+    float* fin_ml = fin_o + 16 * DP;                                                               // [16][2]
     for (int r = 0; r < rows; ++r) {
       float M = -INFINITY;
 #pragma unroll
@@ -313,11 +329,14 @@ flash_attention_kernel(FlashParams p) {
         L += mml[(w * 16 + r) * 2 + 1] * wgt[w];
       }
       const int token = t0 + r / G, head = kvh * G + r % G;
+      if (p.cluster > 0 && tid == 0) { fin_ml[r * 2] = M; fin_ml[r * 2 + 1] = L; }
       for (int dim = tid; dim < d; dim += FA_THREADS) {
         float acc = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) acc += mo[(w * 16 + r) * DP + dim] * wgt[w];
-        if (p.splits == 1) {
+        if (p.cluster > 0) {
+          fin_o[r * DP + dim] = acc;
+        } else if (p.splits == 1) {
           p.out[((size_t)token * p.num_q_heads + head) * d + dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         } else {
           const size_t slot = (((size_t)blockIdx.x * p.num_kv_heads + kvh) * p.splits + split) * p.part_rows + r;
@@ -325,6 +344,29 @@ flash_attention_kernel(FlashParams p) {
           if (dim == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
         }
       }
+    }
+    if (p.cluster > 0) {
+      // Every CTA of the cluster combines its share of the head's dimensions over all splits, in their
+      // order, reading the peers' shared memory.
+      fa_cluster_sync();
+      const int per = (d + p.cluster - 1) / p.cluster;
+      for (int item = tid; item < rows * per; item += FA_THREADS) {
+        const int r = item / per, dim = split * per + item % per;
+        if (dim >= d) continue;
+        float M = -INFINITY;
+        for (int z = 0; z < p.splits; ++z) M = fmaxf(M, fa_ld_cluster(fin_ml + r * 2, z));
+        float L = 0.f, acc = 0.f;
+        for (int z = 0; z < p.splits; ++z) {
+          const float mz = fa_ld_cluster(fin_ml + r * 2, z);
+          if (mz == -INFINITY) continue;
+          const float wz = exp2f(mz - M);
+          L += fa_ld_cluster(fin_ml + r * 2 + 1, z) * wz;
+          acc += fa_ld_cluster(fin_o + r * DP + dim, z) * wz;
+        }
+        const int token = t0 + r / G, head = kvh * G + r % G;
+        p.out[((size_t)token * p.num_q_heads + head) * d + dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      }
+      fa_cluster_sync();                        // nobody leaves while a peer still reads its memory
     }
     return;
   }
@@ -409,13 +451,16 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   LB_CHECK_ARG(group <= lb::FA_ROWS, "attention_flash: %d query heads per kv head, at most %d", group, lb::FA_ROWS);
   LB_CHECK_ARG(head_dim >= 8 && head_dim <= 128 && head_dim % 8 == 0,
                "attention_flash: head_dim %d must be a multiple of 8 between 8 and 128", head_dim);
+  const bool force_workspace = splits < 0;     // a negative count asks for the path through the workspace
+  if (splits < 0) splits = -splits;
   LB_CHECK_ARG(page_size > 0 && max_pages > 0 && window >= 0 && splits >= 1 && splits <= 65535, "attention_flash: bad sizes");
   LB_CHECK_ARG(num_kv_heads <= 65535, "attention_flash: too many kv heads");
   LB_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) &&
                ((uintptr_t)out % 4 == 0), "attention_flash: operands must be 16-byte aligned");
   if (num_tiles == 0) return 0;
   LB_CHECK_ARG(part_rows >= group && part_rows <= lb::FA_ROWS, "attention_flash: rows of a tile must be in %d..%d, got %d", group, lb::FA_ROWS, part_rows);
-  LB_CHECK_ARG(splits == 1 || (workspace && workspace_elems >= lb_attention_flash_workspace(num_tiles, num_kv_heads, splits, part_rows, head_dim)),
+  const bool may_cluster = part_rows <= 16 && splits <= 8 && (splits & (splits - 1)) == 0 && !force_workspace;
+  LB_CHECK_ARG(splits == 1 || may_cluster || (workspace && workspace_elems >= lb_attention_flash_workspace(num_tiles, num_kv_heads, splits, part_rows, head_dim)),
                "attention_flash: the workspace is too small for %d splits", splits);
   lb::FlashParams p;
   p.q = (const lb::bf16*)q; p.out = (lb::bf16*)out; p.k_cache = (const lb::bf16*)k_cache; p.v_cache = (const lb::bf16*)v_cache;
@@ -432,6 +477,9 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   const int dp = head_dim <= 64 ? 64 : 128;
   const int smem = (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2;
   const bool keysplit = part_rows <= 16;      // no tile has more than 16 query rows: the warps share them
+  // Up to 8 splits (a power of two) of such tiles combine inside a thread-block cluster.
+  const bool clustered = keysplit && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && !force_workspace;
+  p.cluster = clustered ? splits : 0;
 #define LB_FLASH_LAUNCH(DP, KS)                                                                                 \
   do {                                                                                                          \
     static bool cfg = false;                                                                                    \
@@ -439,13 +487,25 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
       cudaFuncSetAttribute(lb::flash_attention_kernel<DP, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
       cfg = true;                                                                                               \
     }                                                                                                           \
-    lb::launch(lb::flash_attention_kernel<DP, KS>, grid, dim3(lb::FA_THREADS), smem, stream, p);                \
+    if (clustered) {                                                                                            \
+      cudaLaunchConfig_t cfg = {};                                                                              \
+      cfg.gridDim = grid; cfg.blockDim = dim3(lb::FA_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream; \
+      cudaLaunchAttribute attr[2];                                                                              \
+      attr[0].id = cudaLaunchAttributeClusterDimension;                                                         \
+      attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = splits;            \
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                          \
+      attr[1].val.programmaticStreamSerializationAllowed = 1;                                                   \
+      cfg.attrs = attr; cfg.numAttrs = lb::g_pdl_enabled ? 2 : 1;                                               \
+      cudaLaunchKernelEx(&cfg, lb::flash_attention_kernel<DP, KS>, p);                                          \
+    } else {                                                                                                    \
+      lb::launch(lb::flash_attention_kernel<DP, KS>, grid, dim3(lb::FA_THREADS), smem, stream, p);              \
+    }                                                                                                           \
   } while (0)
   if (dp == 64) { if (keysplit) LB_FLASH_LAUNCH(64, true); else LB_FLASH_LAUNCH(64, false); }
   else { if (keysplit) LB_FLASH_LAUNCH(128, true); else LB_FLASH_LAUNCH(128, false); }
 #undef LB_FLASH_LAUNCH
   LB_CHECK_LAUNCH("attention_flash");
-  if (splits > 1) {
+  if (splits > 1 && !clustered) {
     dim3 cgrid(num_tiles, num_kv_heads), cblock(32, 4);
     lb::launch(lb::flash_combine_kernel, cgrid, cblock, 0, stream, p);
     LB_CHECK_LAUNCH("attention_flash combine");

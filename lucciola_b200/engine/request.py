@@ -23,18 +23,26 @@ class Request:
     callback: Optional[Callable[[int, bool], None]] = None
     status: Status = Status.WAITING
     output: list[int] = field(default_factory=list)
+    all_tokens: list[int] = field(default_factory=list)     # prompt + output, kept as one list for slicing
     num_computed: int = 0              # tokens whose keys and values are in the cache
     finish_reason: Optional[str] = None
     preemptions: int = 0
     admitted_at: int = -1              # order of admission, for the choice of a victim
 
+    def __post_init__(self) -> None:
+        self.all_tokens = list(self.prompt) + list(self.output)
+
     @property
     def tokens(self) -> list[int]:
-        return self.prompt + self.output
+        return self.all_tokens
+
+    def append(self, token: int) -> None:
+        self.output.append(token)
+        self.all_tokens.append(token)
 
     @property
     def length(self) -> int:
-        return len(self.prompt) + len(self.output)
+        return len(self.all_tokens)
 
     @property
     def remaining(self) -> int:

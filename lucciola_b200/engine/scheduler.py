@@ -202,7 +202,7 @@ class Scheduler:
             if not s.sample:
                 continue
             tok = int(next(it))
-            r.output.append(tok)
+            r.append(tok)
             reason = None
             if tok in self.eos_token_ids and not r.params.ignore_eos:
                 reason = "stop"

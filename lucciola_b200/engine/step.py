@@ -94,6 +94,7 @@ class ModelRunner:
         self.steps_run = 0
         self.tokens_run = 0
         self.h2d_bytes = 0                 # bytes of step inputs copied from pinned host memory so far
+        self._table_rows: dict[tuple[Hashable, int], tuple[int, np.ndarray]] = {}
         self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._graph_inputs: dict[tuple[int, int], torch.Tensor] = {}
         self._graph_launches = 0           # kernels replayed from CUDA graphs so far
@@ -126,6 +127,8 @@ class ModelRunner:
         """The request ended (or is preempted): its pages and its slot go back."""
         if self.manager.has_request(rid):
             self.manager.release(rid)
+        for g in range(len(self.groups)):
+            self._table_rows.pop((rid, g), None)
 
     # ---- the step ----------------------------------------------------------
     def _staging_for(self, n: int) -> _Staging:
@@ -249,10 +252,15 @@ class ModelRunner:
                 e = entries[i]
                 tok[t:t + n] = token_arrays[i]
                 slots[i] = self.manager.slot(e.rid)
+                ver = self.manager.version(e.rid)
                 for g in range(G):
-                    bt = self.manager.block_table(e.rid, g)
-                    tables[g][i, :len(bt)] = bt
-                    tables[g][i, len(bt):] = NO_PAGE
+                    hit = self._table_rows.get((e.rid, g))
+                    if hit is None or hit[0] != ver:          # convert the list once per change, not once per step
+                        row = np.full(P, NO_PAGE, dtype=np.int32)
+                        bt = self.manager.block_table(e.rid, g)
+                        row[:len(bt)] = bt
+                        hit = self._table_rows[(e.rid, g)] = (ver, row)
+                    tables[g][i] = hit[1]
                 wanted_rows += [t + w for w in e.want]
             else:
                 tok[t] = 0

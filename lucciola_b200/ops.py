@@ -273,14 +273,19 @@ def attention_flash_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, hea
             and num_q_heads % num_kv_heads == 0 and num_q_heads // num_kv_heads <= 64)
 
 
-def attention_splits(num_tiles: int, num_kv_heads: int, max_span: int, slots: int = 296) -> int:
+def attention_splits(num_tiles: int, num_kv_heads: int, max_span: int, max_rows: int = 64, slots: int = 296) -> int:
     """Into how many key ranges a launch is cut.  `slots` is how many CTAs run at a time (two on each
-    of the 148 SMs).  Fewer CTAs than slots: as many ranges as still fit one wave.  More: the count
-    (up to 8) whose last wave is fullest.  A range has 256 keys at least."""
+    of the 148 SMs).  Fewer CTAs than slots: as many ranges as still fit one wave; for tiles of up to
+    16 query rows a count below 16 becomes a power of two, because up to 8 ranges of such tiles combine
+    inside a thread-block cluster instead of through a workspace and a second kernel.  More CTAs than
+    slots: the count (up to 8) whose last wave is fullest.  A range has 256 keys at least."""
     base = max(num_tiles * num_kv_heads, 1)
     cap = max(1, min(max_span // 256, 64))
     if base <= slots:
-        return max(1, min(slots // base, cap))
+        s = max(1, min(slots // base, cap))
+        if max_rows <= 16 and s < 16:
+            s = 8 if s >= 8 else 4 if s >= 4 else 2 if s >= 2 else 1
+        return s
     best, best_fill = 1, 0.0
     for s in range(1, min(cap, 8) + 1):
         waves = base * s / slots
@@ -293,21 +298,25 @@ def attention_splits(num_tiles: int, num_kv_heads: int, max_span: int, slots: in
 def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, max_rows: int,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-                    splits: int, stream: int) -> None:
-    """Tensor-core attention over pages.  tiles: int32 [n, 4] of (first token, tokens, request index, 0)."""
+                    splits: int, stream: int, force_workspace: bool = False) -> None:
+    """Tensor-core attention over pages.  tiles: int32 [n, 4] of (first token, tokens, request index, 0).
+    `force_workspace` sends the partial results of the splits through the workspace and the combining
+    kernel even where a cluster could combine them."""
     _check(q, "q", torch.bfloat16); _check(out, "attention output", torch.bfloat16)
     _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
     _check(positions, "positions", torch.int32); _check(block_table, "block table", torch.int32)
     _check(tiles, "tiles", torch.int32)
     n = tiles.shape[0]
     ws, ws_elems = None, 0
-    if splits > 1:
+    in_cluster = max_rows <= 16 and splits in (2, 4, 8) and not force_workspace
+    if splits > 1 and not in_cluster:
         ws_elems = n * num_kv_heads * splits * max_rows * (head_dim + 2)
         ws = _attention_workspace(q.device, ws_elems)
         ws_elems = ws.numel()
     _call("lb_attention_flash", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
           positions.data_ptr(), block_table.data_ptr(), tiles.data_ptr(), n, num_q_heads, num_kv_heads, head_dim,
-          page_size, block_table.shape[1], window, scale, splits, max_rows, _ptr(ws), ws_elems, stream)
+          page_size, block_table.shape[1], window, scale, -splits if force_workspace else splits, max_rows, _ptr(ws),
+          ws_elems, stream)
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
@@ -321,7 +330,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         tiles, max_rows = meta
         longest = step.plans.get("span_hint", step.max_context_len)      # a recorded step plans for a bucket of lengths
         span = min(longest, window + step.max_q_len) if window > 0 else longest
-        splits = attention_splits(tiles.shape[0], num_kv_heads, span)
+        splits = attention_splits(tiles.shape[0], num_kv_heads, span, max_rows)
         attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, max_rows,
                         num_q_heads, num_kv_heads, head_dim, page_size, window, scale, splits, stream)
     else:

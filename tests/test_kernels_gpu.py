@@ -167,6 +167,7 @@ def test_attention_plain(env, act, nq, nkv, d, ps, window, seqs):
 
 
 def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=None, k_scale=1.0, q=None, hook=None):
+    """splits < 0: that many key ranges, combined through the workspace even where a cluster could."""
     kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, torch.bfloat16)
     fill_pages(kc, vc, bt.cpu(), seqs, ps, k_scale=k_scale)
     if hook:
@@ -182,9 +183,10 @@ def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=Non
     tl = torch.tensor(tiles, dtype=torch.int32, device=dev)
     scale = scale if scale is not None else 1 / math.sqrt(d)
     out = torch.full_like(q, float("nan"))
-    sp = splits or ops.attention_splits(len(tiles), nkv, max(s + n for s, n in seqs))
-    ops.attention_flash(q, out, kc, vc, pos, bt, tl, min(64, max(n for _, n, _, _ in tiles) * G), nq, nkv, d, ps, window,
-                        scale, sp, st)
+    rows = min(64, max(n for _, n, _, _ in tiles) * G)
+    sp = abs(splits) if splits else ops.attention_splits(len(tiles), nkv, max(s + n for s, n in seqs), rows)
+    ops.attention_flash(q, out, kc, vc, pos, bt, tl, rows, nq, nkv, d, ps, window, scale, sp, st,
+                        force_workspace=bool(splits and splits < 0))
     ref = attention_reference(q, kc, vc, bt, pos.cpu(), seq.cpu(), nq, nkv, ps, window, scale)
     return out, ref
 
@@ -193,6 +195,10 @@ def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=Non
     (4, 2, 64, 16, 0, [(0, 5)], None),
     (8, 2, 128, 16, 0, [(0, 130), (37, 1), (0, 3)], None),
     (32, 8, 128, 16, 0, [(1000, 1), (17, 1), (2047, 1)], 8),
+    (32, 8, 128, 16, 0, [(1000, 1), (17, 1), (2047, 1)], -8),
+    (16, 8, 96, 16, 0, [(700, 1), (5, 1)], 4),
+    (8, 2, 128, 8, 0, [(3000, 1)], 24),
+    (4, 1, 64, 16, 100, [(500, 3), (90, 2)], 2),
     (6, 2, 48, 8, 0, [(5, 40), (63, 2)], None),
     (8, 1, 32, 8, 0, [(0, 100), (99, 1)], 2),
     (5, 5, 16, 16, 24, [(0, 33), (200, 7)], None),
@@ -223,7 +229,7 @@ def test_attention_flash_finds_a_far_key_among_hundreds(env):
             vc[page, kvh, slot] = 7.0
         marks["v"] = vc[page, :, slot].clone()
 
-    for splits in (1, 4, 7):
+    for splits in (1, 4, -4, 7):
         out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, 0, [(L - 1, 1)], splits, k_scale=0.05, q=q, hook=hook)
         assert rel(out.cpu(), ref) < 8e-3
         assert (out[0, 0].float() - 7.0).abs().max() < 0.1 and (out[0, 4].float() - 7.0).abs().max() < 0.1
