@@ -452,6 +452,226 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
   return 0;
 }
 
+// ---- many tokens: persistent CTAs, tokens on the lanes, two accumulators -----------------------------------
+// For more than 256 tokens the product is bound by the tensor cores, and the kernel is arranged for that:
+// one CTA per SM walks over output tiles of 128 tokens x 256 features; tokens sit on the 128 lanes of the
+// accumulator, so an epilogue thread holds one token's row and stores 16 consecutive features as whole
+// 16-byte words; tensor memory holds two accumulators (2 x 256 columns), so the epilogue of one tile runs
+// while the tensor cores work on the next.  Tiles are visited with the token tile running fastest, so that
+// CTAs working at the same time share weight tiles in L2.
+constexpr int PF_BM = 128;       // tokens of a tile (lanes)
+constexpr int PF_BN = 256;       // features of a tile (columns)
+constexpr int PF_STAGES = 4;
+
+struct PrefillSmem {
+  static constexpr int A_BYTES = PF_BM * BK * 2;
+  static constexpr int B_BYTES = PF_BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = PF_STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 2 * PF_STAGES + 4;
+  static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, GemmParams p,
+                            int m_tiles, int num_tiles, int vec_store) {
+  using L = PrefillSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (PF_STAGES + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (2 * PF_STAGES + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * PF_STAGES + 2 + b); };
+  uint32_t* tmem_slot = (uint32_t*)(smem + L::BAR_OFFSET + L::NUM_BARS * 8);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    for (int s = 0; s < PF_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- producer: one ring of stages across all tiles of this CTA -------------------------------------
+    if (lane == 0 && my_tiles > 0) {
+      long long it = 0;                       // stage uses so far
+      bool ok = true;
+      // The weights of the first tile do not depend on the kernel before this one.
+      const int first = blockIdx.x;
+      const int early = num_kb < PF_STAGES ? num_kb : PF_STAGES;
+      for (int i = 0; i < early; ++i) {
+        mbar_expect_tx(full_bar(i), L::STAGE_BYTES);
+        tma_load_2d(smem_base + i * L::STAGE_BYTES + L::A_BYTES, &map_w, i * BK, (first / m_tiles) * PF_BN, full_bar(i));
+      }
+      pdl_wait();
+      for (int i = 0; i < early; ++i)
+        tma_load_2d(smem_base + i * L::STAGE_BYTES, &map_x, i * BK, (first % m_tiles) * PF_BM, full_bar(i));
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        const int tile = blockIdx.x + t * gridDim.x;
+        const int m0 = (tile % m_tiles) * PF_BM, n0 = (tile / m_tiles) * PF_BN;
+        for (int kb = (t == 0 ? early : 0); kb < num_kb; ++kb) {
+          const long long use = (long long)t * num_kb + kb;
+          const int s = (int)(use % PF_STAGES);
+          const uint32_t parity = (uint32_t)((use / PF_STAGES) & 1) ^ 1u;
+          if (!mbar_wait(empty_bar(s), parity, abort_flag, ERR_EMPTY_WAIT)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+          const uint32_t dst = smem_base + s * L::STAGE_BYTES;
+          tma_load_2d(dst, &map_x, kb * BK, m0, full_bar(s));
+          tma_load_2d(dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+          it = use + 1;
+        }
+        if (t == 0 && it < early) it = early;
+      }
+      if (*abort_flag) {
+        for (long long u = it > PF_STAGES ? it - PF_STAGES : 0; u < it; ++u) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(full_bar((int)(u % PF_STAGES)), (uint32_t)((u / PF_STAGES) & 1)) &&
+                 (unsigned long long)(clock64() - t0) < WAIT_CYCLES / 8) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- tensor-core issue -----------------------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(PF_BN);
+      bool ok = true;
+      for (int t = 0; t < my_tiles && ok; ++t) {
+        const int b = t & 1;
+        // the epilogue has drained this accumulator (its use two tiles ago)
+        ok = mbar_wait(acc_empty(b), (uint32_t)((t >> 1) & 1) ^ 1u, abort_flag, ERR_ACCUM_WAIT);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem_base + (uint32_t)b * PF_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const long long use = (long long)t * num_kb + kb;
+          const int s = (int)(use % PF_STAGES);
+          ok = mbar_wait(full_bar(s), (uint32_t)((use / PF_STAGES) & 1), abort_flag, ERR_FULL_WAIT);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
+          const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + L::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) umma_f16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(empty_bar(s));
+        }
+        if (ok) umma_commit(acc_full(b));
+      }
+    }
+  } else {
+    // ---- epilogue: warp w reads lanes (w % 4) * 32 .. + 31, i.e. 32 tokens, 16 features at a time -------------
+    const int quarter = warp & 3;
+    bool ok = true;
+    for (int t = 0; t < my_tiles && ok; ++t) {
+      const int tile = blockIdx.x + t * gridDim.x;
+      const int m = (tile % m_tiles) * PF_BM + quarter * 32 + lane;
+      const int n0 = (tile / m_tiles) * PF_BN;
+      const int b = t & 1;
+      ok = mbar_wait(acc_full(b), (uint32_t)((t >> 1) & 1), abort_flag, ERR_ACCUM_WAIT);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * PF_BN;
+#pragma unroll 2
+      for (int c = 0; c < PF_BN; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int n = n0 + c;
+        if (m < p.M && n < p.N) {
+          if (vec_store && n + 16 <= p.N) {
+            if (p.out_dtype == LB_F32) {
+              float4* dst = reinterpret_cast<float4*>((float*)p.y + (size_t)m * p.ldy + n);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>((bf16*)p.y + (size_t)m * p.ldy + n);
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                w[j] = *reinterpret_cast<uint32_t*>(&v);
+              }
+              dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (n + j < p.N) {
+                const float v = __uint_as_float(r[j]);
+                if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + n + j] = v;
+                else ((bf16*)p.y)[(size_t)m * p.ldy + n + j] = __float2bfloat16_rn(v);
+              }
+            }
+          }
+        }
+      }
+      // this accumulator may be overwritten: one arrival per epilogue warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+static int launch_prefill(const void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
+                          long long ldy, cudaStream_t stream) {
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (num_sms <= 0) num_sms = 148;
+  }
+  CUtensorMap mx, mw;
+  if (!cached_map(&mx, x, M, K, ldx, PF_BM) || !cached_map(&mw, w, N, K, K, PF_BN)) {
+    set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);
+    return 3;
+  }
+  GemmParams p;
+  p.y = const_cast<void*>(y); p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = ldy;
+  p.out_dtype = y_dtype; p.cluster = 0;
+  const int m_tiles = (M + PF_BM - 1) / PF_BM, n_tiles = (N + PF_BN - 1) / PF_BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int el = y_dtype == LB_F32 ? 4 : 2;
+  const int vec_store = ((uintptr_t)y % 16 == 0) && ((ldy * el) % 16 == 0);
+  const int smem = PrefillSmem::TOTAL + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) { set_error("gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e)); return 2; }
+    configured = true;
+  }
+  const int grid = num_tiles < num_sms ? num_tiles : num_sms;
+  launch(gemm_tcgen05_prefill_kernel, dim3(grid), dim3(192), smem, stream, mx, mw, p, m_tiles, num_tiles, vec_store);
+  return 0;
+}
+
 // Stages per token tile: up to 128 tokens the ring is sized so that two CTAs share an SM (about 100 KB
 // each): the product is bound by memory there and a second CTA hides the first one's start and end.
 static int launch_for_tile(int bt, const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, int splits,
@@ -503,6 +723,11 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   LB_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0, "gemm_tcgen05: K=%d and the row stride %lld must be multiples of 8 (TMA strides are multiples of 16 bytes)", K, ldx);
   LB_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
   if (M == 0) return 0;
+  if (M > 256 && force_bt == 0 && force_splits == 0) {
+    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, stream)) return rc;
+    LB_CHECK_LAUNCH("gemm_tcgen05 (many tokens)");
+    return 0;
+  }
   int bt = 16;
   int splits = lb_gemm_tcgen05_plan(M, N, K, &bt);
   if (force_bt) {

@@ -281,6 +281,8 @@ def attention_splits(num_tiles: int, num_kv_heads: int, max_span: int, max_rows:
     slots: the count (up to 8) whose last wave is fullest.  A range has 256 keys at least."""
     base = max(num_tiles * num_kv_heads, 1)
     cap = max(1, min(max_span // 256, 64))
+    if max_rows > 16 and base >= slots // 2:
+        return 1         # portions of prompts fill the SMs by themselves; cutting them only adds partial results
     if base <= slots:
         s = max(1, min(slots // base, cap))
         if max_rows <= 16 and s < 16:

@@ -293,6 +293,8 @@ def test_gemm_plain_is_true_32_bit(env):
     # splits > 0: through a cluster when the count is a power of two up to 8; < 0: through the workspace
     (16, 128, 1024, 16, -4), (9, 300, 2048, 16, 8), (40, 520, 1024, 64, 2), (100, 256, 4096, 128, 8), (64, 4096, 512, 64, -2),
     (200, 384, 2048, 256, 4), (3, 130, 8192, 16, 16),
+    # more than 256 tokens: the persistent kernel (tokens on the lanes, two accumulators)
+    (2048, 512, 4096, 0, 0), (1000, 300, 136, 0, 0), (257, 6144, 64, 0, 0), (5000, 260, 520, 0, 0), (640, 1030, 1024, 0, 0),
 ])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
@@ -302,11 +304,13 @@ def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
     ops.gemm_tcgen05(y, x, w, st, bt, splits)
     torch.cuda.synchronize()
     assert ops.device_error() == 0
-    assert rel(y, x.double() @ w.double().t()) < (2e-6 if ty == torch.float32 else 5e-3)
+    # float32 out: what is left is the rounding of the 32-bit accumulation, which grows like sqrt(K)
+    tol = 2e-6 * max(1.0, math.sqrt(K / 256)) if ty == torch.float32 else 5e-3
+    assert rel(y, x.double() @ w.double().t()) < tol
     # a row-strided view of a wider matrix as input, as the q|k|v product's consumers use it
     wide = torch.randn(M, K + 64, device=dev).bfloat16()
     ops.gemm_tcgen05(y, wide[:, 32:32 + K] if (32 * 2) % 16 == 0 else wide[:, :K], w, st, bt, splits)
-    assert rel(y, wide[:, 32:32 + K].double() @ w.double().t()) < (2e-6 if ty == torch.float32 else 5e-3)
+    assert rel(y, wide[:, 32:32 + K].double() @ w.double().t()) < tol
 
 
 def test_gemm_tcgen05_refuses_what_it_cannot_do(env):
