@@ -401,32 +401,49 @@ flash_attention_kernel(FlashParams p) {
 }
 
 // Combines the partials of the splits, in their order: out = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M).
+// One warp per query row: the lanes first share the work of the weights 2^(m_z - M) (kept in shared
+// memory), then each lane adds up its dimensions over the splits, four independent loads at a time.
 __global__ void flash_combine_kernel(FlashParams p) {
+  extern __shared__ float wsm[];                      // [warps][splits]
   pdl_trigger();
   pdl_wait();
   const int4 tile = p.tiles[blockIdx.x];
   const int kvh = blockIdx.y;
   const int rows = tile.y * p.group, d = p.head_dim;
-  for (int r = threadIdx.y; r < rows; r += blockDim.y) {
-    const size_t base = ((size_t)blockIdx.x * p.num_kv_heads + kvh) * p.splits;
+  const int lane = threadIdx.x, warp = threadIdx.y, nwarps = blockDim.y;
+  float* wz = wsm + warp * p.splits;
+  const size_t base = ((size_t)blockIdx.x * p.num_kv_heads + kvh) * p.splits;
+  for (int r = warp; r < rows; r += nwarps) {
     float M = -INFINITY;
-    for (int z = 0; z < p.splits; ++z) M = fmaxf(M, p.part_ml[((base + z) * p.part_rows + r) * 2]);
+    for (int z = lane; z < p.splits; z += 32) M = fmaxf(M, p.part_ml[((base + z) * p.part_rows + r) * 2]);
+    M = warp_max(M);
     float L = 0.f;
-    for (int z = 0; z < p.splits; ++z) {
+    for (int z = lane; z < p.splits; z += 32) {
       const float mz = p.part_ml[((base + z) * p.part_rows + r) * 2];
-      if (mz != -INFINITY) L += p.part_ml[((base + z) * p.part_rows + r) * 2 + 1] * exp2f(mz - M);
+      const float w = mz == -INFINITY ? 0.f : exp2f(mz - M);
+      wz[z] = w;
+      L += p.part_ml[((base + z) * p.part_rows + r) * 2 + 1] * w;
     }
+    // Sum over the lanes in a fixed pattern; then every lane holds the same L.
+    L = warp_sum(L);
+    __syncwarp();
     const float inv = L > 0.f ? 1.f / L : 0.f;
     const int token = tile.x + r / p.group, head = kvh * p.group + r % p.group;
     bf16* dst = p.out + ((size_t)token * p.num_q_heads + head) * d;
-    for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
+    const size_t zstride = (size_t)p.part_rows * d;
+    for (int dim = lane; dim < d; dim += 32) {
+      const float* src = p.part_o + ((base * p.part_rows) + r) * d + dim;
       float acc = 0.f;
-      for (int z = 0; z < p.splits; ++z) {
-        const float mz = p.part_ml[((base + z) * p.part_rows + r) * 2];
-        if (mz != -INFINITY) acc += p.part_o[((base + z) * p.part_rows + r) * d + dim] * exp2f(mz - M);
+      int z = 0;
+      for (; z + 4 <= p.splits; z += 4) {
+        const float a0 = src[(size_t)z * zstride], a1 = src[(size_t)(z + 1) * zstride];
+        const float a2 = src[(size_t)(z + 2) * zstride], a3 = src[(size_t)(z + 3) * zstride];
+        acc += a0 * wz[z]; acc += a1 * wz[z + 1]; acc += a2 * wz[z + 2]; acc += a3 * wz[z + 3];
       }
+      for (; z < p.splits; ++z) acc += src[(size_t)z * zstride] * wz[z];
       dst[dim] = __float2bfloat16_rn(acc * inv);
     }
+    __syncwarp();
   }
 }
 
@@ -507,7 +524,7 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   LB_CHECK_LAUNCH("attention_flash");
   if (splits > 1 && !clustered) {
     dim3 cgrid(num_tiles, num_kv_heads), cblock(32, 4);
-    lb::launch(lb::flash_combine_kernel, cgrid, cblock, 0, stream, p);
+    lb::launch(lb::flash_combine_kernel, cgrid, cblock, (size_t)4 * splits * sizeof(float), stream, p);
     LB_CHECK_LAUNCH("attention_flash combine");
   }
   return 0;

@@ -14,6 +14,8 @@
 // Page layout of one cache layer: [page][kv_head][slot][d].
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace lb {
 
 struct RopeKvParams {
@@ -100,6 +102,73 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   }
 }
 
+// The same for bfloat16 heads of 64, 128 or 256 elements with the whole head rotated: a lane holds
+// VEC = d / 32 consecutive elements in registers (one 4-, 8- or 16-byte access), lanes 0..15 the first
+// half of the head and lanes 16..31 the second, so the partner of a pair is the lane 16 further on.
+template <int VEC>
+__global__ void rope_kv_vec_kernel(RopeKvParams p) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  constexpr int d = VEC * 32;
+  const int pos = p.positions[t];
+  const int total_heads = p.num_q_heads + 2 * p.num_kv_heads;
+  typedef typename std::conditional<VEC == 2, uint32_t, typename std::conditional<VEC == 4, uint2, uint4>::type>::type Word;
+  for (int h = blockIdx.y * nwarps + warp; h < total_heads; h += gridDim.y * nwarps) {
+    const int kind = h < p.num_q_heads ? 0 : (h < p.num_q_heads + p.num_kv_heads ? 1 : 2);
+    const int hh = kind == 0 ? h : (kind == 1 ? h - p.num_q_heads : h - p.num_q_heads - p.num_kv_heads);
+    const bf16* src = kind == 0 ? (const bf16*)p.q_in + (size_t)t * p.q_stride + (size_t)hh * d
+                    : kind == 1 ? (const bf16*)p.k_in + (size_t)t * p.k_stride + (size_t)hh * d
+                                : (const bf16*)p.v_in + (size_t)t * p.v_stride + (size_t)hh * d;
+    bf16* dst = nullptr;
+    if (kind == 0) {
+      dst = (bf16*)p.q_out + ((size_t)t * p.num_q_heads + hh) * d;
+    } else if (p.k_cache) {
+      const int seq = p.token_seq[t];
+      const int page = p.block_table[(size_t)seq * p.max_pages + pos / p.page_size];
+      if (page >= 0) {
+        bf16* pool = (bf16*)(kind == 1 ? p.k_cache : p.v_cache);
+        dst = pool + (((size_t)page * p.num_kv_heads + hh) * p.page_size + pos % p.page_size) * d;
+      }
+    } else {
+      bf16* o = (bf16*)(kind == 1 ? p.k_out : p.v_out);
+      if (o) dst = o + ((size_t)t * p.num_kv_heads + hh) * d;
+    }
+    if (dst == nullptr) continue;
+    Word raw = reinterpret_cast<const Word*>(src)[lane];
+    if (kind == 2) { reinterpret_cast<Word*>(dst)[lane] = raw; continue; }
+    const bf16* e = reinterpret_cast<const bf16*>(&raw);
+    float x[VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) { x[i] = __bfloat162float(e[i]); ss += x[i] * x[i]; }
+    const float* w = kind == 0 ? p.q_norm_w : p.k_norm_w;
+    if (w) {
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)d + p.eps);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) x[i] = x[i] * inv * w[lane * VEC + i];
+    }
+    if (p.inv_freq) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
+        const float angle = (float)pos * p.inv_freq[(lane & 15) * VEC + i];
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        // first half: x cos - y sin with y the partner; second half: x' sin + y' cos with x' the partner
+        x[i] = lane < 16 ? x[i] * cs - other * sn : other * sn + x[i] * cs;
+      }
+    }
+    Word outw;
+    bf16* o = reinterpret_cast<bf16*>(&outw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o[i] = __float2bfloat16_rn(x[i]);
+    reinterpret_cast<Word*>(dst)[lane] = outw;
+  }
+}
+
 }  // namespace lb
 
 LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const void* v_in,
@@ -128,6 +197,26 @@ LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const vo
   p.rot_dim = rot_dim; p.page_size = page_size; p.max_pages = max_pages; p.eps = eps;
   const int warps = 4;
   const size_t smem = (size_t)warps * head_dim * sizeof(float);
+  // The register version: bfloat16, heads of 64 / 128 / 256, whole head rotated, every row 16-byte aligned.
+  const int vec = head_dim / 32;
+  const size_t word = (size_t)vec * 2;
+  auto aligned = [&](const void* ptr, long long stride) { return ptr == nullptr || ((uintptr_t)ptr % word == 0 && (stride * 2) % (long long)word == 0); };
+  const bool fast = dtype == LB_BF16 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+                    (p.inv_freq == nullptr || rot_dim == head_dim) && aligned(q_in, q_stride) && aligned(k_in, k_stride) &&
+                    aligned(v_in, v_stride) && aligned(q_out, head_dim) && aligned(k_out, head_dim) && aligned(v_out, head_dim) &&
+                    aligned(k_cache, head_dim) && aligned(v_cache, head_dim);
+  if (fast) {
+    const int total_heads = num_q_heads + 2 * num_kv_heads;
+    int head_blocks = (total_heads + warps - 1) / warps;
+    if (head_blocks > 65535) head_blocks = 65535;
+    if (head_blocks < 1) head_blocks = 1;
+    dim3 grid(num_tokens, head_blocks);
+    if (vec == 2) lb::launch(lb::rope_kv_vec_kernel<2>, grid, dim3(warps * 32), 0, stream, p);
+    else if (vec == 4) lb::launch(lb::rope_kv_vec_kernel<4>, grid, dim3(warps * 32), 0, stream, p);
+    else lb::launch(lb::rope_kv_vec_kernel<8>, grid, dim3(warps * 32), 0, stream, p);
+    LB_CHECK_LAUNCH("rope_kv");
+    return 0;
+  }
   LB_DISPATCH_DTYPE(dtype, T, {
     const int total_heads = num_q_heads + 2 * num_kv_heads;
     int head_blocks = (total_heads + warps - 1) / warps;

@@ -87,7 +87,8 @@ def paged_setup(dev, seqs, nkv, d, ps, dtype, seed=0, fill=float("nan")):
 
 
 @pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nq,nkv,d,ps,theta", [(3, 1, 24, 4, 1e4), (8, 2, 64, 16, 5e5), (2, 2, 144, 32, 1e6)])
+@pytest.mark.parametrize("nq,nkv,d,ps,theta", [(3, 1, 24, 4, 1e4), (8, 2, 64, 16, 5e5), (2, 2, 144, 32, 1e6), (6, 3, 128, 16, 1e6),
+                                               (2, 1, 256, 8, 3e4)])
 def test_rope_kv(env, act, nq, nkv, d, ps, theta):
     ops, dev, st = env
     seqs = [(0, 7), (37, 1), (1021, 3)]
