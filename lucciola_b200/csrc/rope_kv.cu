@@ -206,9 +206,12 @@ LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const vo
                     aligned(v_in, v_stride) && aligned(q_out, head_dim) && aligned(k_out, head_dim) && aligned(v_out, head_dim) &&
                     aligned(k_cache, head_dim) && aligned(v_cache, head_dim);
   if (fast) {
+    // With few tokens every head gets a warp of its own; with many a warp walks over several heads,
+    // so that the grid stays near eight blocks per SM instead of tens of thousands of tiny ones.
     const int total_heads = num_q_heads + 2 * num_kv_heads;
     int head_blocks = (total_heads + warps - 1) / warps;
-    if (head_blocks > 65535) head_blocks = 65535;
+    const int wanted = (1184 + num_tokens - 1) / num_tokens;
+    if (head_blocks > wanted) head_blocks = wanted;
     if (head_blocks < 1) head_blocks = 1;
     dim3 grid(num_tokens, head_blocks);
     if (vec == 2) lb::launch(lb::rope_kv_vec_kernel<2>, grid, dim3(warps * 32), 0, stream, p);
