@@ -90,17 +90,22 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 }
 
 template <int DP, bool KEYSPLIT>
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(FA_THREADS, KEYSPLIT ? 2 : 3)
 flash_attention_kernel(FlashParams p) {
   constexpr int CHUNKS = DP / 8;                  // 16-byte chunks of a row
   constexpr int NB = KEYSPLIT ? 2 : FA_KEYS / 8;  // blocks of 8 keys a warp visits in a stage
   constexpr int LOADS = FA_KEYS * CHUNKS / FA_THREADS;      // 16-byte copies a thread makes per stage and matrix
   constexpr int ROW_STEP = FA_THREADS / CHUNKS;             // rows between two copies of one thread
   constexpr int TILE_BYTES = FA_KEYS * DP * 2;
+  // Decoded tokens: three stages, bound by memory.  Portions of prompts: two stages, and the query tile
+  // lies on the second stage's keys (it is in registers before that stage is first filled), so that a CTA
+  // needs 64 KB and three of them share an SM.
+  constexpr int STAGES = KEYSPLIT ? FA_STAGES : 2;
+  constexpr int Q_BYTES = KEYSPLIT ? FA_ROWS * DP * 2 : 0;
   extern __shared__ __align__(128) uint8_t smem[];
-  const uint32_t q_smem = (uint32_t)__cvta_generic_to_shared(smem);
-  const uint32_t k_smem = q_smem + FA_ROWS * DP * 2;
-  const uint32_t v_smem = k_smem + FA_STAGES * TILE_BYTES;
+  const uint32_t k_smem = (uint32_t)__cvta_generic_to_shared(smem) + Q_BYTES;
+  const uint32_t v_smem = k_smem + STAGES * TILE_BYTES;
+  const uint32_t q_smem = KEYSPLIT ? k_smem - Q_BYTES : k_smem + TILE_BYTES;
 
   pdl_trigger();
   pdl_wait();
@@ -140,7 +145,7 @@ flash_attention_kernel(FlashParams p) {
   const size_t head_off = (size_t)kvh * p.page_size * d + ld_chunk * 8;
   const size_t page_stride = (size_t)p.num_kv_heads * p.page_size * d;
   auto load_stage = [&](int stage_idx) {
-    const int buf = stage_idx % FA_STAGES;
+    const int buf = stage_idx % STAGES;
     const int kbase = kbeg + stage_idx * FA_KEYS + ld_row;
     int page[LOADS], slot[LOADS];
 #pragma unroll
@@ -161,7 +166,7 @@ flash_attention_kernel(FlashParams p) {
   };
 
 #pragma unroll
-  for (int s = 0; s < FA_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < num_stages) load_stage(s);
     cp_async_commit();
   }
@@ -178,7 +183,7 @@ flash_attention_kernel(FlashParams p) {
   }
   const bool warp_active = warp_row0 < rows;
 
-  cp_async_wait<FA_STAGES - 1>();     // Q has landed (the stage loads may still be in flight)
+  cp_async_wait<STAGES - 1>();        // Q has landed (the stage loads may still be in flight)
   __syncthreads();
   uint32_t qf[DP / 16][4];
   if (warp_active) {
@@ -196,13 +201,13 @@ flash_attention_kernel(FlashParams p) {
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
   for (int st = 0; st < num_stages; ++st) {
-    cp_async_wait<FA_STAGES - 2>();
+    cp_async_wait<STAGES - 2>();
     __syncthreads();                   // stage st is visible; the buffer of stage st-1 is free
-    if (st + FA_STAGES - 1 < num_stages) load_stage(st + FA_STAGES - 1);
+    if (st + STAGES - 1 < num_stages) load_stage(st + STAGES - 1);
     cp_async_commit();
     if (!warp_active) continue;
 
-    const int buf = st % FA_STAGES;
+    const int buf = st % STAGES;
     const uint32_t kb = k_smem + buf * TILE_BYTES, vb = v_smem + buf * TILE_BYTES;
     const int kbase = kbeg + st * FA_KEYS;
 
@@ -315,7 +320,7 @@ flash_attention_kernel(FlashParams p) {
     __syncthreads();
     // With a cluster the merged (M, L, O) of this CTA stay in shared memory (in the value stages, free by
     // now) for the combination across the cluster; otherwise they go straight out.
-    float* fin_o = reinterpret_cast<float*>(smem + FA_ROWS * DP * 2 + FA_STAGES * TILE_BYTES);    // [16][DP]
+    float* fin_o = reinterpret_cast<float*>(smem + FA_ROWS * DP * 2 + STAGES * TILE_BYTES);    // [16][DP]
     float* fin_ml = fin_o + 16 * DP;                                                               // [16][2]
     for (int r = 0; r < rows; ++r) {
       float M = -INFINITY;
@@ -492,7 +497,8 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   p.scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(num_tiles, num_kv_heads, splits);
   const int dp = head_dim <= 64 ? 64 : 128;
-  const int smem = (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2;
+  const int smem = part_rows <= 16 ? (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2   // query tile + 3 stages
+                                   : 2 * 2 * lb::FA_KEYS * dp * 2;                             // 2 stages, query tile aliased
   const bool keysplit = part_rows <= 16;      // no tile has more than 16 query rows: the warps share them
   // Up to 8 splits (a power of two) of such tiles combine inside a thread-block cluster.
   const bool clustered = keysplit && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && !force_workspace;

@@ -1,0 +1,97 @@
+"""The production kernel paths at the real layer sizes (hidden 4096, 32 query heads, 8 kv heads, head 128,
+intermediate 12288; two layers and a smaller vocabulary to stay quick): the bfloat16 engine against the
+float32 engine of the same weights, under different ways of cutting the work (GPU).
+
+The tiny models cannot reach these paths: the persistent tensor-core product for hundreds of tokens, split
+products in thread-block clusters, 64-row attention tiles of four query heads, decoded tokens whose key
+ranges are combined inside a cluster, CUDA graphs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+CFG = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "intermediate_size": 12288, "vocab_size": 20000, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096, "hidden_act": "silu", "attention_bias": False,
+}
+
+
+@pytest.fixture(scope="module")
+def runners():
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.load import build_runner_random
+    out = {}
+    for dtype in ("float32", "bfloat16"):
+        opts = EngineOptions(dtype=dtype, block_size=16, max_blocks=600, max_num_seqs=8, max_model_len=4096,
+                             max_tokens_per_step=4096)
+        out[dtype] = build_runner_random(CFG, seed=3, options=opts, std=0.02, norm_std=0.05)
+    # the same bfloat16 values in both: the float32 engine widens them exactly
+    a, b = out["float32"].model, out["bfloat16"].model
+    assert torch.equal(a.blocks[1].mixer.qkv.weight, b.blocks[1].mixer.qkv.weight.float())
+    return out
+
+
+def logits_of(runner, ids, cuts, tail=0):
+    """Feed `ids` in portions given by `cuts` (then `tail` tokens one by one); logits at every position."""
+    from lucciola_b200.engine.step import StepEntry
+    rows, pos = [], 0
+    for n in cuts:
+        rows.append(runner.step([StepEntry("r", ids[pos:pos + n], list(range(n)))]).float().cpu())
+        pos += n
+    for _ in range(tail):
+        rows.append(runner.step([StepEntry("r", [ids[pos]], [0])]).float().cpu().clone())
+        pos += 1
+    assert pos == len(ids)
+    runner.finish("r")
+    return torch.cat(rows)
+
+
+def test_bfloat16_engine_against_float32_engine_at_real_layer_sizes(runners):
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, CFG["vocab_size"], (700,), generator=g).tolist()
+    ref = logits_of(runners["float32"], ids, [700])
+    scale = ref.abs().max().item()
+    # float32: cutting changes nothing at all
+    again = logits_of(runners["float32"], ids, [300, 17, 200, 150], tail=33)
+    assert torch.equal(again, ref)
+    # bfloat16: whole, in portions (a portion of 2 tokens among them), and with a decoded tail that goes
+    # through recorded graphs; all within the bound of the tiny models' tests
+    for cuts, tail in (([700], 0), ([300, 17, 2, 198, 150], 33), ([640], 60)):
+        got = logits_of(runners["bfloat16"], ids, cuts, tail)
+        err = ((got - ref).abs().max() / scale).item()
+        assert torch.isfinite(got).all() and err < 3e-2, (cuts, tail, err)
+        agree = (got.argmax(-1) == ref.argmax(-1)).float().mean().item()
+        assert agree > 0.9, (cuts, tail, agree)
+    assert len(runners["bfloat16"]._graphs) > 0
+
+
+def test_mixed_batch_at_real_layer_sizes(runners):
+    """Four live requests: portions beside decoded tokens, long contexts beside short ones."""
+    from lucciola_b200.engine.step import StepEntry
+    g = torch.Generator().manual_seed(1)
+    lens = {"a": 900, "b": 130, "c": 517, "d": 40}
+    ids = {k: torch.randint(0, CFG["vocab_size"], (n,), generator=g).tolist() for k, n in lens.items()}
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        r = runners[dtype]
+        got = {}
+        r.step([StepEntry("a", ids["a"][:800], []), StepEntry("b", ids["b"][:100], [])])
+        steps = [
+            [("a", 800, 850), ("b", 100, 101), ("c", 0, 300)],
+            [("a", 850, 851), ("b", 101, 102), ("c", 300, 517), ("d", 0, 39)],
+            [("a", 851, 900), ("b", 102, 130), ("d", 39, 40)],
+        ]
+        for step in steps:
+            entries = [StepEntry(k, ids[k][s:e], list(range(e - s))) for k, s, e in step]
+            logits = r.step(entries).float().cpu()
+            o = 0
+            for k, s, e in step:
+                got[(k, s)] = logits[o:o + e - s]; o += e - s
+        for k in lens:
+            r.finish(k)
+        outs[dtype] = got
+    for key, ref in outs["float32"].items():
+        err = ((outs["bfloat16"][key] - ref).abs().max() / ref.abs().max()).item()
+        assert err < 3e-2, (key, err)
