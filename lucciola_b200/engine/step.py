@@ -26,6 +26,9 @@ from ..models.decoder import DecoderModel
 from ..parts.base import Runtime, StepContext
 
 
+# Entries with at least this many tokens in a step go to the tensor-memory attention kernel (128-row tiles).
+_BIG_PORTION = 16
+
 # Batch sizes for which decode-only steps are recorded as CUDA graphs; a batch is padded to the next one.
 _GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
@@ -161,13 +164,15 @@ class ModelRunner:
         return logits
 
     @staticmethod
-    def _tiles(q_lens: Sequence[int], group: int) -> list[tuple[int, int, int, int]]:
-        """Runs of up to 64 // group consecutive tokens of one request: (first token, tokens, request, 0)."""
-        per = 64 // group
+    def _tiles(q_lens: Sequence[int], group: int, rows: int = 64, take=None) -> list[tuple[int, int, int, int]]:
+        """Runs of up to rows // group consecutive tokens of one request: (first token, tokens, request, 0),
+        for the requests whose number of tokens passes `take`."""
+        per = rows // group
         tiles, t = [], 0
         for i, n in enumerate(q_lens):
-            for off in range(0, n, per):
-                tiles.append((t + off, min(per, n - off), i, 0))
+            if take is None or take(n):
+                for off in range(0, n, per):
+                    tiles.append((t + off, min(per, n - off), i, 0))
             t += n
         return tiles
 
@@ -226,7 +231,17 @@ class ModelRunner:
         S, T = len(q_lens), sum(q_lens)
         R = T if graph_key else sum(len(e.want) for e in entries)
         G, P = len(self.groups), self.max_pages_per_seq
-        tile_lists = {g: self._tiles(q_lens, g) for g in self.tile_groups}
+        # Work items of the attention kernels, per group size: "all" = every entry in tiles of up to 64 query
+        # rows; when the step holds portions of prompts, also "big" = those portions in tiles of up to 128 rows
+        # (for the tcgen05 kernel) and "rest" = the other entries in 64-row tiles.
+        tile_lists: dict[tuple[int, str], list] = {}
+        for g in self.tile_groups:
+            tile_lists[(g, "all")] = self._tiles(q_lens, g, 64)
+            if max(q_lens) >= _BIG_PORTION and 128 % g == 0:
+                tile_lists[(g, "big")] = self._tiles(q_lens, g, 128, lambda n: n >= _BIG_PORTION)
+                rest = self._tiles(q_lens, g, 64, lambda n: n < _BIG_PORTION)
+                if rest:
+                    tile_lists[(g, "rest")] = rest
         total = 3 * T + (S + 1) + 2 * S + R + G * S * P + sum(4 * len(t) + 3 for t in tile_lists.values())
         st = self._staging_for(total)
         hi, host = st.next_host()
@@ -240,7 +255,7 @@ class ModelRunner:
         tok, pos, seq = take(T), take(T), take(T)
         cu, ctx, slots, rows = take(S + 1), take(S), take(S), take(R)
         tables = [take(S * P).reshape(S, P) for _ in range(G)]
-        for g, tl in tile_lists.items():
+        for tl in tile_lists.values():
             o = (o + 3) & ~3                      # the kernel reads a tile as one 16-byte word
             take(4 * len(tl))[:] = np.asarray(tl, dtype=np.int32).reshape(-1)
         t = r = 0
@@ -292,10 +307,10 @@ class ModelRunner:
         d_tok, d_pos, d_seq = view(T), view(T), view(T)
         d_cu, d_ctx, d_slots, d_rows = view(S + 1), view(S), view(S), view(R)
         d_tables = [view(S * P).view(S, P) for _ in range(G)]
-        attn_meta = {}
-        for g, tl in tile_lists.items():
+        attn_meta: dict[int, dict] = {}
+        for (g, kind), tl in tile_lists.items():
             o = (o + 3) & ~3
-            attn_meta[g] = (view(4 * len(tl)).view(len(tl), 4), min(64, max(n for _, n, _, _ in tl) * g))
+            attn_meta.setdefault(g, {})[kind] = (view(4 * len(tl)).view(len(tl), 4), max(n for _, n, _, _ in tl) * g)
 
         step = StepContext(
             num_tokens=T, num_seqs=S, positions=d_pos, token_seq=d_seq, cu_tokens=d_cu, context_lens=d_ctx,

@@ -44,6 +44,8 @@ _SIGNATURES = {
                         c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
+    "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -240,7 +242,8 @@ def device_error() -> int:
     """Code that a kernel left when one of its bounded waits gave up (0: none).  Synchronises the device."""
     lib = library()
     lib.lb_device_error.restype = c_int
-    return int(lib.lb_device_error())
+    lib.lb_attention_tcgen05_device_error.restype = c_int
+    return int(lib.lb_device_error()) or int(lib.lb_attention_tcgen05_device_error())
 
 
 def linear(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, fast: bool) -> None:
@@ -321,20 +324,51 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
           ws_elems, stream)
 
 
+def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """The conditions of the tensor-memory attention kernel: bfloat16, head size 128, a group size that divides
+    128, pages of 8, 16, 32, 64 or 128 tokens."""
+    lib = library()
+    lib.lb_attention_tcgen05_ok.restype = c_int
+    return q.dtype == torch.bfloat16 and bool(lib.lb_attention_tcgen05_ok(num_q_heads, num_kv_heads, head_dim, page_size))
+
+
+def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, num_q_heads: int,
+                      num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, stream: int) -> None:
+    """Attention of portions of prompts on tcgen05 (S and O in tensor memory).  tiles: int32 [n, 4] of
+    (first token, tokens, request index, 0) with tokens * (nq / nkv) <= 128."""
+    _check(q, "q", torch.bfloat16); _check(out, "attention output", torch.bfloat16)
+    _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
+    _check(positions, "positions", torch.int32); _check(block_table, "block table", torch.int32)
+    _check(tiles, "tiles", torch.int32)
+    _call("lb_attention_tcgen05", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+          positions.data_ptr(), block_table.data_ptr(), tiles.data_ptr(), tiles.shape[0], q.shape[0], num_q_heads,
+          num_kv_heads, head_dim, page_size, k_cache.shape[0], block_table.shape[1], window, scale, stream)
+
+
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
               num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
               stream: int, fast: bool) -> None:
     """Causal attention of this step's queries over the pages of their requests.  `fast` allows the
-    tensor-core kernel where its conditions hold and the step carries tiles for this group size."""
+    tensor-core kernels where their conditions hold and the step carries tiles for this group size:
+    portions of prompts go to the tcgen05 kernel, the rest (decoded tokens, short portions, other head
+    sizes) to the mma.sync kernel; everything else to the plain kernel."""
     G = num_q_heads // num_kv_heads
     meta = step.attn_meta.get(G) if fast else None
-    if meta is not None and attention_flash_ok(q, num_q_heads, num_kv_heads, head_dim):
-        tiles, max_rows = meta
-        longest = step.plans.get("span_hint", step.max_context_len)      # a recorded step plans for a bucket of lengths
-        span = min(longest, window + step.max_q_len) if window > 0 else longest
-        splits = attention_splits(tiles.shape[0], num_kv_heads, span, max_rows)
-        attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, max_rows,
-                        num_q_heads, num_kv_heads, head_dim, page_size, window, scale, splits, stream)
-    else:
+    if meta is None or not attention_flash_ok(q, num_q_heads, num_kv_heads, head_dim):
         attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
                         num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
+        return
+    longest = step.plans.get("span_hint", step.max_context_len)      # a recorded step plans for a bucket of lengths
+    span = min(longest, window + step.max_q_len) if window > 0 else longest
+    kinds = ["all"]
+    if "big" in meta and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size):
+        attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"][0],
+                          num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
+        kinds = ["rest"] if "rest" in meta else []
+    for kind in kinds:
+        tiles, rows = meta[kind]
+        rows = min(rows, 64)
+        splits = attention_splits(tiles.shape[0], num_kv_heads, span, rows)
+        attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, rows,
+                        num_q_heads, num_kv_heads, head_dim, page_size, window, scale, splits, stream)

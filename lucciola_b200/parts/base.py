@@ -101,8 +101,10 @@ class StepContext:
     max_context_len: int = 0
     # Per step scratch that parts of the same kind may share (plans of the attention kernels).
     plans: dict = field(default_factory=dict)
-    # Work items of the tensor-core attention kernel, by query-group size G: (tiles int32 [n, 4] of
-    # (first token, tokens, request index, 0) on the device, most query rows of a tile).
+    # Work items of the tensor-core attention kernels, by query-group size G: a dict of kind ->
+    # (tiles int32 [n, 4] of (first token, tokens, request index, 0) on the device, most query rows of a tile).
+    # Kinds: "all" every entry in tiles of up to 64 rows; "big" the long portions in tiles of up to 128
+    # rows; "rest" what "big" leaves out, in 64-row tiles.
     attn_meta: dict = field(default_factory=dict)
 
 

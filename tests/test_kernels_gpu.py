@@ -214,6 +214,81 @@ def test_attention_flash(env, nq, nkv, d, ps, window, seqs, splits):
     assert rel(out.cpu(), ref) < 8e-3
 
 
+def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None):
+    """The tensor-memory kernel for portions of prompts (head size 128) against the float64 statement."""
+    d = 128
+    kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, torch.bfloat16)
+    fill_pages(kc, vc, bt.cpu(), seqs, ps)
+    if hook:
+        hook(kc, vc, bt.cpu())
+    T = pos.shape[0]
+    q = torch.randn(T, nq, d, device=dev).bfloat16() if q is None else q
+    per = 128 // (nq // nkv)
+    tiles, t = [], 0
+    for i, (_, n) in enumerate(seqs):
+        for off in range(0, n, per):
+            tiles.append((t + off, min(per, n - off), i, 0))
+        t += n
+    tl = torch.tensor(tiles, dtype=torch.int32, device=dev)
+    out = torch.full_like(q, float("nan"))
+    ops.attention_tcgen05(q, out, kc, vc, pos, bt, tl, nq, nkv, d, ps, window, 1 / math.sqrt(d), st)
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
+    ref = attention_reference(q, kc, vc, bt, pos.cpu(), seq.cpu(), nq, nkv, ps, window, 1 / math.sqrt(d))
+    return out, ref
+
+
+@pytest.mark.parametrize("nq,nkv,ps,window,seqs", [
+    (4, 1, 16, 0, [(0, 32)]),                       # one tile, one block, a quarter of the rows
+    (4, 1, 16, 0, [(0, 128)]),                      # several tiles, the diagonal block only
+    (32, 8, 16, 0, [(0, 300), (100, 17), (0, 1)]),  # the real head counts; a portion behind cached tokens; one token
+    (8, 8, 8, 0, [(50, 70)]),                       # no grouping, pages of 8
+    (4, 2, 32, 64, [(500, 100)]),                   # a window that leaves whole blocks and pages out
+    (2, 2, 128, 0, [(0, 130)]),                     # a page as large as a block
+    (16, 1, 64, 0, [(0, 40), (1000, 9)]),           # sixteen heads on one kv head; nine tokens after a thousand
+    (8, 2, 16, 200, [(0, 700)]),                    # a window inside a long portion
+])
+def test_attention_tcgen05(env, nq, nkv, ps, window, seqs):
+    ops, dev, st = env
+    out, ref = run_tc(ops, dev, st, nq, nkv, ps, window, seqs)
+    assert torch.isfinite(out).all()                # unused slots and freed pages hold NaN and must not reach a sum
+    assert rel(out.cpu(), ref) < 8e-3
+
+
+def test_attention_tcgen05_window_edge_and_far_key(env):
+    ops, dev, st = env
+    nq, nkv, ps = 8, 2, 16
+    for window in (16, 17, 128, 129):
+        pos_q = 400
+
+        def hook(kc, vc, bt):
+            j = pos_q - window                               # the last key that must NOT be seen by the query at pos_q
+            vc[int(bt[0, j // ps]), :, j % ps] = 1000.0
+
+        out, ref = run_tc(ops, dev, st, nq, nkv, ps, window, [(pos_q - 40, 41)], hook=hook)
+        assert rel(out.cpu(), ref) < 8e-3 and out[-1].float().abs().max() < 50
+    # one far key carries nearly all the weight of the last query
+    q = torch.randn(300, nq, 128, device=dev).bfloat16()
+
+    def far(kc, vc, bt):
+        for kvh in range(nkv):
+            kc[int(bt[0, 1]), kvh, 3] = (q[-1, kvh * 4].float() * 3).bfloat16()      # key 19
+            vc[int(bt[0, 1]), kvh, 3] = 7.0
+
+    out, ref = run_tc(ops, dev, st, nq, nkv, ps, 0, [(0, 300)], hook=far, q=q)
+    assert rel(out.cpu(), ref) < 8e-3 and (out[-1, 0].float() - 7.0).abs().max() < 0.2
+
+
+def test_attention_tcgen05_refuses_other_sizes(env):
+    ops, dev, st = env
+    q = torch.zeros(4, 4, 64, device=dev, dtype=torch.bfloat16)
+    assert not ops.attention_tcgen05_ok(q, 4, 2, 64, 16)           # head size
+    q = torch.zeros(4, 6, 128, device=dev, dtype=torch.bfloat16)
+    assert not ops.attention_tcgen05_ok(q, 6, 2, 128, 16)          # three heads per kv head do not divide 128
+    assert not ops.attention_tcgen05_ok(q, 6, 6, 128, 24)          # page size
+    assert ops.attention_tcgen05_ok(q, 6, 6, 128, 16)
+
+
 def test_attention_flash_finds_a_far_key_among_hundreds(env):
     """Random keys make every score alike, so a key that is skipped changes little.  Here one key far back
     (at a page's first slot, in another split than the query) is made to carry nearly all the weight."""

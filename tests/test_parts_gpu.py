@@ -56,7 +56,7 @@ def one_request_step(rt, T, page, nkv, d, start=0, window=0, group=None):
     if group and rt.fast_kernels:
         per = 64 // group
         tiles = [(o, min(per, T - o), 0, 0) for o in range(0, T, per)]
-        meta[group] = (torch.tensor(tiles, dtype=torch.int32, device=dev), min(64, max(t[1] for t in tiles) * group))
+        meta[group] = {"all": (torch.tensor(tiles, dtype=torch.int32, device=dev), max(t[1] for t in tiles) * group)}
     step = StepContext(num_tokens=T, num_seqs=1, positions=pos, token_seq=torch.zeros(T, dtype=torch.int32, device=dev),
                        cu_tokens=torch.tensor([0, T], dtype=torch.int32, device=dev),
                        context_lens=torch.tensor([L], dtype=torch.int32, device=dev), block_tables=[bt.to(dev)],
