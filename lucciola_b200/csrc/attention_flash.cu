@@ -262,7 +262,7 @@ flash_attention_kernel(FlashParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
-        pv[e] = exp2f(s[nb][e] * p.scale_log2 - m_use[h]);       // exp2(-inf) = 0 for masked keys
+        pv[e] = exp2_approx(fmaf(s[nb][e], p.scale_log2, -m_use[h]));   // 2^-inf = 0 for masked keys
         row_sum[h] += pv[e];
       }
       // C fragments of two key blocks become one A fragment of 16 keys

@@ -81,6 +81,24 @@ __device__ __forceinline__ bool ta_mbar_wait(uint32_t bar, uint32_t parity, vola
     }
   }
 }
+// The same for the single producer and issue threads: they sleep between polls, so that their spinning
+// does not take issue slots from the softmax warps that share their schedulers.
+__device__ __forceinline__ bool ta_mbar_wait_idle(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (ta_mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (unsigned it = 1;; ++it) {
+    __nanosleep(40);
+    if (ta_mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if ((unsigned long long)(clock64() - t0) > TA_WAIT_CYCLES) {
+        *abort_flag = code;
+        atomicCAS(&g_attention_tc_error, 0, code);
+        return false;
+      }
+    }
+  }
+}
 __device__ __forceinline__ void ta_tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
@@ -132,7 +150,9 @@ constexpr int TA_KV_STAGE = 2 * TA_TILE_BYTES;                 // K then V: 64 K
 constexpr int TA_P_OFF = TA_KV_OFF + 2 * TA_KV_STAGE;          // 160 KB
 constexpr int TA_BAR_OFF = TA_P_OFF + TA_TILE_BYTES;           // 192 KB
 constexpr int TA_NUM_BARS = 15;
-constexpr int TA_SMEM_BYTES = TA_BAR_OFF + TA_NUM_BARS * 8 + 16;
+constexpr int TA_MAX_TILE_PAGES = 4096;                        // pages a tile's keys may span (32 K keys of 8-token pages)
+constexpr int TA_PAGES_OFF = TA_BAR_OFF + TA_NUM_BARS * 8 + 16;
+constexpr int TA_SMEM_BYTES = TA_PAGES_OFF + TA_MAX_TILE_PAGES * 4;
 
 __global__ void __launch_bounds__(192, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -190,6 +210,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int kend = pos_last + 1;                // exclusive
   const int nblocks = (kend - kbeg + TA_KEYS - 1) / TA_KEYS;
   const int* bt = p.block_table + (size_t)seq * p.max_pages;
+  // The page ids of the keys this tile visits, copied once into shared memory for the producer.
+  int* spages = reinterpret_cast<int*>(smem + TA_PAGES_OFF);
+  const int first_page = kbeg >> p.page_shift;
+  const int num_tile_pages = min(((kend - 1) >> p.page_shift) - first_page + 1, TA_MAX_TILE_PAGES);
+  for (int i = threadIdx.x; i < num_tile_pages; i += blockDim.x) spages[i] = bt[first_page + i];
+  __syncthreads();
 
   if (warp == 0) {
     // ---- producer ----------------------------------------------------------------------------------------
@@ -201,18 +227,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const uint32_t page_bytes = (uint32_t)p.page_size * 128u;       // one half of one page
       for (int i = 0; i < nblocks; ++i) {
         const int s = i & 1;
-        if (!ta_mbar_wait(kv_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_KV_EMPTY)) break;
+        if (!ta_mbar_wait_idle(kv_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_KV_EMPTY)) break;
         const int kb = kbeg + i * TA_KEYS;
         // pages of this block that exist and hold keys the tile may see
         int first = 0, last = pages_per_block;        // [first, last) in pages of the block
         while (first < last && (kb + (first + 1) * p.page_size <= lo_tile)) ++first;
         while (last > first && (kb + (last - 1) * p.page_size >= kend)) --last;
+        const int* blk_pages = spages + ((kb - kbeg) >> p.page_shift);
         int npages = 0;
-        for (int pg = first; pg < last; ++pg) npages += bt[(kb >> p.page_shift) + pg] >= 0;
+        for (int pg = first; pg < last; ++pg) npages += blk_pages[pg] >= 0;
         ta_mbar_expect_tx(kv_full(s), (uint32_t)npages * page_bytes * 4u);
         const uint32_t kdst = sbase + TA_KV_OFF + s * TA_KV_STAGE, vdst = kdst + TA_TILE_BYTES;
         for (int pg = first; pg < last; ++pg) {
-          const int page = bt[(kb >> p.page_shift) + pg];
+          const int page = blk_pages[pg];
           if (page < 0) continue;
           const int y = (page * p.num_kv_heads + kvh) * p.page_size;
           const uint32_t off = (uint32_t)pg * page_bytes;
@@ -227,11 +254,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // ---- tensor-core issue ---------------------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ta_idesc(0), idesc_pv = ta_idesc(1);
-      bool ok = ta_mbar_wait(q_full, 0, abort_flag, TA_ERR_Q);
+      bool ok = ta_mbar_wait_idle(q_full, 0, abort_flag, TA_ERR_Q);
       auto issue_qk = [&](int i) -> bool {
         const int s = i & 1;
-        if (!ta_mbar_wait(kv_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL)) return false;
-        if (!ta_mbar_wait(s_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_S_EMPTY)) return false;
+        if (!ta_mbar_wait_idle(kv_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL)) return false;
+        if (!ta_mbar_wait_idle(s_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_S_EMPTY)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t qa = sbase + TA_Q_OFF, ka = sbase + TA_KV_OFF + s * TA_KV_STAGE;
 #pragma unroll
@@ -247,9 +274,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int s = i & 1;
         if (i + 1 < nblocks) { ok = issue_qk(i + 1); if (!ok) break; }
         // O_blk(i) = P(i) V(i)
-        ok = ta_mbar_wait(p_full, (uint32_t)(i & 1), abort_flag, TA_ERR_P_FULL);
+        ok = ta_mbar_wait_idle(p_full, (uint32_t)(i & 1), abort_flag, TA_ERR_P_FULL);
         if (!ok) break;
-        ok = ta_mbar_wait(o_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_O_EMPTY);
+        ok = ta_mbar_wait_idle(o_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_O_EMPTY);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t pa = sbase + TA_P_OFF, va = sbase + TA_KV_OFF + s * TA_KV_STAGE + TA_TILE_BYTES;
@@ -294,7 +321,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       return true;
     };
 
-    for (int i = 0; i < nblocks && ok; ++i) {
+    // Iteration i: the softmax of block i (if there is one), then the addition of block i-1's O_blk.
+    for (int i = 0; i <= nblocks && ok; ++i) {
+      float alpha = 1.f;
+      if (i < nblocks) do {
       const int s = i & 1;
       const int kb = kbeg + i * TA_KEYS;
       ok = ta_mbar_wait(s_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_S_FULL);
@@ -304,7 +334,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const uint32_t saddr = tmem + tlane + (uint32_t)s * 128u;
       // pass 1: the row's maximum
       float m_new = m_run;
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < TA_KEYS; c += 32) {
         uint32_t v[32];
         ta_tmem_ld32(saddr + (uint32_t)c, v);
@@ -316,14 +346,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
       }
       const float m_use = m_new == -INFINITY ? 0.f : m_new * p.scale_log2;
-      const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run * p.scale_log2 - m_use);
+      alpha = m_run == -INFINITY ? 0.f : exp2f(m_run * p.scale_log2 - m_use);
       m_run = m_new;
       // the P buffer is free once P V of the previous block has been read by the tensor cores
       if (i > 0) { ok = ta_mbar_wait(p_empty, (uint32_t)((i - 1) & 1), abort_flag, TA_ERR_P_EMPTY); if (!ok) break; }
       // pass 2: p = 2^(s * scale - m), the row's sum, P into shared memory (K-major, swizzled)
       float sum = 0.f;
       uint8_t* prow = smem + TA_P_OFF + r * 128;
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < TA_KEYS; c += 32) {
         uint32_t v[32];
         ta_tmem_ld32(saddr + (uint32_t)c, v);
@@ -336,7 +366,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (key > row_pos || key < row_lo) x0 = -INFINITY;
             if (key + 1 > row_pos || key + 1 < row_lo) x1 = -INFINITY;
           }
-          const float p0 = exp2f(x0 * p.scale_log2 - m_use), p1 = exp2f(x1 * p.scale_log2 - m_use);
+          const float p0 = exp2_approx(fmaf(x0, p.scale_log2, -m_use)), p1 = exp2_approx(fmaf(x1, p.scale_log2, -m_use));
           sum += p0 + p1;
           __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
           packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b);
@@ -351,16 +381,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       l_run = l_run * alpha + sum;
       // value rows the tile may not see hold whatever the page or the shared memory held: zero them
+      // (keys before the window's first key and keys past the last one; 16 threads a row)
       if ((kb < lo_tile) || (kb + TA_KEYS > kend)) {
         uint8_t* vb = smem + TA_KV_OFF + s * TA_KV_STAGE + TA_TILE_BYTES;
-        for (int key = 0; key < TA_KEYS; ++key) {
-          const int j = kb + key;
-          bool dead = j < lo_tile || j >= kend;
-          if (!dead) dead = bt[j >> p.page_shift] < 0;
-          if (dead) {                                        // 256 bytes of the row = 16 chunks, by 16 of this warp group's threads
-            const int t = (quarter * 32 + lane);
-            if (t < 16) *reinterpret_cast<uint4*>(vb + (t >> 3) * TA_HALF_BYTES + key * 128 + ((t & 7) << 4)) = make_uint4(0, 0, 0, 0);
-          }
+        const int head_rows = min(max(lo_tile - kb, 0), TA_KEYS), tail_from = min(max(kend - kb, 0), TA_KEYS);
+        const int chunk = r & 15;
+        for (int key = r >> 4; key < TA_KEYS; key += 8) {
+          if (key < head_rows || key >= tail_from)
+            *reinterpret_cast<uint4*>(vb + (chunk >> 3) * TA_HALF_BYTES + key * 128 + ((chunk & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
       // hand P (and the cleaned V) to the tensor cores, give the S buffer back
@@ -368,11 +396,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) { ta_mbar_arrive(p_full); ta_mbar_arrive(s_empty(s)); }
+      } while (0);
+      if (!ok) break;
       // add the previous block's O_blk while the tensor cores work on this one
       if (i > 0) ok = accumulate(i - 1, alpha_prev);
       alpha_prev = alpha;
     }
-    if (ok && nblocks > 0) ok = accumulate(nblocks - 1, alpha_prev);
     if (ok && r < rows) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const int token = t0 + r / G, head = kvh * G + r % G;
@@ -493,6 +522,7 @@ LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache
   LB_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)out % 16 == 0),
                "attention_tcgen05: operands must be 16-byte aligned");
   if (num_tiles == 0) return 0;
+  LB_CHECK_ARG(max_pages <= lb::TA_MAX_TILE_PAGES, "attention_tcgen05: a request may span %d pages, at most %d", max_pages, lb::TA_MAX_TILE_PAGES);
   const int group = num_q_heads / num_kv_heads;
   CUtensorMap mq, mk, mv;
   const long long pool_rows = (long long)num_pages * num_kv_heads * page_size;

@@ -235,10 +235,16 @@ class ModelRunner:
         # rows; when the step holds portions of prompts, also "big" = those portions in tiles of up to 128 rows
         # (for the tcgen05 kernel) and "rest" = the other entries in 64-row tiles.
         tile_lists: dict[tuple[int, str], list] = {}
+        first_token = [0] * S
+        for i in range(1, S):
+            first_token[i] = first_token[i - 1] + q_lens[i - 1]
         for g in self.tile_groups:
             tile_lists[(g, "all")] = self._tiles(q_lens, g, 64)
             if max(q_lens) >= _BIG_PORTION and 128 % g == 0:
-                tile_lists[(g, "big")] = self._tiles(q_lens, g, 128, lambda n: n >= _BIG_PORTION)
+                big = self._tiles(q_lens, g, 128, lambda n: n >= _BIG_PORTION)
+                # tiles that see the most keys first: the short ones then fill the end of the last wave
+                big.sort(key=lambda tl: -(starts[tl[2]] + (tl[0] - first_token[tl[2]]) + tl[1]))
+                tile_lists[(g, "big")] = big
                 rest = self._tiles(q_lens, g, 64, lambda n: n < _BIG_PORTION)
                 if rest:
                     tile_lists[(g, "rest")] = rest
