@@ -115,6 +115,13 @@ __global__ void rope_kv_vec_kernel(RopeKvParams p) {
   const int pos = p.positions[t];
   const int total_heads = p.num_q_heads + 2 * p.num_kv_heads;
   typedef typename std::conditional<VEC == 2, uint32_t, typename std::conditional<VEC == 4, uint2, uint4>::type>::type Word;
+  // The angles depend on the token and the lane only: one sine and cosine per element for all heads
+  // this warp walks over.
+  float cs[VEC], sn[VEC];
+  if (p.inv_freq) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sincosf((float)pos * p.inv_freq[(lane & 15) * VEC + i], &sn[i], &cs[i]);
+  }
   for (int h = blockIdx.y * nwarps + warp; h < total_heads; h += gridDim.y * nwarps) {
     const int kind = h < p.num_q_heads ? 0 : (h < p.num_q_heads + p.num_kv_heads ? 1 : 2);
     const int hh = kind == 0 ? h : (kind == 1 ? h - p.num_q_heads : h - p.num_q_heads - p.num_kv_heads);
@@ -154,11 +161,8 @@ __global__ void rope_kv_vec_kernel(RopeKvParams p) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
         const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
-        const float angle = (float)pos * p.inv_freq[(lane & 15) * VEC + i];
-        float sn, cs;
-        sincosf(angle, &sn, &cs);
         // first half: x cos - y sin with y the partner; second half: x' sin + y' cos with x' the partner
-        x[i] = lane < 16 ? x[i] * cs - other * sn : other * sn + x[i] * cs;
+        x[i] = lane < 16 ? x[i] * cs[i] - other * sn[i] : other * sn[i] + x[i] * cs[i];
       }
     }
     Word outw;
