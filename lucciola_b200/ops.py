@@ -324,12 +324,14 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
           ws_elems, stream)
 
 
-def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                         max_pages: int = 0) -> bool:
     """The conditions of the tensor-memory attention kernel: bfloat16, head size 128, a group size that divides
-    128, pages of 8, 16, 32, 64 or 128 tokens."""
+    128, pages of 8, 16, 32, 64 or 128 tokens, at most 4096 pages a request."""
     lib = library()
     lib.lb_attention_tcgen05_ok.restype = c_int
-    return q.dtype == torch.bfloat16 and bool(lib.lb_attention_tcgen05_ok(num_q_heads, num_kv_heads, head_dim, page_size))
+    return (q.dtype == torch.bfloat16 and max_pages <= 4096
+            and bool(lib.lb_attention_tcgen05_ok(num_q_heads, num_kv_heads, head_dim, page_size)))
 
 
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -362,7 +364,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     longest = step.plans.get("span_hint", step.max_context_len)      # a recorded step plans for a bucket of lengths
     span = min(longest, window + step.max_q_len) if window > 0 else longest
     kinds = ["all"]
-    if "big" in meta and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size):
+    if "big" in meta and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size,
+                                              step.block_tables[group].shape[1]):
         attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"][0],
                           num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
         kinds = ["rest"] if "rest" in meta else []

@@ -16,7 +16,7 @@ def pytest_configure(config):
 
 
 # Three tiny configurations of the architecture that differ in every size and option.
-# A and B are the two tiny workloads of the baseline description; C adds sliding layers.
+# A and B have the sizes of the two tiny Qwen3 workloads this engine is specified on; C adds sliding layers.
 TINY_A = {
     "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
     "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,

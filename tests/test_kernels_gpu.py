@@ -200,6 +200,9 @@ def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=Non
     (16, 8, 96, 16, 0, [(700, 1), (5, 1)], 4),
     (8, 2, 128, 8, 0, [(3000, 1)], 24),
     (4, 1, 64, 16, 100, [(500, 3), (90, 2)], 2),
+    (8, 2, 128, 8, 77, [(1000, 1), (30, 1), (76, 1), (77, 1)], 4),      # a window that starts inside a page and a stage
+    (32, 8, 128, 64, 0, [(63, 1), (64, 1), (65, 1), (700, 1)], None),   # a page as large as a stage
+    (4, 4, 64, 32, 0, [(3999, 1)], 16),
     (6, 2, 48, 8, 0, [(5, 40), (63, 2)], None),
     (8, 1, 32, 8, 0, [(0, 100), (99, 1)], 2),
     (5, 5, 16, 16, 24, [(0, 33), (200, 7)], None),
