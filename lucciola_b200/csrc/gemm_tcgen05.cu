@@ -144,7 +144,11 @@ struct GemmParams {
   int out_dtype;        // LB_F32 or LB_BF16
   int cluster;          // > 0: the splits of a tile form a thread-block cluster of this size and add
                         // their partials through distributed shared memory (no workspace, no counters)
+  int swiglu;           // 1: the weight rows alternate in blocks of 64 between "gate" and "up" rows of the same 64
+                        // features; the output has N/2 columns and holds silu(gate) * up (computed in 32-bit)
 };
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
 
 template <int BT>
 __host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
@@ -270,7 +274,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (ok) {
       const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
       const bool direct = splits == 1;
-      const bool via_cluster = !direct && p.cluster > 0;
+      const bool via_cluster = (!direct && p.cluster > 0) || (direct && p.swiglu);   // the tile goes to shared memory first
       float* part = (direct || via_cluster) ? nullptr : p.workspace + (size_t)split * p.M * p.N;
       float* part_smem = reinterpret_cast<float*>(smem);          // [BT][128]; the stages are drained by now
 #pragma unroll 1
@@ -291,6 +295,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
               else if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + n] = v;
               else ((bf16*)p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(v);
             }
+          }
+        }
+      }
+      if (direct && p.swiglu) {
+        // gate and up of a feature sit 64 lanes apart: pair them through shared memory
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int t = threadIdx.x - 64, f = t & 63;
+        const int feature = (n0 >> 1) + f;
+        if (feature < (p.N >> 1)) {
+          for (int j = t >> 6; j < BT && m0 + j < p.M; j += 2) {
+            const float v = silu_mul(part_smem[j * BM + f], part_smem[j * BM + f + 64]);
+            if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)(m0 + j) * p.ldy + feature] = v;
+            else ((bf16*)p.y)[(size_t)(m0 + j) * p.ldy + feature] = __float2bfloat16_rn(v);
           }
         }
       }
@@ -346,7 +363,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int n = n0 + nl;
       const int per = BT / p.cluster;                 // columns (tokens) of the tile this CTA adds up
       const uint32_t base = smem_base + (uint32_t)nl * 4u;
-      if (n < p.N) {
+      if (p.swiglu) {
+        const int f = nl & 63, feature = (n0 >> 1) + f;
+        if (feature < (p.N >> 1)) {
+          for (int j = split * per + (nl >> 6); j < (split + 1) * per; j += 2) {
+            const int m = m0 + j;
+            if (m >= p.M) break;
+            float g = 0.f, u = 0.f;
+            const uint32_t a = smem_base + (uint32_t)j * (BM * 4u) + (uint32_t)f * 4u;
+            for (int z = 0; z < splits; ++z) { g += ld_cluster_f32(a, (uint32_t)z); u += ld_cluster_f32(a + 256u, (uint32_t)z); }
+            const float v = silu_mul(g, u);
+            if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + feature] = v;
+            else ((bf16*)p.y)[(size_t)m * p.ldy + feature] = __float2bfloat16_rn(v);
+          }
+        }
+      } else if (n < p.N) {
         for (int j = split * per; j < (split + 1) * per; ++j) {
           const int m = m0 + j;
           if (m >= p.M) break;
@@ -589,6 +620,48 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * PF_BN;
+      if (p.swiglu) {
+        // columns [128b, 128b+64) are gate rows, [128b+64, 128b+128) the up rows of the same 64 features
+#pragma unroll 1
+        for (int cc = 0; cc < PF_BN / 2; cc += 16) {
+          const int c = (cc >> 6) * 128 + (cc & 63);
+          uint32_t g[16], u[16];
+          tmem_ld16(taddr + c, g);
+          tmem_ld16(taddr + c + 64, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const int feature = (n0 >> 1) + cc;
+          if (m < p.M && feature < (p.N >> 1)) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+            if (vec_store && feature + 16 <= (p.N >> 1)) {
+              if (p.out_dtype == LB_F32) {
+                float4* dst = reinterpret_cast<float4*>((float*)p.y + (size_t)m * p.ldy + feature);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              } else {
+                uint4* dst = reinterpret_cast<uint4*>((bf16*)p.y + (size_t)m * p.ldy + feature);
+                uint32_t w[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  __nv_bfloat162 b2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                  w[j] = *reinterpret_cast<uint32_t*>(&b2);
+                }
+                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (feature + j < (p.N >> 1)) {
+                  if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + feature + j] = v[j];
+                  else ((bf16*)p.y)[(size_t)m * p.ldy + feature + j] = __float2bfloat16_rn(v[j]);
+                }
+              }
+            }
+          }
+        }
+      } else
 #pragma unroll 2
       for (int c = 0; c < PF_BN; c += 16) {
         uint32_t r[16];
@@ -640,7 +713,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
 }
 
 static int launch_prefill(const void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
-                          long long ldy, cudaStream_t stream) {
+                          long long ldy, int swiglu, cudaStream_t stream) {
   static int num_sms = 0;
   if (num_sms == 0) {
     int dev = 0;
@@ -655,7 +728,7 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
   }
   GemmParams p;
   p.y = const_cast<void*>(y); p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = ldy;
-  p.out_dtype = y_dtype; p.cluster = 0;
+  p.out_dtype = y_dtype; p.cluster = 0; p.swiglu = swiglu;
   const int m_tiles = (M + PF_BM - 1) / PF_BM, n_tiles = (N + PF_BN - 1) / PF_BN;
   const int num_tiles = m_tiles * n_tiles;
   const int el = y_dtype == LB_F32 ? 4 : 2;
@@ -717,14 +790,15 @@ LB_EXPORT int lb_gemm_tcgen05_plan(int M, int N, int K, int* bt) {
 // force_bt / force_splits (0: choose) are for tests.
 LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
                               long long ldy, float* workspace, long long workspace_elems, int* counters,
-                              int counters_len, int force_bt, int force_splits, cudaStream_t stream) {
+                              int counters_len, int force_bt, int force_splits, int swiglu, cudaStream_t stream) {
   LB_CHECK_ARG(lb::valid_dtype(y_dtype), "gemm_tcgen05: bad output dtype %d", y_dtype);
-  LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && ldx >= K && ldy >= N, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+  LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && ldx >= K && ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+  LB_CHECK_ARG(!swiglu || N % 128 == 0, "gemm_tcgen05: the fused SwiGLU needs gate and up rows in blocks of 64 (N=%d is no multiple of 128)", N);
   LB_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0, "gemm_tcgen05: K=%d and the row stride %lld must be multiples of 8 (TMA strides are multiples of 16 bytes)", K, ldx);
   LB_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
   if (M == 0) return 0;
   if (M > 256 && force_bt == 0 && force_splits == 0) {
-    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, stream)) return rc;
+    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, stream)) return rc;
     LB_CHECK_LAUNCH("gemm_tcgen05 (many tokens)");
     return 0;
   }
@@ -742,6 +816,7 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   if (splits > 16) splits = 16;            // the reduction holds at most 16 partials of an element at a time
   const long long tiles = (long long)((N + lb::BM - 1) / lb::BM) * ((M + bt - 1) / bt);
   const bool cluster_ok = !workspace_path && splits <= 8 && (splits & (splits - 1)) == 0 && bt % splits == 0;
+  if (swiglu && splits > 1 && !cluster_ok) splits = 1;       // the pairing of gate and up is done in shared memory
   if (splits > 1 && !cluster_ok && (workspace == nullptr || counters == nullptr || (long long)splits * M * N > workspace_elems ||
                                     tiles > counters_len))
     splits = 1;
@@ -757,6 +832,7 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   // Clusters when the split count allows it and the caller did not ask for the workspace path
   // (force_splits < 0 asks for -force_splits splits through the workspace).
   p.cluster = (!workspace_path && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && bt % splits == 0) ? splits : 0;
+  p.swiglu = swiglu;
   if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
   LB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
@@ -845,6 +921,7 @@ LB_EXPORT int lb_gemm_tcgen05_static_scratch(void* y, int y_dtype, const void* x
   lb::GemmParams p;
   p.y = y; p.workspace = partials; p.counters = counters; p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.out_dtype = y_dtype;
   p.cluster = 0;                           // this entry point is the workspace path, with the workspace built in
+  p.swiglu = 0;
   if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
   LB_CHECK_LAUNCH("gemm_tcgen05_static_scratch");
   return 0;

@@ -41,7 +41,7 @@ _SIGNATURES = {
     "lb_gemm_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
                       c_longlong, c_void_p],
     "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
-                        c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
+                        c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -217,18 +217,30 @@ def gemm_tcgen05_ok(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, force_bt: int = 0,
-                 force_splits: int = 0) -> None:
-    """y[M, N] = x[M, K] . w[N, K]^T on the tensor cores (tcgen05, accumulators in tensor memory)."""
+                 force_splits: int = 0, swiglu: bool = False) -> None:
+    """y[M, N] = x[M, K] . w[N, K]^T on the tensor cores (tcgen05, accumulators in tensor memory).
+
+    With `swiglu` the rows of w alternate in blocks of 64 between gate rows and up rows of the same 64
+    features (see interleave_gate_up), and y[M, N/2] = silu(x . gate^T) * (x . up^T), formed in the epilogue."""
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or tuple(y.shape) != (M, N):
+    if w.shape[1] != K or tuple(y.shape) != (M, N // 2 if swiglu else N):
         raise KernelError(f"gemm shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     if not gemm_tcgen05_ok(y, x, w):
         raise KernelError("gemm_tcgen05 takes bfloat16 operands with K a multiple of 8, 16-byte aligned, unit column stride")
     ws, counters = _gemm_scratch(x.device)
     _call("lb_gemm_tcgen05", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), w.data_ptr(), M, N, K,
-          x.stride(0) if M > 1 else K, y.stride(0) if M > 1 else N, ws.data_ptr(), ws.numel(), counters.data_ptr(),
-          counters.numel(), force_bt, force_splits, stream)
+          x.stride(0) if M > 1 else K, y.stride(0) if M > 1 else y.shape[1], ws.data_ptr(), ws.numel(), counters.data_ptr(),
+          counters.numel(), force_bt, force_splits, 1 if swiglu else 0, stream)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[gate rows 0..63 | up rows 0..63 | gate rows 64..127 | up rows 64..127 | ...]: the row order the
+    fused SwiGLU epilogue of gemm_tcgen05 expects.  The number of rows must be a multiple of 64."""
+    I, K = gate.shape
+    if up.shape != gate.shape or I % 64:
+        raise KernelError(f"gate and up must have the same shape with a multiple of 64 rows, got {tuple(gate.shape)}, {tuple(up.shape)}")
+    return torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
 def launch_count() -> int:

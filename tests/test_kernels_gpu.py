@@ -392,6 +392,24 @@ def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
     assert rel(y, wide[:, 32:32 + K].double() @ w.double().t()) < tol
 
 
+@pytest.mark.parametrize("M,I,K,bt,splits", [(5, 128, 96, 0, 0), (16, 256, 1024, 16, 4), (40, 640, 512, 64, 1), (8, 12288, 512, 0, 0),
+                                             (64, 192, 2048, 0, 0), (300, 320, 264, 0, 0), (2048, 1024, 256, 0, 0), (700, 64, 4096, 0, 0)])
+@pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_with_swiglu_epilogue(env, M, I, K, bt, splits, ty):
+    """gate and up rows interleaved in blocks of 64; the product's epilogue forms silu(gate) * up."""
+    ops, dev, st = env
+    x = torch.randn(M, K, device=dev).bfloat16()
+    gate, up = (torch.randn(I, K, device=dev) * 0.1).bfloat16(), (torch.randn(I, K, device=dev) * 0.1).bfloat16()
+    w = ops.interleave_gate_up(gate, up)
+    assert torch.equal(w[:64], gate[:64]) and torch.equal(w[64:128], up[:64])
+    y = torch.full((M, I), float("nan"), device=dev, dtype=ty)
+    ops.gemm_tcgen05(y, x, w, st, bt, splits, swiglu=True)
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
+    want = plain.swiglu(x.double() @ gate.double().t(), x.double() @ up.double().t())
+    assert rel(y, want) < (1e-5 if ty == torch.float32 else 5e-3)
+
+
 def test_gemm_tcgen05_refuses_what_it_cannot_do(env):
     ops, dev, st = env
     from lucciola_b200.ops import KernelError

@@ -94,12 +94,16 @@ def test_linear_and_stacked_linear(act):
 
 
 @pytest.mark.parametrize("act", ACTS)
-def test_feed_forward_part(act):
+@pytest.mark.parametrize("inter,tokens", [(200, 7), (192, 7), (192, 300)])
+def test_feed_forward_part(act, inter, tokens):
+    """An intermediate size that is no multiple of 64 (separate SwiGLU kernel) and one that is (on the bfloat16
+    path gate and up rows are interleaved and the activation is formed in the product's epilogue)."""
     from lucciola_b200.parts import SwiGLUFeedForward
     rt = make_rt(act)
-    ffn = SwiGLUFeedForward(rt, "mlp", 72, 200)
+    ffn = SwiGLUFeedForward(rt, "mlp", 72, inter)
     w = bind_random(ffn, act)
-    x = torch.randn(7, 72, device="cuda:0").to(act)
+    assert ffn.fused == (act == torch.bfloat16 and inter % 64 == 0)
+    x = torch.randn(tokens, 72, device="cuda:0").to(act)
     assert rel(ffn.forward(x, None), plain.feed_forward(x.double().cpu(), w, "mlp")) < TOL[act]
 
 
