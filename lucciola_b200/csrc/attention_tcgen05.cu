@@ -6,18 +6,20 @@
 // blocks of 128 keys.  Per block
 //     S = Q K^T          tcgen05.mma, both operands K-major from shared memory, S (128 x 128 float32) in
 //                        tensor memory, two S buffers
-//     P = softmax part   four warps, ONE THREAD PER QUERY ROW: the thread reads its row of S with
-//                        tcgen05.ld, needs no shuffles for the row's maximum and sum, and writes its row
-//                        of P (bfloat16) into shared memory in the swizzled layout the tensor core reads
+//     P = softmax part   eight warps, TWO THREADS PER QUERY ROW (64 keys each): a thread reads its half of the
+//                        row of S with one tcgen05.ld into registers, gives the S buffer back at once, needs
+//                        no shuffles, exchanges the row's maximum with the other thread through shared
+//                        memory, and writes its half of the row of P (bfloat16) into shared memory in the
+//                        swizzled layout the tensor core reads
 //     O_blk = P V        tcgen05.mma, P K-major, V MN-major (as it lies in the pages), two O buffers
-//     O = O alpha + O_blk in registers of the row's thread (128 float32)
+//     O = O alpha + O_blk in registers of the row's threads (64 float32 columns each)
 // The formulas are the online softmax of src/kernels/flash_attention.cu:246-298 of lucciola (m, l, o per
 // row in 32-bit).  Keys and values come through TMA, one box per page and half of the head
-// (cp.async.bulk.tensor.2d, 128-byte swizzle) into a ring of two blocks; the queries through one
+// (cp.async.bulk.tensor.2d, 128-byte swizzle) into rings of two blocks, keys and values apart; the queries through one
 // three-dimensional box per half (head size, heads of the group, tokens).
 //
-// Warp roles (192 threads): warp 0 producer (one thread), warp 1 tensor-core issue (one thread) and
-// tensor-memory allocation, warps 2..5 softmax.  The softmax of block i+1 is computed before O_blk of
+// Warp roles (320 threads): warp 0 producer (one thread), warp 1 tensor-core issue (one thread) and
+// tensor-memory allocation, warps 2..9 softmax.  The softmax of block i+1 is computed before O_blk of
 // block i is added, so that the tensor cores work on P V of block i and Q K^T of block i+2 meanwhile.
 // Every wait on an mbarrier is bounded; when one gives up the CTA records it and leaves.
 //
@@ -128,20 +130,20 @@ __device__ __forceinline__ void ta_umma(uint32_t tmem_d, uint64_t da, uint64_t d
 __device__ __forceinline__ void ta_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void ta_tmem_ld32(uint32_t taddr, uint32_t* r) {
+__device__ __forceinline__ void ta_tmem_ld64(uint32_t taddr, uint32_t* r) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
 }
 
 enum : int { TA_ERR_Q = 301, TA_ERR_KV_FULL = 302, TA_ERR_KV_EMPTY = 303, TA_ERR_S_FULL = 304, TA_ERR_S_EMPTY = 305,
-             TA_ERR_P_FULL = 306, TA_ERR_P_EMPTY = 307, TA_ERR_O_FULL = 308, TA_ERR_O_EMPTY = 309 };
+             TA_ERR_P_FULL = 306, TA_ERR_P_EMPTY = 307, TA_ERR_O_FULL = 308, TA_ERR_O_EMPTY = 309, TA_ERR_EXCHANGE = 310 };
 
 // Shared memory: Q (2 halves) | K,V ring of 2 blocks (each K 2 halves, V 2 halves) | P (2 halves) | barriers
 constexpr int TA_Q_OFF = 0;
@@ -149,12 +151,14 @@ constexpr int TA_KV_OFF = TA_TILE_BYTES;                       // 32 KB
 constexpr int TA_KV_STAGE = 2 * TA_TILE_BYTES;                 // K then V: 64 KB
 constexpr int TA_P_OFF = TA_KV_OFF + 2 * TA_KV_STAGE;          // 160 KB
 constexpr int TA_BAR_OFF = TA_P_OFF + TA_TILE_BYTES;           // 192 KB
-constexpr int TA_NUM_BARS = 15;
+constexpr int TA_NUM_BARS = 20;
 constexpr int TA_MAX_TILE_PAGES = 4096;                        // pages a tile's keys may span (32 K keys of 8-token pages)
 constexpr int TA_PAGES_OFF = TA_BAR_OFF + TA_NUM_BARS * 8 + 16;
-constexpr int TA_SMEM_BYTES = TA_PAGES_OFF + TA_MAX_TILE_PAGES * 4;
+constexpr int TA_XCH_OFF = TA_PAGES_OFF + TA_MAX_TILE_PAGES * 4;   // maxima and sums that the two threads of a row exchange
+constexpr int TA_SMEM_BYTES = TA_XCH_OFF + 2 * 2 * 128 * 4;
+constexpr int TA_THREADS = 320;
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(TA_THREADS, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -162,13 +166,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const uint32_t sbase = ta_smem_u32(smem);
   const uint32_t bars = sbase + TA_BAR_OFF;
   const uint32_t q_full = bars;
-  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bars + 8u * (3 + s); };
+  auto k_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bars + 8u * (16 + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (18 + s); };
   auto s_full = [&](int b) { return bars + 8u * (5 + b); };
   auto s_empty = [&](int b) { return bars + 8u * (7 + b); };
   const uint32_t p_full = bars + 8u * 9, p_empty = bars + 8u * 10;
   auto o_full = [&](int b) { return bars + 8u * (11 + b); };
   auto o_empty = [&](int b) { return bars + 8u * (13 + b); };
+  const uint32_t x_bar = bars + 8u * 15;
   uint32_t* tmem_slot = (uint32_t*)(smem + TA_BAR_OFF + TA_NUM_BARS * 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -185,11 +192,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     ta_mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      ta_mbar_init(kv_full(i), 1); ta_mbar_init(kv_empty(i), 1);
-      ta_mbar_init(s_full(i), 1); ta_mbar_init(s_empty(i), 4);
-      ta_mbar_init(o_full(i), 1); ta_mbar_init(o_empty(i), 4);
+      ta_mbar_init(k_full(i), 1); ta_mbar_init(k_empty(i), 1);
+      ta_mbar_init(v_full(i), 1); ta_mbar_init(v_empty(i), 1);
+      ta_mbar_init(s_full(i), 1); ta_mbar_init(s_empty(i), 8);
+      ta_mbar_init(o_full(i), 1); ta_mbar_init(o_empty(i), 8);
     }
-    ta_mbar_init(p_full, 4); ta_mbar_init(p_empty, 1);
+    ta_mbar_init(p_full, 8); ta_mbar_init(p_empty, 1);
+    ta_mbar_init(x_bar, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -218,47 +227,56 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   __syncthreads();
 
   if (warp == 0) {
-    // ---- producer ----------------------------------------------------------------------------------------
+    // ---- producer: the whole warp; lane 0 waits and announces the bytes, every lane issues its share of the
+    // boxes (a page and a half of the head, keys or values) -------------------------------------------------
     if (lane == 0) {
       ta_mbar_expect_tx(q_full, TA_TILE_BYTES);
       ta_tma_3d(sbase + TA_Q_OFF, &map_q, 0, kvh * G, t0, q_full);
       ta_tma_3d(sbase + TA_Q_OFF + TA_HALF_BYTES, &map_q, 64, kvh * G, t0, q_full);
-      const int pages_per_block = TA_KEYS / p.page_size;
-      const uint32_t page_bytes = (uint32_t)p.page_size * 128u;       // one half of one page
-      for (int i = 0; i < nblocks; ++i) {
-        const int s = i & 1;
-        if (!ta_mbar_wait_idle(kv_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_KV_EMPTY)) break;
-        const int kb = kbeg + i * TA_KEYS;
-        // pages of this block that exist and hold keys the tile may see
-        int first = 0, last = pages_per_block;        // [first, last) in pages of the block
-        while (first < last && (kb + (first + 1) * p.page_size <= lo_tile)) ++first;
-        while (last > first && (kb + (last - 1) * p.page_size >= kend)) --last;
-        const int* blk_pages = spages + ((kb - kbeg) >> p.page_shift);
-        int npages = 0;
-        for (int pg = first; pg < last; ++pg) npages += blk_pages[pg] >= 0;
-        ta_mbar_expect_tx(kv_full(s), (uint32_t)npages * page_bytes * 4u);
-        const uint32_t kdst = sbase + TA_KV_OFF + s * TA_KV_STAGE, vdst = kdst + TA_TILE_BYTES;
-        for (int pg = first; pg < last; ++pg) {
-          const int page = blk_pages[pg];
-          if (page < 0) continue;
-          const int y = (page * p.num_kv_heads + kvh) * p.page_size;
-          const uint32_t off = (uint32_t)pg * page_bytes;
-          ta_tma_2d(kdst + off, &map_k, 0, y, kv_full(s));
-          ta_tma_2d(kdst + TA_HALF_BYTES + off, &map_k, 64, y, kv_full(s));
-          ta_tma_2d(vdst + off, &map_v, 0, y, kv_full(s));
-          ta_tma_2d(vdst + TA_HALF_BYTES + off, &map_v, 64, y, kv_full(s));
-        }
+    }
+    const int pages_per_block = TA_KEYS / p.page_size;
+    const uint32_t page_bytes = (uint32_t)p.page_size * 128u;       // one half of one page
+    // Keys and values have rings and barriers of their own: the keys of block i+2 may come as soon as Q K^T of
+    // block i is done, which is a whole block earlier than P V of block i gives the values' buffer back.
+    for (int step = 0; step < 2 * nblocks; ++step) {
+      const int i = step >> 1, is_v = step & 1, s = i & 1;
+      int go = 1;
+      if (lane == 0)
+        go = ta_mbar_wait_idle(is_v ? v_empty(s) : k_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_KV_EMPTY) ? 1 : 0;
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (!go) break;
+      const int kb = kbeg + i * TA_KEYS;
+      const int* blk_pages = spages + ((kb - kbeg) >> p.page_shift);
+      const uint32_t full = is_v ? v_full(s) : k_full(s);
+      // pages of this block that exist and hold keys the tile may see
+      int npages = 0;
+      for (int pg = lane; pg < pages_per_block; pg += 32) {
+        const bool seen = (kb + (pg + 1) * p.page_size > lo_tile) && (kb + pg * p.page_size < kend);
+        npages += (seen && blk_pages[pg] >= 0) ? 1 : 0;
+      }
+      npages = __reduce_add_sync(0xffffffffu, npages);
+      if (lane == 0) ta_mbar_expect_tx(full, (uint32_t)npages * page_bytes * 2u);
+      __syncwarp();
+      const uint32_t dst0 = sbase + TA_KV_OFF + s * TA_KV_STAGE + (is_v ? TA_TILE_BYTES : 0);
+      const CUtensorMap* map = is_v ? &map_v : &map_k;
+      for (int b = lane; b < pages_per_block * 2; b += 32) {
+        const int pg = b >> 1, hf = b & 1;
+        const bool seen = (kb + (pg + 1) * p.page_size > lo_tile) && (kb + pg * p.page_size < kend);
+        const int page = seen ? blk_pages[pg] : -1;
+        if (page < 0) continue;
+        const int y = (page * p.num_kv_heads + kvh) * p.page_size;
+        ta_tma_2d(dst0 + (uint32_t)hf * TA_HALF_BYTES + (uint32_t)pg * page_bytes, map, hf * 64, y, full);
       }
     }
   } else if (warp == 1) {
     // ---- tensor-core issue ---------------------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ta_idesc(0), idesc_pv = ta_idesc(1);
-      bool ok = ta_mbar_wait_idle(q_full, 0, abort_flag, TA_ERR_Q);
+      bool ok = ta_mbar_wait(q_full, 0, abort_flag, TA_ERR_Q);
       auto issue_qk = [&](int i) -> bool {
         const int s = i & 1;
-        if (!ta_mbar_wait_idle(kv_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL)) return false;
-        if (!ta_mbar_wait_idle(s_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_S_EMPTY)) return false;
+        if (!ta_mbar_wait(k_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL)) return false;
+        if (!ta_mbar_wait(s_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_S_EMPTY)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t qa = sbase + TA_Q_OFF, ka = sbase + TA_KV_OFF + s * TA_KV_STAGE;
 #pragma unroll
@@ -267,6 +285,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           ta_umma(tmem + (uint32_t)s * 128u, ta_desc_kmajor(qa + o), ta_desc_kmajor(ka + o), idesc_qk, k != 0);
         }
         ta_commit(s_full(s));
+        ta_commit(k_empty(s));
         return true;
       };
       if (ok && nblocks > 0) ok = issue_qk(0);
@@ -274,9 +293,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int s = i & 1;
         if (i + 1 < nblocks) { ok = issue_qk(i + 1); if (!ok) break; }
         // O_blk(i) = P(i) V(i)
-        ok = ta_mbar_wait_idle(p_full, (uint32_t)(i & 1), abort_flag, TA_ERR_P_FULL);
+        ok = ta_mbar_wait(p_full, (uint32_t)(i & 1), abort_flag, TA_ERR_P_FULL);
         if (!ok) break;
-        ok = ta_mbar_wait_idle(o_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_O_EMPTY);
+        ok = ta_mbar_wait(o_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_O_EMPTY);
+        if (!ok) break;
+        ok = ta_mbar_wait(v_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t pa = sbase + TA_P_OFF, va = sbase + TA_KV_OFF + s * TA_KV_STAGE + TA_TILE_BYTES;
@@ -288,33 +309,47 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         ta_commit(o_full(s));
         ta_commit(p_empty);
-        ta_commit(kv_empty(s));
+        ta_commit(v_empty(s));
       }
     }
   } else {
-    // ---- softmax: warp w owns lanes (w % 4) * 32 .. + 31 of tensor memory; thread = query row -----------------
+    // ---- softmax: eight warps; warp w reads lanes (w % 4) * 32 .. + 31 of tensor memory, so two warps share a
+    // quarter of the rows: the first four warps take keys 0..63 of a block and columns 0..63 of O, the other four
+    // the upper halves.  The two threads of a row exchange their maxima through shared memory once a block and
+    // their sums once at the end; everything else they do alone. ------------------------------------------------
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;                       // row of the tile
     const uint32_t tlane = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tcol = (uint32_t)half * 64u;
     const int row_pos = r < rows ? pos0 + r / G : -1;
     const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
-    float o_acc[TA_D];
+    float* xch = reinterpret_cast<float*>(smem + TA_XCH_OFF);          // [2 block parities][2 halves][128 rows]
+    float o_acc[TA_D / 2];
 #pragma unroll
-    for (int i = 0; i < TA_D; ++i) o_acc[i] = 0.f;
+    for (int i = 0; i < TA_D / 2; ++i) o_acc[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
     bool ok = true;
 
-    auto accumulate = [&](int i, float alpha) -> bool {      // O = O * alpha + O_blk(i)
+    // gives this thread's value to the row's other thread and returns that thread's value (exchange number i)
+    auto exchange = [&](int i, float mine, float& other) -> bool {
+      float* slot = xch + (i & 1) * 256;
+      slot[half * 128 + r] = mine;
+      __syncwarp();
+      if (lane == 0) ta_mbar_arrive(x_bar);
+      if (!ta_mbar_wait(x_bar, (uint32_t)(i & 1), abort_flag, TA_ERR_EXCHANGE)) return false;
+      other = slot[(half ^ 1) * 128 + r];
+      return true;
+    };
+
+    auto accumulate = [&](int i, float alpha) -> bool {      // O = O * alpha + O_blk(i), this thread's 64 columns
       const int s = i & 1;
       if (!ta_mbar_wait(o_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_O_FULL)) return false;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t v[64];
+      ta_tmem_ld64(tmem + tlane + 256u + (uint32_t)s * 128u + tcol, v);
 #pragma unroll
-      for (int c = 0; c < TA_D; c += 32) {
-        uint32_t v[32];
-        ta_tmem_ld32(tmem + tlane + 256u + (uint32_t)s * 128u + (uint32_t)c, v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o_acc[c + j] = fmaf(o_acc[c + j], alpha, __uint_as_float(v[j]));
-      }
+      for (int j = 0; j < 64; ++j) o_acc[j] = fmaf(o_acc[j], alpha, __uint_as_float(v[j]));
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) ta_mbar_arrive(o_empty(s));
@@ -331,88 +366,92 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool need_mask = (kb + TA_KEYS - 1 > pos0) || (p.window > 0) || (kb < lo_tile) || (kb + TA_KEYS > kend);
-      const uint32_t saddr = tmem + tlane + (uint32_t)s * 128u;
-      // pass 1: the row's maximum
-      float m_new = m_run;
-#pragma unroll 1
-      for (int c = 0; c < TA_KEYS; c += 32) {
-        uint32_t v[32];
-        ta_tmem_ld32(saddr + (uint32_t)c, v);
+      // this thread's 64 scores into registers; the S buffer goes back to the tensor cores at once
+      float x[64];
+      {
+        uint32_t v[64];
+        ta_tmem_ld64(tmem + tlane + (uint32_t)s * 128u + tcol, v);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float x = __uint_as_float(v[j]);
-          if (need_mask) { const int key = kb + c + j; if (key > row_pos || key < row_lo) x = -INFINITY; }
-          m_new = fmaxf(m_new, x);
+        for (int j = 0; j < 64; ++j) x[j] = __uint_as_float(v[j]);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) ta_mbar_arrive(s_empty(s));
+      float mx = -INFINITY;
+      if (need_mask) {
+        const int key0 = kb + half * 64;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const int key = key0 + j;
+          if (key > row_pos || key < row_lo) x[j] = -INFINITY;
         }
       }
+#pragma unroll
+      for (int j = 0; j < 64; ++j) mx = fmaxf(mx, x[j]);
+      float other;
+      ok = exchange(i, mx, other);
+      if (!ok) break;
+      const float m_new = fmaxf(m_run, fmaxf(mx, other));
       const float m_use = m_new == -INFINITY ? 0.f : m_new * p.scale_log2;
       alpha = m_run == -INFINITY ? 0.f : exp2f(m_run * p.scale_log2 - m_use);
       m_run = m_new;
       // the P buffer is free once P V of the previous block has been read by the tensor cores
       if (i > 0) { ok = ta_mbar_wait(p_empty, (uint32_t)((i - 1) & 1), abort_flag, TA_ERR_P_EMPTY); if (!ok) break; }
-      // pass 2: p = 2^(s * scale - m), the row's sum, P into shared memory (K-major, swizzled)
+      // p = 2^(s * scale - m), the sum over this thread's keys, its half of the row of P into shared memory
+      // (K-major, swizzled: the 16-byte chunk index within the 128-byte row is permuted by the row)
       float sum = 0.f;
-      uint8_t* prow = smem + TA_P_OFF + r * 128;
-#pragma unroll 1
-      for (int c = 0; c < TA_KEYS; c += 32) {
-        uint32_t v[32];
-        ta_tmem_ld32(saddr + (uint32_t)c, v);
-        uint32_t packed[16];
+      uint8_t* prow = smem + TA_P_OFF + half * TA_HALF_BYTES + r * 128;
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float x0 = __uint_as_float(v[j]), x1 = __uint_as_float(v[j + 1]);
-          if (need_mask) {
-            const int key = kb + c + j;
-            if (key > row_pos || key < row_lo) x0 = -INFINITY;
-            if (key + 1 > row_pos || key + 1 < row_lo) x1 = -INFINITY;
-          }
-          const float p0 = exp2_approx(fmaf(x0, p.scale_log2, -m_use)), p1 = exp2_approx(fmaf(x1, p.scale_log2, -m_use));
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float p0 = exp2_approx(fmaf(x[8 * c + 2 * j], p.scale_log2, -m_use));
+          const float p1 = exp2_approx(fmaf(x[8 * c + 2 * j + 1], p.scale_log2, -m_use));
           sum += p0 + p1;
-          __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-          packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b);
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+          w[j] = *reinterpret_cast<uint32_t*>(&b2);
         }
-        // 32 keys = four 16-byte chunks of the row; chunk index within the 128-byte row is permuted by the row
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (c >> 3) + q4;                   // 0..15 over the 128 keys
-          uint8_t* dst = prow + (chunk >> 3) * TA_HALF_BYTES + (((chunk & 7) ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-        }
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       l_run = l_run * alpha + sum;
       // value rows the tile may not see hold whatever the page or the shared memory held: zero them
       // (keys before the window's first key and keys past the last one; 16 threads a row)
       if ((kb < lo_tile) || (kb + TA_KEYS > kend)) {
+        ok = ta_mbar_wait(v_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL);     // the values have landed
+        if (!ok) break;
         uint8_t* vb = smem + TA_KV_OFF + s * TA_KV_STAGE + TA_TILE_BYTES;
         const int head_rows = min(max(lo_tile - kb, 0), TA_KEYS), tail_from = min(max(kend - kb, 0), TA_KEYS);
-        const int chunk = r & 15;
-        for (int key = r >> 4; key < TA_KEYS; key += 8) {
+        const int idx = (warp - 2) * 32 + lane, chunk = idx & 15;
+        for (int key = idx >> 4; key < TA_KEYS; key += 16) {
           if (key < head_rows || key >= tail_from)
             *reinterpret_cast<uint4*>(vb + (chunk >> 3) * TA_HALF_BYTES + key * 128 + ((chunk & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
-      // hand P (and the cleaned V) to the tensor cores, give the S buffer back
+      // hand P (and the cleaned V) to the tensor cores
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) { ta_mbar_arrive(p_full); ta_mbar_arrive(s_empty(s)); }
+      if (lane == 0) ta_mbar_arrive(p_full);
       } while (0);
       if (!ok) break;
       // add the previous block's O_blk while the tensor cores work on this one
       if (i > 0) ok = accumulate(i - 1, alpha_prev);
       alpha_prev = alpha;
     }
+    float l_other = 0.f;
+    if (ok) ok = exchange(nblocks, l_run, l_other);
     if (ok && r < rows) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const float l = l_run + l_other;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
       const int token = t0 + r / G, head = kvh * G + r % G;
-      uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)token * p.num_q_heads + head) * TA_D);
+      uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)token * p.num_q_heads + head) * TA_D + half * 64);
 #pragma unroll
-      for (int c = 0; c < TA_D; c += 8) {
+      for (int c = 0; c < 64; c += 8) {
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 b = __floats2bfloat162_rn(o_acc[c + 2 * j] * inv, o_acc[c + 2 * j + 1] * inv);
-          w[j] = *reinterpret_cast<uint32_t*>(&b);
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(o_acc[c + 2 * j] * inv, o_acc[c + 2 * j + 1] * inv);
+          w[j] = *reinterpret_cast<uint32_t*>(&b2);
         }
         dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
       }
@@ -544,7 +583,7 @@ LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache
     if (e != cudaSuccess) { lb::set_error("attention_tcgen05: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e)); return 2; }
     configured = true;
   }
-  lb::launch(lb::attention_tcgen05_kernel, dim3(num_tiles, num_kv_heads), dim3(192), smem, stream, mq, mk, mv, p);
+  lb::launch(lb::attention_tcgen05_kernel, dim3(num_tiles, num_kv_heads), dim3(lb::TA_THREADS), smem, stream, mq, mk, mv, p);
   LB_CHECK_LAUNCH("attention_tcgen05");
   return 0;
 }
