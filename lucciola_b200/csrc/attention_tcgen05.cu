@@ -1,26 +1,31 @@
 // Causal grouped-query attention for portions of prompts on the 5th-generation tensor cores
 // (bfloat16, head size 128, page sizes 8..128 that divide 128).
 //
-// A work item is a run of up to 128/G consecutive tokens of one request and one kv head (G = query
-// heads per kv head): its G*tokens query rows form a 128-row tile.  Keys and values are visited in
-// blocks of 128 keys.  Per block
+// A work item is a run of up to 256/G consecutive tokens of one request and one kv head (G = query
+// heads per kv head): its G*tokens query rows form TWO tiles of 128 rows, A and B, that share the keys
+// and values the CTA loads (half the traffic from L2 per query row) and run as two pipelines a half
+// period apart, so that the tensor cores work for one tile while the other tile's softmax runs.
+// Keys and values are visited in blocks of 128 keys.  Per block and tile
 //     S = Q K^T          tcgen05.mma, both operands K-major from shared memory, S (128 x 128 float32) in
-//                        tensor memory, two S buffers
-//     P = softmax part   eight warps, TWO THREADS PER QUERY ROW (64 keys each): a thread reads its half of the
-//                        row of S with one tcgen05.ld into registers, gives the S buffer back at once, needs
-//                        no shuffles, exchanges the row's maximum with the other thread through shared
-//                        memory, and writes its half of the row of P (bfloat16) into shared memory in the
-//                        swizzled layout the tensor core reads
-//     O_blk = P V        tcgen05.mma, P K-major, V MN-major (as it lies in the pages), two O buffers
-//     O = O alpha + O_blk in registers of the row's threads (64 float32 columns each)
+//                        tensor memory
+//     P = softmax part   four warps, ONE THREAD PER QUERY ROW: the thread reads its row of S with tcgen05.ld,
+//                        needs no shuffles for the row's maximum and sum, and writes its row of P (bfloat16,
+//                        two keys a column) with tcgen05.st over the first 64 columns of S
+//     O += P V           tcgen05.mma, P from TENSOR MEMORY, V MN-major from shared memory (as it lies in the
+//                        pages), O (128 x 128 float32) accumulated in tensor memory over all blocks
 // The formulas are the online softmax of src/kernels/flash_attention.cu:246-298 of lucciola (m, l, o per
-// row in 32-bit).  Keys and values come through TMA, one box per page and half of the head
-// (cp.async.bulk.tensor.2d, 128-byte swizzle) into rings of two blocks, keys and values apart; the queries through one
-// three-dimensional box per half (head size, heads of the group, tokens).
+// row in 32-bit), with one change of bookkeeping: the reference value m that the exponentials are taken
+// against follows the row's maximum only when that has grown by more than 2^8, so that O in tensor memory
+// is rescaled (tcgen05.ld, multiply, tcgen05.st by the row's thread) a few times per row instead of once
+// per block; p <= 2^8 then, and O / l is the same quotient whatever m was.
+// Keys and values come through TMA, one box per page and half of the head (cp.async.bulk.tensor.2d,
+// 128-byte swizzle) into rings of two blocks, keys and values apart; the queries through one
+// three-dimensional box per tile and half (head size, heads of the group, tokens).
 //
-// Warp roles (320 threads): warp 0 producer (one thread), warp 1 tensor-core issue (one thread) and
-// tensor-memory allocation, warps 2..9 softmax.  The softmax of block i+1 is computed before O_blk of
-// block i is added, so that the tensor cores work on P V of block i and Q K^T of block i+2 meanwhile.
+// Warp roles (320 threads): warp 0 producer, warp 1 tensor-core issue (one thread) and tensor-memory
+// allocation, warps 2..5 softmax of tile A, warps 6..9 softmax of tile B.  The tensor cores execute what
+// one thread issues in order, which is what orders P V of block i before Q K^T of block i+1 overwrites
+// the columns P lies in, and O's rescaling (after S of block i is complete, so P V of block i-1 is too).
 // Every wait on an mbarrier is bounded; when one gives up the CTA records it and leaves.
 //
 // Value rows outside the range a tile may see (past the last key, before the window, pages that were
@@ -142,21 +147,44 @@ __device__ __forceinline__ void ta_tmem_ld64(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 
-enum : int { TA_ERR_Q = 301, TA_ERR_KV_FULL = 302, TA_ERR_KV_EMPTY = 303, TA_ERR_S_FULL = 304, TA_ERR_S_EMPTY = 305,
-             TA_ERR_P_FULL = 306, TA_ERR_P_EMPTY = 307, TA_ERR_O_FULL = 308, TA_ERR_O_EMPTY = 309, TA_ERR_EXCHANGE = 310 };
+__device__ __forceinline__ void ta_tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// The caller waits with ta_tmem_wait_st() before it tells anyone.
+__device__ __forceinline__ void ta_tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+      :: "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void ta_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// A from tensor memory (rows on lanes, two bfloat16 of the K side a column), B from shared memory.
+__device__ __forceinline__ void ta_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
 
-// Shared memory: Q (2 halves) | K,V ring of 2 blocks (each K 2 halves, V 2 halves) | P (2 halves) | barriers
+enum : int { TA_ERR_Q = 301, TA_ERR_KV_FULL = 302, TA_ERR_KV_EMPTY = 303, TA_ERR_S_FULL = 304, TA_ERR_S_EMPTY = 305,
+             TA_ERR_P_FULL = 306, TA_ERR_P_EMPTY = 307, TA_ERR_O_FULL = 308 };
+
+// Shared memory: Q of tile A, Q of tile B (2 halves each) | K ring of 2 blocks | V ring of 2 blocks | barriers | page ids
 constexpr int TA_Q_OFF = 0;
-constexpr int TA_KV_OFF = TA_TILE_BYTES;                       // 32 KB
-constexpr int TA_KV_STAGE = 2 * TA_TILE_BYTES;                 // K then V: 64 KB
-constexpr int TA_P_OFF = TA_KV_OFF + 2 * TA_KV_STAGE;          // 160 KB
-constexpr int TA_BAR_OFF = TA_P_OFF + TA_TILE_BYTES;           // 192 KB
-constexpr int TA_NUM_BARS = 20;
+constexpr int TA_K_OFF = 2 * TA_TILE_BYTES;                    // 64 KB
+constexpr int TA_V_OFF = TA_K_OFF + 2 * TA_TILE_BYTES;         // 128 KB
+constexpr int TA_BAR_OFF = TA_V_OFF + 2 * TA_TILE_BYTES;       // 192 KB
+constexpr int TA_NUM_BARS = 15;
 constexpr int TA_MAX_TILE_PAGES = 4096;                        // pages a tile's keys may span (32 K keys of 8-token pages)
 constexpr int TA_PAGES_OFF = TA_BAR_OFF + TA_NUM_BARS * 8 + 16;
-constexpr int TA_XCH_OFF = TA_PAGES_OFF + TA_MAX_TILE_PAGES * 4;   // maxima and sums that the two threads of a row exchange
-constexpr int TA_SMEM_BYTES = TA_XCH_OFF + 2 * 2 * 128 * 4;
+constexpr int TA_SMEM_BYTES = TA_PAGES_OFF + TA_MAX_TILE_PAGES * 4;
 constexpr int TA_THREADS = 320;
+constexpr float TA_RESCALE_STEP = 8.f;                         // log2 of the growth of a row's maximum that moves its reference
 
 __global__ void __launch_bounds__(TA_THREADS, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -168,14 +196,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const uint32_t q_full = bars;
   auto k_full = [&](int s) { return bars + 8u * (1 + s); };
   auto k_empty = [&](int s) { return bars + 8u * (3 + s); };
-  auto v_full = [&](int s) { return bars + 8u * (16 + s); };
-  auto v_empty = [&](int s) { return bars + 8u * (18 + s); };
-  auto s_full = [&](int b) { return bars + 8u * (5 + b); };
-  auto s_empty = [&](int b) { return bars + 8u * (7 + b); };
-  const uint32_t p_full = bars + 8u * 9, p_empty = bars + 8u * 10;
-  auto o_full = [&](int b) { return bars + 8u * (11 + b); };
-  auto o_empty = [&](int b) { return bars + 8u * (13 + b); };
-  const uint32_t x_bar = bars + 8u * 15;
+  auto v_full = [&](int s) { return bars + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (7 + s); };
+  auto s_full = [&](int t) { return bars + 8u * (9 + t); };      // per tile
+  auto p_full = [&](int t) { return bars + 8u * (11 + t); };
+  auto o_done = [&](int t) { return bars + 8u * (13 + t); };
   uint32_t* tmem_slot = (uint32_t*)(smem + TA_BAR_OFF + TA_NUM_BARS * 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -184,7 +209,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int4 tile = p.tiles[blockIdx.x];
   const int t0 = tile.x, ntok = tile.y, seq = tile.z;
   const int kvh = blockIdx.y, G = p.group;
-  const int rows = ntok * G;
+  const int per = TA_ROWS / G;                  // tokens of a 128-row tile
+  const bool two = ntok > per;                  // is there a tile B
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -194,11 +220,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     for (int i = 0; i < 2; ++i) {
       ta_mbar_init(k_full(i), 1); ta_mbar_init(k_empty(i), 1);
       ta_mbar_init(v_full(i), 1); ta_mbar_init(v_empty(i), 1);
-      ta_mbar_init(s_full(i), 1); ta_mbar_init(s_empty(i), 8);
-      ta_mbar_init(o_full(i), 1); ta_mbar_init(o_empty(i), 8);
+      ta_mbar_init(s_full(i), 1); ta_mbar_init(p_full(i), 4); ta_mbar_init(o_done(i), 1);
     }
-    ta_mbar_init(p_full, 8); ta_mbar_init(p_empty, 1);
-    ta_mbar_init(x_bar, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -209,7 +232,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = *tmem_slot;            // S0: +0, S1: +128, O0: +256, O1: +384 (columns)
+  const uint32_t tmem = *tmem_slot;            // columns: S/P of tile A +0, of tile B +128; O of tile A +256, of tile B +384
 
   pdl_wait();                                   // everything below reads what earlier kernels wrote
   const int pos0 = p.positions[t0];
@@ -219,7 +242,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int kend = pos_last + 1;                // exclusive
   const int nblocks = (kend - kbeg + TA_KEYS - 1) / TA_KEYS;
   const int* bt = p.block_table + (size_t)seq * p.max_pages;
-  // The page ids of the keys this tile visits, copied once into shared memory for the producer.
+  // The page ids of the keys this work item visits, copied once into shared memory for the producer.
   int* spages = reinterpret_cast<int*>(smem + TA_PAGES_OFF);
   const int first_page = kbeg >> p.page_shift;
   const int num_tile_pages = min(((kend - 1) >> p.page_shift) - first_page + 1, TA_MAX_TILE_PAGES);
@@ -228,11 +251,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (warp == 0) {
     // ---- producer: the whole warp; lane 0 waits and announces the bytes, every lane issues its share of the
-    // boxes (a page and a half of the head, keys or values) -------------------------------------------------
+    // boxes (a page and a half of the head) -----------------------------------------------------------------
     if (lane == 0) {
-      ta_mbar_expect_tx(q_full, TA_TILE_BYTES);
-      ta_tma_3d(sbase + TA_Q_OFF, &map_q, 0, kvh * G, t0, q_full);
-      ta_tma_3d(sbase + TA_Q_OFF + TA_HALF_BYTES, &map_q, 64, kvh * G, t0, q_full);
+      ta_mbar_expect_tx(q_full, (two ? 2u : 1u) * TA_TILE_BYTES);
+      for (int t = 0; t < (two ? 2 : 1); ++t) {
+        ta_tma_3d(sbase + TA_Q_OFF + t * TA_TILE_BYTES, &map_q, 0, kvh * G, t0 + t * per, q_full);
+        ta_tma_3d(sbase + TA_Q_OFF + t * TA_TILE_BYTES + TA_HALF_BYTES, &map_q, 64, kvh * G, t0 + t * per, q_full);
+      }
     }
     const int pages_per_block = TA_KEYS / p.page_size;
     const uint32_t page_bytes = (uint32_t)p.page_size * 128u;       // one half of one page
@@ -248,7 +273,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const int kb = kbeg + i * TA_KEYS;
       const int* blk_pages = spages + ((kb - kbeg) >> p.page_shift);
       const uint32_t full = is_v ? v_full(s) : k_full(s);
-      // pages of this block that exist and hold keys the tile may see
+      // pages of this block that exist and hold keys the work item may see
       int npages = 0;
       for (int pg = lane; pg < pages_per_block; pg += 32) {
         const bool seen = (kb + (pg + 1) * p.page_size > lo_tile) && (kb + pg * p.page_size < kend);
@@ -257,7 +282,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       npages = __reduce_add_sync(0xffffffffu, npages);
       if (lane == 0) ta_mbar_expect_tx(full, (uint32_t)npages * page_bytes * 2u);
       __syncwarp();
-      const uint32_t dst0 = sbase + TA_KV_OFF + s * TA_KV_STAGE + (is_v ? TA_TILE_BYTES : 0);
+      const uint32_t dst0 = sbase + (is_v ? TA_V_OFF : TA_K_OFF) + s * TA_TILE_BYTES;
       const CUtensorMap* map = is_v ? &map_v : &map_k;
       for (int b = lane; b < pages_per_block * 2; b += 32) {
         const int pg = b >> 1, hf = b & 1;
@@ -272,188 +297,177 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // ---- tensor-core issue ---------------------------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ta_idesc(0), idesc_pv = ta_idesc(1);
+      const int ntiles = two ? 2 : 1;
       bool ok = ta_mbar_wait(q_full, 0, abort_flag, TA_ERR_Q);
-      auto issue_qk = [&](int i) -> bool {
+      // S_t = Q_t K(i)^T; the keys' buffer goes back after the last tile's product
+      auto issue_qk = [&](int t, int i) {
         const int s = i & 1;
-        if (!ta_mbar_wait(k_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL)) return false;
-        if (!ta_mbar_wait(s_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_S_EMPTY)) return false;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t qa = sbase + TA_Q_OFF, ka = sbase + TA_KV_OFF + s * TA_KV_STAGE;
+        const uint32_t qa = sbase + TA_Q_OFF + t * TA_TILE_BYTES, ka = sbase + TA_K_OFF + s * TA_TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t o = (uint32_t)(k >> 2) * TA_HALF_BYTES + (uint32_t)(k & 3) * 32u;
-          ta_umma(tmem + (uint32_t)s * 128u, ta_desc_kmajor(qa + o), ta_desc_kmajor(ka + o), idesc_qk, k != 0);
+          ta_umma(tmem + (uint32_t)t * 128u, ta_desc_kmajor(qa + o), ta_desc_kmajor(ka + o), idesc_qk, k != 0);
         }
-        ta_commit(s_full(s));
-        ta_commit(k_empty(s));
-        return true;
+        ta_commit(s_full(t));
+        if (t == ntiles - 1) ta_commit(k_empty(s));
       };
-      if (ok && nblocks > 0) ok = issue_qk(0);
+      if (ok) ok = ta_mbar_wait(k_full(0), 0, abort_flag, TA_ERR_KV_FULL);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int t = 0; t < ntiles; ++t) issue_qk(t, 0);
+      }
       for (int i = 0; i < nblocks && ok; ++i) {
         const int s = i & 1;
-        if (i + 1 < nblocks) { ok = issue_qk(i + 1); if (!ok) break; }
-        // O_blk(i) = P(i) V(i)
-        ok = ta_mbar_wait(p_full, (uint32_t)(i & 1), abort_flag, TA_ERR_P_FULL);
-        if (!ok) break;
-        ok = ta_mbar_wait(o_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_O_EMPTY);
-        if (!ok) break;
-        ok = ta_mbar_wait(v_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t pa = sbase + TA_P_OFF, va = sbase + TA_KV_OFF + s * TA_KV_STAGE + TA_TILE_BYTES;
+        for (int t = 0; t < ntiles && ok; ++t) {
+          // O_t += P_t(i) V(i)
+          ok = ta_mbar_wait(p_full(t), (uint32_t)(i & 1), abort_flag, TA_ERR_P_FULL);
+          if (!ok) break;
+          if (t == 0) { ok = ta_mbar_wait(v_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL); if (!ok) break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t va = sbase + TA_V_OFF + s * TA_TILE_BYTES;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t po = (uint32_t)(k >> 2) * TA_HALF_BYTES + (uint32_t)(k & 3) * 32u;     // 16 keys further in P's rows
-          const uint32_t vo = (uint32_t)k * 16u * 128u;                                           // 16 key rows further in V
-          ta_umma(tmem + 256u + (uint32_t)s * 128u, ta_desc_kmajor(pa + po), ta_desc_mnmajor(va + vo, TA_HALF_BYTES), idesc_pv, k != 0);
+          for (int k = 0; k < 8; ++k)                  // 16 keys a step: 8 columns of P, 16 rows of V
+            ta_umma_ts(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u + (uint32_t)k * 8u,
+                       ta_desc_mnmajor(va + (uint32_t)k * 16u * 128u, TA_HALF_BYTES), idesc_pv, (i | k) != 0);
+          ta_commit(o_done(t));
+          if (t == ntiles - 1) ta_commit(v_empty(s));
+          // S_t of the next block overwrites P_t: issued behind P V, which the tensor cores finish first
+          if (i + 1 < nblocks) {
+            if (t == 0) {
+              ok = ta_mbar_wait(k_full(s ^ 1), (uint32_t)(((i + 1) >> 1) & 1), abort_flag, TA_ERR_KV_FULL);
+              if (!ok) break;
+              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            issue_qk(t, i + 1);
+          }
         }
-        ta_commit(o_full(s));
-        ta_commit(p_empty);
-        ta_commit(v_empty(s));
       }
     }
-  } else {
-    // ---- softmax: eight warps; warp w reads lanes (w % 4) * 32 .. + 31 of tensor memory, so two warps share a
-    // quarter of the rows: the first four warps take keys 0..63 of a block and columns 0..63 of O, the other four
-    // the upper halves.  The two threads of a row exchange their maxima through shared memory once a block and
-    // their sums once at the end; everything else they do alone. ------------------------------------------------
+  } else if (warp < 6 || two) {
+    // ---- softmax: warps 2..5 tile A, warps 6..9 tile B; warp w reads lanes (w % 4) * 32 .. + 31 of tensor memory;
+    // thread = query row -------------------------------------------------------------------------------------
+    const int t = (warp - 2) >> 2;
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;                       // row of the tile
     const uint32_t tlane = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tcol = (uint32_t)half * 64u;
-    const int row_pos = r < rows ? pos0 + r / G : -1;
+    const uint32_t s_addr = tmem + tlane + (uint32_t)t * 128u, o_addr = tmem + tlane + 256u + (uint32_t)t * 128u;
+    const int tok_in_item = t * per + r / G;
+    const bool row_valid = tok_in_item < ntok;
+    const int row_pos = row_valid ? pos0 + tok_in_item : -1;
     const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
-    float* xch = reinterpret_cast<float*>(smem + TA_XCH_OFF);          // [2 block parities][2 halves][128 rows]
-    float o_acc[TA_D / 2];
-#pragma unroll
-    for (int i = 0; i < TA_D / 2; ++i) o_acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+    const int tile_pos0 = pos0 + t * per;                    // the smallest position among the tile's rows
+    float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-    // gives this thread's value to the row's other thread and returns that thread's value (exchange number i)
-    auto exchange = [&](int i, float mine, float& other) -> bool {
-      float* slot = xch + (i & 1) * 256;
-      slot[half * 128 + r] = mine;
-      __syncwarp();
-      if (lane == 0) ta_mbar_arrive(x_bar);
-      if (!ta_mbar_wait(x_bar, (uint32_t)(i & 1), abort_flag, TA_ERR_EXCHANGE)) return false;
-      other = slot[(half ^ 1) * 128 + r];
-      return true;
-    };
-
-    auto accumulate = [&](int i, float alpha) -> bool {      // O = O * alpha + O_blk(i), this thread's 64 columns
-      const int s = i & 1;
-      if (!ta_mbar_wait(o_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_O_FULL)) return false;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t v[64];
-      ta_tmem_ld64(tmem + tlane + 256u + (uint32_t)s * 128u + tcol, v);
-#pragma unroll
-      for (int j = 0; j < 64; ++j) o_acc[j] = fmaf(o_acc[j], alpha, __uint_as_float(v[j]));
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) ta_mbar_arrive(o_empty(s));
-      return true;
-    };
-
-    // Iteration i: the softmax of block i (if there is one), then the addition of block i-1's O_blk.
-    for (int i = 0; i <= nblocks && ok; ++i) {
-      float alpha = 1.f;
-      if (i < nblocks) do {
+    for (int i = 0; i < nblocks; ++i) {
       const int s = i & 1;
       const int kb = kbeg + i * TA_KEYS;
-      ok = ta_mbar_wait(s_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_S_FULL);
+      ok = ta_mbar_wait(s_full(t), (uint32_t)(i & 1), abort_flag, TA_ERR_S_FULL);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool need_mask = (kb + TA_KEYS - 1 > pos0) || (p.window > 0) || (kb < lo_tile) || (kb + TA_KEYS > kend);
-      // this thread's 64 scores into registers; the S buffer goes back to the tensor cores at once
-      float x[64];
+      const bool need_mask = (kb + TA_KEYS - 1 > tile_pos0) || (p.window > 0) || (kb < lo_tile) || (kb + TA_KEYS > kend);
+      float x[TA_KEYS];
       {
         uint32_t v[64];
-        ta_tmem_ld64(tmem + tlane + (uint32_t)s * 128u + tcol, v);
+        ta_tmem_ld64(s_addr, v);
 #pragma unroll
         for (int j = 0; j < 64; ++j) x[j] = __uint_as_float(v[j]);
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) ta_mbar_arrive(s_empty(s));
-      float mx = -INFINITY;
-      if (need_mask) {
-        const int key0 = kb + half * 64;
+        ta_tmem_ld64(s_addr + 64u, v);
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const int key = key0 + j;
+        for (int j = 0; j < 64; ++j) x[64 + j] = __uint_as_float(v[j]);
+      }
+      if (need_mask) {
+#pragma unroll
+        for (int j = 0; j < TA_KEYS; ++j) {
+          const int key = kb + j;
           if (key > row_pos || key < row_lo) x[j] = -INFINITY;
         }
       }
+      float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 64; ++j) mx = fmaxf(mx, x[j]);
-      float other;
-      ok = exchange(i, mx, other);
-      if (!ok) break;
-      const float m_new = fmaxf(m_run, fmaxf(mx, other));
-      const float m_use = m_new == -INFINITY ? 0.f : m_new * p.scale_log2;
-      alpha = m_run == -INFINITY ? 0.f : exp2f(m_run * p.scale_log2 - m_use);
-      m_run = m_new;
-      // the P buffer is free once P V of the previous block has been read by the tensor cores
-      if (i > 0) { ok = ta_mbar_wait(p_empty, (uint32_t)((i - 1) & 1), abort_flag, TA_ERR_P_EMPTY); if (!ok) break; }
-      // p = 2^(s * scale - m), the sum over this thread's keys, its half of the row of P into shared memory
-      // (K-major, swizzled: the 16-byte chunk index within the 128-byte row is permuted by the row)
+      for (int j = 0; j < TA_KEYS; ++j) mx = fmaxf(mx, x[j]);
+      // The reference follows the maximum only when that has grown much; then O (complete up to block i-1, since
+      // S of block i is) is rescaled.  The warp goes together: tcgen05.ld and st are warp-wide.
+      const float m_loc = mx * p.scale_log2;
+      const bool grow = m_loc > m_ref + TA_RESCALE_STEP;      // also true for the first finite maximum (m_ref = -inf)
+      if (__any_sync(0xffffffffu, grow)) {
+        float f = 1.f;
+        if (grow) {
+          if (m_ref != -INFINITY) f = exp2f(m_ref - m_loc);
+          m_ref = m_loc;
+          l_run *= f;
+        }
+        if (i > 0) {
+#pragma unroll 1
+          for (int c = 0; c < TA_D; c += 32) {
+            uint32_t v[32];
+            ta_tmem_ld32(o_addr + (uint32_t)c, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * f);
+            ta_tmem_st32(o_addr + (uint32_t)c, v);
+          }
+          ta_tmem_wait_st();
+        }
+      }
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      // p = 2^(s * scale - m), the row's sum, P (two keys a column) over the first 64 columns of S
       float sum = 0.f;
-      uint8_t* prow = smem + TA_P_OFF + half * TA_HALF_BYTES + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t w[4];
+      for (int c = 0; c < TA_KEYS; c += 64) {
+        uint32_t w[32];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float p0 = exp2_approx(fmaf(x[8 * c + 2 * j], p.scale_log2, -m_use));
-          const float p1 = exp2_approx(fmaf(x[8 * c + 2 * j + 1], p.scale_log2, -m_use));
+        for (int j = 0; j < 32; ++j) {
+          const float p0 = exp2_approx(fmaf(x[c + 2 * j], p.scale_log2, -m_use));
+          const float p1 = exp2_approx(fmaf(x[c + 2 * j + 1], p.scale_log2, -m_use));
           sum += p0 + p1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           w[j] = *reinterpret_cast<uint32_t*>(&b2);
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        ta_tmem_st32(s_addr + (uint32_t)(c >> 1), w);
       }
-      l_run = l_run * alpha + sum;
-      // value rows the tile may not see hold whatever the page or the shared memory held: zero them
-      // (keys before the window's first key and keys past the last one; 16 threads a row)
-      if ((kb < lo_tile) || (kb + TA_KEYS > kend)) {
+      ta_tmem_wait_st();
+      l_run += sum;
+      // value rows the work item may not see hold whatever the page or the shared memory held: tile A's threads
+      // zero them (keys before the window's first key and keys past the last one; 16 threads a row)
+      if (t == 0 && ((kb < lo_tile) || (kb + TA_KEYS > kend))) {
         ok = ta_mbar_wait(v_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL);     // the values have landed
         if (!ok) break;
-        uint8_t* vb = smem + TA_KV_OFF + s * TA_KV_STAGE + TA_TILE_BYTES;
+        uint8_t* vb = smem + TA_V_OFF + s * TA_TILE_BYTES;
         const int head_rows = min(max(lo_tile - kb, 0), TA_KEYS), tail_from = min(max(kend - kb, 0), TA_KEYS);
         const int idx = (warp - 2) * 32 + lane, chunk = idx & 15;
-        for (int key = idx >> 4; key < TA_KEYS; key += 16) {
+        for (int key = idx >> 4; key < TA_KEYS; key += 8) {
           if (key < head_rows || key >= tail_from)
             *reinterpret_cast<uint4*>(vb + (chunk >> 3) * TA_HALF_BYTES + key * 128 + ((chunk & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
       // hand P (and the cleaned V) to the tensor cores
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) ta_mbar_arrive(p_full);
-      } while (0);
-      if (!ok) break;
-      // add the previous block's O_blk while the tensor cores work on this one
-      if (i > 0) ok = accumulate(i - 1, alpha_prev);
-      alpha_prev = alpha;
+      if (lane == 0) ta_mbar_arrive(p_full(t));
     }
-    float l_other = 0.f;
-    if (ok) ok = exchange(nblocks, l_run, l_other);
-    if (ok && r < rows) {
-      const float l = l_run + l_other;
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int token = t0 + r / G, head = kvh * G + r % G;
-      uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)token * p.num_q_heads + head) * TA_D + half * 64);
+    if (ok) ok = ta_mbar_wait(o_done(t), (uint32_t)((nblocks - 1) & 1), abort_flag, TA_ERR_O_FULL);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const int token = t0 + tok_in_item, head = kvh * G + r % G;
+      uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)token * p.num_q_heads + head) * TA_D);
+#pragma unroll 1
+      for (int c = 0; c < TA_D; c += 32) {
+        uint32_t v[32];
+        ta_tmem_ld32(o_addr + (uint32_t)c, v);              // warp-wide: rows without a token take part and write nothing
+        if (row_valid) {
 #pragma unroll
-      for (int c = 0; c < 64; c += 8) {
-        uint32_t w[4];
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t w[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(o_acc[c + 2 * j] * inv, o_acc[c + 2 * j + 1] * inv);
-          w[j] = *reinterpret_cast<uint32_t*>(&b2);
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q4 + 2 * j]) * inv, __uint_as_float(v[8 * q4 + 2 * j + 1]) * inv);
+              w[j] = *reinterpret_cast<uint32_t*>(&b2);
+            }
+            dst[(c >> 3) + q4] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
         }
-        dst[c >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
   }
@@ -549,7 +563,8 @@ LB_EXPORT int lb_attention_tcgen05_ok(int num_q_heads, int num_kv_heads, int hea
 }
 
 // q, out: [T, nq, 128] bfloat16.  k_cache, v_cache: [pages, nkv, page_size, 128].  tiles: {first token,
-// tokens, request index, 0} with tokens * (nq / nkv) <= 128.
+// tokens, request index, 0} with tokens * (nq / nkv) <= 256; the tokens of a tile are consecutive tokens of one
+// request at consecutive positions.
 LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache, const void* v_cache, const int* positions,
                                    const int* block_table, const void* tiles, int num_tiles, int num_tokens,
                                    int num_q_heads, int num_kv_heads, int head_dim, int page_size, int num_pages,

@@ -232,8 +232,8 @@ class ModelRunner:
         R = T if graph_key else sum(len(e.want) for e in entries)
         G, P = len(self.groups), self.max_pages_per_seq
         # Work items of the attention kernels, per group size: "all" = every entry in tiles of up to 64 query
-        # rows; when the step holds portions of prompts, also "big" = those portions in tiles of up to 128 rows
-        # (for the tcgen05 kernel) and "rest" = the other entries in 64-row tiles.
+        # rows; when the step holds portions of prompts, also "big" = those portions in work items of up to 256
+        # rows (for the tcgen05 kernel) and "rest" = the other entries in 64-row tiles.
         tile_lists: dict[tuple[int, str], list] = {}
         first_token = [0] * S
         for i in range(1, S):
@@ -241,7 +241,7 @@ class ModelRunner:
         for g in self.tile_groups:
             tile_lists[(g, "all")] = self._tiles(q_lens, g, 64)
             if max(q_lens) >= _BIG_PORTION and 128 % g == 0:
-                big = self._tiles(q_lens, g, 128, lambda n: n >= _BIG_PORTION)
+                big = self._tiles(q_lens, g, 256, lambda n: n >= _BIG_PORTION)
                 # tiles that see the most keys first: the short ones then fill the end of the last wave
                 big.sort(key=lambda tl: -(starts[tl[2]] + (tl[0] - first_token[tl[2]]) + tl[1]))
                 tile_lists[(g, "big")] = big

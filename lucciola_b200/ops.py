@@ -350,7 +350,7 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, num_q_heads: int,
                       num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, stream: int) -> None:
     """Attention of portions of prompts on tcgen05 (S and O in tensor memory).  tiles: int32 [n, 4] of
-    (first token, tokens, request index, 0) with tokens * (nq / nkv) <= 128."""
+    (first token, tokens, request index, 0) with tokens * (nq / nkv) <= 256."""
     _check(q, "q", torch.bfloat16); _check(out, "attention output", torch.bfloat16)
     _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
     _check(positions, "positions", torch.int32); _check(block_table, "block table", torch.int32)

@@ -217,8 +217,9 @@ def test_attention_flash(env, nq, nkv, d, ps, window, seqs, splits):
     assert rel(out.cpu(), ref) < 8e-3
 
 
-def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None):
-    """The tensor-memory kernel for portions of prompts (head size 128) against the float64 statement."""
+def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None, rows=256):
+    """The tensor-memory kernel for portions of prompts (head size 128) against the float64 statement; work items
+    of up to `rows` query rows (256: two tiles in a CTA, 128: one)."""
     d = 128
     kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, torch.bfloat16)
     fill_pages(kc, vc, bt.cpu(), seqs, ps)
@@ -226,7 +227,7 @@ def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None):
         hook(kc, vc, bt.cpu())
     T = pos.shape[0]
     q = torch.randn(T, nq, d, device=dev).bfloat16() if q is None else q
-    per = 128 // (nq // nkv)
+    per = rows // (nq // nkv)
     tiles, t = [], 0
     for i, (_, n) in enumerate(seqs):
         for off in range(0, n, per):
@@ -251,10 +252,34 @@ def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None):
     (16, 1, 64, 0, [(0, 40), (1000, 9)]),           # sixteen heads on one kv head; nine tokens after a thousand
     (8, 2, 16, 200, [(0, 700)]),                    # a window inside a long portion
 ])
-def test_attention_tcgen05(env, nq, nkv, ps, window, seqs):
+@pytest.mark.parametrize("rows", [256, 128])
+def test_attention_tcgen05(env, nq, nkv, ps, window, seqs, rows):
     ops, dev, st = env
-    out, ref = run_tc(ops, dev, st, nq, nkv, ps, window, seqs)
+    out, ref = run_tc(ops, dev, st, nq, nkv, ps, window, seqs, rows=rows)
     assert torch.isfinite(out).all()                # unused slots and freed pages hold NaN and must not reach a sum
+    assert rel(out.cpu(), ref) < 8e-3
+
+
+@pytest.mark.parametrize("order", ["growing", "shrinking", "late spike"])
+def test_attention_tcgen05_moving_maximum(env, order):
+    """The row's reference value moves only when the maximum has grown by 2^8: keys whose scores grow from block to
+    block (many rescalings of O), shrink (none after the first block), or jump once at the end."""
+    ops, dev, st = env
+    nq, nkv, ps, n = 8, 2, 16, 1000
+
+    def hook(kc, vc, bt):
+        for j in range(n):
+            if order == "growing":
+                f = 0.2 + 6.0 * j / n
+            elif order == "shrinking":
+                f = 6.2 - 6.0 * j / n
+            else:
+                f = 8.0 if j >= n - 3 else 0.3
+            page, slot = int(bt[0, j // ps]), j % ps
+            kc[page, :, slot] = (kc[page, :, slot].float() * f).bfloat16()
+
+    out, ref = run_tc(ops, dev, st, nq, nkv, ps, 0, [(0, n)], hook=hook)
+    assert torch.isfinite(out).all()
     assert rel(out.cpu(), ref) < 8e-3
 
 
