@@ -18,19 +18,21 @@
 // against follows the row's maximum only when that has grown by more than 2^8, so that O in tensor memory
 // is rescaled (tcgen05.ld, multiply, tcgen05.st by the row's thread) a few times per row instead of once
 // per block; p <= 2^8 then, and O / l is the same quotient whatever m was.
-// Keys and values come through TMA, one box per page and half of the head (cp.async.bulk.tensor.2d,
-// 128-byte swizzle) into rings of two blocks, keys and values apart; the queries through one
-// three-dimensional box per tile and half (head size, heads of the group, tokens).
+// The queries come through TMA, one three-dimensional box per tile and half (head size, heads of the
+// group, tokens).  Keys and values come through cp.async, 16 bytes a thread and instruction, written in the
+// 128-byte swizzle the tensor cores read, into rings of two blocks, keys and values apart, one warp each:
+// with pages of 16 tokens a TMA box is 2 KB, a block needs 32 of them, and a CTA issues a box in about 125
+// cycles, which made the producer the slowest part of the pipeline (4000 of its 4400 cycles a block).
 //
-// Warp roles (320 threads): warp 0 producer, warp 1 tensor-core issue (one thread) and tensor-memory
-// allocation, warps 2..5 softmax of tile A, warps 6..9 softmax of tile B.  The tensor cores execute what
+// Warp roles (352 threads): warp 0 loads the queries and the keys, warp 10 the values, warp 1 issues to the
+// tensor cores (one thread) and owns the tensor memory, warps 2..5 softmax of tile A, warps 6..9 of tile B.  The tensor cores execute what
 // one thread issues in order, which is what orders P V of block i before Q K^T of block i+1 overwrites
 // the columns P lies in, and O's rescaling (after S of block i is complete, so P V of block i-1 is too).
 // Every wait on an mbarrier is bounded; when one gives up the CTA records it and leaves.
 //
-// Value rows outside the range a tile may see (past the last key, before the window, pages that were
-// given back) are set to zero in shared memory before they are multiplied, so that whatever a reused
-// page holds cannot reach a sum; scores there are set to -inf by assignment.
+// Key and value rows outside the range a work item may see (past the last key, before the window, pages
+// that were given back) are filled with zeros instead of being read, so that whatever a reused page holds
+// cannot reach a sum; scores there are set to -inf by assignment.
 #include "common.cuh"
 
 #include <cuda.h>
@@ -50,6 +52,7 @@ constexpr unsigned long long TA_WAIT_CYCLES = 4000000000ull;
 
 struct TcAttnParams {
   bf16* out;                                // [T, nq, d]
+  const uint8_t* k_cache; const uint8_t* v_cache;   // [pages, nkv, page_size, d] bfloat16
   const int* positions;                     // [T]
   const int* block_table; int max_pages;    // [S, max_pages]
   const int4* tiles;                        // {first token, tokens, request index, unused}
@@ -105,10 +108,6 @@ __device__ __forceinline__ bool ta_mbar_wait_idle(uint32_t bar, uint32_t parity,
       }
     }
   }
-}
-__device__ __forceinline__ void ta_tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void ta_tma_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -174,7 +173,9 @@ __device__ __forceinline__ void ta_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uin
 enum : int { TA_ERR_Q = 301, TA_ERR_KV_FULL = 302, TA_ERR_KV_EMPTY = 303, TA_ERR_S_FULL = 304, TA_ERR_S_EMPTY = 305,
              TA_ERR_P_FULL = 306, TA_ERR_P_EMPTY = 307, TA_ERR_O_FULL = 308 };
 
-// Shared memory: Q of tile A, Q of tile B (2 halves each) | K ring of 2 blocks | V ring of 2 blocks | barriers | page ids
+// Shared memory: Q of tile A, Q of tile B (2 halves each) | K ring of 2 blocks | V ring of 2 blocks | barriers | page ids.
+// A 128 x 128 bfloat16 tile is two halves of 128 rows x 128 bytes (64 elements); within a half the 16-byte chunk c
+// of row r lies at r * 128 + ((c ^ (r & 7)) << 4).
 constexpr int TA_Q_OFF = 0;
 constexpr int TA_K_OFF = 2 * TA_TILE_BYTES;                    // 64 KB
 constexpr int TA_V_OFF = TA_K_OFF + 2 * TA_TILE_BYTES;         // 128 KB
@@ -183,12 +184,50 @@ constexpr int TA_NUM_BARS = 15;
 constexpr int TA_MAX_TILE_PAGES = 4096;                        // pages a tile's keys may span (32 K keys of 8-token pages)
 constexpr int TA_PAGES_OFF = TA_BAR_OFF + TA_NUM_BARS * 8 + 16;
 constexpr int TA_SMEM_BYTES = TA_PAGES_OFF + TA_MAX_TILE_PAGES * 4;
-constexpr int TA_THREADS = 320;
+constexpr int TA_THREADS = 352;
 constexpr float TA_RESCALE_STEP = 8.f;                         // log2 of the growth of a row's maximum that moves its reference
 
+// One block of 128 keys (or values) of one kv head from the pages into a stage of the ring, by one warp.  A lane
+// copies chunk c (16 bytes) of every second row: rows rp, rp + 2, ... of every page.  `ring_lane` is the stage's
+// address plus the lane's fixed part (its half of the head and row rp); xr[u] the swizzled chunk offset of the
+// rows rp + 2u (mod 8).  Rows the work item may not see, and pages that are not there, are filled with zeros.
+template <int PS>
+__device__ __forceinline__ void ta_copy_block(uint32_t ring_lane, const uint32_t (&xr)[4], const uint8_t* pool_lane, const int* blk_pages,
+                                              int kb, int lo_tile, int kend, size_t page_stride, size_t head_off, int rp) {
+  const bool inner = kb >= lo_tile && kb + TA_KEYS <= kend;           // every key of the block may be seen
+  uint32_t dst_u[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) dst_u[u] = ring_lane + xr[u];
+  if (inner) {
+#pragma unroll
+    for (int pg = 0; pg < TA_KEYS / PS; ++pg) {
+      const int page = blk_pages[pg];
+      const uint8_t* src = pool_lane + (size_t)max(page, 0) * page_stride + head_off;
+      const uint32_t bytes = page >= 0 ? 16u : 0u;
+#pragma unroll
+      for (int j = 0; j < PS / 2; ++j)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                     ::"r"(dst_u[j & 3] + (uint32_t)(pg * PS * 128 + j * 256)), "l"(src + (size_t)j * 512u), "r"(bytes) : "memory");
+    }
+  } else {
+#pragma unroll 1
+    for (int pg = 0; pg < TA_KEYS / PS; ++pg) {
+      const int key0 = kb + pg * PS;
+      const int page = (key0 + PS > lo_tile && key0 < kend) ? blk_pages[pg] : -1;
+      const uint8_t* src = pool_lane + (size_t)max(page, 0) * page_stride + head_off;
+#pragma unroll
+      for (int j = 0; j < PS / 2; ++j) {
+        const int key = key0 + rp + 2 * j;
+        const uint32_t bytes = (page >= 0 && key >= lo_tile && key < kend) ? 16u : 0u;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                     ::"r"(dst_u[j & 3] + (uint32_t)(pg * PS * 128 + j * 256)), "l"(src + (size_t)j * 512u), "r"(bytes) : "memory");
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(TA_THREADS, 1)
-attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                         const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = ta_smem_u32(smem);
@@ -206,16 +245,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int4 tile = p.tiles[blockIdx.x];
+  const int4 tile = p.tiles[blockIdx.y];        // kv heads run fastest: the tiles come heaviest first over the whole grid
   const int t0 = tile.x, ntok = tile.y, seq = tile.z;
-  const int kvh = blockIdx.y, G = p.group;
+  const int kvh = blockIdx.x, G = p.group;
   const int per = TA_ROWS / G;                  // tokens of a 128-row tile
   const bool two = ntok > per;                  // is there a tile B
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     ta_mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       ta_mbar_init(k_full(i), 1); ta_mbar_init(k_empty(i), 1);
@@ -249,22 +286,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   for (int i = threadIdx.x; i < num_tile_pages; i += blockDim.x) spages[i] = bt[first_page + i];
   __syncthreads();
 
-  if (warp == 0) {
-    // ---- producer: the whole warp; lane 0 waits and announces the bytes, every lane issues its share of the
-    // boxes (a page and a half of the head) -----------------------------------------------------------------
-    if (lane == 0) {
+  if (warp == 0 || warp == 10) {
+    // ---- producers: warp 0 the queries (TMA) and the keys, warp 10 the values ---------------------------------
+    const bool is_v = warp == 10;
+    if (!is_v && lane == 0) {
       ta_mbar_expect_tx(q_full, (two ? 2u : 1u) * TA_TILE_BYTES);
       for (int t = 0; t < (two ? 2 : 1); ++t) {
         ta_tma_3d(sbase + TA_Q_OFF + t * TA_TILE_BYTES, &map_q, 0, kvh * G, t0 + t * per, q_full);
         ta_tma_3d(sbase + TA_Q_OFF + t * TA_TILE_BYTES + TA_HALF_BYTES, &map_q, 64, kvh * G, t0 + t * per, q_full);
       }
     }
-    const int pages_per_block = TA_KEYS / p.page_size;
-    const uint32_t page_bytes = (uint32_t)p.page_size * 128u;       // one half of one page
-    // Keys and values have rings and barriers of their own: the keys of block i+2 may come as soon as Q K^T of
-    // block i is done, which is a whole block earlier than P V of block i gives the values' buffer back.
-    for (int step = 0; step < 2 * nblocks; ++step) {
-      const int i = step >> 1, is_v = step & 1, s = i & 1;
+    const int ps = p.page_size;
+    const int c = lane & 15, rp = lane >> 4;
+    const uint8_t* pool_lane = (is_v ? p.v_cache : p.k_cache) + c * 16 + rp * 256;
+    const size_t page_stride = (size_t)p.num_kv_heads * ps * 256u, head_off = (size_t)kvh * ps * 256u;
+    uint32_t xr[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) xr[u] = (uint32_t)(((c & 7) ^ ((rp + 2 * u) & 7)) << 4);
+    const uint32_t ring = sbase + (is_v ? TA_V_OFF : TA_K_OFF) + (uint32_t)(c >> 3) * TA_HALF_BYTES + (uint32_t)rp * 128u;
+    for (int i = 0; i < nblocks; ++i) {
+      const int s = i & 1;
       int go = 1;
       if (lane == 0)
         go = ta_mbar_wait_idle(is_v ? v_empty(s) : k_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_KV_EMPTY) ? 1 : 0;
@@ -272,26 +313,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (!go) break;
       const int kb = kbeg + i * TA_KEYS;
       const int* blk_pages = spages + ((kb - kbeg) >> p.page_shift);
-      const uint32_t full = is_v ? v_full(s) : k_full(s);
-      // pages of this block that exist and hold keys the work item may see
-      int npages = 0;
-      for (int pg = lane; pg < pages_per_block; pg += 32) {
-        const bool seen = (kb + (pg + 1) * p.page_size > lo_tile) && (kb + pg * p.page_size < kend);
-        npages += (seen && blk_pages[pg] >= 0) ? 1 : 0;
+      const uint32_t stage = ring + (uint32_t)s * TA_TILE_BYTES;
+      switch (ps) {
+        case 8: ta_copy_block<8>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
+        case 16: ta_copy_block<16>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
+        case 32: ta_copy_block<32>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
+        case 64: ta_copy_block<64>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
+        default: ta_copy_block<128>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
       }
-      npages = __reduce_add_sync(0xffffffffu, npages);
-      if (lane == 0) ta_mbar_expect_tx(full, (uint32_t)npages * page_bytes * 2u);
+      // the block has landed: make it visible to the tensor cores' reads, then say so
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      const uint32_t dst0 = sbase + (is_v ? TA_V_OFF : TA_K_OFF) + s * TA_TILE_BYTES;
-      const CUtensorMap* map = is_v ? &map_v : &map_k;
-      for (int b = lane; b < pages_per_block * 2; b += 32) {
-        const int pg = b >> 1, hf = b & 1;
-        const bool seen = (kb + (pg + 1) * p.page_size > lo_tile) && (kb + pg * p.page_size < kend);
-        const int page = seen ? blk_pages[pg] : -1;
-        if (page < 0) continue;
-        const int y = (page * p.num_kv_heads + kvh) * p.page_size;
-        ta_tma_2d(dst0 + (uint32_t)hf * TA_HALF_BYTES + (uint32_t)pg * page_bytes, map, hf * 64, y, full);
-      }
+      if (lane == 0) ta_mbar_arrive(is_v ? v_full(s) : k_full(s));
     }
   } else if (warp == 1) {
     // ---- tensor-core issue ---------------------------------------------------------------------------------
@@ -343,7 +378,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
       }
     }
-  } else if (warp < 6 || two) {
+  } else if (warp < 6 || (two && warp < 10)) {
     // ---- softmax: warps 2..5 tile A, warps 6..9 tile B; warp w reads lanes (w % 4) * 32 .. + 31 of tensor memory;
     // thread = query row -------------------------------------------------------------------------------------
     const int t = (warp - 2) >> 2;
@@ -360,7 +395,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     bool ok = true;
 
     for (int i = 0; i < nblocks; ++i) {
-      const int s = i & 1;
       const int kb = kbeg + i * TA_KEYS;
       ok = ta_mbar_wait(s_full(t), (uint32_t)(i & 1), abort_flag, TA_ERR_S_FULL);
       if (!ok) break;
@@ -383,9 +417,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           if (key > row_pos || key < row_lo) x[j] = -INFINITY;
         }
       }
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one of 128 dependent maxima
 #pragma unroll
-      for (int j = 0; j < TA_KEYS; ++j) mx = fmaxf(mx, x[j]);
+      for (int j = 0; j < TA_KEYS; j += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], x[j + u]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // The reference follows the maximum only when that has grown much; then O (complete up to block i-1, since
       // S of block i is) is rescaled.  The warp goes together: tcgen05.ld and st are warp-wide.
       const float m_loc = mx * p.scale_log2;
@@ -411,7 +449,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       // p = 2^(s * scale - m), the row's sum, P (two keys a column) over the first 64 columns of S
-      float sum = 0.f;
+      float sum2[2] = {0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < TA_KEYS; c += 64) {
         uint32_t w[32];
@@ -419,29 +457,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int j = 0; j < 32; ++j) {
           const float p0 = exp2_approx(fmaf(x[c + 2 * j], p.scale_log2, -m_use));
           const float p1 = exp2_approx(fmaf(x[c + 2 * j + 1], p.scale_log2, -m_use));
-          sum += p0 + p1;
+          sum2[0] += p0; sum2[1] += p1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           w[j] = *reinterpret_cast<uint32_t*>(&b2);
         }
         ta_tmem_st32(s_addr + (uint32_t)(c >> 1), w);
       }
       ta_tmem_wait_st();
-      l_run += sum;
-      // value rows the work item may not see hold whatever the page or the shared memory held: tile A's threads
-      // zero them (keys before the window's first key and keys past the last one; 16 threads a row)
-      if (t == 0 && ((kb < lo_tile) || (kb + TA_KEYS > kend))) {
-        ok = ta_mbar_wait(v_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL);     // the values have landed
-        if (!ok) break;
-        uint8_t* vb = smem + TA_V_OFF + s * TA_TILE_BYTES;
-        const int head_rows = min(max(lo_tile - kb, 0), TA_KEYS), tail_from = min(max(kend - kb, 0), TA_KEYS);
-        const int idx = (warp - 2) * 32 + lane, chunk = idx & 15;
-        for (int key = idx >> 4; key < TA_KEYS; key += 8) {
-          if (key < head_rows || key >= tail_from)
-            *reinterpret_cast<uint4*>(vb + (chunk >> 3) * TA_HALF_BYTES + key * 128 + ((chunk & 7) << 4)) = make_uint4(0, 0, 0, 0);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      }
-      // hand P (and the cleaned V) to the tensor cores
+      l_run += sum2[0] + sum2[1];
+      // hand P to the tensor cores
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) ta_mbar_arrive(p_full(t));
@@ -511,26 +535,6 @@ struct TaMapKeyHash {
 static std::unordered_map<TaMapKey, CUtensorMap, TaMapKeyHash> g_ta_maps;
 static std::mutex g_ta_mu;
 
-// Keys or values of one cache layer: [pages * kv_heads * page_size, 128] bfloat16, boxes of page_size rows x 64.
-static bool ta_pool_map(CUtensorMap* out, const void* pool, long long rows, int page_size) {
-  TaMapKey key{pool, rows, page_size, 0, 1};
-  std::lock_guard<std::mutex> g(g_ta_mu);
-  auto it = g_ta_maps.find(key);
-  if (it != g_ta_maps.end()) { *out = it->second; return true; }
-  TaEncodeFn fn = ta_encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {128, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {256};
-  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
-  cuuint32_t estr[2] = {1, 1};
-  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return false;
-  if (g_ta_maps.size() > 4096) g_ta_maps.clear();
-  g_ta_maps.emplace(key, *out);
-  return true;
-}
-
 // Queries [T, nq, 128]: boxes of 64 x G heads x (128 / G) tokens; rows of a box are (token, head of the group).
 static bool ta_q_map(CUtensorMap* out, const void* q, long long tokens, int num_q_heads, int group) {
   TaMapKey key{q, tokens, num_q_heads, group, 2};
@@ -576,17 +580,16 @@ LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache
   LB_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)out % 16 == 0),
                "attention_tcgen05: operands must be 16-byte aligned");
   if (num_tiles == 0) return 0;
+  LB_CHECK_ARG(num_tiles <= 65535, "attention_tcgen05: %d tiles, at most 65535 a launch", num_tiles);
   LB_CHECK_ARG(max_pages <= lb::TA_MAX_TILE_PAGES, "attention_tcgen05: a request may span %d pages, at most %d", max_pages, lb::TA_MAX_TILE_PAGES);
   const int group = num_q_heads / num_kv_heads;
-  CUtensorMap mq, mk, mv;
-  const long long pool_rows = (long long)num_pages * num_kv_heads * page_size;
-  if (!lb::ta_q_map(&mq, q, num_tokens, num_q_heads, group) || !lb::ta_pool_map(&mk, k_cache, pool_rows, page_size) ||
-      !lb::ta_pool_map(&mv, v_cache, pool_rows, page_size)) {
+  CUtensorMap mq;
+  if (!lb::ta_q_map(&mq, q, num_tokens, num_q_heads, group)) {
     lb::set_error("attention_tcgen05: cuTensorMapEncodeTiled failed");
     return 3;
   }
   lb::TcAttnParams p;
-  p.out = (lb::bf16*)out; p.positions = positions; p.block_table = block_table; p.max_pages = max_pages;
+  p.out = (lb::bf16*)out; p.k_cache = (const uint8_t*)k_cache; p.v_cache = (const uint8_t*)v_cache; p.positions = positions; p.block_table = block_table; p.max_pages = max_pages;
   p.tiles = (const int4*)tiles; p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.group = group;
   p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
   p.page_shift = 0;
@@ -598,7 +601,7 @@ LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache
     if (e != cudaSuccess) { lb::set_error("attention_tcgen05: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e)); return 2; }
     configured = true;
   }
-  lb::launch(lb::attention_tcgen05_kernel, dim3(num_tiles, num_kv_heads), dim3(lb::TA_THREADS), smem, stream, mq, mk, mv, p);
+  lb::launch(lb::attention_tcgen05_kernel, dim3(num_kv_heads, num_tiles), dim3(lb::TA_THREADS), smem, stream, mq, p);
   LB_CHECK_LAUNCH("attention_tcgen05");
   return 0;
 }
