@@ -1,5 +1,5 @@
 """Each part alone against the plain implementation's function for it, the order of layers as data,
-and a toy mixer with state of its own that is registered, built and stepped without a change to
+a toy feed-forward with routing, and a toy mixer with state of its own that is registered, built and stepped without a change to
 the framework's files (GPU)."""
 import json
 import math
@@ -296,3 +296,95 @@ def test_toy_mixer_with_state_of_its_own(tmp_path):
     assert ((got_a - wa).abs().max() / wa.abs().max()) < 1e-5 and ((got_b - wb).abs().max() / wb.abs().max()) < 1e-5
     runner.finish("a"); runner.finish("b")
     runner.manager.check_invariants()
+
+
+def test_toy_feed_forward_with_routing_chosen_layer_by_layer(tmp_path):
+    """A feed-forward with a router and experts, defined here: top-2 of 3 small SwiGLU experts, router logits and
+    the softmax over the chosen ones in 32-bit.  Layer 0 uses it, layer 1 the framework's dense feed-forward, both
+    behind the framework's attention: the block takes either without knowing which."""
+    from lucciola_b200.config import EngineOptions, register_architecture
+    from lucciola_b200.engine.load import build_runner
+    from lucciola_b200.engine.step import StepEntry
+    from lucciola_b200.models import DecoderModel, LayerCall
+    from lucciola_b200.parts import (FeedForward, GQAttention, Linear, OutputHead, PreNormBlock, RMSNorm, RotaryEmbedding,
+                                     Runtime, SwiGLUFeedForward, TokenEmbedding)
+    from lucciola_b200.weights import write_safetensors
+    from lucciola_b200.weights.random_init import RandomWeights
+
+    class RoutedExperts(FeedForward):
+        def __init__(self, rt, prefix, hidden, inner, experts, top_k):
+            self.rt, self.top_k = rt, top_k
+            self.router = Linear(rt, f"{prefix}.router.weight", hidden, experts)
+            self.experts = [SwiGLUFeedForward(rt, f"{prefix}.experts.{e}", hidden, inner) for e in range(experts)]
+
+        def children(self):
+            return [self.router] + self.experts
+
+        def forward(self, h, step):
+            logits = self.router.forward(h, out_dtype=torch.float32)
+            top, idx = torch.topk(logits, self.top_k, dim=-1)
+            gate = torch.softmax(top, dim=-1)
+            out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+            for e, expert in enumerate(self.experts):
+                rows = (idx == e).any(dim=-1).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                weight = (gate * (idx == e)).sum(dim=-1)[rows]
+                out[rows] += weight[:, None] * expert.forward(h[rows].contiguous(), step).float()
+            return out.to(h.dtype)
+
+    def build(cfg, rt):
+        H, V, d, nq, nkv = cfg["hidden_size"], cfg["vocab_size"], cfg["head_dim"], cfg["heads"], cfg["kv_heads"]
+        rope = RotaryEmbedding(rt, d, cfg["theta"])
+        def ff(i):
+            return RoutedExperts(rt, f"l{i}.moe", H, cfg["inner"], 3, 2) if i == 0 else SwiGLUFeedForward(rt, f"l{i}.mlp", H, cfg["inner"])
+        blocks = [PreNormBlock(GQAttention(rt, f"l{i}.attn", H, nq, nkv, d, rope, cfg["eps"]), ff(i),
+                               RMSNorm(rt, f"l{i}.n1.weight", H, cfg["eps"]), RMSNorm(rt, f"l{i}.n2.weight", H, cfg["eps"]),
+                               rt.act_dtype) for i in range(2)]
+        return DecoderModel(rt, TokenEmbedding(rt, "emb.weight", V, H), blocks, [LayerCall(0, 0), LayerCall(1, 1)],
+                            RMSNorm(rt, "norm.weight", H, cfg["eps"]), OutputHead(rt, "head.weight", V, H, None), V, cfg["max_len"])
+
+    register_architecture("ToyRoutedLM", dict, build, replace=True)
+    cfg = {"architectures": ["ToyRoutedLM"], "hidden_size": 48, "vocab_size": 53, "inner": 40, "heads": 3, "kv_heads": 1,
+           "head_dim": 16, "theta": 10000.0, "eps": 1e-5, "max_len": 64}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    specs = build(cfg, Runtime("cpu", torch.float32)).all_param_specs()
+    src = RandomWeights(specs, 5, std=0.3, norm_std=0.1)
+    weights = {n: src.get(n) for n in src.names()}
+    write_safetensors(tmp_path / "model.safetensors", weights)
+    w = {k: v.double() for k, v in weights.items()}
+
+    pcfg = {"num_attention_heads": cfg["heads"], "num_key_value_heads": cfg["kv_heads"], "head_dim": cfg["head_dim"],
+            "hidden_size": cfg["hidden_size"], "rms_norm_eps": cfg["eps"], "rope_theta": cfg["theta"]}
+
+    def plain_forward(ids):
+        x = w["emb.weight"][torch.tensor(ids)]
+        pos = torch.arange(len(ids))
+        for i in range(2):
+            h = plain.rms_norm(x, w[f"l{i}.n1.weight"], cfg["eps"])
+            x = x + plain.attention_block(h, w, f"l{i}.attn", pcfg, pos, 0)[0]
+            h = plain.rms_norm(x, w[f"l{i}.n2.weight"], cfg["eps"])
+            if i == 0:
+                logits = plain.linear(h, w["l0.moe.router.weight"])
+                top, idx = torch.topk(logits, 2, dim=-1)
+                gate = torch.softmax(top, dim=-1)
+                y = torch.zeros_like(h)
+                for t in range(len(ids)):
+                    for j in range(2):
+                        e = int(idx[t, j])
+                        ew = {k.replace(f"l0.moe.experts.{e}.", "m."): v for k, v in w.items() if k.startswith(f"l0.moe.experts.{e}.")}
+                        y[t] += gate[t, j] * plain.feed_forward(h[t:t + 1], ew, "m")[0]
+                x = x + y
+            else:
+                x = x + plain.feed_forward(h, {k.replace("l1.mlp.", "m."): v for k, v in w.items() if k.startswith("l1.mlp.")}, "m")
+        return plain.linear(plain.rms_norm(x, w["norm.weight"], cfg["eps"]), w["head.weight"])
+
+    runner = build_runner(tmp_path, EngineOptions(dtype="float32", block_size=16, max_blocks=8, max_num_seqs=2, use_cuda_graph=False))
+    ids = [(7 * i * i + 3 * i + 1) % 53 for i in range(37)]
+    want = plain_forward(ids)
+    got = runner.step([StepEntry("w", ids, list(range(len(ids))))]).double().cpu()
+    assert ((got - want).abs().max() / want.abs().max()) < 1e-5
+    runner.finish("w")
+    parts = [runner.step([StepEntry("p", ids[a:b], list(range(b - a)))]) for a, b in ((0, 20), (20, 22), (22, 36), (36, 37))]
+    got2 = torch.cat(parts).double().cpu()
+    assert ((got2 - want).abs().max() / want.abs().max()) < 1e-5
