@@ -231,8 +231,9 @@ def main() -> int:
         """B requests brought to a context just short of `ctx`, then 2 x (W + K) decode steps."""
         total_steps = (2 if with_e2e else 1) * (W + K) + 2
         # requests whose prompt is done decode while the prompts behind them are still read: leave room
-        ctx0 = ctx - total_steps - (B - 1) * -(-ctx // options.max_tokens_per_step) - 1
-        params = SamplingParams(max_new_tokens=total_steps + 8, temperature=0.0, ignore_eos=True)
+        early = (B - 1) * -(-ctx // options.max_tokens_per_step)
+        ctx0 = ctx - total_steps - early - 1
+        params = SamplingParams(max_new_tokens=total_steps + early + 8, temperature=0.0, ignore_eos=True)
         reqs = [engine.add_request(rng.integers(0, V, size=ctx0).tolist(), params) for _ in range(B)]
         while any(r.remaining > 1 or not r.output for r in reqs):       # prompts, in portions under the budget
             engine.step()
