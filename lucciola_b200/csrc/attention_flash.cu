@@ -407,7 +407,7 @@ flash_attention_kernel(FlashParams p) {
 
 // Combines the partials of the splits, in their order: out = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M).
 // One warp per query row: the lanes first share the work of the weights 2^(m_z - M) (kept in shared
-// memory), then each lane adds up its dimensions over the splits, four independent loads at a time.
+// memory), then each lane adds up four dimensions over the splits, eight independent 16-byte loads at a time.
 __global__ void flash_combine_kernel(FlashParams p) {
   extern __shared__ float wsm[];                      // [warps][splits]
   pdl_trigger();
@@ -436,17 +436,23 @@ __global__ void flash_combine_kernel(FlashParams p) {
     const int token = tile.x + r / p.group, head = kvh * p.group + r % p.group;
     bf16* dst = p.out + ((size_t)token * p.num_q_heads + head) * d;
     const size_t zstride = (size_t)p.part_rows * d;
-    for (int dim = lane; dim < d; dim += 32) {
+    // a lane adds up four neighbouring dimensions (one 16-byte load a split), eight splits in flight at a time
+    for (int dim = lane * 4; dim < d; dim += 128) {
       const float* src = p.part_o + ((base * p.part_rows) + r) * d + dim;
-      float acc = 0.f;
-      int z = 0;
-      for (; z + 4 <= p.splits; z += 4) {
-        const float a0 = src[(size_t)z * zstride], a1 = src[(size_t)(z + 1) * zstride];
-        const float a2 = src[(size_t)(z + 2) * zstride], a3 = src[(size_t)(z + 3) * zstride];
-        acc += a0 * wz[z]; acc += a1 * wz[z + 1]; acc += a2 * wz[z + 2]; acc += a3 * wz[z + 3];
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int z0 = 0; z0 < p.splits; z0 += 8) {
+        float4 a[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          a[u] = z0 + u < p.splits ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(z0 + u) * zstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float w = z0 + u < p.splits ? wz[z0 + u] : 0.f;
+          acc[0] += a[u].x * w; acc[1] += a[u].y * w; acc[2] += a[u].z * w; acc[3] += a[u].w * w;
+        }
       }
-      for (; z < p.splits; ++z) acc += src[(size_t)z * zstride] * wz[z];
-      dst[dim] = __float2bfloat16_rn(acc * inv);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv), hi = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+      *reinterpret_cast<uint2*>(dst + dim) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
     }
     __syncwarp();
   }
