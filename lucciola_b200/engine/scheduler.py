@@ -134,9 +134,10 @@ class Scheduler:
         reserved = [0] * len(self.manager.pools)
         budget = self.max_tokens_per_step
 
-        def take(r: Request, n: int) -> None:
+        def take(r: Request, n: int, need: Optional[Sequence[int]] = None) -> None:
             nonlocal budget
-            need = self._pages_needed(r, r.num_computed + n)
+            if need is None:
+                need = self._pages_needed(r, r.num_computed + n)
             for g, k in enumerate(need):
                 reserved[g] += k
             plan.append(Scheduled(r, r.num_computed, n, r.num_computed + n == r.length))
@@ -157,7 +158,7 @@ class Scheduler:
                 if victim is r:
                     break
             if r in self.running:
-                take(r, 1)
+                take(r, 1, need)
 
         # 2. Prompts under way (and requests that are recomputed), oldest first.  After a preemption
         # nothing new starts in this step, or the victim would come straight back.

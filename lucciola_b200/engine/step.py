@@ -50,22 +50,22 @@ class _Staging:
     def __init__(self, device: torch.device, capacity: int, ring: int = 4):
         self.device, self.capacity = device, capacity
         self.host = [torch.empty(capacity, dtype=torch.int32, pin_memory=True) for _ in range(ring)]
-        self.events: list[Optional[torch.cuda.Event]] = [None] * ring
+        self.events = [torch.cuda.Event() for _ in range(ring)]
+        self.recorded = [False] * ring
         self.dev = torch.empty(capacity, dtype=torch.int32, device=device)
         self.turn = 0
 
     def next_host(self) -> tuple[int, torch.Tensor]:
         i = self.turn
         self.turn = (self.turn + 1) % len(self.host)
-        if self.events[i] is not None:
+        if self.recorded[i]:
             self.events[i].synchronize()        # the copy that read this buffer has finished
         return i, self.host[i]
 
     def upload(self, i: int, n: int, dev: Optional[torch.Tensor] = None) -> None:
         (self.dev if dev is None else dev)[:n].copy_(self.host[i][:n], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self.events[i] = ev
+        self.events[i].record()
+        self.recorded[i] = True
 
 
 class ModelRunner:
@@ -90,6 +90,10 @@ class ModelRunner:
         self.cache = DeviceCache(requests, self.groups, self.page_size, [self.num_pages] * len(self.groups),
                                  options.max_num_seqs, rt.act_dtype, self.device)
         self.max_pages_per_seq = -(-self.max_model_len // self.page_size)
+        self._any_window = any(g.window > 0 for g in self.groups)
+        self._arange_cache = np.arange(512, dtype=np.int32)
+        self._decode_tiles: dict[int, list] = {}               # tiles of a decode-only step, by its (padded) size
+        self._decode_tiles_flat: dict[int, np.ndarray] = {}
         # Group sizes for which a step carries tiles of the tensor-core attention kernel.
         self.tile_groups = sorted({g for b in model.blocks if (g := b.mixer.query_group_size()) and g <= 64}) \
             if rt.fast_kernels else []
@@ -196,11 +200,15 @@ class ModelRunner:
             for w in e.want:
                 if not (0 <= w < n):
                     raise ValueError(f"request {e.rid!r} wants logits at place {w} of {n} tokens")
-            arr = np.asarray(e.tokens, dtype=np.int64)
-            token_arrays.append(arr)
-            if int(arr.min()) < 0 or int(arr.max()) >= vocab:
-                bad = int(arr.min()) if int(arr.min()) < 0 else int(arr.max())
-                raise ValueError(f"request {e.rid!r}: token id {bad} is outside the vocabulary of {vocab}")
+            if n == 1:                         # a decoded token: no array for one number
+                lo = hi = int(e.tokens[0])
+                token_arrays.append(lo)
+            else:
+                arr = np.asarray(e.tokens, dtype=np.int64)
+                token_arrays.append(arr)
+                lo, hi = int(arr.min()), int(arr.max())
+            if lo < 0 or hi >= vocab:
+                raise ValueError(f"request {e.rid!r}: token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab}")
         if not self.can_run(entries):
             raise OutOfPages(f"the step needs more pages or slots than are free ({[p.num_free for p in self.manager.pools]} pages free)")
 
@@ -239,6 +247,9 @@ class ModelRunner:
         for i in range(1, S):
             first_token[i] = first_token[i - 1] + q_lens[i - 1]
         for g in self.tile_groups:
+            if graph_key:                         # one token each: the same tiles for every step of this size
+                tile_lists[(g, "all")] = self._decode_tiles.get(S) or self._decode_tiles.setdefault(S, self._tiles(q_lens, g, 64))
+                continue
             tile_lists[(g, "all")] = self._tiles(q_lens, g, 64)
             if max(q_lens) >= _BIG_PORTION and 128 % g == 0:
                 big = self._tiles(q_lens, g, 256, lambda n: n >= _BIG_PORTION)
@@ -263,45 +274,61 @@ class ModelRunner:
         tables = [take(S * P).reshape(S, P) for _ in range(G)]
         for tl in tile_lists.values():
             o = (o + 3) & ~3                      # the kernel reads a tile as one 16-byte word
-            take(4 * len(tl))[:] = np.asarray(tl, dtype=np.int32).reshape(-1)
-        t = r = 0
-        cu[0] = 0
+            flat = self._decode_tiles_flat.get(len(tl)) if graph_key else None
+            if flat is None:
+                flat = np.asarray(tl, dtype=np.int32).reshape(-1)
+                if graph_key:
+                    self._decode_tiles_flat[len(tl)] = flat
+            take(4 * len(tl))[:] = flat
         wanted_rows: list[int] = []
-        for i in range(S):
-            n = q_lens[i]
-            if i < S_real:
-                e = entries[i]
+        if graph_key:
+            # One token each: everything but the tables is a handful of whole-array assignments.
+            ar = self._arange(S + 1)
+            tok[:S_real] = token_arrays
+            tok[S_real:] = 0
+            pos[:] = starts
+            seq[:] = ar[:S]
+            cu[:] = ar
+            ctx[:] = pos + 1
+            rows[:] = ar[:T]
+            slots[S_real:] = 0
+            for g in range(G):
+                tables[g][S_real:] = NO_PAGE
+            for i, e in enumerate(entries):
+                slots[i] = self.manager.slot(e.rid)
+                for g in range(G):
+                    tables[g][i] = self._table_row(e.rid, g)
+                if e.want:
+                    wanted_rows.append(i)
+        else:
+            t = 0
+            cu[0] = 0
+            for i, e in enumerate(entries):
+                n = q_lens[i]
                 tok[t:t + n] = token_arrays[i]
                 slots[i] = self.manager.slot(e.rid)
-                ver = self.manager.version(e.rid)
                 for g in range(G):
-                    hit = self._table_rows.get((e.rid, g))
-                    if hit is None or hit[0] != ver:          # convert the list once per change, not once per step
-                        row = np.full(P, NO_PAGE, dtype=np.int32)
-                        bt = self.manager.block_table(e.rid, g)
-                        row[:len(bt)] = bt
-                        hit = self._table_rows[(e.rid, g)] = (ver, row)
-                    tables[g][i] = hit[1]
+                    tables[g][i] = self._table_row(e.rid, g)
                 wanted_rows += [t + w for w in e.want]
-            else:
-                tok[t] = 0
-                slots[i] = 0
-                for g in range(G):
-                    tables[g][i, :] = NO_PAGE
-            pos[t:t + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
-            seq[t:t + n] = i
-            t += n
-            cu[i + 1] = t
-            ctx[i] = starts[i] + n
-        if graph_key:
-            rows[:] = np.arange(T, dtype=np.int32)
-        else:
+                pos[t:t + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
+                seq[t:t + n] = i
+                t += n
+                cu[i + 1] = t
+                ctx[i] = starts[i] + n
+        if graph_key is None:
             rows[:] = np.asarray(wanted_rows, dtype=np.int32)
         dev = self._graph_inputs.get(graph_key) if graph_key else None
         if graph_key and dev is None:
             dev = self._graph_inputs[graph_key] = torch.empty(total, dtype=torch.int32, device=self.device)
         st.upload(hi, total, dev)
         self.h2d_bytes += 4 * total
+
+        if graph_key and graph_key in self._graphs:
+            # The recording reads its inputs from the buffer just filled: nothing else to set up.
+            graph, logits, kernels = self._graphs[graph_key]
+            graph.replay()
+            self._graph_launches += kernels
+            return self._after_step(entries, T, self._wanted(logits, wanted_rows))
 
         d = st.dev if dev is None else dev
         o = 0
@@ -329,16 +356,38 @@ class ModelRunner:
             logits = self.model.forward(d_tok, step, self.cache.views, d_rows if R else None)
         else:
             step.plans["span_hint"] = graph_key[1]
-            logits = self._run_graph(graph_key, d_tok, step, d_rows)
-            if not wanted_rows:
-                logits = None
-            elif wanted_rows == list(range(len(wanted_rows))):
-                logits = logits[:len(wanted_rows)]
-            else:
-                logits = logits.index_select(0, torch.tensor(wanted_rows, dtype=torch.long, device=self.device))
+            logits = self._wanted(self._run_graph(graph_key, d_tok, step, d_rows), wanted_rows)
+        return self._after_step(entries, T, logits)
 
-        for e in entries:
-            self.manager.release_behind_window(e.rid)
+    def _table_row(self, rid: Hashable, g: int) -> np.ndarray:
+        """The request's block table of group g as a row of the step's table: converted once per change of the
+        request's pages, not once per step."""
+        ver = self.manager.version(rid)
+        hit = self._table_rows.get((rid, g))
+        if hit is None or hit[0] != ver:
+            row = np.full(self.max_pages_per_seq, NO_PAGE, dtype=np.int32)
+            bt = self.manager.block_table(rid, g)
+            row[:len(bt)] = bt
+            hit = self._table_rows[(rid, g)] = (ver, row)
+        return hit[1]
+
+    def _arange(self, n: int) -> np.ndarray:
+        if self._arange_cache.shape[0] < n:
+            self._arange_cache = np.arange(max(n, 512), dtype=np.int32)
+        return self._arange_cache[:n]
+
+    def _wanted(self, logits: torch.Tensor, wanted_rows: list[int]) -> Optional[torch.Tensor]:
+        """The wanted rows of a recording's logits (it computes one row per token)."""
+        if not wanted_rows:
+            return None
+        if wanted_rows == list(range(len(wanted_rows))):
+            return logits[:len(wanted_rows)]
+        return logits.index_select(0, torch.tensor(wanted_rows, dtype=torch.long, device=self.device))
+
+    def _after_step(self, entries: Sequence[StepEntry], T: int, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        if self._any_window:
+            for e in entries:
+                self.manager.release_behind_window(e.rid)
         self.steps_run += 1
         self.tokens_run += T
         return logits
