@@ -490,8 +490,12 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
 // 16-byte words; tensor memory holds two accumulators (2 x 256 columns), so the epilogue of one tile runs
 // while the tensor cores work on the next.  Tiles are visited with the token tile running fastest, so that
 // CTAs working at the same time share weight tiles in L2.
+//
+// The feature width of a tile is a launch parameter (a multiple of 16 up to 256; 128 or 256 with the fused
+// SwiGLU): with few token tiles, 256 features a tile can leave most SMs without a tile (512 tokens x 4096 features:
+// 64 tiles for 148 SMs), and the launcher picks the width with the smallest waves x width.
 constexpr int PF_BM = 128;       // tokens of a tile (lanes)
-constexpr int PF_BN = 256;       // features of a tile (columns)
+constexpr int PF_BN = 256;       // the most features of a tile (columns of an accumulator)
 constexpr int PF_STAGES = 4;
 
 struct PrefillSmem {
@@ -505,7 +509,7 @@ struct PrefillSmem {
 
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, GemmParams p,
-                            int m_tiles, int num_tiles, int vec_store) {
+                            int m_tiles, int num_tiles, int bn, int vec_store) {
   using L = PrefillSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -520,6 +524,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK - 1) / BK;
+  const uint32_t stage_tx = (uint32_t)(L::A_BYTES + bn * BK * 2);       // bytes a stage receives
   const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
 
   pdl_trigger();
@@ -549,21 +554,21 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       const int first = blockIdx.x;
       const int early = num_kb < PF_STAGES ? num_kb : PF_STAGES;
       for (int i = 0; i < early; ++i) {
-        mbar_expect_tx(full_bar(i), L::STAGE_BYTES);
-        tma_load_2d(smem_base + i * L::STAGE_BYTES + L::A_BYTES, &map_w, i * BK, (first / m_tiles) * PF_BN, full_bar(i));
+        mbar_expect_tx(full_bar(i), stage_tx);
+        tma_load_2d(smem_base + i * L::STAGE_BYTES + L::A_BYTES, &map_w, i * BK, (first / m_tiles) * bn, full_bar(i));
       }
       pdl_wait();
       for (int i = 0; i < early; ++i)
         tma_load_2d(smem_base + i * L::STAGE_BYTES, &map_x, i * BK, (first % m_tiles) * PF_BM, full_bar(i));
       for (int t = 0; t < my_tiles && ok; ++t) {
         const int tile = blockIdx.x + t * gridDim.x;
-        const int m0 = (tile % m_tiles) * PF_BM, n0 = (tile / m_tiles) * PF_BN;
+        const int m0 = (tile % m_tiles) * PF_BM, n0 = (tile / m_tiles) * bn;
         for (int kb = (t == 0 ? early : 0); kb < num_kb; ++kb) {
           const long long use = (long long)t * num_kb + kb;
           const int s = (int)(use % PF_STAGES);
           const uint32_t parity = (uint32_t)((use / PF_STAGES) & 1) ^ 1u;
           if (!mbar_wait(empty_bar(s), parity, abort_flag, ERR_EMPTY_WAIT)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+          mbar_expect_tx(full_bar(s), stage_tx);
           const uint32_t dst = smem_base + s * L::STAGE_BYTES;
           tma_load_2d(dst, &map_x, kb * BK, m0, full_bar(s));
           tma_load_2d(dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
@@ -582,7 +587,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   } else if (warp == 1) {
     // ---- tensor-core issue -----------------------------------------------------------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(PF_BN);
+      const uint32_t idesc = umma_idesc(bn);
       bool ok = true;
       for (int t = 0; t < my_tiles && ok; ++t) {
         const int b = t & 1;
@@ -613,7 +618,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
     for (int t = 0; t < my_tiles && ok; ++t) {
       const int tile = blockIdx.x + t * gridDim.x;
       const int m = (tile % m_tiles) * PF_BM + quarter * 32 + lane;
-      const int n0 = (tile / m_tiles) * PF_BN;
+      const int n0 = (tile / m_tiles) * bn;
       const int b = t & 1;
       ok = mbar_wait(acc_full(b), (uint32_t)((t >> 1) & 1), abort_flag, ERR_ACCUM_WAIT);
       ok = __all_sync(0xffffffffu, ok);
@@ -623,7 +628,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       if (p.swiglu) {
         // columns [128b, 128b+64) are gate rows, [128b+64, 128b+128) the up rows of the same 64 features
 #pragma unroll 1
-        for (int cc = 0; cc < PF_BN / 2; cc += 16) {
+        for (int cc = 0; cc < bn / 2; cc += 16) {
           const int c = (cc >> 6) * 128 + (cc & 63);
           uint32_t g[16], u[16];
           tmem_ld16(taddr + c, g);
@@ -663,7 +668,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
         }
       } else
 #pragma unroll 2
-      for (int c = 0; c < PF_BN; c += 16) {
+      for (int c = 0; c < bn; c += 16) {
         uint32_t r[16];
         tmem_ld16(taddr + c, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -712,8 +717,28 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   }
 }
 
+// The feature width of the tiles: 256 unless a narrower multiple of 16 (of 128 with the fused SwiGLU, whose gate and
+// up rows come in blocks of 64) needs clearly less waves x (width + 64); the 64 stand for what a tile costs whatever
+// its width (its token tile is loaded again for every feature tile, and narrow MMAs use the tensor cores less well).
+// Measured at 8B sizes: 512 x 4096 x 4096 27.6 -> 23.4 us (width 144), 2048 x 6144 x 4096 81.3 -> 80.0 (240); with
+// ten waves and more a narrower tile only lost (2048 x 24576 x 4096, width 224: 305 -> 314 us), hence the margin.
+static int prefill_tile_width(int m_tiles, int N, int swiglu, int num_sms) {
+  auto cost = [&](int bn) {
+    const long long tiles = (long long)m_tiles * ((N + bn - 1) / bn);
+    return ((tiles + num_sms - 1) / num_sms) * (long long)(bn + 64);
+  };
+  int best = PF_BN;
+  long long best_cost = cost(PF_BN) * 93 / 100;          // a narrower tile has to win by 7 %
+  for (int bn = PF_BN - (swiglu ? 128 : 16); bn >= 64; bn -= swiglu ? 128 : 16) {
+    const long long c = cost(bn);
+    if (c < best_cost) { best = bn; best_cost = c; }
+  }
+  return best;
+}
+
+// force_bn: 0 choose, else the feature width of the tiles (tests).
 static int launch_prefill(const void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
-                          long long ldy, int swiglu, cudaStream_t stream) {
+                          long long ldy, int swiglu, int force_bn, cudaStream_t stream) {
   static int num_sms = 0;
   if (num_sms == 0) {
     int dev = 0;
@@ -721,15 +746,17 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     if (num_sms <= 0) num_sms = 148;
   }
+  const int m_tiles = (M + PF_BM - 1) / PF_BM;
+  const int bn = force_bn ? force_bn : prefill_tile_width(m_tiles, N, swiglu, num_sms);
   CUtensorMap mx, mw;
-  if (!cached_map(&mx, x, M, K, ldx, PF_BM) || !cached_map(&mw, w, N, K, K, PF_BN)) {
+  if (!cached_map(&mx, x, M, K, ldx, PF_BM) || !cached_map(&mw, w, N, K, K, bn)) {
     set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);
     return 3;
   }
   GemmParams p;
   p.y = const_cast<void*>(y); p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = ldy;
   p.out_dtype = y_dtype; p.cluster = 0; p.swiglu = swiglu;
-  const int m_tiles = (M + PF_BM - 1) / PF_BM, n_tiles = (N + PF_BN - 1) / PF_BN;
+  const int n_tiles = (N + bn - 1) / bn;
   const int num_tiles = m_tiles * n_tiles;
   const int el = y_dtype == LB_F32 ? 4 : 2;
   const int vec_store = ((uintptr_t)y % 16 == 0) && ((ldy * el) % 16 == 0);
@@ -741,7 +768,7 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
     configured = true;
   }
   const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-  launch(gemm_tcgen05_prefill_kernel, dim3(grid), dim3(192), smem, stream, mx, mw, p, m_tiles, num_tiles, vec_store);
+  launch(gemm_tcgen05_prefill_kernel, dim3(grid), dim3(192), smem, stream, mx, mw, p, m_tiles, num_tiles, bn, vec_store);
   return 0;
 }
 
@@ -797,8 +824,12 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   LB_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0, "gemm_tcgen05: K=%d and the row stride %lld must be multiples of 8 (TMA strides are multiples of 16 bytes)", K, ldx);
   LB_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
   if (M == 0) return 0;
-  if (M > 256 && force_bt == 0 && force_splits == 0) {
-    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, stream)) return rc;
+  if (M > 256 && force_bt == 0) {
+    // with many tokens force_splits stands for the feature width of the tiles (0: choose)
+    LB_CHECK_ARG(force_splits == 0 || (force_splits >= 16 && force_splits <= lb::PF_BN && force_splits % 16 == 0 &&
+                                       (!swiglu || force_splits % 128 == 0)),
+                 "gemm_tcgen05: tile width %d is no multiple of 16 (128 with SwiGLU) up to 256", force_splits);
+    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, force_splits, stream)) return rc;
     LB_CHECK_LAUNCH("gemm_tcgen05 (many tokens)");
     return 0;
   }

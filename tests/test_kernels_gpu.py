@@ -399,6 +399,9 @@ def test_gemm_plain_is_true_32_bit(env):
     (200, 384, 2048, 256, 4), (3, 130, 8192, 16, 16),
     # more than 256 tokens: the persistent kernel (tokens on the lanes, two accumulators)
     (2048, 512, 4096, 0, 0), (1000, 300, 136, 0, 0), (257, 6144, 64, 0, 0), (5000, 260, 520, 0, 0), (640, 1030, 1024, 0, 0),
+    # the same with a given feature width of the tiles (here `splits` stands for it): narrow, odd multiples of 16, the widest
+    (2048, 512, 4096, 0, 128), (384, 4096, 1024, 0, 144), (1000, 300, 136, 0, 64), (640, 1030, 1024, 0, 240), (512, 4096, 512, 0, 16),
+    (576, 4096, 1024, 0, 0), (512, 1000, 2048, 0, 256),
 ])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
@@ -418,7 +421,8 @@ def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
 
 
 @pytest.mark.parametrize("M,I,K,bt,splits", [(5, 128, 96, 0, 0), (16, 256, 1024, 16, 4), (40, 640, 512, 64, 1), (8, 12288, 512, 0, 0),
-                                             (64, 192, 2048, 0, 0), (300, 320, 264, 0, 0), (2048, 1024, 256, 0, 0), (700, 64, 4096, 0, 0)])
+                                             (64, 192, 2048, 0, 0), (300, 320, 264, 0, 0), (2048, 1024, 256, 0, 0), (700, 64, 4096, 0, 0),
+                                             (700, 1024, 2048, 0, 128), (512, 2048, 512, 0, 0)])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05_with_swiglu_epilogue(env, M, I, K, bt, splits, ty):
     """gate and up rows interleaved in blocks of 64; the product's epilogue forms silu(gate) * up."""
@@ -432,7 +436,9 @@ def test_gemm_tcgen05_with_swiglu_epilogue(env, M, I, K, bt, splits, ty):
     torch.cuda.synchronize()
     assert ops.device_error() == 0
     want = plain.swiglu(x.double() @ gate.double().t(), x.double() @ up.double().t())
-    assert rel(y, want) < (1e-5 if ty == torch.float32 else 5e-3)
+    # float32 out: the rounding of two 32-bit accumulations (it grows like sqrt(K)) meets in the product silu(gate) * up
+    tol = 4e-6 * max(1.0, math.sqrt(K / 256)) if ty == torch.float32 else 5e-3
+    assert rel(y, want) < tol
 
 
 def test_gemm_tcgen05_refuses_what_it_cannot_do(env):
