@@ -231,7 +231,9 @@ flash_attention_kernel(FlashParams p) {
     }
 
     // ---- mask, online softmax ----------------------------------------------------------------
-    const bool need_mask = (kbase + FA_KEYS - 1 > pos0) || (p.window > 0) || (kbase + FA_KEYS > kend) || (rows < FA_ROWS);
+    // Rows past the tile's last (zero queries, positions -1) need no mask of their own: what they gather is never
+    // written, and it is finite, because keys and values of slots that hold nothing lie at or past kend.
+    const bool need_mask = (kbase + FA_KEYS - 1 > pos0) || (p.window > 0) || (kbase + FA_KEYS > kend);
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
@@ -271,9 +273,12 @@ flash_attention_kernel(FlashParams p) {
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * alpha[h] + row_sum[h];
+    // Once the maxima have settled the factors are exactly 1 for stage after stage: skip the multiplications then.
+    if (!__all_sync(0xffffffffu, alpha[0] == 1.f && alpha[1] == 1.f)) {
 #pragma unroll
-    for (int i = 0; i < DP / 8; ++i) {
-      o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      for (int i = 0; i < DP / 8; ++i) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      }
     }
 
     // ---- O += P V ----------------------------------------------------------------------------------
