@@ -170,6 +170,14 @@ __device__ __forceinline__ void ta_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uin
                ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// Two float32 in one 64-bit register for the packed instructions of sm_100 (one issue slot for two elements).
+__device__ __forceinline__ uint64_t ta_pack2(float a, float b) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void ta_unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t ta_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d;
+}
+__device__ __forceinline__ uint64_t ta_add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ float ta_max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
 enum : int { TA_ERR_Q = 301, TA_ERR_KV_FULL = 302, TA_ERR_KV_EMPTY = 303, TA_ERR_S_FULL = 304, TA_ERR_S_EMPTY = 305,
              TA_ERR_P_FULL = 306, TA_ERR_P_EMPTY = 307, TA_ERR_O_FULL = 308 };
 
@@ -417,11 +425,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
           if (key > row_pos || key < row_lo) x[j] = -INFINITY;
         }
       }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one of 128 dependent maxima
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains of three-input maxima
 #pragma unroll
-      for (int j = 0; j < TA_KEYS; j += 4) {
+      for (int j = 0; j < TA_KEYS; j += 8) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], x[j + u]);
+        for (int u = 0; u < 4; ++u) mx4[u] = ta_max3(mx4[u], x[j + 2 * u], x[j + 2 * u + 1]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // The reference follows the maximum only when that has grown much; then O (complete up to block i-1, since
@@ -449,22 +457,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       // p = 2^(s * scale - m), the row's sum, P (two keys a column) over the first 64 columns of S
-      float sum2[2] = {0.f, 0.f};
+      // Pairs of keys in packed instructions.  (Tried: a cubic for 2^f on the FMA pipe for half or a quarter of the
+      // pairs, to take load off the special-function unit.  Slower: the softmax warps are short of issue slots, not
+      // of that unit.)
+      const uint64_t scale2 = ta_pack2(p.scale_log2, p.scale_log2), negm2 = ta_pack2(-m_use, -m_use);
+      uint64_t sum2 = ta_pack2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < TA_KEYS; c += 64) {
         uint32_t w[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const float p0 = exp2_approx(fmaf(x[c + 2 * j], p.scale_log2, -m_use));
-          const float p1 = exp2_approx(fmaf(x[c + 2 * j + 1], p.scale_log2, -m_use));
-          sum2[0] += p0; sum2[1] += p1;
+          float y0, y1;
+          ta_unpack2(ta_fma2(ta_pack2(x[c + 2 * j], x[c + 2 * j + 1]), scale2, negm2), y0, y1);
+          const float p0 = exp2_approx(y0), p1 = exp2_approx(y1);          // 2^-inf = 0 for masked keys
+          sum2 = ta_add2(sum2, ta_pack2(p0, p1));
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           w[j] = *reinterpret_cast<uint32_t*>(&b2);
         }
         ta_tmem_st32(s_addr + (uint32_t)(c >> 1), w);
       }
       ta_tmem_wait_st();
-      l_run += sum2[0] + sum2[1];
+      {
+        float s0, s1;
+        ta_unpack2(sum2, s0, s1);
+        l_run += s0 + s1;
+      }
       // hand P to the tensor cores
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
