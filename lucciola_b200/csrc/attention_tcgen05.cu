@@ -372,7 +372,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
           for (int k = 0; k < 8; ++k)                  // 16 keys a step: 8 columns of P, 16 rows of V
             ta_umma_ts(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u + (uint32_t)k * 8u,
                        ta_desc_mnmajor(va + (uint32_t)k * 16u * 128u, TA_HALF_BYTES), idesc_pv, (i | k) != 0);
-          ta_commit(o_done(t));
+          if (i == nblocks - 1) ta_commit(o_done(t));            // O is read once, after the last block
           if (t == ntiles - 1) ta_commit(v_empty(s));
           // S_t of the next block overwrites P_t: issued behind P V, which the tensor cores finish first
           if (i + 1 < nblocks) {
@@ -487,7 +487,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
       __syncwarp();
       if (lane == 0) ta_mbar_arrive(p_full(t));
     }
-    if (ok) ok = ta_mbar_wait(o_done(t), (uint32_t)((nblocks - 1) & 1), abort_flag, TA_ERR_O_FULL);
+    if (ok) ok = ta_mbar_wait(o_done(t), 0, abort_flag, TA_ERR_O_FULL);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
