@@ -1,16 +1,16 @@
 // Causal grouped-query attention for portions of prompts on the 5th-generation tensor cores
-// (bfloat16, head size 128, page sizes 8..128 that divide 128).
+// (bfloat16, head size 128, page sizes 8..128 that are powers of two).
 //
 // A work item is a run of up to 256/G consecutive tokens of one request and one kv head (G = query
 // heads per kv head): its G*tokens query rows form TWO tiles of 128 rows, A and B, that share the keys
-// and values the CTA loads (half the traffic from L2 per query row) and run as two pipelines a half
-// period apart, so that the tensor cores work for one tile while the other tile's softmax runs.
-// Keys and values are visited in blocks of 128 keys.  Per block and tile
-//     S = Q K^T          tcgen05.mma, both operands K-major from shared memory, S (128 x 128 float32) in
-//                        tensor memory
+// and values the CTA loads (half the traffic from L2 per query row).  Keys and values are visited in
+// blocks of 64 keys.  Per block and tile
+//     S = Q K^T          tcgen05.mma, both operands K-major from shared memory, S (128 x 64 float32) in
+//                        tensor memory, TWO S buffers a tile: Q K^T of block i+1 is done while the softmax
+//                        of block i runs
 //     P = softmax part   four warps, ONE THREAD PER QUERY ROW: the thread reads its row of S with tcgen05.ld,
 //                        needs no shuffles for the row's maximum and sum, and writes its row of P (bfloat16,
-//                        two keys a column) with tcgen05.st over the first 64 columns of S
+//                        two keys a column) with tcgen05.st over the first 32 columns of that S buffer
 //     O += P V           tcgen05.mma, P from TENSOR MEMORY, V MN-major from shared memory (as it lies in the
 //                        pages), O (128 x 128 float32) accumulated in tensor memory over all blocks
 // The formulas are the online softmax of src/kernels/flash_attention.cu:246-298 of lucciola (m, l, o per
@@ -20,14 +20,16 @@
 // per block; p <= 2^8 then, and O / l is the same quotient whatever m was.
 // The queries come through TMA, one three-dimensional box per tile and half (head size, heads of the
 // group, tokens).  Keys and values come through cp.async, 16 bytes a thread and instruction, written in the
-// 128-byte swizzle the tensor cores read, into rings of two blocks, keys and values apart, one warp each:
-// with pages of 16 tokens a TMA box is 2 KB, a block needs 32 of them, and a CTA issues a box in about 125
-// cycles, which made the producer the slowest part of the pipeline (4000 of its 4400 cycles a block).
+// 128-byte swizzle the tensor cores read, into rings of four blocks, keys and values apart, one warp each
+// with three blocks in flight: with pages of 16 tokens a TMA box is 2 KB, a CTA issues a box in about 125
+// cycles, and the boxes alone took longer than the tensor cores need for a block.
 //
-// Warp roles (352 threads): warp 0 loads the queries and the keys, warp 10 the values, warp 1 issues to the
-// tensor cores (one thread) and owns the tensor memory, warps 2..5 softmax of tile A, warps 6..9 of tile B.  The tensor cores execute what
-// one thread issues in order, which is what orders P V of block i before Q K^T of block i+1 overwrites
-// the columns P lies in, and O's rescaling (after S of block i is complete, so P V of block i-1 is too).
+// Warp roles (384 threads): warp 0 loads the queries and the keys, warp 10 the values; warp 1 issues tile A's
+// products to the tensor cores (one thread) and owns the tensor memory, warp 11 issues tile B's; warps 2..5
+// softmax of tile A, warps 6..9 of tile B.  One issuing thread per tile, because between two products of a
+// tile stand three waits and as many commits: with one thread for both tiles those alone filled the time the
+// tensor cores need for a block.  The tensor cores execute what one thread issues in order, which is what
+// orders P V of block i before Q K^T of block i+2 overwrites the columns P lies in.
 // Every wait on an mbarrier is bounded; when one gives up the CTA records it and leaves.
 //
 // Key and value rows outside the range a work item may see (past the last key, before the window, pages
@@ -45,7 +47,7 @@ __device__ int g_attention_tc_error = 0;
 
 constexpr int TA_D = 128;                 // head size
 constexpr int TA_ROWS = 128;              // query rows of a tile
-constexpr int TA_KEYS = 128;              // keys of a block
+constexpr int TA_KEYS = 64;               // keys of a block
 constexpr int TA_HALF_BYTES = 128 * 128;  // 128 rows of 128 bytes (64 bfloat16): one half of a 128-wide tile
 constexpr int TA_TILE_BYTES = 2 * TA_HALF_BYTES;
 constexpr unsigned long long TA_WAIT_CYCLES = 4000000000ull;
@@ -123,9 +125,9 @@ __device__ __forceinline__ uint64_t ta_desc_mnmajor(uint32_t addr, uint32_t lbo)
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
          (2ull << 61);
 }
-// D float32, A and B bfloat16, A K-major, B K-major (b_mn = 0) or MN-major (1), M = 128, N = 128.
-__host__ __device__ constexpr uint32_t ta_idesc(int b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// D float32, A and B bfloat16, A K-major, B K-major (b_mn = 0) or MN-major (1), M = 128, N = n.
+__host__ __device__ constexpr uint32_t ta_idesc(int b_mn, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 __device__ __forceinline__ void ta_umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -181,55 +183,47 @@ __device__ __forceinline__ float ta_max3(float a, float b, float c) { float d; a
 enum : int { TA_ERR_Q = 301, TA_ERR_KV_FULL = 302, TA_ERR_KV_EMPTY = 303, TA_ERR_S_FULL = 304, TA_ERR_S_EMPTY = 305,
              TA_ERR_P_FULL = 306, TA_ERR_P_EMPTY = 307, TA_ERR_O_FULL = 308 };
 
-// Shared memory: Q of tile A, Q of tile B (2 halves each) | K ring of 2 blocks | V ring of 2 blocks | barriers | page ids.
-// A 128 x 128 bfloat16 tile is two halves of 128 rows x 128 bytes (64 elements); within a half the 16-byte chunk c
-// of row r lies at r * 128 + ((c ^ (r & 7)) << 4).
+// Shared memory: Q of tile A, Q of tile B | K ring of 4 blocks | V ring of 4 blocks | barriers | page ids.
+// A tile of R rows x 128 bfloat16 is two halves of R rows x 128 bytes (64 elements); within a half the 16-byte
+// chunk c of row r lies at r * 128 + ((c ^ (r & 7)) << 4).  R = 128 for Q, 64 for a block of keys or values.
+constexpr int TA_STAGES = 4;
+constexpr int TA_KV_HALF = TA_KEYS * 128;                      // one half of a block of keys: 8 KB
+constexpr int TA_KV_TILE = 2 * TA_KV_HALF;                     // 16 KB
 constexpr int TA_Q_OFF = 0;
 constexpr int TA_K_OFF = 2 * TA_TILE_BYTES;                    // 64 KB
-constexpr int TA_V_OFF = TA_K_OFF + 2 * TA_TILE_BYTES;         // 128 KB
-constexpr int TA_BAR_OFF = TA_V_OFF + 2 * TA_TILE_BYTES;       // 192 KB
-constexpr int TA_NUM_BARS = 15;
+constexpr int TA_V_OFF = TA_K_OFF + TA_STAGES * TA_KV_TILE;    // 128 KB
+constexpr int TA_BAR_OFF = TA_V_OFF + TA_STAGES * TA_KV_TILE;  // 192 KB
+constexpr int TA_NUM_BARS = 1 + 4 * TA_STAGES + 2 * 6;
 constexpr int TA_MAX_TILE_PAGES = 4096;                        // pages a tile's keys may span (32 K keys of 8-token pages)
 constexpr int TA_PAGES_OFF = TA_BAR_OFF + TA_NUM_BARS * 8 + 16;
 constexpr int TA_SMEM_BYTES = TA_PAGES_OFF + TA_MAX_TILE_PAGES * 4;
-constexpr int TA_THREADS = 352;
+constexpr int TA_THREADS = 384;
+constexpr int TA_IN_FLIGHT = 2;                                // blocks a producer warp has requested beyond the one it waits for
 constexpr float TA_RESCALE_STEP = 8.f;                         // log2 of the growth of a row's maximum that moves its reference
 
-// One block of 128 keys (or values) of one kv head from the pages into a stage of the ring, by one warp.  A lane
-// copies chunk c (16 bytes) of every second row: rows rp, rp + 2, ... of every page.  `ring_lane` is the stage's
-// address plus the lane's fixed part (its half of the head and row rp); xr[u] the swizzled chunk offset of the
-// rows rp + 2u (mod 8).  Rows the work item may not see, and pages that are not there, are filled with zeros.
+// One block of 64 keys (or values) of one kv head from the pages into a stage of the ring, by one warp.  A lane
+// copies chunk c (16 bytes) of every second row: rows rp, rp + 2, ...  `ring_lane` is the stage's address plus the
+// lane's fixed part (its half of the head and row rp); xr[u] the swizzled chunk offset of the rows rp + 2u (mod 8).
+// Rows the work item may not see, and pages that are not there, are filled with zeros.  PS: tokens of a page, at
+// most 64 here (a page of 128 is walked as two of 64: `sub` is the half the block lies in).
 template <int PS>
 __device__ __forceinline__ void ta_copy_block(uint32_t ring_lane, const uint32_t (&xr)[4], const uint8_t* pool_lane, const int* blk_pages,
-                                              int kb, int lo_tile, int kend, size_t page_stride, size_t head_off, int rp) {
+                                              int kb, int lo_tile, int kend, size_t page_stride, size_t head_off, int rp, int sub) {
   const bool inner = kb >= lo_tile && kb + TA_KEYS <= kend;           // every key of the block may be seen
   uint32_t dst_u[4];
 #pragma unroll
   for (int u = 0; u < 4; ++u) dst_u[u] = ring_lane + xr[u];
-  if (inner) {
 #pragma unroll
-    for (int pg = 0; pg < TA_KEYS / PS; ++pg) {
-      const int page = blk_pages[pg];
-      const uint8_t* src = pool_lane + (size_t)max(page, 0) * page_stride + head_off;
-      const uint32_t bytes = page >= 0 ? 16u : 0u;
+  for (int pg = 0; pg < TA_KEYS / PS; ++pg) {
+    const int key0 = kb + pg * PS;
+    const int page = (inner || (key0 + PS > lo_tile && key0 < kend)) ? blk_pages[pg] : -1;
+    const uint8_t* src = pool_lane + (size_t)max(page, 0) * page_stride + head_off + (size_t)sub * (64 * 256);
 #pragma unroll
-      for (int j = 0; j < PS / 2; ++j)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                     ::"r"(dst_u[j & 3] + (uint32_t)(pg * PS * 128 + j * 256)), "l"(src + (size_t)j * 512u), "r"(bytes) : "memory");
-    }
-  } else {
-#pragma unroll 1
-    for (int pg = 0; pg < TA_KEYS / PS; ++pg) {
-      const int key0 = kb + pg * PS;
-      const int page = (key0 + PS > lo_tile && key0 < kend) ? blk_pages[pg] : -1;
-      const uint8_t* src = pool_lane + (size_t)max(page, 0) * page_stride + head_off;
-#pragma unroll
-      for (int j = 0; j < PS / 2; ++j) {
-        const int key = key0 + rp + 2 * j;
-        const uint32_t bytes = (page >= 0 && key >= lo_tile && key < kend) ? 16u : 0u;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                     ::"r"(dst_u[j & 3] + (uint32_t)(pg * PS * 128 + j * 256)), "l"(src + (size_t)j * 512u), "r"(bytes) : "memory");
-      }
+    for (int j = 0; j < PS / 2; ++j) {
+      const int key = key0 + rp + 2 * j;
+      const uint32_t bytes = (page >= 0 && (inner || (key >= lo_tile && key < kend))) ? 16u : 0u;       // 0: sixteen zeros
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                   ::"r"(dst_u[j & 3] + (uint32_t)(pg * PS * 128 + j * 256)), "l"(src + (size_t)j * 512u), "r"(bytes) : "memory");
     }
   }
 }
@@ -242,12 +236,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
   const uint32_t bars = sbase + TA_BAR_OFF;
   const uint32_t q_full = bars;
   auto k_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto k_empty = [&](int s) { return bars + 8u * (3 + s); };
-  auto v_full = [&](int s) { return bars + 8u * (5 + s); };
-  auto v_empty = [&](int s) { return bars + 8u * (7 + s); };
-  auto s_full = [&](int t) { return bars + 8u * (9 + t); };      // per tile
-  auto p_full = [&](int t) { return bars + 8u * (11 + t); };
-  auto o_done = [&](int t) { return bars + 8u * (13 + t); };
+  auto k_empty = [&](int s) { return bars + 8u * (1 + TA_STAGES + s); };
+  auto v_full = [&](int s) { return bars + 8u * (1 + 2 * TA_STAGES + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (1 + 3 * TA_STAGES + s); };
+  // per tile t and S buffer b: S complete, P written, P V complete
+  auto s_full = [&](int t, int b) { return bars + 8u * (1 + 4 * TA_STAGES + t * 6 + b); };
+  auto p_full = [&](int t, int b) { return bars + 8u * (1 + 4 * TA_STAGES + t * 6 + 2 + b); };
+  auto pv_done = [&](int t, int b) { return bars + 8u * (1 + 4 * TA_STAGES + t * 6 + 4 + b); };
   uint32_t* tmem_slot = (uint32_t*)(smem + TA_BAR_OFF + TA_NUM_BARS * 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -258,15 +253,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
   const int kvh = blockIdx.x, G = p.group;
   const int per = TA_ROWS / G;                  // tokens of a 128-row tile
   const bool two = ntok > per;                  // is there a tile B
+  const int ntiles = two ? 2 : 1;
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     ta_mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      ta_mbar_init(k_full(i), 1); ta_mbar_init(k_empty(i), 1);
-      ta_mbar_init(v_full(i), 1); ta_mbar_init(v_empty(i), 1);
-      ta_mbar_init(s_full(i), 1); ta_mbar_init(p_full(i), 4); ta_mbar_init(o_done(i), 1);
+    for (int i = 0; i < TA_STAGES; ++i) {
+      ta_mbar_init(k_full(i), 1); ta_mbar_init(k_empty(i), ntiles);       // a stage goes back when every tile's product has read it
+      ta_mbar_init(v_full(i), 1); ta_mbar_init(v_empty(i), ntiles);
     }
+    for (int t = 0; t < 2; ++t)
+      for (int b = 0; b < 2; ++b) { ta_mbar_init(s_full(t, b), 1); ta_mbar_init(p_full(t, b), 4); ta_mbar_init(pv_done(t, b), 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -277,7 +274,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = *tmem_slot;            // columns: S/P of tile A +0, of tile B +128; O of tile A +256, of tile B +384
+  const uint32_t tmem = *tmem_slot;            // columns: tile t's S buffers at t * 128 and t * 128 + 64 (P over their first 32), O at 256 + t * 128
 
   pdl_wait();                                   // everything below reads what earlier kernels wrote
   const int pos0 = p.positions[t0];
@@ -287,7 +284,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
   const int kend = pos_last + 1;                // exclusive
   const int nblocks = (kend - kbeg + TA_KEYS - 1) / TA_KEYS;
   const int* bt = p.block_table + (size_t)seq * p.max_pages;
-  // The page ids of the keys this work item visits, copied once into shared memory for the producer.
+  // The page ids of the keys this work item visits, copied once into shared memory for the producers.
   int* spages = reinterpret_cast<int*>(smem + TA_PAGES_OFF);
   const int first_page = kbeg >> p.page_shift;
   const int num_tile_pages = min(((kend - 1) >> p.page_shift) - first_page + 1, TA_MAX_TILE_PAGES);
@@ -298,8 +295,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
     // ---- producers: warp 0 the queries (TMA) and the keys, warp 10 the values ---------------------------------
     const bool is_v = warp == 10;
     if (!is_v && lane == 0) {
-      ta_mbar_expect_tx(q_full, (two ? 2u : 1u) * TA_TILE_BYTES);
-      for (int t = 0; t < (two ? 2 : 1); ++t) {
+      ta_mbar_expect_tx(q_full, (uint32_t)ntiles * TA_TILE_BYTES);
+      for (int t = 0; t < ntiles; ++t) {
         ta_tma_3d(sbase + TA_Q_OFF + t * TA_TILE_BYTES, &map_q, 0, kvh * G, t0 + t * per, q_full);
         ta_tma_3d(sbase + TA_Q_OFF + t * TA_TILE_BYTES + TA_HALF_BYTES, &map_q, 64, kvh * G, t0 + t * per, q_full);
       }
@@ -311,79 +308,78 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
     uint32_t xr[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) xr[u] = (uint32_t)(((c & 7) ^ ((rp + 2 * u) & 7)) << 4);
-    const uint32_t ring = sbase + (is_v ? TA_V_OFF : TA_K_OFF) + (uint32_t)(c >> 3) * TA_HALF_BYTES + (uint32_t)rp * 128u;
-    for (int i = 0; i < nblocks; ++i) {
-      const int s = i & 1;
-      int go = 1;
-      if (lane == 0)
-        go = ta_mbar_wait_idle(is_v ? v_empty(s) : k_empty(s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag, TA_ERR_KV_EMPTY) ? 1 : 0;
-      go = __shfl_sync(0xffffffffu, go, 0);
-      if (!go) break;
-      const int kb = kbeg + i * TA_KEYS;
-      const int* blk_pages = spages + ((kb - kbeg) >> p.page_shift);
-      const uint32_t stage = ring + (uint32_t)s * TA_TILE_BYTES;
-      switch (ps) {
-        case 8: ta_copy_block<8>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
-        case 16: ta_copy_block<16>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
-        case 32: ta_copy_block<32>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
-        case 64: ta_copy_block<64>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
-        default: ta_copy_block<128>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp); break;
+    const uint32_t ring = sbase + (is_v ? TA_V_OFF : TA_K_OFF) + (uint32_t)(c >> 3) * TA_KV_HALF + (uint32_t)rp * 128u;
+    // Block i is requested, then block i - TA_IN_FLIGHT is waited for and handed over: three blocks in flight.
+    bool go_on = true;
+    for (int i = 0; i < nblocks + TA_IN_FLIGHT && go_on; ++i) {
+      if (i < nblocks) {
+        const int s = i % TA_STAGES;
+        int go = 1;
+        if (lane == 0)
+          go = ta_mbar_wait_idle(is_v ? v_empty(s) : k_empty(s), (uint32_t)((i / TA_STAGES) & 1) ^ 1u, abort_flag, TA_ERR_KV_EMPTY) ? 1 : 0;
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) { go_on = false; break; }
+        const int kb = kbeg + i * TA_KEYS;
+        const int* blk_pages = spages + ((kb >> p.page_shift) - first_page);
+        const uint32_t stage = ring + (uint32_t)s * TA_KV_TILE;
+        switch (ps) {
+          case 8: ta_copy_block<8>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp, 0); break;
+          case 16: ta_copy_block<16>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp, 0); break;
+          case 32: ta_copy_block<32>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp, 0); break;
+          default: ta_copy_block<64>(stage, xr, pool_lane, blk_pages, kb, lo_tile, kend, page_stride, head_off, rp, ps == 128 ? (kb >> 6) & 1 : 0); break;
+        }
       }
-      // the block has landed: make it visible to the tensor cores' reads, then say so
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) ta_mbar_arrive(is_v ? v_full(s) : k_full(s));
+      asm volatile("cp.async.commit_group;" ::: "memory");          // (an empty group past the last block)
+      if (i >= TA_IN_FLIGHT) {
+        // block i - TA_IN_FLIGHT has landed: make it visible to the tensor cores' reads, then say so
+        asm volatile("cp.async.wait_group %0;" ::"n"(TA_IN_FLIGHT) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        const int s = (i - TA_IN_FLIGHT) % TA_STAGES;
+        if (lane == 0) ta_mbar_arrive(is_v ? v_full(s) : k_full(s));
+      }
     }
-  } else if (warp == 1) {
-    // ---- tensor-core issue ---------------------------------------------------------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = ta_idesc(0), idesc_pv = ta_idesc(1);
-      const int ntiles = two ? 2 : 1;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else if (warp == 1 || warp == 11) {
+    // ---- tensor-core issue, one thread per tile --------------------------------------------------------------
+    const int t = warp == 1 ? 0 : 1;
+    if (lane == 0 && t < ntiles) {
+      constexpr uint32_t idesc_qk = ta_idesc(0, TA_KEYS), idesc_pv = ta_idesc(1, TA_D);
+      const uint32_t s_col = tmem + (uint32_t)t * 128u, o_col = tmem + 256u + (uint32_t)t * 128u;
+      const uint32_t qa = sbase + TA_Q_OFF + t * TA_TILE_BYTES;
       bool ok = ta_mbar_wait(q_full, 0, abort_flag, TA_ERR_Q);
-      // S_t = Q_t K(i)^T; the keys' buffer goes back after the last tile's product
-      auto issue_qk = [&](int t, int i) {
-        const int s = i & 1;
-        const uint32_t qa = sbase + TA_Q_OFF + t * TA_TILE_BYTES, ka = sbase + TA_K_OFF + s * TA_TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t o = (uint32_t)(k >> 2) * TA_HALF_BYTES + (uint32_t)(k & 3) * 32u;
-          ta_umma(tmem + (uint32_t)t * 128u, ta_desc_kmajor(qa + o), ta_desc_kmajor(ka + o), idesc_qk, k != 0);
-        }
-        ta_commit(s_full(t));
-        if (t == ntiles - 1) ta_commit(k_empty(s));
-      };
-      if (ok) ok = ta_mbar_wait(k_full(0), 0, abort_flag, TA_ERR_KV_FULL);
-      if (ok) {
+      // S(j) = Q K(j)^T into S buffer j & 1; the keys' stage goes back when every tile's product is done
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j % TA_STAGES;
+        if (!ta_mbar_wait(k_full(s), (uint32_t)((j / TA_STAGES) & 1), abort_flag, TA_ERR_KV_FULL)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int t = 0; t < ntiles; ++t) issue_qk(t, 0);
-      }
-      for (int i = 0; i < nblocks && ok; ++i) {
-        const int s = i & 1;
-        for (int t = 0; t < ntiles && ok; ++t) {
-          // O_t += P_t(i) V(i)
-          ok = ta_mbar_wait(p_full(t), (uint32_t)(i & 1), abort_flag, TA_ERR_P_FULL);
-          if (!ok) break;
-          if (t == 0) { ok = ta_mbar_wait(v_full(s), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_KV_FULL); if (!ok) break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t va = sbase + TA_V_OFF + s * TA_TILE_BYTES;
+        const uint32_t ka = sbase + TA_K_OFF + s * TA_KV_TILE;
 #pragma unroll
-          for (int k = 0; k < 8; ++k)                  // 16 keys a step: 8 columns of P, 16 rows of V
-            ta_umma_ts(tmem + 256u + (uint32_t)t * 128u, tmem + (uint32_t)t * 128u + (uint32_t)k * 8u,
-                       ta_desc_mnmajor(va + (uint32_t)k * 16u * 128u, TA_HALF_BYTES), idesc_pv, (i | k) != 0);
-          if (i == nblocks - 1) ta_commit(o_done(t));            // O is read once, after the last block
-          if (t == ntiles - 1) ta_commit(v_empty(s));
-          // S_t of the next block overwrites P_t: issued behind P V, which the tensor cores finish first
-          if (i + 1 < nblocks) {
-            if (t == 0) {
-              ok = ta_mbar_wait(k_full(s ^ 1), (uint32_t)(((i + 1) >> 1) & 1), abort_flag, TA_ERR_KV_FULL);
-              if (!ok) break;
-              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            issue_qk(t, i + 1);
-          }
-        }
+        for (int k = 0; k < 8; ++k)
+          ta_umma(s_col + (uint32_t)(j & 1) * 64u, ta_desc_kmajor(qa + (uint32_t)(k >> 2) * TA_HALF_BYTES + (uint32_t)(k & 3) * 32u),
+                  ta_desc_kmajor(ka + (uint32_t)(k >> 2) * TA_KV_HALF + (uint32_t)(k & 3) * 32u), idesc_qk, k != 0);
+        ta_commit(s_full(t, j & 1));
+        ta_commit(k_empty(s));
+        return true;
+      };
+      for (int j = 0; j < 2 && j < nblocks && ok; ++j) ok = issue_qk(j);
+      for (int i = 0; i < nblocks && ok; ++i) {
+        const int s = i % TA_STAGES, b = i & 1;
+        // O += P(i) V(i)
+        ok = ta_mbar_wait(p_full(t, b), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_P_FULL);
+        if (!ok) break;
+        ok = ta_mbar_wait(v_full(s), (uint32_t)((i / TA_STAGES) & 1), abort_flag, TA_ERR_KV_FULL);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t va = sbase + TA_V_OFF + s * TA_KV_TILE;
+#pragma unroll
+        for (int k = 0; k < TA_KEYS / 16; ++k)            // 16 keys a step: 8 columns of P, 16 rows of V
+          ta_umma_ts(o_col, s_col + (uint32_t)b * 64u + (uint32_t)k * 8u, ta_desc_mnmajor(va + (uint32_t)k * 16u * 128u, TA_KV_HALF),
+                     idesc_pv, (i | k) != 0);
+        ta_commit(pv_done(t, b));
+        ta_commit(v_empty(s));
+        // S(i+2) goes where P(i) lies: issued behind P V(i), which the tensor cores finish first
+        if (i + 2 < nblocks) ok = issue_qk(i + 2);
       }
     }
   } else if (warp < 6 || (two && warp < 10)) {
@@ -403,20 +399,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
     bool ok = true;
 
     for (int i = 0; i < nblocks; ++i) {
+      const int b = i & 1;
       const int kb = kbeg + i * TA_KEYS;
-      ok = ta_mbar_wait(s_full(t), (uint32_t)(i & 1), abort_flag, TA_ERR_S_FULL);
+      ok = ta_mbar_wait(s_full(t, b), (uint32_t)((i >> 1) & 1), abort_flag, TA_ERR_S_FULL);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool need_mask = (kb + TA_KEYS - 1 > tile_pos0) || (p.window > 0) || (kb < lo_tile) || (kb + TA_KEYS > kend);
       float x[TA_KEYS];
       {
         uint32_t v[64];
-        ta_tmem_ld64(s_addr, v);
+        ta_tmem_ld64(s_addr + (uint32_t)b * 64u, v);
 #pragma unroll
         for (int j = 0; j < 64; ++j) x[j] = __uint_as_float(v[j]);
-        ta_tmem_ld64(s_addr + 64u, v);
-#pragma unroll
-        for (int j = 0; j < 64; ++j) x[64 + j] = __uint_as_float(v[j]);
       }
       if (need_mask) {
 #pragma unroll
@@ -432,8 +426,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
         for (int u = 0; u < 4; ++u) mx4[u] = ta_max3(mx4[u], x[j + 2 * u], x[j + 2 * u + 1]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // The reference follows the maximum only when that has grown much; then O (complete up to block i-1, since
-      // S of block i is) is rescaled.  The warp goes together: tcgen05.ld and st are warp-wide.
+      // The reference follows the maximum only when that has grown much; then O is rescaled, once P V of the block
+      // before is complete.  The warp goes together: tcgen05.ld and st are warp-wide.
       const float m_loc = mx * p.scale_log2;
       const bool grow = m_loc > m_ref + TA_RESCALE_STEP;      // also true for the first finite maximum (m_ref = -inf)
       if (__any_sync(0xffffffffu, grow)) {
@@ -444,6 +438,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
           l_run *= f;
         }
         if (i > 0) {
+          ok = ta_mbar_wait(pv_done(t, b ^ 1), (uint32_t)(((i - 1) >> 1) & 1), abort_flag, TA_ERR_O_FULL);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
           for (int c = 0; c < TA_D; c += 32) {
             uint32_t v[32];
@@ -456,26 +453,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
         }
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      // p = 2^(s * scale - m), the row's sum, P (two keys a column) over the first 64 columns of S
+      // p = 2^(s * scale - m), the row's sum, P (two keys a column) over the first 32 columns of this S buffer.
       // Pairs of keys in packed instructions.  (Tried: a cubic for 2^f on the FMA pipe for half or a quarter of the
       // pairs, to take load off the special-function unit.  Slower: the softmax warps are short of issue slots, not
       // of that unit.)
       const uint64_t scale2 = ta_pack2(p.scale_log2, p.scale_log2), negm2 = ta_pack2(-m_use, -m_use);
       uint64_t sum2 = ta_pack2(0.f, 0.f);
+      uint32_t w[32];
 #pragma unroll
-      for (int c = 0; c < TA_KEYS; c += 64) {
-        uint32_t w[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float y0, y1;
-          ta_unpack2(ta_fma2(ta_pack2(x[c + 2 * j], x[c + 2 * j + 1]), scale2, negm2), y0, y1);
-          const float p0 = exp2_approx(y0), p1 = exp2_approx(y1);          // 2^-inf = 0 for masked keys
-          sum2 = ta_add2(sum2, ta_pack2(p0, p1));
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-          w[j] = *reinterpret_cast<uint32_t*>(&b2);
-        }
-        ta_tmem_st32(s_addr + (uint32_t)(c >> 1), w);
+      for (int j = 0; j < 32; ++j) {
+        float y0, y1;
+        ta_unpack2(ta_fma2(ta_pack2(x[2 * j], x[2 * j + 1]), scale2, negm2), y0, y1);
+        const float p0 = exp2_approx(y0), p1 = exp2_approx(y1);          // 2^-inf = 0 for masked keys
+        sum2 = ta_add2(sum2, ta_pack2(p0, p1));
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+        w[j] = *reinterpret_cast<uint32_t*>(&b2);
       }
+      ta_tmem_st32(s_addr + (uint32_t)b * 64u, w);
       ta_tmem_wait_st();
       {
         float s0, s1;
@@ -485,9 +479,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
       // hand P to the tensor cores
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) ta_mbar_arrive(p_full(t));
+      if (lane == 0) ta_mbar_arrive(p_full(t, b));
     }
-    if (ok) ok = ta_mbar_wait(o_done(t), 0, abort_flag, TA_ERR_O_FULL);
+    if (ok) ok = ta_mbar_wait(pv_done(t, (nblocks - 1) & 1), (uint32_t)(((nblocks - 1) >> 1) & 1), abort_flag, TA_ERR_O_FULL);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
