@@ -95,3 +95,36 @@ def test_mixed_batch_at_real_layer_sizes(runners):
     for key, ref in outs["float32"].items():
         err = ((outs["bfloat16"][key] - ref).abs().max() / ref.abs().max()).item()
         assert err < 3e-2, (key, err)
+
+
+def test_sliding_window_at_the_real_head_size():
+    """A full layer and a sliding layer with heads of 128 in groups of four: the tensor-memory prompt kernel and the
+    decode kernel with a window, pages given back behind the window and used again by a second request; bfloat16
+    against float32 under two ways of cutting, float32 unchanged by the cutting."""
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.load import build_runner_random
+    from lucciola_b200.engine.step import StepEntry
+    cfg = dict(CFG, hidden_size=512, num_attention_heads=8, num_key_value_heads=2, intermediate_size=1024, vocab_size=3000,
+               layer_types=["full_attention", "sliding_attention"], sliding_window=150, use_sliding_window=True)
+    runners = {}
+    for dtype in ("float32", "bfloat16"):
+        opts = EngineOptions(dtype=dtype, block_size=16, max_blocks=80, max_num_seqs=4, max_model_len=1024, max_tokens_per_step=1024)
+        runners[dtype] = build_runner_random(cfg, seed=5, options=opts, std=0.05, norm_std=0.05)
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, cfg["vocab_size"], (600,), generator=g).tolist()
+    other = torch.randint(0, cfg["vocab_size"], (300,), generator=g).tolist()
+    ref = logits_of(runners["float32"], ids, [600])
+    assert torch.equal(logits_of(runners["float32"], ids, [130, 270, 3, 160], tail=37), ref)
+    scale = ref.abs().max().item()
+    r = runners["bfloat16"]
+    for cuts, tail in (([600], 0), ([130, 270, 3, 160], 37)):
+        # a second request takes pages in between, so that the window's freed pages are used again
+        r.step([StepEntry("o", other[:200], [])])
+        got = logits_of(r, ids, cuts, tail)
+        r.step([StepEntry("o", other[200:], [])])
+        r.finish("o")
+        r.manager.check_invariants()
+        err = ((got - ref).abs().max() / scale).item()
+        assert torch.isfinite(got).all() and err < 3e-2, (cuts, tail, err)
+    sliding = [gi for gi, grp in enumerate(r.groups) if grp.window > 0]
+    assert sliding and r.manager.pools[sliding[0]].high_water < 2 * (600 // 16)       # the window's group never held both requests whole
