@@ -135,7 +135,27 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
   return v;
 }
 
+// What the epilogue of the q|k|v product does instead of storing its tile when the tile is one head (128 weight
+// rows = a head of 128): per-head RMSNorm of query and key heads, the rotation, queries into the attention layout,
+// keys and values into their cache page.  The formulas are those of rope_kv.cu (src/qwen.cc:600-663 of lucciola),
+// taken from the 32-bit accumulator instead of a rounded bfloat16 copy.  The layout mirrors LbHeadEpilogue in ops.py.
+struct HeadEpilogue {
+  int on;
+  int num_q_heads, num_kv_heads, page_size, max_pages;
+  float eps;
+  const int* positions;       // [M]
+  const int* token_seq;       // [M] row of the block table
+  const int* block_table;     // [S, max_pages]; a negative page: the token's key and value are written nowhere
+  const float* q_norm_w;      // [128] or null
+  const float* k_norm_w;      // [128] or null
+  const float* inv_freq;      // [64] or null (no rotation)
+  bf16* q_out;                // [M, num_q_heads, 128]
+  bf16* k_cache;              // [pages, num_kv_heads, page_size, 128]
+  bf16* v_cache;
+};
+
 struct GemmParams {
+  HeadEpilogue he = {};   // off unless a caller fills it in
   void* y;              // [M, N] output, row stride ldy
   float* workspace;     // [splits, M, N] partials (split-K only)
   int* counters;        // one per output tile, zero between launches (split-K only)
@@ -375,6 +395,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const float v = silu_mul(g, u);
             if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + feature] = v;
             else ((bf16*)p.y)[(size_t)m * p.ldy + feature] = __float2bfloat16_rn(v);
+          }
+        }
+      } else if (p.he.on) {
+        // The tile is one head; this CTA finishes `per` tokens of it, all 128 threads together (thread = feature).
+        const HeadEpilogue& he = p.he;
+        const int head = n0 / BM;
+        const int kind = head < he.num_q_heads ? 0 : (head < he.num_q_heads + he.num_kv_heads ? 1 : 2);
+        const int hh = kind == 0 ? head : (kind == 1 ? head - he.num_q_heads : head - he.num_q_heads - he.num_kv_heads);
+        float* scratch = reinterpret_cast<float*>(smem) + BT * BM;      // behind the partial tile: 128 values, 4 sums
+        const float* w = kind == 0 ? he.q_norm_w : he.k_norm_w;
+        for (int j = split * per; j < (split + 1) * per; ++j) {
+          const int m = m0 + j;
+          if (m >= p.M) break;                                        // the same for every thread
+          float v = 0.f;
+          for (int z = 0; z < splits; ++z) v += ld_cluster_f32(base + (uint32_t)j * (BM * 4u), (uint32_t)z);
+          const int pos = he.positions[m];
+          if (kind != 2) {
+            if (w) {
+              const float ss = warp_sum(v * v);
+              if (lane == 0) scratch[BM + quarter] = ss;
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              const float total = scratch[BM] + scratch[BM + 1] + scratch[BM + 2] + scratch[BM + 3];
+              v = v * rsqrtf(total / (float)BM + he.eps) * w[nl];
+            }
+            if (he.inv_freq) {
+              scratch[nl] = v;
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              const float other = scratch[nl ^ 64];
+              float sn, cs;
+              sincosf((float)pos * he.inv_freq[nl & 63], &sn, &cs);
+              // first half: x cos - y sin with y the partner; second half: x' sin + y' cos with x' the partner
+              v = nl < 64 ? v * cs - other * sn : other * sn + v * cs;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");              // the scratch is free for the next token
+          }
+          if (kind == 0) {
+            he.q_out[((size_t)m * he.num_q_heads + hh) * BM + nl] = __float2bfloat16_rn(v);
+          } else {
+            const int page = he.block_table[(size_t)he.token_seq[m] * he.max_pages + pos / he.page_size];
+            if (page >= 0) {
+              bf16* pool = kind == 1 ? he.k_cache : he.v_cache;
+              pool[(((size_t)page * he.num_kv_heads + hh) * he.page_size + pos % he.page_size) * BM + nl] = __float2bfloat16_rn(v);
+            }
           }
         }
       } else if (n < p.N) {
@@ -866,6 +929,51 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   p.swiglu = swiglu;
   if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
   LB_CHECK_LAUNCH("gemm_tcgen05");
+  return 0;
+}
+
+// The plan of the q|k|v product with the head epilogue: token tile and splits, or 0 splits when the sizes do not
+// allow it (it needs heads of 128, at most 32 tokens, and a split count whose CTAs form a cluster: the epilogue
+// lives in the cluster's reduction).
+static int heads_plan(int M, int N, int K, int head_dim, int* bt) {
+  // Up to 32 tokens: there a CTA finishes at most 8 tokens one after the other.  With 64 tokens the separate kernel,
+  // which spreads the heads over the whole GPU, was the faster of the two (decode step of 64 requests 19.3 against 19.7 ms).
+  if (head_dim != lb::BM || N % lb::BM || M <= 0 || M > 32 || K % 8) return 0;
+  int t = 16;
+  int splits = lb_gemm_tcgen05_plan(M, N, K, &t);
+  const int kb = (K + lb::BK - 1) / lb::BK;
+  if (splits > kb) splits = kb;
+  if (splits < 2 || splits > 8 || (splits & (splits - 1)) || t % splits) return 0;
+  if (bt) *bt = t;
+  return splits;
+}
+
+// 1 when lb_gemm_tcgen05_heads takes these sizes.
+LB_EXPORT int lb_gemm_tcgen05_heads_ok(int M, int N, int K, int head_dim) { return heads_plan(M, N, K, head_dim, nullptr) > 0; }
+
+// The q|k|v product x[M,K] . w[N,K]^T with N = (num_q_heads + 2 num_kv_heads) * 128, whose epilogue norms and rotates
+// the heads and writes queries to he->q_out and keys and values into their cache pages (see HeadEpilogue): the
+// product's output is never stored as such.
+LB_EXPORT int lb_gemm_tcgen05_heads(const void* x, const void* w, int M, int N, int K, long long ldx, const lb::HeadEpilogue* he,
+                                    cudaStream_t stream) {
+  int bt = 16;
+  const int splits = heads_plan(M, N, K, lb::BM, &bt);
+  LB_CHECK_ARG(splits > 0, "gemm_tcgen05_heads: sizes M=%d N=%d K=%d are not taken (heads of 128, up to 32 tokens, a split product)", M, N, K);
+  LB_CHECK_ARG(he && he->positions && he->token_seq && he->block_table && he->q_out && he->k_cache && he->v_cache, "gemm_tcgen05_heads: null argument");
+  LB_CHECK_ARG(N == (he->num_q_heads + 2 * he->num_kv_heads) * lb::BM && he->page_size > 0 && he->max_pages > 0,
+               "gemm_tcgen05_heads: %d output features for %d + 2 x %d heads of 128", N, he->num_q_heads, he->num_kv_heads);
+  LB_CHECK_ARG(ldx >= K && ldx % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05_heads: operands must be 16-byte aligned");
+  CUtensorMap mw, mx;
+  if (!lb::cached_map(&mw, w, N, K, K, lb::BM) || !lb::cached_map(&mx, x, M, K, ldx, bt)) {
+    lb::set_error("gemm_tcgen05_heads: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);
+    return 3;
+  }
+  lb::GemmParams p;
+  p.he = *he; p.he.on = 1;
+  p.y = nullptr; p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = N; p.out_dtype = LB_BF16;
+  p.cluster = splits; p.swiglu = 0;
+  if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
+  LB_CHECK_LAUNCH("gemm_tcgen05_heads");
   return 0;
 }
 

@@ -42,6 +42,7 @@ _SIGNATURES = {
                       c_longlong, c_void_p],
     "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
                         c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -232,6 +233,47 @@ def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int,
     _call("lb_gemm_tcgen05", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), w.data_ptr(), M, N, K,
           x.stride(0) if M > 1 else K, y.stride(0) if M > 1 else y.shape[1], ws.data_ptr(), ws.numel(), counters.data_ptr(),
           counters.numel(), force_bt, force_splits, 1 if swiglu else 0, stream)
+
+
+class LbHeadEpilogue(ctypes.Structure):
+    """Mirror of HeadEpilogue in csrc/gemm_tcgen05.cu."""
+    _fields_ = [("on", c_int), ("num_q_heads", c_int), ("num_kv_heads", c_int), ("page_size", c_int), ("max_pages", c_int),
+                ("eps", c_float), ("positions", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
+                ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("inv_freq", c_void_p), ("q_out", c_void_p),
+                ("k_cache", c_void_p), ("v_cache", c_void_p)]
+
+
+def gemm_tcgen05_heads_ok(x: torch.Tensor, w: torch.Tensor, head_dim: int, rot_dim: int | None) -> bool:
+    """The conditions of the q|k|v product whose epilogue norms, rotates and stores the heads: bfloat16, heads of
+    128 rotated whole (or not at all), at most 32 tokens, a product that is split over a cluster."""
+    lib = library()
+    lib.lb_gemm_tcgen05_heads_ok.argtypes = [c_int, c_int, c_int, c_int]
+    lib.lb_gemm_tcgen05_heads_ok.restype = c_int
+    M, K = x.shape
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.stride(1) == 1
+            and (M == 1 or x.stride(0) % 8 == 0) and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and rot_dim in (None, head_dim) and bool(lib.lb_gemm_tcgen05_heads_ok(M, w.shape[0], K, head_dim)))
+
+
+def gemm_tcgen05_heads(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
+                       block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, num_q_heads: int,
+                       num_kv_heads: int, page_size: int, eps: float, stream: int, q_norm_w: torch.Tensor | None = None,
+                       k_norm_w: torch.Tensor | None = None, inv_freq: torch.Tensor | None = None) -> None:
+    """x . w^T for w = [q | k | v] rows with heads of 128, finished per head in the product's epilogue: RMSNorm of
+    query and key heads, rotation, queries to q_out [M, nq, 128], keys and values into their cache pages."""
+    M, K = x.shape
+    _check(x, "x", torch.bfloat16); _check(w, "w", torch.bfloat16); _check(q_out, "q output", torch.bfloat16)
+    _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
+    _check(positions, "positions", torch.int32); _check(token_seq, "token map", torch.int32)
+    _check(block_table, "block table", torch.int32)
+    for t, what in ((q_norm_w, "q norm weight"), (k_norm_w, "k norm weight"), (inv_freq, "rotary table")):
+        if t is not None:
+            _check(t, what, torch.float32)
+    he = LbHeadEpilogue(1, num_q_heads, num_kv_heads, page_size, block_table.shape[1], eps, positions.data_ptr(),
+                        token_seq.data_ptr(), block_table.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
+                        q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr())
+    _call("lb_gemm_tcgen05_heads", x.data_ptr(), w.data_ptr(), M, w.shape[0], K, x.stride(0) if M > 1 else K,
+          ctypes.byref(he), stream)
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:

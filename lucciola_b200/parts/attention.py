@@ -65,6 +65,18 @@ class GQAttention(Mixer):
         table = cache_table = step.block_tables[cache.group]
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         q = rt.empty((T, nq, d))
+        rotary = self.position_encoding.rotary_table() if self.position_encoding is not None else None
+        if (write_cache and rt.fast_kernels and (self.position_encoding is None or rotary is not None)
+                and ops.gemm_tcgen05_heads_ok(h, self.qkv.weight, d, rotary[1] if rotary is not None else None)):
+            # Few tokens and heads of 128: the q|k|v product finishes the heads in its own epilogue (norm, rotation,
+            # queries into their layout, keys and values into the pages); its output never exists as a matrix.
+            ops.gemm_tcgen05_heads(h, self.qkv.weight, q, step.positions, step.token_seq, cache_table, cache.k, cache.v,
+                                   nq, nkv, cache.page_size, eps, rt.stream, q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w,
+                                   inv_freq=rotary[0] if rotary is not None else None)
+            out = rt.empty((T, nq, d))
+            ops.attention(q, out, cache.k, cache.v, step, cache.group, nq, nkv, d, cache.page_size, self.window,
+                          self.scale, rt.stream, fast=rt.fast_kernels)
+            return self.o.forward(out.view(T, self.q_size))
         if write_cache:
             qkv = self.qkv.forward(h)
             q_in, k_in, v_in = qkv[:, :self.q_size], qkv[:, self.q_size:self.q_size + self.kv_size], qkv[:, self.q_size + self.kv_size:]
@@ -73,7 +85,6 @@ class GQAttention(Mixer):
             # This call reads a cache another call has written: only q is needed.
             q_in = k_in = v_in = self.qkv.forward(h, rows=self.q_size)
             n_kv = 0
-        rotary = self.position_encoding.rotary_table() if self.position_encoding is not None else None
         if self.position_encoding is None or rotary is not None:
             inv_freq, rot = rotary if rotary is not None else (None, 0)
             ops.rope_kv(q_in, k_in, v_in, q, step.positions, nq, n_kv, d, eps, rt.stream,

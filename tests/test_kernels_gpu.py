@@ -120,6 +120,52 @@ def test_rope_kv(env, act, nq, nkv, d, ps, theta):
     assert torch.isnan(untouched).all()                                         # no other slot was written
 
 
+@pytest.mark.parametrize("nq,nkv,ps,K,seqs,norm,rotate", [
+    (8, 2, 16, 1024, [(0, 1), (37, 1), (1021, 1), (5, 1), (300, 1)], True, True),      # decoded tokens of five requests
+    (4, 4, 8, 512, [(0, 7), (100, 3)], True, True),                                    # short portions
+    (32, 8, 16, 4096, [(i * 11, 1) for i in range(8)], True, True),                    # the real head counts and width
+    (6, 1, 32, 512, [(9, 30)], False, True), (2, 2, 64, 640, [(0, 20), (63, 2)], True, False),
+    (3, 1, 16, 2048, [(0, 32)], True, True),                                           # the most tokens it takes
+])
+def test_gemm_tcgen05_with_head_epilogue(env, nq, nkv, ps, K, seqs, norm, rotate):
+    """The q|k|v product that finishes the heads itself against product, norm, rotation and cache write done plainly."""
+    ops, dev, st = env
+    d, theta, eps = 128, 1e6, 1e-6
+    kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, torch.bfloat16)
+    T = pos.shape[0]
+    x = torch.randn(T, K, device=dev).bfloat16()
+    w = (torch.randn((nq + 2 * nkv) * d, K, device=dev) / math.sqrt(K)).bfloat16()
+    qw = (1 + 0.2 * torch.randn(d, device=dev)) if norm else None
+    kw = (1 + 0.2 * torch.randn(d, device=dev)) if norm else None
+    inv = (1.0 / torch.pow(torch.tensor(theta), torch.arange(0, d, 2, dtype=torch.float32) / d)).to(dev) if rotate else None
+    assert ops.gemm_tcgen05_heads_ok(x, w, d, d if rotate else None)
+    q_out = torch.full((T, nq, d), float("nan"), device=dev, dtype=torch.bfloat16)
+    ops.gemm_tcgen05_heads(x, w, q_out, pos, seq, bt, kc, vc, nq, nkv, ps, eps, st, q_norm_w=qw, k_norm_w=kw, inv_freq=inv)
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
+    y = (x.double() @ w.double().t()).cpu()
+    a, b = nq * d, (nq + nkv) * d
+    p = pos.cpu().tolist()
+    q_ref, k_ref, v_ref = y[:, :a].reshape(T, nq, d), y[:, a:b].reshape(T, nkv, d), y[:, b:].reshape(T, nkv, d)
+    if norm:
+        q_ref, k_ref = plain.rms_norm(q_ref, qw.double().cpu(), eps), plain.rms_norm(k_ref, kw.double().cpu(), eps)
+    if rotate:
+        q_ref, k_ref = plain.rope(q_ref, p, theta), plain.rope(k_ref, p, theta)
+    assert rel(q_out.cpu(), q_ref) < 6e-3
+    btc, seqc = bt.cpu(), seq.cpu().tolist()
+    written = torch.zeros(kc.shape[0], ps, dtype=torch.bool)
+    for t in range(T):
+        page, slot = int(btc[seqc[t], p[t] // ps]), p[t] % ps
+        written[page, slot] = True
+        assert rel(kc[page, :, slot].cpu(), k_ref[t]) < 6e-3 and rel(vc[page, :, slot].cpu(), v_ref[t]) < 6e-3
+    assert torch.isnan(kc.cpu().float().permute(0, 2, 1, 3)[~written]).all()      # no other slot was written
+    assert torch.isnan(vc.cpu().float().permute(0, 2, 1, 3)[~written]).all()
+    # what it does not take: other head sizes, a rotation of part of the head, more than 32 tokens
+    assert not ops.gemm_tcgen05_heads_ok(x, w, 64, 64) and not ops.gemm_tcgen05_heads_ok(x, w, d, 64)
+    assert not ops.gemm_tcgen05_heads_ok(torch.empty(33, K, device=dev, dtype=torch.bfloat16), w, d, d)
+    assert not ops.gemm_tcgen05_heads_ok(x[:, :192], w[:, :192].contiguous(), d, d)          # too short a k to split
+
+
 # ---- attention ------------------------------------------------------------------------------------------------
 def attention_reference(q, kc, vc, bt, pos, seq, nq, nkv, ps, window, scale):
     """Plain float64 attention of each query over the keys its request holds in the pages."""
