@@ -403,28 +403,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int head = n0 / BM;
         const int kind = head < he.num_q_heads ? 0 : (head < he.num_q_heads + he.num_kv_heads ? 1 : 2);
         const int hh = kind == 0 ? head : (kind == 1 ? head - he.num_q_heads : head - he.num_q_heads - he.num_kv_heads);
-        float* scratch = reinterpret_cast<float*>(smem) + BT * BM;      // behind the partial tile: 128 values, 4 sums
+        float* scratch = reinterpret_cast<float*>(smem) + BT * BM;      // behind the partial tile: 128 values, 4 sums,
+        int* tok_pos = reinterpret_cast<int*>(scratch + BM + 4);        // then position and page of this CTA's tokens
+        int* tok_page = tok_pos + BT;
         const float* w = kind == 0 ? he.q_norm_w : he.k_norm_w;
+        // What does not depend on the sums is fetched first, all at once: the loop below then waits for nothing but
+        // its own barriers.
+        const float w_n = (kind != 2 && w) ? w[nl] : 1.f;
+        const float freq = (kind != 2 && he.inv_freq) ? he.inv_freq[nl & 63] : 0.f;
+        if (nl < per && m0 + split * per + nl < p.M) {
+          const int m = m0 + split * per + nl;
+          const int pos = he.positions[m];
+          tok_pos[nl] = pos;
+          tok_page[nl] = kind == 0 ? 0 : he.block_table[(size_t)he.token_seq[m] * he.max_pages + pos / he.page_size];
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         for (int j = split * per; j < (split + 1) * per; ++j) {
           const int m = m0 + j;
           if (m >= p.M) break;                                        // the same for every thread
           float v = 0.f;
           for (int z = 0; z < splits; ++z) v += ld_cluster_f32(base + (uint32_t)j * (BM * 4u), (uint32_t)z);
-          const int pos = he.positions[m];
+          const int pos = tok_pos[j - split * per];
           if (kind != 2) {
             if (w) {
               const float ss = warp_sum(v * v);
               if (lane == 0) scratch[BM + quarter] = ss;
               asm volatile("bar.sync 1, 128;" ::: "memory");
               const float total = scratch[BM] + scratch[BM + 1] + scratch[BM + 2] + scratch[BM + 3];
-              v = v * rsqrtf(total / (float)BM + he.eps) * w[nl];
+              v = v * rsqrtf(total / (float)BM + he.eps) * w_n;
             }
             if (he.inv_freq) {
               scratch[nl] = v;
               asm volatile("bar.sync 1, 128;" ::: "memory");
               const float other = scratch[nl ^ 64];
               float sn, cs;
-              sincosf((float)pos * he.inv_freq[nl & 63], &sn, &cs);
+              sincosf((float)pos * freq, &sn, &cs);
               // first half: x cos - y sin with y the partner; second half: x' sin + y' cos with x' the partner
               v = nl < 64 ? v * cs - other * sn : other * sn + v * cs;
             }
@@ -433,7 +446,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           if (kind == 0) {
             he.q_out[((size_t)m * he.num_q_heads + hh) * BM + nl] = __float2bfloat16_rn(v);
           } else {
-            const int page = he.block_table[(size_t)he.token_seq[m] * he.max_pages + pos / he.page_size];
+            const int page = tok_page[j - split * per];
             if (page >= 0) {
               bf16* pool = kind == 1 ? he.k_cache : he.v_cache;
               pool[(((size_t)page * he.num_kv_heads + hh) * he.page_size + pos % he.page_size) * BM + nl] = __float2bfloat16_rn(v);
