@@ -37,7 +37,7 @@ def test_embedding(env, dtype, hidden):
 
 
 # ---- residual add + RMSNorm ------------------------------------------------------------------------------
-@pytest.mark.parametrize("hidden,eps", [(7, 1e-5), (100, 1e-6), (4100, 3e-3)])
+@pytest.mark.parametrize("hidden,eps", [(7, 1e-5), (100, 1e-6), (4100, 3e-3), (1024, 1e-6), (4096, 1e-6), (8192, 1e-5)])   # the last three: rows held in registers
 @pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(env, hidden, eps, act):
     ops, dev, st = env
