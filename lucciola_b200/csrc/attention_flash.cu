@@ -108,7 +108,6 @@ flash_attention_kernel(FlashParams p) {
   const uint32_t q_smem = KEYSPLIT ? k_smem - Q_BYTES : k_smem + TILE_BYTES;
 
   pdl_trigger();
-  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int4 tile = p.tiles[blockIdx.x];
   const int t0 = tile.x, ntok = tile.y, seq = tile.z;
@@ -126,6 +125,15 @@ flash_attention_kernel(FlashParams p) {
   const int kbeg = lo_tile + split * per_split;
   const int kend = min(pos_last + 1, kbeg + per_split);      // exclusive
   const int num_stages = kend > kbeg ? (kend - kbeg + FA_KEYS - 1) / FA_KEYS : 0;
+  // Tiles, positions and block tables were written before the step began: they are read, and the lines of the block
+  // table this CTA will need are fetched, while the kernel ahead may still run.  Queries, and the keys and values that
+  // kernel wrote, only after the wait.
+  if (num_stages > 0) {
+    const int first = p.page_shift >= 0 ? (kbeg >> p.page_shift) : (kbeg / p.page_size);
+    const int last = p.page_shift >= 0 ? ((kend - 1) >> p.page_shift) : ((kend - 1) / p.page_size);
+    for (int i = first + tid * 32; i <= last; i += FA_THREADS * 32) asm volatile("prefetch.global.L1 [%0];" ::"l"(bt + i));
+  }
+  pdl_wait();
 
   // ---- Q: global -> shared (zero padded), then into A fragments ------------------------------
   for (int idx = tid; idx < FA_ROWS * CHUNKS; idx += FA_THREADS) {

@@ -276,7 +276,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;            // columns: tile t's S buffers at t * 128 and t * 128 + 64 (P over their first 32), O at 256 + t * 128
 
-  pdl_wait();                                   // everything below reads what earlier kernels wrote
+  // Positions and block tables were written before the step began: they are read while the kernel ahead may still run.
   const int pos0 = p.positions[t0];
   const int pos_last = pos0 + ntok - 1;
   const int lo_tile = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
@@ -290,6 +290,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
   const int num_tile_pages = min(((kend - 1) >> p.page_shift) - first_page + 1, TA_MAX_TILE_PAGES);
   for (int i = threadIdx.x; i < num_tile_pages; i += blockDim.x) spages[i] = bt[first_page + i];
   __syncthreads();
+  pdl_wait();                                   // the queries, keys and values below are what earlier kernels wrote
 
   if (warp == 0 || warp == 10) {
     // ---- producers: warp 0 the queries (TMA) and the keys, warp 10 the values ---------------------------------

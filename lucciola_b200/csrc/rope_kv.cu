@@ -108,7 +108,6 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
 template <int VEC>
 __global__ void rope_kv_vec_kernel(RopeKvParams p) {
   pdl_trigger();
-  pdl_wait();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   constexpr int d = VEC * 32;
@@ -122,6 +121,10 @@ __global__ void rope_kv_vec_kernel(RopeKvParams p) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) sincosf((float)pos * p.inv_freq[(lane & 15) * VEC + i], &sn[i], &cs[i]);
   }
+  // The token's page does not depend on the kernel ahead either (positions and block tables are the step's inputs).
+  int page = -1;
+  if (p.k_cache) page = p.block_table[(size_t)p.token_seq[t] * p.max_pages + pos / p.page_size];
+  pdl_wait();                                   // what follows reads the q|k|v product
   // Four heads at a time: their loads are issued together, so that a warp keeps a kilobyte in flight
   // instead of 256 bytes.
   constexpr int UNR = 4;
@@ -144,8 +147,6 @@ __global__ void rope_kv_vec_kernel(RopeKvParams p) {
       if (kind == 0) {
         dst = (bf16*)p.q_out + ((size_t)t * p.num_q_heads + hh) * d;
       } else if (p.k_cache) {
-        const int seq = p.token_seq[t];
-        const int page = p.block_table[(size_t)seq * p.max_pages + pos / p.page_size];
         if (page >= 0) {
           bf16* pool = (bf16*)(kind == 1 ? p.k_cache : p.v_cache);
           dst = pool + (((size_t)page * p.num_kv_heads + hh) * p.page_size + pos % p.page_size) * d;
