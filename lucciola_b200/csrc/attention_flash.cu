@@ -371,15 +371,25 @@ flash_attention_kernel(FlashParams p) {
       for (int item = tid; item < rows * per; item += FA_THREADS) {
         const int r = item / per, dim = split * per + item % per;
         if (dim >= d) continue;
+        // All loads from the peers' shared memory first (each takes several hundred cycles), then the arithmetic.
+        float mz[8], lz[8], oz[8];
+#pragma unroll
+        for (int z = 0; z < 8; ++z) {
+          const bool in = z < p.splits;
+          mz[z] = in ? fa_ld_cluster(fin_ml + r * 2, z) : -INFINITY;
+          lz[z] = in ? fa_ld_cluster(fin_ml + r * 2 + 1, z) : 0.f;
+          oz[z] = in ? fa_ld_cluster(fin_o + r * DP + dim, z) : 0.f;
+        }
         float M = -INFINITY;
-        for (int z = 0; z < p.splits; ++z) M = fmaxf(M, fa_ld_cluster(fin_ml + r * 2, z));
+#pragma unroll
+        for (int z = 0; z < 8; ++z) M = fmaxf(M, mz[z]);
         float L = 0.f, acc = 0.f;
-        for (int z = 0; z < p.splits; ++z) {
-          const float mz = fa_ld_cluster(fin_ml + r * 2, z);
-          if (mz == -INFINITY) continue;
-          const float wz = exp2f(mz - M);
-          L += fa_ld_cluster(fin_ml + r * 2 + 1, z) * wz;
-          acc += fa_ld_cluster(fin_o + r * DP + dim, z) * wz;
+#pragma unroll
+        for (int z = 0; z < 8; ++z) {
+          if (mz[z] == -INFINITY) continue;
+          const float wz = exp2f(mz[z] - M);
+          L += lz[z] * wz;
+          acc += oz[z] * wz;
         }
         const int token = t0 + r / G, head = kvh * G + r % G;
         p.out[((size_t)token * p.num_q_heads + head) * d + dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);

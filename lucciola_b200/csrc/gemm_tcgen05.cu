@@ -154,6 +154,18 @@ struct HeadEpilogue {
   bf16* v_cache;
 };
 
+// The sum over the cluster's CTAs of the float at `addr` of each one's shared memory, in the order of their ranks.
+// All loads are issued before the first is used (a load from another SM's shared memory takes several hundred cycles).
+__device__ __forceinline__ float cluster_sum_f32(uint32_t addr, int splits) {
+  float v[8];
+#pragma unroll
+  for (int z = 0; z < 8; ++z) v[z] = z < splits ? ld_cluster_f32(addr, (uint32_t)z) : 0.f;
+  float acc = 0.f;
+#pragma unroll
+  for (int z = 0; z < 8; ++z) acc += v[z];
+  return acc;
+}
+
 struct GemmParams {
   HeadEpilogue he = {};   // off unless a caller fills it in
   void* y;              // [M, N] output, row stride ldy
@@ -389,9 +401,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           for (int j = split * per + (nl >> 6); j < (split + 1) * per; j += 2) {
             const int m = m0 + j;
             if (m >= p.M) break;
-            float g = 0.f, u = 0.f;
             const uint32_t a = smem_base + (uint32_t)j * (BM * 4u) + (uint32_t)f * 4u;
-            for (int z = 0; z < splits; ++z) { g += ld_cluster_f32(a, (uint32_t)z); u += ld_cluster_f32(a + 256u, (uint32_t)z); }
+            const float g = cluster_sum_f32(a, splits), u = cluster_sum_f32(a + 256u, splits);
             const float v = silu_mul(g, u);
             if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + feature] = v;
             else ((bf16*)p.y)[(size_t)m * p.ldy + feature] = __float2bfloat16_rn(v);
@@ -421,8 +432,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (int j = split * per; j < (split + 1) * per; ++j) {
           const int m = m0 + j;
           if (m >= p.M) break;                                        // the same for every thread
-          float v = 0.f;
-          for (int z = 0; z < splits; ++z) v += ld_cluster_f32(base + (uint32_t)j * (BM * 4u), (uint32_t)z);
+          float v = cluster_sum_f32(base + (uint32_t)j * (BM * 4u), splits);
           const int pos = tok_pos[j - split * per];
           if (kind != 2) {
             if (w) {
@@ -457,8 +467,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (int j = split * per; j < (split + 1) * per; ++j) {
           const int m = m0 + j;
           if (m >= p.M) break;
-          float acc = 0.f;
-          for (int z = 0; z < splits; ++z) acc += ld_cluster_f32(base + (uint32_t)j * (BM * 4u), (uint32_t)z);
+          const float acc = cluster_sum_f32(base + (uint32_t)j * (BM * 4u), splits);
           if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + n] = acc;
           else ((bf16*)p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(acc);
         }
