@@ -15,7 +15,7 @@ device_cache.py.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, Sequence
+from typing import Optional, Hashable, Sequence
 
 from ..parts.base import KVPages, StateSlot
 from .page_pool import PagePool, PagePoolError
@@ -121,6 +121,34 @@ class CacheManager:
             rc.version = self._versions
         rc.length = new_length
         return True
+
+    def extend_by_one(self, rids: Sequence[Hashable]) -> Optional[list[int]]:
+        """One more position for each of these admitted requests, all or nothing: the step of a decoding batch.
+        Returns the positions the new tokens take (the lengths before), or None when a group lacks the pages."""
+        ps = self.page_size
+        reqs = [self._requests[rid] for rid in rids]
+        need = [0] * len(self.groups)
+        for rc in reqs:
+            want = rc.length // ps + 1                       # pages that back positions 0 .. length
+            for g, t in enumerate(rc.tables):
+                if want > len(t):
+                    need[g] += want - len(t)
+        if any(need) and not all(self.pools[g].can_allocate(n) for g, n in enumerate(need)):
+            return None
+        starts = []
+        for rc in reqs:
+            want = rc.length // ps + 1
+            grew = False
+            for g, t in enumerate(rc.tables):
+                while len(t) < want:
+                    t.append(self.pools[g].allocate())
+                    grew = True
+            if grew:
+                self._versions += 1
+                rc.version = self._versions
+            starts.append(rc.length)
+            rc.length += 1
+        return starts
 
     def max_extension(self, rid: Hashable, upto: int) -> int:
         """The largest length <= upto that the free pages allow for this request."""

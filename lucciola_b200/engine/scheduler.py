@@ -131,6 +131,15 @@ class Scheduler:
 
     def _schedule_once(self) -> list[Scheduled]:
         plan: list[Scheduled] = []
+        # The common step of a running engine: nobody waits, everybody decodes, and there is a free page in every
+        # group for each of them (more than they can need).  Nothing to weigh then.
+        if not self.waiting and self.running and all(p.num_free >= len(self.running) for p in self.manager.pools) \
+                and all(r.remaining == 1 for r in self.running):
+            for r in sorted(self.running, key=lambda r: r.admitted_at):
+                plan.append(Scheduled(r, r.num_computed, 1, True))
+            self.num_steps += 1
+            self.num_scheduled_tokens += len(plan)
+            return plan
         reserved = [0] * len(self.manager.pools)
         budget = self.max_tokens_per_step
 

@@ -209,20 +209,26 @@ class ModelRunner:
                 lo, hi = int(arr.min()), int(arr.max())
             if lo < 0 or hi >= vocab:
                 raise ValueError(f"request {e.rid!r}: token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab}")
-        if not self.can_run(entries):
-            raise OutOfPages(f"the step needs more pages or slots than are free ({[p.num_free for p in self.manager.pools]} pages free)")
-
         # Take pages; collect the batch on the host.
         new_slots: list[int] = []
         starts, q_lens = [], []
-        for e in entries:
-            if not self.manager.has_request(e.rid):
-                new_slots.append(self.manager.admit(e.rid))
-            start = self.manager.length(e.rid)
-            if not self.manager.extend(e.rid, start + len(e.tokens)):
-                raise OutOfPages("pages ran out while a step was being prepared")   # can_run() said yes
-            starts.append(start)
-            q_lens.append(len(e.tokens))
+        if all(isinstance(a, int) for a in token_arrays) and all(self.manager.has_request(e.rid) for e in entries):
+            # every entry is one more token of a request that is under way: one pass over the page tables
+            taken = self.manager.extend_by_one([e.rid for e in entries])
+            if taken is None:
+                raise OutOfPages(f"the step needs more pages than are free ({[p.num_free for p in self.manager.pools]} pages free)")
+            starts, q_lens = taken, [1] * len(entries)
+        else:
+            if not self.can_run(entries):
+                raise OutOfPages(f"the step needs more pages or slots than are free ({[p.num_free for p in self.manager.pools]} pages free)")
+            for e in entries:
+                if not self.manager.has_request(e.rid):
+                    new_slots.append(self.manager.admit(e.rid))
+                start = self.manager.length(e.rid)
+                if not self.manager.extend(e.rid, start + len(e.tokens)):
+                    raise OutOfPages("pages ran out while a step was being prepared")   # can_run() said yes
+                starts.append(start)
+                q_lens.append(len(e.tokens))
 
         S_real = len(entries)
         max_ctx = max(s + n for s, n in zip(starts, q_lens))

@@ -124,3 +124,42 @@ def test_random_orders_keep_every_page_accounted_for(seed):
     for rid in list(live):
         m.release(rid)
     assert all(p.num_free == p.num_pages for p in m.pools)
+
+
+def test_extend_by_one_equals_extend_and_is_all_or_nothing():
+    """The decoding batch's one-pass extension takes the same pages as one extend() per request, and nothing when
+    a group lacks pages."""
+    import random
+    from lucciola_b200.cache.manager import CacheGroup, CacheManager
+    groups = [CacheGroup(2, 16, 0, (0,)), CacheGroup(2, 16, 6, (1,))]
+    rnd = random.Random(3)
+    a, b = CacheManager(groups, 4, 40, 4), CacheManager(groups, 4, 40, 4)
+    rids = ["x", "y", "z"]
+    for m in (a, b):
+        for i, rid in enumerate(rids):
+            m.admit(rid)
+            assert m.extend(rid, 3 + 5 * i)
+    for step in range(30):
+        batch = [r for r in rids if rnd.random() < 0.8] or rids[:1]
+        starts = a.extend_by_one(batch)
+        assert starts == [b.length(r) for r in batch]
+        for r in batch:
+            assert b.extend(r, b.length(r) + 1)
+        for r in rids:
+            assert a.length(r) == b.length(r)
+            for g in range(2):
+                assert len(a.block_table(r, g)) == len(b.block_table(r, g))
+            a.release_behind_window(r); b.release_behind_window(r)
+        a.check_invariants(); b.check_invariants()
+        assert [p.num_free for p in a.pools] == [p.num_free for p in b.pools]
+    # all or nothing: with too few pages left for the whole batch nothing changes
+    small = CacheManager([CacheGroup(1, 8, 0, (0,))], 4, 3, 4)
+    for rid in ("p", "q"):
+        small.admit(rid)
+        assert small.extend(rid, 4)                 # one page each, full
+    before = ([small.length(r) for r in ("p", "q")], small.pools[0].num_free)
+    assert small.pools[0].num_free == 1
+    assert small.extend_by_one(["p", "q"]) is None   # both need a new page, one is free
+    assert ([small.length(r) for r in ("p", "q")], small.pools[0].num_free) == before
+    small.check_invariants()
+    assert small.extend_by_one(["p"]) == [4]
