@@ -50,6 +50,7 @@ class _Staging:
     def __init__(self, device: torch.device, capacity: int, ring: int = 4):
         self.device, self.capacity = device, capacity
         self.host = [torch.empty(capacity, dtype=torch.int32, pin_memory=True) for _ in range(ring)]
+        self.host_np = [h.numpy() for h in self.host]                 # the same memory, for the host-side fill
         self.events = [torch.cuda.Event() for _ in range(ring)]
         self.recorded = [False] * ring
         self.dev = torch.empty(capacity, dtype=torch.int32, device=device)
@@ -267,8 +268,8 @@ class ModelRunner:
                     tile_lists[(g, "rest")] = rest
         total = 3 * T + (S + 1) + 2 * S + R + G * S * P + sum(4 * len(t) + 3 for t in tile_lists.values())
         st = self._staging_for(total)
-        hi, host = st.next_host()
-        h = host.numpy()
+        hi, _ = st.next_host()
+        h = st.host_np[hi]
         o = 0
         def take(n):
             nonlocal o
