@@ -34,6 +34,8 @@ def sampling_key(seed: int) -> int:
 class Sampler:
     def __init__(self, device: torch.device):
         self.device = device
+        self._host: torch.Tensor | None = None          # pinned memory the sampled ids are read back into
+        self._done = torch.cuda.Event() if torch.device(device).type == "cuda" else None
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], generated: Sequence[int]) -> list[int]:
         """One token for each row; `generated[r]` is how many tokens request r has generated so far."""
@@ -48,4 +50,11 @@ class Sampler:
             keys_t = torch.from_numpy(keys).to(self.device, non_blocking=True)
             counters = torch.tensor(list(generated), dtype=torch.int32).to(self.device, non_blocking=True)
             ops.sample(tokens, logits, stream, temps, keys_t, counters)
-        return tokens.cpu().tolist()
+        if self._done is None:
+            return tokens.cpu().tolist()
+        if self._host is None or self._host.shape[0] < R:
+            self._host = torch.empty(max(R, 256), dtype=torch.int32, pin_memory=True)
+        self._host[:R].copy_(tokens, non_blocking=True)
+        self._done.record()
+        self._done.synchronize()
+        return self._host[:R].tolist()
