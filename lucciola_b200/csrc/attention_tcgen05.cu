@@ -1,8 +1,8 @@
 // Causal grouped-query attention for portions of prompts on the 5th-generation tensor cores
 // (bfloat16, head size 128, page sizes 8..128 that are powers of two).
 //
-// A work item is a run of up to 256/G consecutive tokens of one request and one kv head (G = query
-// heads per kv head): its G*tokens query rows form TWO tiles of 128 rows, A and B, that share the keys
+// A work item is a run of up to 2 * floor(128/G) consecutive tokens of one request and one kv head (G = query
+// heads per kv head): its G*tokens query rows form TWO tiles of up to 128 rows, A and B, that share the keys
 // and values the CTA loads (half the traffic from L2 per query row).  Keys and values are visited in
 // blocks of 64 keys.  Per block and tile
 //     S = Q K^T          tcgen05.mma, both operands K-major from shared memory, S (128 x 64 float32) in
@@ -296,7 +296,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
     // ---- producers: warp 0 the queries (TMA) and the keys, warp 10 the values ---------------------------------
     const bool is_v = warp == 10;
     if (!is_v && lane == 0) {
-      ta_mbar_expect_tx(q_full, (uint32_t)ntiles * TA_TILE_BYTES);
+      ta_mbar_expect_tx(q_full, (uint32_t)(ntiles * G * per) * 256u);      // a tile's box: G * per rows of 256 bytes, in two halves
       for (int t = 0; t < ntiles; ++t) {
         ta_tma_3d(sbase + TA_Q_OFF + t * TA_TILE_BYTES, &map_q, 0, kvh * G, t0 + t * per, q_full);
         ta_tma_3d(sbase + TA_Q_OFF + t * TA_TILE_BYTES + TA_HALF_BYTES, &map_q, 64, kvh * G, t0 + t * per, q_full);
@@ -392,7 +392,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
     const uint32_t tlane = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_addr = tmem + tlane + (uint32_t)t * 128u, o_addr = tmem + tlane + 256u + (uint32_t)t * 128u;
     const int tok_in_item = t * per + r / G;
-    const bool row_valid = tok_in_item < ntok;
+    const bool row_valid = r < per * G && tok_in_item < ntok;       // (128 - per * G rows of a tile stay unused when G does not divide 128)
     const int row_pos = row_valid ? pos0 + tok_in_item : -1;
     const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
     const int tile_pos0 = pos0 + t * per;                    // the smallest position among the tile's rows
@@ -573,20 +573,20 @@ static bool ta_q_map(CUtensorMap* out, const void* q, long long tokens, int num_
 LB_EXPORT int lb_attention_tcgen05_ok(int num_q_heads, int num_kv_heads, int head_dim, int page_size) {
   if (head_dim != 128 || num_kv_heads <= 0 || num_q_heads % num_kv_heads) return 0;
   const int g = num_q_heads / num_kv_heads;
-  if (g > 128 || 128 % g) return 0;                          // the query box is G heads x 128/G tokens
+  if (g > 128) return 0;                                     // the query box is G heads x floor(128/G) tokens
   if (page_size < 8 || page_size > 128 || 128 % page_size || (page_size & (page_size - 1))) return 0;
   return 1;
 }
 
 // q, out: [T, nq, 128] bfloat16.  k_cache, v_cache: [pages, nkv, page_size, 128].  tiles: {first token,
-// tokens, request index, 0} with tokens * (nq / nkv) <= 256; the tokens of a tile are consecutive tokens of one
+// tokens, request index, 0} with tokens <= 2 * floor(128 / (nq / nkv)); the tokens of a tile are consecutive tokens of one
 // request at consecutive positions.
 LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache, const void* v_cache, const int* positions,
                                    const int* block_table, const void* tiles, int num_tiles, int num_tokens,
                                    int num_q_heads, int num_kv_heads, int head_dim, int page_size, int num_pages,
                                    int max_pages, int window, float scale, cudaStream_t stream) {
   LB_CHECK_ARG(lb_attention_tcgen05_ok(num_q_heads, num_kv_heads, head_dim, page_size),
-               "attention_tcgen05: needs head_dim 128, a group size that divides 128 and a page size among 8, 16, 32, 64, 128 "
+               "attention_tcgen05: needs head_dim 128, at most 128 query heads per kv head and a page size among 8, 16, 32, 64, 128 "
                "(got head_dim %d, %d/%d heads, pages of %d)", head_dim, num_q_heads, num_kv_heads, page_size);
   LB_CHECK_ARG(max_pages > 0 && window >= 0 && num_tokens > 0 && num_pages > 0, "attention_tcgen05: bad sizes");
   LB_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)out % 16 == 0),

@@ -121,10 +121,14 @@ LB_EXPORT int lb_add_rmsnorm(void* out, int out_dtype, float* residual, const vo
   LB_CHECK_ARG(lb::valid_dtype(out_dtype) && lb::valid_dtype(delta_dtype), "add_rmsnorm: bad dtype");
   LB_CHECK_ARG(num_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", num_rows, hidden);
   if (num_rows == 0) return 0;
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   const bool vec4 = (hidden % 4 == 0);
-  // rows of 4, 8 or 16 elements a thread, 16-byte aligned operands: the one-pass kernel
-  const int per = hidden % threads == 0 ? hidden / threads : 0;
+  // rows of 4, 8 or 16 elements a thread (a whole number of warps, 64 to 1024 threads), 16-byte aligned operands:
+  // the one-pass kernel.  8 elements a thread where that works (4096 -> 512 threads, 5120 -> 640), else 4, else 16.
+  int per = 0;
+  for (int cand : {8, 4, 16}) {
+    if (hidden % cand == 0 && (hidden / cand) % 32 == 0 && hidden / cand >= 64 && hidden / cand <= 1024) { per = cand; threads = hidden / cand; break; }
+  }
   const bool aligned = ((uintptr_t)out % 16 == 0) && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)weight % 16 == 0);
   LB_DISPATCH_DTYPE(delta_dtype, TD, {
     LB_DISPATCH_DTYPE(out_dtype, TO, {

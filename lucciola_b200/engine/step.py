@@ -258,8 +258,9 @@ class ModelRunner:
                 tile_lists[(g, "all")] = self._decode_tiles.get(S) or self._decode_tiles.setdefault(S, self._tiles(q_lens, g, 64))
                 continue
             tile_lists[(g, "all")] = self._tiles(q_lens, g, 64)
-            if max(q_lens) >= _BIG_PORTION and 128 % g == 0:
-                big = self._tiles(q_lens, g, 256, lambda n: n >= _BIG_PORTION)
+            if max(q_lens) >= _BIG_PORTION:
+                # two tiles of floor(128 / g) tokens each
+                big = self._tiles(q_lens, g, 2 * (128 // g) * g, lambda n: n >= _BIG_PORTION)
                 # tiles that see the most keys first: the short ones then fill the end of the last wave
                 big.sort(key=lambda tl: -(starts[tl[2]] + (tl[0] - first_token[tl[2]]) + tl[1]))
                 tile_lists[(g, "big")] = big

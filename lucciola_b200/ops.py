@@ -380,8 +380,8 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
 
 def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
                          max_pages: int = 0) -> bool:
-    """The conditions of the tensor-memory attention kernel: bfloat16, head size 128, a group size that divides
-    128, pages of 8, 16, 32, 64 or 128 tokens, at most 4096 pages a request."""
+    """The conditions of the tensor-memory attention kernel: bfloat16, head size 128, at most 128 query heads per
+    kv head, pages of 8, 16, 32, 64 or 128 tokens, at most 4096 pages a request."""
     lib = library()
     lib.lb_attention_tcgen05_ok.restype = c_int
     return (q.dtype == torch.bfloat16 and max_pages <= 4096
@@ -392,7 +392,7 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, num_q_heads: int,
                       num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, stream: int) -> None:
     """Attention of portions of prompts on tcgen05 (S and O in tensor memory).  tiles: int32 [n, 4] of
-    (first token, tokens, request index, 0) with tokens * (nq / nkv) <= 256."""
+    (first token, tokens, request index, 0) with tokens <= 2 * (128 // (nq // nkv))."""
     _check(q, "q", torch.bfloat16); _check(out, "attention output", torch.bfloat16)
     _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
     _check(positions, "positions", torch.int32); _check(block_table, "block table", torch.int32)

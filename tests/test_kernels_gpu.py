@@ -37,7 +37,7 @@ def test_embedding(env, dtype, hidden):
 
 
 # ---- residual add + RMSNorm ------------------------------------------------------------------------------
-@pytest.mark.parametrize("hidden,eps", [(7, 1e-5), (100, 1e-6), (4100, 3e-3), (1024, 1e-6), (4096, 1e-6), (8192, 1e-5)])   # the last three: rows held in registers
+@pytest.mark.parametrize("hidden,eps", [(7, 1e-5), (100, 1e-6), (4100, 3e-3), (1024, 1e-6), (4096, 1e-6), (8192, 1e-5), (5120, 1e-6), (2560, 1e-6), (16384, 1e-6)])   # from 1024 on: rows held in registers
 @pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(env, hidden, eps, act):
     ops, dev, st = env
@@ -273,7 +273,7 @@ def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None, rows=256)
         hook(kc, vc, bt.cpu())
     T = pos.shape[0]
     q = torch.randn(T, nq, d, device=dev).bfloat16() if q is None else q
-    per = rows // (nq // nkv)
+    per = (rows // 128) * (128 // (nq // nkv))
     tiles, t = [], 0
     for i, (_, n) in enumerate(seqs):
         for off in range(0, n, per):
@@ -297,6 +297,8 @@ def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None, rows=256)
     (2, 2, 128, 0, [(0, 130)]),                     # a page as large as a block
     (16, 1, 64, 0, [(0, 40), (1000, 9)]),           # sixteen heads on one kv head; nine tokens after a thousand
     (8, 2, 16, 200, [(0, 700)]),                    # a window inside a long portion
+    (40, 8, 16, 0, [(0, 260), (77, 30)]),           # five heads per kv head: tiles of 25 tokens, three rows unused
+    (6, 2, 32, 90, [(10, 300)]), (7, 1, 16, 0, [(0, 150)]),      # three and seven heads per kv head
 ])
 @pytest.mark.parametrize("rows", [256, 128])
 def test_attention_tcgen05(env, nq, nkv, ps, window, seqs, rows):
@@ -358,7 +360,8 @@ def test_attention_tcgen05_refuses_other_sizes(env):
     q = torch.zeros(4, 4, 64, device=dev, dtype=torch.bfloat16)
     assert not ops.attention_tcgen05_ok(q, 4, 2, 64, 16)           # head size
     q = torch.zeros(4, 6, 128, device=dev, dtype=torch.bfloat16)
-    assert not ops.attention_tcgen05_ok(q, 6, 2, 128, 16)          # three heads per kv head do not divide 128
+    assert ops.attention_tcgen05_ok(q, 6, 2, 128, 16)              # three heads per kv head: tiles of 42 tokens
+    assert not ops.attention_tcgen05_ok(q, 258, 2, 128, 16)        # more than 128 heads per kv head
     assert not ops.attention_tcgen05_ok(q, 6, 6, 128, 24)          # page size
     assert ops.attention_tcgen05_ok(q, 6, 6, 128, 16)
 
