@@ -42,7 +42,12 @@ QWEN3_8B = {
     "tie_word_embeddings": False, "max_position_embeddings": 40960, "hidden_act": "silu", "attention_bias": False,
     "torch_dtype": "bfloat16",
 }
-FULL_LAYERS = 36
+# Other shapes of the family (--shape), for measurements beside the default one.
+SHAPES = {
+    "8b": ("Qwen3-8B shape", QWEN3_8B),
+    "14b": ("Qwen3-14B shape", dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)),
+    "32b": ("Qwen3-32B shape", dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)),
+}
 
 
 def peaks() -> dict:
@@ -132,7 +137,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192, help="context length the decode steps end at")
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes: the default Qwen3-8B shape or another of the family")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps from CUDA graphs")
@@ -161,7 +167,10 @@ def main() -> int:
     from lucciola_b200.sampling.params import SamplingParams
 
     pk = peaks()
-    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    full_layers = shape["num_hidden_layers"]
+    args.layers = args.layers or full_layers
+    cfg = dict(shape, num_hidden_layers=args.layers)
     K, W, ctx = args.steps, args.warmup, args.context
     batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
     page = 16
@@ -295,15 +304,15 @@ def main() -> int:
     err = ops.device_error()
 
     line = {
-        "metric": "decode tokens/s (Qwen3-8B shape, bf16, batch %d, context %d)" % (args.batch, ctx),
+        "metric": "decode tokens/s (%s, bf16, batch %d, context %d)" % (shape_name, args.batch, ctx),
         "value": round(main_r["value"], 2), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(main_r["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0, 0.02)", "impl": "ours",
-        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_configuration": FULL_LAYERS,
+        "config": {"model": shape_name, "layers": args.layers, "layers_of_configuration": full_layers,
                    "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
                    "intermediate_size": 12288, "vocab_size": 151936, "global_batch": args.batch, "seq_len": ctx,
                    "context_len": main_r["final_context"], "page_size": page, "parallelism": "single GPU",
-                   "cuda_graph": bool(options.use_cuda_graph), "l2": "inputs larger than L2 (16 GB of weights a step)",
+                   "cuda_graph": bool(options.use_cuda_graph), "l2": "inputs larger than L2 (%.0f GB of weights a step)" % (weight_bytes / 1e9),
                    "prefill_tokens": T, "peaks": pk["source"]},
         "e2e": main_r.get("e2e"),
         "gpu_launches": int(main_r["launches"]),
