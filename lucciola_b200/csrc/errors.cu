@@ -23,6 +23,14 @@ LB_EXPORT unsigned long long lb_launch_count() { return __atomic_load_n(&lb::g_l
 // Switches programmatic dependent launch on (default) or off for all later launches.
 LB_EXPORT void lb_set_pdl(int on) { lb::g_pdl_enabled = on ? 1 : 0; }
 
+// One asynchronous copy of a step's integers from pinned host memory to the device, in stream order.
+LB_EXPORT int lb_upload(void* dst, const void* src, long long bytes, cudaStream_t stream) {
+  LB_CHECK_ARG(dst && src && bytes >= 0, "upload: bad arguments");
+  const cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) { lb::set_error("upload: %s", cudaGetErrorString(e)); return 2; }
+  return 0;
+}
+
 // Message of the last failed call on this thread.
 LB_EXPORT const char* lb_last_error() { return lb::g_error; }
 

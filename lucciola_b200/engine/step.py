@@ -64,8 +64,10 @@ class _Staging:
         return i, self.host[i]
 
     def upload(self, i: int, n: int, dev: Optional[torch.Tensor] = None) -> None:
-        (self.dev if dev is None else dev)[:n].copy_(self.host[i][:n], non_blocking=True)
-        self.events[i].record()
+        from .. import ops
+        stream = torch.cuda.current_stream(self.device)
+        ops.upload((self.dev if dev is None else dev).data_ptr(), self.host[i].data_ptr(), 4 * n, stream.cuda_stream)
+        self.events[i].record(stream)
         self.recorded[i] = True
 
 

@@ -42,6 +42,7 @@ _SIGNATURES = {
                       c_longlong, c_void_p],
     "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
                         c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "lb_upload": [c_void_p, c_void_p, c_longlong, c_void_p],
     "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
@@ -283,6 +284,11 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     if up.shape != gate.shape or I % 64:
         raise KernelError(f"gate and up must have the same shape with a multiple of 64 rows, got {tuple(gate.shape)}, {tuple(up.shape)}")
     return torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+def upload(dst_ptr: int, src_ptr: int, nbytes: int, stream: int) -> None:
+    """One asynchronous copy from pinned host memory to the device, in the order of `stream`."""
+    _call("lb_upload", dst_ptr, src_ptr, nbytes, stream)
 
 
 def launch_count() -> int:
