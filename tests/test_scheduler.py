@@ -230,3 +230,28 @@ def test_random_arrivals_under_pressure_finish_with_the_unpressured_output(seed)
     for r in reqs:
         assert r.status is Status.FINISHED and r.output == expected_output(r), (r.rid, r.preemptions)
     assert all(p.num_free == p.num_pages for p in m.pools) and m.num_requests() == 0
+
+
+def test_a_decoding_batch_with_pages_to_spare_is_planned_as_it_stands():
+    """Nobody waits, everybody decodes, every group has a free page for each: the plan is one token for each running
+    request in the order of admission, and it equals what the weighing path decides when pages are short of that."""
+    m, s = make(pages=64, page=4, budget=4, seqs=8)
+    for rid, n in ((1, 5), (2, 9), (3, 2)):
+        s.add_request(req(rid, n, new=20))
+    log = []
+    while any(r.remaining > 1 for r in s.running) or s.waiting:
+        run_step(m, s, log)
+    assert all(p.num_free >= len(s.running) for p in m.pools)
+    plan, _ = run_step(m, s, log)
+    assert [(e.request.rid, e.num_tokens, e.sample) for e in plan] == [(1, 1, True), (2, 1, True), (3, 1, True)]   # budget 4 does not bind
+    # the same requests in a pool so small that the short cut does not apply: same plan while the pages last
+    m2, s2 = make(pages=8, page=4, budget=4, seqs=8)
+    for rid, n in ((1, 5), (2, 9), (3, 2)):
+        s2.add_request(req(rid, n, new=20))
+    while any(r.remaining > 1 for r in s2.running) or s2.waiting:
+        run_step(m2, s2)
+    assert not all(p.num_free >= len(s2.running) for p in m2.pools)
+    plan2, _ = run_step(m2, s2)
+    assert [(e.request.rid, e.start, e.num_tokens, e.sample) for e in plan2] == \
+        [(e.request.rid, e.request.num_computed - 1, 1, True) for e in plan2]
+    assert [e.request.rid for e in plan2] == [1, 2, 3]
