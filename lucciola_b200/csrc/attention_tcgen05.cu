@@ -180,8 +180,8 @@ __device__ __forceinline__ uint64_t ta_fma2(uint64_t a, uint64_t b, uint64_t c) 
 }
 __device__ __forceinline__ uint64_t ta_add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 __device__ __forceinline__ float ta_max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
-enum : int { TA_ERR_Q = 301, TA_ERR_KV_FULL = 302, TA_ERR_KV_EMPTY = 303, TA_ERR_S_FULL = 304, TA_ERR_S_EMPTY = 305,
-             TA_ERR_P_FULL = 306, TA_ERR_P_EMPTY = 307, TA_ERR_O_FULL = 308 };
+// Which wait gave up (what lb_attention_tcgen05_device_error reports).
+enum : int { TA_ERR_Q = 301, TA_ERR_KV_FULL = 302, TA_ERR_KV_EMPTY = 303, TA_ERR_S_FULL = 304, TA_ERR_P_FULL = 306, TA_ERR_O_FULL = 308 };
 
 // Shared memory: Q of tile A, Q of tile B | K ring of 4 blocks | V ring of 4 blocks | barriers | page ids.
 // A tile of R rows x 128 bfloat16 is two halves of R rows x 128 bytes (64 elements); within a half the 16-byte
