@@ -26,6 +26,10 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--block-size", type=int, default=16, help="tokens in a page")
     ap.add_argument("--max-new-tokens", type=int, default=100)
     ap.add_argument("--max-tokens-per-step", type=int, default=576)
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="most tokens of one prompt in a step (0: what the step's budget leaves)")
+    ap.add_argument("--max-num-seqs", type=int, default=None, help="requests that hold pages at a time")
+    ap.add_argument("--max-model-len", type=int, default=None, help="longest sequence (default: the model's positions)")
+    ap.add_argument("--no-cuda-graph", action="store_true", help="run decode steps kernel by kernel instead of replaying recorded graphs")
     ap.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--ignore-eos", action="store_true")
@@ -37,7 +41,12 @@ def main(argv: list[str] | None = None) -> int:
     from .sampling.params import SamplingParams
 
     options = EngineOptions(dtype=args.dtype, max_blocks=args.max_blocks, block_size=args.block_size,
-                            max_tokens_per_step=args.max_tokens_per_step)
+                            max_tokens_per_step=args.max_tokens_per_step, prefill_chunk=args.prefill_chunk,
+                            use_cuda_graph=not args.no_cuda_graph)
+    if args.max_num_seqs is not None:
+        options.max_num_seqs = args.max_num_seqs
+    if args.max_model_len is not None:
+        options.max_model_len = args.max_model_len
     engine = Engine(args.model, options=options)
     params = SamplingParams(max_new_tokens=args.max_new_tokens, temperature=args.temperature, seed=args.seed,
                             ignore_eos=args.ignore_eos)

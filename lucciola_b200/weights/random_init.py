@@ -76,3 +76,28 @@ def write_random_model(config_dict: Mapping[str, Any], folder: str | Path, seed:
     write_safetensors(folder / "model.safetensors", ((n, src.get(n)) for n in src.names()),
                       metadata={"format": "pt", "seed": str(seed)})
     return folder
+
+
+def main(argv: list[str] | None = None) -> int:
+    """lucciola_random_model --config FILE --seed N --out DIR: a model folder with random weights."""
+    import argparse
+    ap = argparse.ArgumentParser(prog="lucciola_random_model",
+                                 description="Write a model folder (config.json, model.safetensors) with random weights "
+                                             "for the architecture a config.json names.")
+    ap.add_argument("--config", required=True, help="a config.json (its `architectures` entry chooses the model)")
+    ap.add_argument("--seed", type=int, required=True)
+    ap.add_argument("--out", required=True, help="folder to write")
+    ap.add_argument("--std", type=float, default=0.02, help="standard deviation of matrix weights")
+    ap.add_argument("--norm-std", type=float, default=0.0, help="norm weights are 1 + N(0, this)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="type the tensors are stored in")
+    args = ap.parse_args(argv)
+    config = json.loads(Path(args.config).read_text())
+    folder = write_random_model(config, args.out, args.seed, std=args.std, norm_std=args.norm_std,
+                                dtype=torch.bfloat16 if args.dtype == "bfloat16" else torch.float32)
+    print(folder)
+    return 0
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(main())

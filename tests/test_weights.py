@@ -150,3 +150,24 @@ def test_types_kept(tmp_path):
     assert m.blocks[0].mixer.qkv.weight.dtype == torch.bfloat16
     assert m.blocks[0].mixer.qkv.weight.shape == (64 + 2 * 32, 64)
     assert m.blocks[0].mixer_norm.weight.dtype == torch.float32        # norm weights are read as float32 (exact)
+
+
+def test_random_model_program_writes_a_loadable_folder(tmp_path):
+    """bin/lucciola_random_model: config.json + seed -> a folder the loader accepts; same seed, same bytes."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    from conftest import TINY
+    cfg = TINY["B"][0]
+    (tmp_path / "c.json").write_text(json.dumps(cfg))
+    prog = Path(__file__).resolve().parents[1] / "bin" / "lucciola_random_model"
+    for out in ("m1", "m2"):
+        r = subprocess.run([sys.executable, str(prog), "--config", str(tmp_path / "c.json"), "--seed", "4", "--out", str(tmp_path / out),
+                            "--std", "0.05", "--norm-std", "0.1"], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr
+    a, b = (tmp_path / "m1" / "model.safetensors").read_bytes(), (tmp_path / "m2" / "model.safetensors").read_bytes()
+    assert a == b and json.loads((tmp_path / "m1" / "config.json").read_text()) == cfg
+    from lucciola_b200.weights.loader import CheckpointFolder
+    folder = CheckpointFolder(tmp_path / "m1")
+    assert "model.embed_tokens.weight" in folder.names()
