@@ -25,6 +25,10 @@
 // Head sizes: any multiple of 8 up to 128 (padded with zeros to 64 or 128 in shared memory).
 #include "common.cuh"
 
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
 namespace lb {
 
 constexpr int FA_ROWS = 64;      // query rows of a tile
@@ -87,6 +91,105 @@ __device__ __forceinline__ float fa_ld_cluster(const float* local, uint32_t rank
 template <int DP>
 __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
   return (uint32_t)(row * (DP * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+// What the four warps that shared a tile's rows do when the keys are through: merge their (m, l, o) through shared
+// memory in the order of the warps, then write the result, hand it to the combining kernel, or combine it with the
+// other splits of the cluster.  scratch: 4 * 16 * (DP + 2) floats, fin: 16 * (DP + 2) floats, both free by now; with
+// NAMED only the 128 computing threads of a larger CTA take part in the barriers.
+template <bool NAMED>
+__device__ __forceinline__ void keysplit_sync() {
+  if (NAMED) asm volatile("bar.sync 1, 128;" ::: "memory");
+  else __syncthreads();
+}
+template <int DP, bool NAMED>
+__device__ __forceinline__ void keysplit_finish(const FlashParams& p, float* scratch, float* fin, const float (&o)[DP / 8][4],
+                                                const float (&m_run)[2], const float (&l_run)[2], int t0, int rows, int kvh, int split) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.group, d = p.head_dim;
+  // Merge the four warps' (m, l, o) through shared memory (the stages are no longer needed).
+  keysplit_sync<NAMED>();
+  float* mo = scratch;                                                       // [4][16][DP]
+  float* mml = mo + 4 * 16 * DP;                                           // [4][16][2]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = (lane >> 2) + 8 * h;
+#pragma unroll
+    for (int i = 0; i < DP / 8; ++i) {
+      const int dim = i * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(mo + ((warp * 16 + r) * DP + dim)) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+    }
+    if ((lane & 3) == 0) {
+      mml[(warp * 16 + r) * 2 + 0] = m_run[h] == -INFINITY ? -INFINITY : m_run[h] * p.scale_log2;
+      mml[(warp * 16 + r) * 2 + 1] = l_run[h];
+    }
+  }
+  keysplit_sync<NAMED>();
+  // With a cluster the merged (M, L, O) of this CTA stay in shared memory (in the value stages, free by
+  // now) for the combination across the cluster; otherwise they go straight out.
+  float* fin_o = fin;                                                        // [16][DP]
+  float* fin_ml = fin_o + 16 * DP;                                                               // [16][2]
+  for (int r = 0; r < rows; ++r) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
+    float L = 0.f, wgt[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mml[(w * 16 + r) * 2];
+      wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += mml[(w * 16 + r) * 2 + 1] * wgt[w];
+    }
+    const int token = t0 + r / G, head = kvh * G + r % G;
+    if (p.cluster > 0 && tid == 0) { fin_ml[r * 2] = M; fin_ml[r * 2 + 1] = L; }
+    for (int dim = tid; dim < d; dim += FA_THREADS) {
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) acc += mo[(w * 16 + r) * DP + dim] * wgt[w];
+      if (p.cluster > 0) {
+        fin_o[r * DP + dim] = acc;
+      } else if (p.splits == 1) {
+        p.out[((size_t)token * p.num_q_heads + head) * d + dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      } else {
+        const size_t slot = (((size_t)blockIdx.x * p.num_kv_heads + kvh) * p.splits + split) * p.part_rows + r;
+        p.part_o[slot * d + dim] = acc;
+        if (dim == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
+      }
+    }
+  }
+  if (p.cluster > 0) {
+    // Every CTA of the cluster combines its share of the head's dimensions over all splits, in their
+    // order, reading the peers' shared memory.
+    fa_cluster_sync();
+    const int per = (d + p.cluster - 1) / p.cluster;
+    for (int item = tid; item < rows * per; item += FA_THREADS) {
+      const int r = item / per, dim = split * per + item % per;
+      if (dim >= d) continue;
+      // All loads from the peers' shared memory first (each takes several hundred cycles), then the arithmetic.
+      float mz[8], lz[8], oz[8];
+#pragma unroll
+      for (int z = 0; z < 8; ++z) {
+        const bool in = z < p.splits;
+        mz[z] = in ? fa_ld_cluster(fin_ml + r * 2, z) : -INFINITY;
+        lz[z] = in ? fa_ld_cluster(fin_ml + r * 2 + 1, z) : 0.f;
+        oz[z] = in ? fa_ld_cluster(fin_o + r * DP + dim, z) : 0.f;
+      }
+      float M = -INFINITY;
+#pragma unroll
+      for (int z = 0; z < 8; ++z) M = fmaxf(M, mz[z]);
+      float L = 0.f, acc = 0.f;
+#pragma unroll
+      for (int z = 0; z < 8; ++z) {
+        if (mz[z] == -INFINITY) continue;
+        const float wz = exp2f(mz[z] - M);
+        L += lz[z] * wz;
+        acc += oz[z] * wz;
+      }
+      const int token = t0 + r / G, head = kvh * G + r % G;
+      p.out[((size_t)token * p.num_q_heads + head) * d + dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+    fa_cluster_sync();                        // nobody leaves while a peer still reads its memory
+  }
 }
 
 template <int DP, bool KEYSPLIT>
@@ -313,89 +416,8 @@ flash_attention_kernel(FlashParams p) {
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
   }
   if (KEYSPLIT) {
-    // Merge the four warps' (m, l, o) through shared memory (the stages are no longer needed).
-    __syncthreads();
-    float* mo = reinterpret_cast<float*>(smem + FA_ROWS * DP * 2);          // [4][16][DP]
-    float* mml = mo + 4 * 16 * DP;                                           // [4][16][2]
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = (lane >> 2) + 8 * h;
-#pragma unroll
-      for (int i = 0; i < DP / 8; ++i) {
-        const int dim = i * 8 + (lane & 3) * 2;
-        *reinterpret_cast<float2*>(mo + ((warp * 16 + r) * DP + dim)) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
-      }
-      if ((lane & 3) == 0) {
-        mml[(warp * 16 + r) * 2 + 0] = m_run[h] == -INFINITY ? -INFINITY : m_run[h] * p.scale_log2;
-        mml[(warp * 16 + r) * 2 + 1] = l_run[h];
-      }
-    }
-    __syncthreads();
-    // With a cluster the merged (M, L, O) of this CTA stay in shared memory (in the value stages, free by
-    // now) for the combination across the cluster; otherwise they go straight out.
-    float* fin_o = reinterpret_cast<float*>(smem + FA_ROWS * DP * 2 + STAGES * TILE_BYTES);    // [16][DP]
-    float* fin_ml = fin_o + 16 * DP;                                                               // [16][2]
-    for (int r = 0; r < rows; ++r) {
-      float M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
-      float L = 0.f, wgt[4];
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float mw = mml[(w * 16 + r) * 2];
-        wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - M);
-        L += mml[(w * 16 + r) * 2 + 1] * wgt[w];
-      }
-      const int token = t0 + r / G, head = kvh * G + r % G;
-      if (p.cluster > 0 && tid == 0) { fin_ml[r * 2] = M; fin_ml[r * 2 + 1] = L; }
-      for (int dim = tid; dim < d; dim += FA_THREADS) {
-        float acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) acc += mo[(w * 16 + r) * DP + dim] * wgt[w];
-        if (p.cluster > 0) {
-          fin_o[r * DP + dim] = acc;
-        } else if (p.splits == 1) {
-          p.out[((size_t)token * p.num_q_heads + head) * d + dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-        } else {
-          const size_t slot = (((size_t)blockIdx.x * p.num_kv_heads + kvh) * p.splits + split) * p.part_rows + r;
-          p.part_o[slot * d + dim] = acc;
-          if (dim == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
-        }
-      }
-    }
-    if (p.cluster > 0) {
-      // Every CTA of the cluster combines its share of the head's dimensions over all splits, in their
-      // order, reading the peers' shared memory.
-      fa_cluster_sync();
-      const int per = (d + p.cluster - 1) / p.cluster;
-      for (int item = tid; item < rows * per; item += FA_THREADS) {
-        const int r = item / per, dim = split * per + item % per;
-        if (dim >= d) continue;
-        // All loads from the peers' shared memory first (each takes several hundred cycles), then the arithmetic.
-        float mz[8], lz[8], oz[8];
-#pragma unroll
-        for (int z = 0; z < 8; ++z) {
-          const bool in = z < p.splits;
-          mz[z] = in ? fa_ld_cluster(fin_ml + r * 2, z) : -INFINITY;
-          lz[z] = in ? fa_ld_cluster(fin_ml + r * 2 + 1, z) : 0.f;
-          oz[z] = in ? fa_ld_cluster(fin_o + r * DP + dim, z) : 0.f;
-        }
-        float M = -INFINITY;
-#pragma unroll
-        for (int z = 0; z < 8; ++z) M = fmaxf(M, mz[z]);
-        float L = 0.f, acc = 0.f;
-#pragma unroll
-        for (int z = 0; z < 8; ++z) {
-          if (mz[z] == -INFINITY) continue;
-          const float wz = exp2f(mz[z] - M);
-          L += lz[z] * wz;
-          acc += oz[z] * wz;
-        }
-        const int token = t0 + r / G, head = kvh * G + r % G;
-        p.out[((size_t)token * p.num_q_heads + head) * d + dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-      }
-      fa_cluster_sync();                        // nobody leaves while a peer still reads its memory
-    }
+    keysplit_finish<DP, false>(p, reinterpret_cast<float*>(smem + FA_ROWS * DP * 2),
+                               reinterpret_cast<float*>(smem + FA_ROWS * DP * 2 + STAGES * TILE_BYTES), o, m_run, l_run, t0, rows, kvh, split);
     return;
   }
   if (!warp_active) return;
@@ -426,6 +448,285 @@ flash_attention_kernel(FlashParams p) {
       }
     }
   }
+}
+
+// ---- decoded tokens, keys and values fetched by TMA -----------------------------------------------------------------------
+// The kernel above spends most of its instructions on fetching: every thread computes the addresses of sixteen 16-byte
+// copies a stage and looks their pages up, and with two CTAs of four warps on an SM nothing hides the latency of that
+// chain, so the warps, not the memory, set the pace.  Here a fifth warp fetches: each of its lanes looks one page up and
+// issues one TMA copy (a box of 64 dimensions x the page's keys, up to 64, in the 128-byte swizzle, 32 KB a stage in at most
+// 32 copies), and the four computing warps only wait on the stage's barrier, multiply and give the stage back.
+// Needs a page size among 8, 16, 32, 64, 128 and tiles of at most 16 query rows.  Keys before the window's start down to
+// a multiple of 64 are fetched as well and masked; a page that the table no longer holds (behind the window, or past the
+// end) is replaced by page 0, whose keys are masked all the same.
+constexpr int FD_THREADS = 160;
+constexpr int FD_STAGES = 3;
+constexpr unsigned long long FD_WAIT_CYCLES = 4000000000ull;
+enum { FD_ERR_FULL = 401, FD_ERR_EMPTY = 402 };
+__device__ int g_flash_decode_error = 0;
+
+__device__ __forceinline__ void fd_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fd_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fd_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool fd_mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded: gives up after about two seconds, leaves a code for the host and tells the rest of the CTA.
+template <bool SLEEP>
+__device__ __forceinline__ bool fd_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (fd_mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (unsigned it = 1;; ++it) {
+    if (SLEEP) __nanosleep(64);
+    if (fd_mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if ((unsigned long long)(clock64() - t0) > FD_WAIT_CYCLES) {
+        *abort_flag = code;
+        atomicCAS(&g_flash_decode_error, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void fd_tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// Byte offset of 16-byte chunk `chunk` (of DP / 8) of key `key` in a stage's keys or values: halves of 64 dimensions,
+// each [64 keys][128 bytes] in the 128-byte swizzle that the copies write.
+__device__ __forceinline__ uint32_t fd_offset(int key, int chunk) {
+  return (uint32_t)((chunk >> 3) * 8192 + key * 128 + (((chunk & 7) ^ (key & 7)) << 4));
+}
+
+template <int DP>
+__global__ void __launch_bounds__(FD_THREADS, 2)
+flash_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, FlashParams p) {
+  constexpr int CHUNKS = DP / 8;
+  constexpr int NH = DP / 64;                       // halves of 64 dimensions
+  constexpr int MAT_BYTES = NH * 8192;              // a stage's keys (or values)
+  constexpr int STAGE_BYTES = 2 * MAT_BYTES;
+  extern __shared__ uint8_t fd_smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[2 * FD_STAGES];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const uint32_t base = ((uint32_t)__cvta_generic_to_shared(fd_smem_raw) + 1023u) & ~1023u;     // the swizzle wants 1024
+  uint8_t* base_ptr = fd_smem_raw + (base - (uint32_t)__cvta_generic_to_shared(fd_smem_raw));
+  const uint32_t q_smem = base + FD_STAGES * STAGE_BYTES;                                         // [16][DP] bfloat16
+  auto full = [&](int s) { return (uint32_t)__cvta_generic_to_shared(&bars[s]); };
+  auto empty = [&](int s) { return (uint32_t)__cvta_generic_to_shared(&bars[FD_STAGES + s]); };
+
+  pdl_trigger();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int4 tile = p.tiles[blockIdx.x];
+  const int t0 = tile.x, ntok = tile.y, seq = tile.z;
+  const int kvh = blockIdx.y, split = blockIdx.z;
+  const int G = p.group, d = p.head_dim;
+  const int rows = ntok * G;
+  const int pos0 = p.positions[t0];
+  const int pos_last = pos0 + ntok - 1;
+  const int* bt = p.block_table + (size_t)seq * p.max_pages;
+
+  // Keys this tile can see, from a multiple of a stage, and the part of them this split handles.
+  const int lo_tile = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int lo_al = lo_tile & ~(FA_KEYS - 1);
+  const int span = pos_last - lo_al + 1;
+  const int per_split = ((span + p.splits - 1) / p.splits + FA_KEYS - 1) / FA_KEYS * FA_KEYS;
+  const int kbeg = lo_al + split * per_split;
+  const int kend = min(pos_last + 1, kbeg + per_split);      // exclusive
+  const int num_stages = kend > kbeg ? (kend - kbeg + FA_KEYS - 1) / FA_KEYS : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < FD_STAGES; ++s) { fd_mbar_init(full(s), 1); fd_mbar_init(empty(s), 4); }
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // ---- the fetching warp: lane = (box of keys, half of the dimensions, keys or values) ----------------------------------
+    const int box_keys = min(p.page_size, FA_KEYS);
+    const int nops = 2 * NH * (FA_KEYS / box_keys);
+    const int kv = lane & 1, half = (lane >> 1) % NH, box = (lane >> 1) / NH;
+    const bool active = lane < nops;
+    const CUtensorMap* map = kv ? &vmap : &kmap;
+    const uint32_t dst_off = (uint32_t)(kv * MAT_BYTES + half * 8192 + box * box_keys * 128);
+    auto row_of = [&](int st) -> int {            // first row of this lane's box in the pool's [pages * kv heads * page size, d]
+      const int key0 = kbeg + st * FA_KEYS + box * box_keys;
+      int page = -1;
+      if (active && st < num_stages && key0 < kend) page = bt[key0 >> p.page_shift];
+      if (page < 0) return kvh * p.page_size;                                        // page 0: masked whatever it holds
+      return (page * p.num_kv_heads + kvh) * p.page_size + (key0 & (p.page_size - 1));
+    };
+    int row = row_of(0);                            // the tables were written before the step began
+    auto fetch = [&](int st) {
+      const int b = st % FD_STAGES;
+      if (lane == 0) fd_mbar_expect_tx(full(b), STAGE_BYTES);
+      __syncwarp();
+      if (active) fd_tma_2d(base + b * STAGE_BYTES + dst_off, map, half * 64, row, full(b));
+      row = row_of(st + 1);                         // looked up while the stage is awaited
+    };
+    // Keys before this step's first token were written by earlier steps: the first stages of them are requested while
+    // the kernel ahead (which writes this step's keys and values) may still run.
+    int st = 0;
+    for (; st < min(num_stages, FD_STAGES) && kbeg + (st + 1) * FA_KEYS <= pos0; ++st) fetch(st);
+    pdl_wait();
+    for (; st < num_stages; ++st) {
+      if (!fd_mbar_wait<true>(empty(st % FD_STAGES), (uint32_t)((st / FD_STAGES) & 1) ^ 1u, abort_flag, FD_ERR_EMPTY)) break;
+      fetch(st);
+    }
+    if (p.cluster > 0) { fa_cluster_sync(); fa_cluster_sync(); }      // the cluster's barriers count every thread
+    return;
+  }
+
+  // ---- the computing warps ----------------------------------------------------------------------------------------------------
+  pdl_wait();
+  for (int idx = tid; idx < 16 * CHUNKS; idx += 128) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool valid = r < rows && c * 8 < d;
+    const bf16* src = p.q;
+    if (valid) src = p.q + ((size_t)(t0 + r / G) * p.num_q_heads + kvh * G + r % G) * d + c * 8;
+    cp_async16(q_smem + tile_offset<DP>(r, c), src, valid);
+  }
+  cp_async_commit();
+
+  const int r0 = lane >> 2;
+  int row_pos[2], row_lo[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = r0 + 8 * h;
+    row_pos[h] = r < rows ? pos0 + r / G : -1;                  // -1: no key passes the mask
+    row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+  }
+  cp_async_wait<0>();
+  keysplit_sync<true>();
+  uint32_t qf[DP / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < DP / 16; ++kk) {
+    const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int c = kk * 2 + (lane >> 4);
+    ldmatrix_x4(q_smem + tile_offset<DP>(r, c), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+  }
+
+  float o[DP / 8][4];
+#pragma unroll
+  for (int i = 0; i < DP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int key0 = warp * 16;                        // the 16 keys of a stage this warp visits
+
+  for (int st = 0; st < num_stages; ++st) {
+    const int b = st % FD_STAGES;
+    if (!fd_mbar_wait<false>(full(b), (uint32_t)((st / FD_STAGES) & 1), abort_flag, FD_ERR_FULL)) break;
+    const uint32_t kb = base + b * STAGE_BYTES, vb = kb + MAT_BYTES;
+    const int kbase = kbeg + st * FA_KEYS;
+
+    // ---- S = Q K^T: 16 rows x this warp's 16 keys -----------------------------------------------------------------------
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < DP / 16; ++kk) {
+      // matrices: (keys lo, dims lo), (keys lo, dims hi), (keys hi, dims lo), (keys hi, dims hi)
+      const int key = key0 + (lane & 7) + (lane >> 4) * 8;
+      const int c = kk * 2 + ((lane >> 3) & 1);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(kb + fd_offset(key, c), b0, b1, b2, b3);
+      mma_bf16(s[0], qf[kk], b0, b1);
+      mma_bf16(s[1], qf[kk], b2, b3);
+    }
+    // The values of keys past the end, or before the first key any row of the tile sees, are whatever a page still
+    // holds: zeros instead, so that nothing a reused page holds can reach a sum (their weights are zeros, but zero
+    // times a NaN is not).
+    if (kbase + FA_KEYS > kend || kbase < lo_tile) {
+      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+      for (int idx = lane; idx < 16 * CHUNKS; idx += 32) {
+        const int key = key0 + idx / CHUNKS, c = idx % CHUNKS;
+        if (kbase + key >= kend || kbase + key < lo_tile)
+          *reinterpret_cast<uint4*>(base_ptr + b * STAGE_BYTES + MAT_BYTES + fd_offset(key, c)) = zero;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // a later copy into this stage comes after these stores
+      __syncwarp();
+    }
+
+    // ---- mask, online softmax ---------------------------------------------------------------------------------------------
+    const bool need_mask = (kbase + FA_KEYS - 1 > pos0) || (p.window > 0) || (kbase + FA_KEYS > kend);
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        if (need_mask) {
+          const int j = kbase + key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+          if (j > row_pos[h] || j < row_lo[h] || j >= kend) s[nb][e] = -INFINITY;
+        }
+        m_new[h] = fmaxf(m_new[h], s[nb][e]);
+      }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+      m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+      m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h] * p.scale_log2;
+      alpha[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] * p.scale_log2 - m_use[h]);
+      m_run[h] = m_new[h];
+    }
+    float row_sum[2] = {0.f, 0.f};
+    uint32_t pf[4];
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      float pv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        pv[e] = exp2_approx(fmaf(s[nb][e], p.scale_log2, -m_use[h]));   // 2^-inf = 0 for masked keys
+        row_sum[h] += pv[e];
+      }
+      pf[nb * 2 + 0] = pack_bf16(pv[0], pv[1]);       // C fragments of two key blocks become one A fragment of 16 keys
+      pf[nb * 2 + 1] = pack_bf16(pv[2], pv[3]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * alpha[h] + row_sum[h];
+    if (!__all_sync(0xffffffffu, alpha[0] == 1.f && alpha[1] == 1.f)) {
+#pragma unroll
+      for (int i = 0; i < DP / 8; ++i) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      }
+    }
+
+    // ---- O += P V ------------------------------------------------------------------------------------------------------------
+#pragma unroll
+    for (int db = 0; db < DP / 8; db += 2) {
+      // matrices (transposed on load): (keys lo, dims db), (keys hi, dims db), (keys lo, dims db+1), (keys hi, dims db+1)
+      const int key = key0 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int c = db + (lane >> 4);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(vb + fd_offset(key, c), b0, b1, b2, b3);
+      mma_bf16(o[db], pf, b0, b1);
+      mma_bf16(o[db + 1], pf, b2, b3);
+    }
+    __syncwarp();
+    if (lane == 0) fd_mbar_arrive(empty(b));          // this warp has read the stage
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  // the stages are free now (every copy that was issued has been waited for): the merge uses them
+  float* scratch = reinterpret_cast<float*>(base_ptr);
+  keysplit_finish<DP, true>(p, scratch, scratch + 4 * 16 * (DP + 2), o, m_run, l_run, t0, rows, kvh, split);
 }
 
 // Combines the partials of the splits, in their order: out = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M).
@@ -481,7 +782,66 @@ __global__ void flash_combine_kernel(FlashParams p) {
   }
 }
 
+// ---- host side of the TMA kernel: tensor maps of the pools, made once per pool ----------------------------------------------------
+typedef CUresult (*FdEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static FdEncodeFn fd_encode_fn() {
+  static FdEncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (FdEncodeFn)sym;
+  });
+  return fn;
+}
+struct FdMapKey {
+  const void* base; long long rows; int d, box;
+  bool operator==(const FdMapKey& o) const { return base == o.base && rows == o.rows && d == o.d && box == o.box; }
+};
+struct FdMapKeyHash {
+  size_t operator()(const FdMapKey& k) const {
+    size_t h = std::hash<const void*>()(k.base);
+    h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.d; h = h * 1000003u ^ (size_t)k.box;
+    return h;
+  }
+};
+static std::unordered_map<FdMapKey, CUtensorMap, FdMapKeyHash> g_fd_maps;
+static std::mutex g_fd_mu;
+
+// A pool [pages, kv heads, page size, d] as rows of d: boxes of 64 dimensions x `box` rows, 128-byte swizzle; what lies past
+// d reads as zeros.
+static bool fd_pool_map(CUtensorMap* out, const void* pool, long long rows, int d, int box) {
+  FdMapKey key{pool, rows, d, box};
+  std::lock_guard<std::mutex> g(g_fd_mu);
+  auto it = g_fd_maps.find(key);
+  if (it != g_fd_maps.end()) { *out = it->second; return true; }
+  FdEncodeFn fn = fd_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)d * 2};
+  cuuint32_t bx[2] = {64, (cuuint32_t)box};
+  cuuint32_t estr[2] = {1, 1};
+  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (g_fd_maps.size() > 4096) g_fd_maps.clear();
+  g_fd_maps.emplace(key, *out);
+  return true;
+}
+
 }  // namespace lb
+
+// Reads and clears the flag a bounded wait of the TMA kernel sets when it gives up (0: none).
+LB_EXPORT int lb_attention_flash_device_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, lb::g_flash_decode_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(lb::g_flash_decode_error, &zero, sizeof(int));
+  return v;
+}
 
 // Floats of workspace a launch with these sizes needs (partials of o, then of m and l).
 LB_EXPORT long long lb_attention_flash_workspace(int num_tiles, int num_kv_heads, int splits, int part_rows, int head_dim) {
@@ -494,7 +854,7 @@ LB_EXPORT long long lb_attention_flash_workspace(int num_tiles, int num_kv_heads
 LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, const void* v_cache,
                                  const int* positions, const int* block_table, const void* tiles, int num_tiles,
                                  int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
-                                 int window, float scale, int splits, int part_rows, float* workspace,
+                                 int num_pages, int window, float scale, int splits, int part_rows, float* workspace,
                                  long long workspace_elems, cudaStream_t stream) {
   LB_CHECK_ARG(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
                "attention_flash: %d query heads are not a multiple of %d kv heads", num_q_heads, num_kv_heads);
@@ -532,6 +892,49 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   // Up to 8 splits (a power of two) of such tiles combine inside a thread-block cluster.
   const bool clustered = keysplit && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && !force_workspace;
   p.cluster = clustered ? splits : 0;
+  // Decoded tokens over pages of 8 to 128 keys: the kernel whose fifth warp fetches by TMA.  num_pages <= 0 keeps it off.
+  const bool by_tma = keysplit && num_pages > 0 && p.page_shift >= 3 && page_size <= 128 &&
+                      (long long)num_pages * num_kv_heads * page_size < (1ll << 31);
+  if (by_tma) {
+    CUtensorMap mk, mv;
+    const long long pool_rows = (long long)num_pages * num_kv_heads * page_size;
+    const int box = page_size < lb::FA_KEYS ? page_size : lb::FA_KEYS;
+    if (!lb::fd_pool_map(&mk, k_cache, pool_rows, head_dim, box) || !lb::fd_pool_map(&mv, v_cache, pool_rows, head_dim, box)) {
+      lb::set_error("attention_flash: cuTensorMapEncodeTiled failed (pool of %lld rows of %d)", pool_rows, head_dim);
+      return 3;
+    }
+    const int fd_smem = 1024 + lb::FD_STAGES * 2 * (dp / 64) * 8192 + 16 * dp * 2;
+    static bool fd_cfg[2] = {false, false};
+    void (*kern)(CUtensorMap, CUtensorMap, lb::FlashParams) = dp == 64 ? lb::flash_decode_tma_kernel<64> : lb::flash_decode_tma_kernel<128>;
+    if (!fd_cfg[dp == 64]) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fd_smem);
+      if (e != cudaSuccess) { lb::set_error("attention_flash: cannot reserve %d bytes of shared memory: %s", fd_smem, cudaGetErrorString(e)); return 2; }
+      fd_cfg[dp == 64] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(lb::FD_THREADS); cfg.dynamicSmemBytes = fd_smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (clustered) {
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = 1; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = splits;
+      ++na;
+    }
+    if (lb::g_pdl_enabled) {
+      attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[na].val.programmaticStreamSerializationAllowed = 1;
+      ++na;
+    }
+    cfg.attrs = attr; cfg.numAttrs = na;
+    cudaLaunchKernelEx(&cfg, kern, mk, mv, p);
+    LB_CHECK_LAUNCH("attention_flash (tma)");
+    if (splits > 1 && !clustered) {
+      dim3 cgrid(num_tiles, num_kv_heads), cblock(32, 4);
+      lb::launch(lb::flash_combine_kernel, cgrid, cblock, (size_t)4 * splits * sizeof(float), stream, p);
+      LB_CHECK_LAUNCH("attention_flash combine");
+    }
+    return 0;
+  }
 #define LB_FLASH_LAUNCH(DP, KS)                                                                                 \
   do {                                                                                                          \
     static bool cfg = false;                                                                                    \

@@ -45,7 +45,7 @@ _SIGNATURES = {
     "lb_upload": [c_void_p, c_void_p, c_longlong, c_void_p],
     "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                           c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
+                           c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -303,7 +303,9 @@ def device_error() -> int:
     lib = library()
     lib.lb_device_error.restype = c_int
     lib.lb_attention_tcgen05_device_error.restype = c_int
-    return int(lib.lb_device_error()) or int(lib.lb_attention_tcgen05_device_error())
+    lib.lb_attention_flash_device_error.restype = c_int
+    return (int(lib.lb_device_error()) or int(lib.lb_attention_tcgen05_device_error())
+            or int(lib.lb_attention_flash_device_error()))
 
 
 def linear(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, fast: bool) -> None:
@@ -341,7 +343,8 @@ def attention_splits(num_tiles: int, num_kv_heads: int, max_span: int, max_rows:
     of the 148 SMs).  Fewer CTAs than slots: as many ranges as still fit one wave; for tiles of up to
     16 query rows a count below 16 becomes a power of two, because up to 8 ranges of such tiles combine
     inside a thread-block cluster instead of through a workspace and a second kernel.  More CTAs than
-    slots: the count (up to 8) whose last wave is fullest.  A range has 256 keys at least."""
+    slots: the count (up to 8) that costs least by a model of the last wave and of the CTAs' fixed costs.  A range
+    has 256 keys at least."""
     base = max(num_tiles * num_kv_heads, 1)
     cap = max(1, min(max_span // 256, 64))
     if max_rows > 16 and base >= slots // 2:
@@ -351,22 +354,28 @@ def attention_splits(num_tiles: int, num_kv_heads: int, max_span: int, max_rows:
         if max_rows <= 16 and s < 16:
             s = 8 if s >= 8 else 4 if s >= 4 else 2 if s >= 2 else 1
         return s
-    best, best_fill = 1, 0.0
+    # More tiles than slots.  The memory is busy as long as about half the slots are filled, so only a last wave of fewer
+    # CTAs than that costs (the more the longer a CTA runs), and every CTA costs its start and its end: measured,
+    # about 6 us of a slot per CTA, 0.022 us per key of a CTA's range while a full wave shares the memory.
+    best, best_cost = 1, float("inf")
     for s in range(1, min(cap, 8) + 1):
-        waves = base * s / slots
-        fill = waves / -(-base * s // slots)
-        if fill > best_fill + 0.02:
-            best, best_fill = s, fill
+        rest = (base * s) % slots
+        tail = 0.6 * (0.022 * max_span / s) * max(0.0, 1.0 - rest / (slots / 2)) if rest else 0.0
+        cost = 6.0 * base * s / slots + tail
+        if cost < best_cost - 1e-9:
+            best, best_cost = s, cost
     return best
 
 
 def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, max_rows: int,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-                    splits: int, stream: int, force_workspace: bool = False) -> None:
+                    splits: int, stream: int, force_workspace: bool = False, tma: bool = True) -> None:
     """Tensor-core attention over pages.  tiles: int32 [n, 4] of (first token, tokens, request index, 0).
     `force_workspace` sends the partial results of the splits through the workspace and the combining
-    kernel even where a cluster could combine them."""
+    kernel even where a cluster could combine them.  Tiles of at most 16 query rows (decoded tokens) over pages of
+    8 to 128 tokens run in the kernel whose keys and values a warp of its own fetches by TMA; `tma=False` keeps them
+    in the kernel that fetches with 16-byte copies, which takes every page size."""
     _check(q, "q", torch.bfloat16); _check(out, "attention output", torch.bfloat16)
     _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
     _check(positions, "positions", torch.int32); _check(block_table, "block table", torch.int32)
@@ -380,8 +389,8 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
         ws_elems = ws.numel()
     _call("lb_attention_flash", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
           positions.data_ptr(), block_table.data_ptr(), tiles.data_ptr(), n, num_q_heads, num_kv_heads, head_dim,
-          page_size, block_table.shape[1], window, scale, -splits if force_workspace else splits, max_rows, _ptr(ws),
-          ws_elems, stream)
+          page_size, block_table.shape[1], k_cache.shape[0] if tma else 0, window, scale,
+          -splits if force_workspace else splits, max_rows, _ptr(ws), ws_elems, stream)
 
 
 def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,

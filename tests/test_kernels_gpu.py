@@ -213,8 +213,9 @@ def test_attention_plain(env, act, nq, nkv, d, ps, window, seqs):
     assert rel(out.cpu(), ref) < (3e-6 if act == torch.float32 else 6e-3)
 
 
-def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=None, k_scale=1.0, q=None, hook=None):
-    """splits < 0: that many key ranges, combined through the workspace even where a cluster could."""
+def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=None, k_scale=1.0, q=None, hook=None, tma=True):
+    """splits < 0: that many key ranges, combined through the workspace even where a cluster could.  tma=False: decoded
+    tokens, too, in the kernel that fetches with 16-byte copies."""
     kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, torch.bfloat16)
     fill_pages(kc, vc, bt.cpu(), seqs, ps, k_scale=k_scale)
     if hook:
@@ -233,7 +234,9 @@ def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=Non
     rows = min(64, max(n for _, n, _, _ in tiles) * G)
     sp = abs(splits) if splits else ops.attention_splits(len(tiles), nkv, max(s + n for s, n in seqs), rows)
     ops.attention_flash(q, out, kc, vc, pos, bt, tl, rows, nq, nkv, d, ps, window, scale, sp, st,
-                        force_workspace=bool(splits and splits < 0))
+                        force_workspace=bool(splits and splits < 0), tma=tma)
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
     ref = attention_reference(q, kc, vc, bt, pos.cpu(), seq.cpu(), nq, nkv, ps, window, scale)
     return out, ref
 
@@ -256,9 +259,10 @@ def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=Non
     (3, 1, 104, 64, 0, [(0, 64), (64, 64), (127, 1)], None),
     (64, 1, 64, 16, 0, [(10, 3)], None),
 ])
-def test_attention_flash(env, nq, nkv, d, ps, window, seqs, splits):
+@pytest.mark.parametrize("tma", [True, False])
+def test_attention_flash(env, nq, nkv, d, ps, window, seqs, splits, tma):
     ops, dev, st = env
-    out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits)
+    out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits, tma=tma)
     assert torch.isfinite(out).all()
     assert rel(out.cpu(), ref) < 8e-3
 
@@ -382,14 +386,15 @@ def test_attention_flash_finds_a_far_key_among_hundreds(env):
             vc[page, kvh, slot] = 7.0
         marks["v"] = vc[page, :, slot].clone()
 
-    for splits in (1, 4, -4, 7):
-        out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, 0, [(L - 1, 1)], splits, k_scale=0.05, q=q, hook=hook)
+    for splits, tma in ((1, True), (4, True), (-4, True), (7, True), (1, False), (4, False), (-4, False), (7, False)):
+        out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, 0, [(L - 1, 1)], splits, k_scale=0.05, q=q, hook=hook, tma=tma)
         assert rel(out.cpu(), ref) < 8e-3
         assert (out[0, 0].float() - 7.0).abs().max() < 0.1 and (out[0, 4].float() - 7.0).abs().max() < 0.1
 
 
+@pytest.mark.parametrize("tma", [True, False])
 @pytest.mark.parametrize("window", [1, 16, 17, 63, 64, 65])
-def test_attention_flash_window_edge(env, window):
+def test_attention_flash_window_edge(env, window, tma):
     """The key just outside the window carries a huge value: if the edge is off by one it shows."""
     ops, dev, st = env
     nq, nkv, d, ps = 2, 1, 64, 16
@@ -401,9 +406,9 @@ def test_attention_flash_window_edge(env, window):
         j = pos_q - window + 1                                   # the first key that must be seen
         vc[int(bt[0, j // ps]), :, j % ps] = -5.0
 
-    out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, window, [(pos_q, 1)], 1, hook=hook)
+    out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, window, [(pos_q, 1)], 1, hook=hook, tma=tma)
     assert out.float().abs().max() < 50 and rel(out.cpu(), ref) < 8e-3
-    out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, window, [(pos_q - 30, 31)], 1, hook=hook)
+    out, ref = run_flash(ops, dev, st, nq, nkv, d, ps, window, [(pos_q - 30, 31)], 1, hook=hook, tma=tma)
     assert rel(out.cpu(), ref) < 8e-3
 
 
