@@ -95,8 +95,10 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 
 // What the four warps that shared a tile's rows do when the keys are through: merge their (m, l, o) through shared
 // memory in the order of the warps, then write the result, hand it to the combining kernel, or combine it with the
-// other splits of the cluster.  scratch: 4 * 16 * (DP + 2) floats, fin: 16 * (DP + 2) floats, both free by now; with
-// NAMED only the 128 computing threads of a larger CTA take part in the barriers.
+// other splits of the cluster.  scratch: keysplit_scratch_floats(DP) floats, fin: 16 * (DP + 2) floats, both free by now;
+// with NAMED only the 128 computing threads of a larger CTA take part in the barriers.  Rows of the partial results are
+// DP + 8 floats apart, so that the eight rows a warp stores at a time fall into different banks.
+__host__ __device__ constexpr int keysplit_scratch_floats(int dp) { return 4 * 16 * (dp + 8) + 4 * 16 * 2; }
 template <bool NAMED>
 __device__ __forceinline__ void keysplit_sync() {
   if (NAMED) asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -109,15 +111,17 @@ __device__ __forceinline__ void keysplit_finish(const FlashParams& p, float* scr
   const int G = p.group, d = p.head_dim;
   // Merge the four warps' (m, l, o) through shared memory (the stages are no longer needed).
   keysplit_sync<NAMED>();
-  float* mo = scratch;                                                       // [4][16][DP]
-  float* mml = mo + 4 * 16 * DP;                                           // [4][16][2]
+  constexpr int MS = DP + 8;
+  float* mo = scratch;                                                       // [4][16][MS]
+  float* mml = mo + 4 * 16 * MS;                                             // [4][16][2]
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = (lane >> 2) + 8 * h;
+    if (r >= rows) continue;                                                 // rows past the tile's last are never read
 #pragma unroll
     for (int i = 0; i < DP / 8; ++i) {
       const int dim = i * 8 + (lane & 3) * 2;
-      *reinterpret_cast<float2*>(mo + ((warp * 16 + r) * DP + dim)) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+      *reinterpret_cast<float2*>(mo + ((warp * 16 + r) * MS + dim)) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
     }
     if ((lane & 3) == 0) {
       mml[(warp * 16 + r) * 2 + 0] = m_run[h] == -INFINITY ? -INFINITY : m_run[h] * p.scale_log2;
@@ -145,7 +149,7 @@ __device__ __forceinline__ void keysplit_finish(const FlashParams& p, float* scr
     for (int dim = tid; dim < d; dim += FA_THREADS) {
       float acc = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) acc += mo[(w * 16 + r) * DP + dim] * wgt[w];
+      for (int w = 0; w < 4; ++w) acc += mo[(w * 16 + r) * MS + dim] * wgt[w];
       if (p.cluster > 0) {
         fin_o[r * DP + dim] = acc;
       } else if (p.splits == 1) {
@@ -726,7 +730,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
   }
   // the stages are free now (every copy that was issued has been waited for): the merge uses them
   float* scratch = reinterpret_cast<float*>(base_ptr);
-  keysplit_finish<DP, true>(p, scratch, scratch + 4 * 16 * (DP + 2), o, m_run, l_run, t0, rows, kvh, split);
+  keysplit_finish<DP, true>(p, scratch, scratch + keysplit_scratch_floats(DP), o, m_run, l_run, t0, rows, kvh, split);
 }
 
 // Combines the partials of the splits, in their order: out = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M).
