@@ -258,6 +258,11 @@ def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=Non
     (4, 4, 80, 32, 64, [(300, 50)], 3),
     (3, 1, 104, 64, 0, [(0, 64), (64, 64), (127, 1)], None),
     (64, 1, 64, 16, 0, [(10, 3)], None),
+    (4, 2, 48, 8, 0, [(300, 1), (17, 2)], 2),                           # decoded tokens with heads narrower than a TMA box
+    (2, 2, 16, 16, 0, [(100, 1), (15, 1), (16, 1)], None),              # rows of 32 bytes
+    (8, 2, 128, 128, 0, [(1000, 1), (130, 3), (127, 1), (128, 1)], 4),  # pages of two stages
+    (8, 2, 112, 32, 50, [(1000, 2), (49, 1), (50, 1), (51, 1)], 2),     # a window over decoded tokens, head of 112
+    (12, 4, 128, 16, 0, [(5000, 1)], 3),                                # three ranges: through the workspace
 ])
 @pytest.mark.parametrize("tma", [True, False])
 def test_attention_flash(env, nq, nkv, d, ps, window, seqs, splits, tma):
