@@ -250,7 +250,10 @@ class ModelRunner:
         G, P = len(self.groups), self.max_pages_per_seq
         # Work items of the attention kernels, per group size: "all" = every entry in tiles of up to 64 query
         # rows; when the step holds portions of prompts, also "big" = those portions in work items of up to 256
-        # rows (for the tcgen05 kernel) and "rest" = the other entries in 64-row tiles.
+        # rows (for the tcgen05 kernel) and "rest" = the other entries in 64-row tiles; and when the entries that are
+        # not "big" mix tiles of at most 16 query rows (decoded tokens) with larger ones (a few tokens of a prompt),
+        # "one" = the former and "rest" = the latter: tiles of at most 16 rows have a kernel of their own, which a
+        # launch uses only if all of its tiles are such.
         tile_lists: dict[tuple[int, str], list] = {}
         first_token = [0] * S
         for i in range(1, S):
@@ -260,15 +263,20 @@ class ModelRunner:
                 tile_lists[(g, "all")] = self._decode_tiles.get(S) or self._decode_tiles.setdefault(S, self._tiles(q_lens, g, 64))
                 continue
             tile_lists[(g, "all")] = self._tiles(q_lens, g, 64)
-            if max(q_lens) >= _BIG_PORTION:
+            has_big = max(q_lens) >= _BIG_PORTION
+            if has_big:
                 # two tiles of floor(128 / g) tokens each
                 big = self._tiles(q_lens, g, 2 * (128 // g) * g, lambda n: n >= _BIG_PORTION)
                 # tiles that see the most keys first: the short ones then fill the end of the last wave
                 big.sort(key=lambda tl: -(starts[tl[2]] + (tl[0] - first_token[tl[2]]) + tl[1]))
                 tile_lists[(g, "big")] = big
-                rest = self._tiles(q_lens, g, 64, lambda n: n < _BIG_PORTION)
-                if rest:
-                    tile_lists[(g, "rest")] = rest
+            others = [n for n in q_lens if n < _BIG_PORTION]
+            mixed = any(n * g <= 16 for n in others) and any(n * g > 16 for n in others)
+            if mixed:
+                tile_lists[(g, "rest")] = self._tiles(q_lens, g, 64, lambda n: n < _BIG_PORTION and n * g > 16)
+                tile_lists[(g, "one")] = self._tiles(q_lens, g, 64, lambda n: n * g <= 16)
+            elif has_big and others:
+                tile_lists[(g, "rest")] = self._tiles(q_lens, g, 64, lambda n: n < _BIG_PORTION)
         total = 3 * T + (S + 1) + 2 * S + R + G * S * P + sum(4 * len(t) + 3 for t in tile_lists.values())
         st = self._staging_for(total)
         hi, _ = st.next_host()

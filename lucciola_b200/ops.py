@@ -423,7 +423,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     """Causal attention of this step's queries over the pages of their requests.  `fast` allows the
     tensor-core kernels where their conditions hold and the step carries tiles for this group size:
     portions of prompts go to the tcgen05 kernel, the rest (decoded tokens, short portions, other head
-    sizes) to the mma.sync kernel; everything else to the plain kernel."""
+    sizes) to the mma.sync kernels, decoded tokens in a launch of their own when the step lists them apart
+    ("one"); everything else to the plain kernel."""
     G = num_q_heads // num_kv_heads
     meta = step.attn_meta.get(G) if fast else None
     if meta is None or not attention_flash_ok(q, num_q_heads, num_kv_heads, head_dim):
@@ -437,7 +438,9 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                                               step.block_tables[group].shape[1]):
         attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"][0],
                           num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
-        kinds = ["rest"] if "rest" in meta else []
+        kinds = [k for k in ("rest", "one") if k in meta]
+    elif "big" not in meta and "one" in meta:
+        kinds = ["rest", "one"]          # decoded tokens beside a few tokens of a prompt: a launch for each
     for kind in kinds:
         tiles, rows = meta[kind]
         rows = min(rows, 64)

@@ -103,8 +103,9 @@ class StepContext:
     plans: dict = field(default_factory=dict)
     # Work items of the tensor-core attention kernels, by query-group size G: a dict of kind ->
     # (tiles int32 [n, 4] of (first token, tokens, request index, 0) on the device, most query rows of a tile).
-    # Kinds: "all" every entry in tiles of up to 64 rows; "big" the long portions in tiles of up to 128
-    # rows; "rest" what "big" leaves out, in 64-row tiles.
+    # Kinds: "all" every entry in tiles of up to 64 rows; "big" the long portions in work items of up to 256
+    # rows; "rest" what "big" leaves out, in 64-row tiles; "one" the tiles of at most 16 rows (decoded tokens),
+    # listed apart from "rest" when a step mixes them with larger tiles.
     attn_meta: dict = field(default_factory=dict)
 
 

@@ -68,10 +68,11 @@ def test_bfloat16_engine_against_float32_engine_at_real_layer_sizes(runners):
 
 
 def test_mixed_batch_at_real_layer_sizes(runners):
-    """Four live requests: portions beside decoded tokens, long contexts beside short ones."""
+    """Up to five live requests: long portions, portions of a few tokens and decoded tokens side by side (each kind
+    goes to its own attention launch), long contexts beside short ones."""
     from lucciola_b200.engine.step import StepEntry
     g = torch.Generator().manual_seed(1)
-    lens = {"a": 900, "b": 130, "c": 517, "d": 40}
+    lens = {"a": 900, "b": 140, "c": 517, "d": 45, "e": 19}
     ids = {k: torch.randint(0, CFG["vocab_size"], (n,), generator=g).tolist() for k, n in lens.items()}
     outs = {}
     for dtype in ("float32", "bfloat16"):
@@ -79,9 +80,10 @@ def test_mixed_batch_at_real_layer_sizes(runners):
         got = {}
         r.step([StepEntry("a", ids["a"][:800], []), StepEntry("b", ids["b"][:100], [])])
         steps = [
-            [("a", 800, 850), ("b", 100, 101), ("c", 0, 300)],
-            [("a", 850, 851), ("b", 101, 102), ("c", 300, 517), ("d", 0, 39)],
-            [("a", 851, 900), ("b", 102, 130), ("d", 39, 40)],
+            [("a", 800, 850), ("b", 100, 101), ("c", 0, 300), ("e", 0, 7)],          # a few tokens beside long portions
+            [("a", 850, 851), ("b", 101, 102), ("c", 300, 517), ("d", 0, 39), ("e", 7, 12)],
+            [("a", 851, 900), ("b", 102, 130), ("d", 39, 40), ("e", 12, 13)],
+            [("b", 130, 131), ("d", 40, 41), ("e", 13, 19)],                          # decoded tokens beside a few tokens only
         ]
         for step in steps:
             entries = [StepEntry(k, ids[k][s:e], list(range(e - s))) for k, s, e in step]
