@@ -170,9 +170,9 @@ __device__ __forceinline__ void keysplit_finish(const FlashParams& p, float* scr
       const int r = item / per, dim = split * per + item % per;
       if (dim >= d) continue;
       // All loads from the peers' shared memory first (each takes several hundred cycles), then the arithmetic.
-      float mz[8], lz[8], oz[8];
+      float mz[16], lz[16], oz[16];
 #pragma unroll
-      for (int z = 0; z < 8; ++z) {
+      for (int z = 0; z < 16; ++z) {
         const bool in = z < p.splits;
         mz[z] = in ? fa_ld_cluster(fin_ml + r * 2, z) : -INFINITY;
         lz[z] = in ? fa_ld_cluster(fin_ml + r * 2 + 1, z) : 0.f;
@@ -180,10 +180,10 @@ __device__ __forceinline__ void keysplit_finish(const FlashParams& p, float* scr
       }
       float M = -INFINITY;
 #pragma unroll
-      for (int z = 0; z < 8; ++z) M = fmaxf(M, mz[z]);
+      for (int z = 0; z < 16; ++z) M = fmaxf(M, mz[z]);
       float L = 0.f, acc = 0.f;
 #pragma unroll
-      for (int z = 0; z < 8; ++z) {
+      for (int z = 0; z < 16; ++z) {
         if (mz[z] == -INFINITY) continue;
         const float wz = exp2f(mz[z] - M);
         L += lz[z] * wz;
@@ -786,6 +786,11 @@ __global__ void flash_combine_kernel(FlashParams p) {
   }
 }
 
+static int log2_exact(int v) {          // log2 of a power of two, else -1
+  for (int b = 0; b < 31; ++b) if ((1 << b) == v) return b;
+  return -1;
+}
+
 // ---- host side of the TMA kernel: tensor maps of the pools, made once per pool ----------------------------------------------------
 typedef CUresult (*FdEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -847,6 +852,33 @@ LB_EXPORT int lb_attention_flash_device_error() {
   return v;
 }
 
+// How many clusters of 16 CTAs of the TMA kernel the GPU keeps resident at a time (0: it does not schedule them).
+// Callers use clusters of 16 only for launches of at most this many clusters.
+LB_EXPORT int lb_attention_flash_wide_clusters(int head_dim) {
+  static int cached[2] = {-1, -1};
+  const int dp = head_dim <= 64 ? 64 : 128;
+  int& c = cached[dp == 64];
+  if (c >= 0) return c;
+  void (*kern)(CUtensorMap, CUtensorMap, lb::FlashParams) = dp == 64 ? lb::flash_decode_tma_kernel<64> : lb::flash_decode_tma_kernel<128>;
+  const int fd_smem = 1024 + lb::FD_STAGES * 2 * (dp / 64) * 8192 + 16 * dp * 2;
+  c = 0;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess ||
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fd_smem) != cudaSuccess) {
+    cudaGetLastError();
+    return c;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, 1, 16); cfg.blockDim = dim3(lb::FD_THREADS); cfg.dynamicSmemBytes = fd_smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 16;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) c = n;
+  else cudaGetLastError();
+  return c;
+}
+
 // Floats of workspace a launch with these sizes needs (partials of o, then of m and l).
 LB_EXPORT long long lb_attention_flash_workspace(int num_tiles, int num_kv_heads, int splits, int part_rows, int head_dim) {
   if (splits <= 1) return 0;
@@ -874,7 +906,13 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
                ((uintptr_t)out % 4 == 0), "attention_flash: operands must be 16-byte aligned");
   if (num_tiles == 0) return 0;
   LB_CHECK_ARG(part_rows >= group && part_rows <= lb::FA_ROWS, "attention_flash: rows of a tile must be in %d..%d, got %d", group, lb::FA_ROWS, part_rows);
-  const bool may_cluster = part_rows <= 16 && splits <= 8 && (splits & (splits - 1)) == 0 && !force_workspace;
+  const int page_shift = lb::log2_exact(page_size);
+  // Decoded tokens over pages of 8 to 128 keys: the kernel whose fifth warp fetches by TMA.  num_pages <= 0 keeps it off.
+  const bool by_tma = part_rows <= 16 && num_pages > 0 && page_shift >= 3 && page_size <= 128 &&
+                      (long long)num_pages * num_kv_heads * page_size < (1ll << 31);
+  // Up to 8 splits (a power of two) of tiles of at most 16 rows combine inside a thread-block cluster; the TMA kernel
+  // also takes clusters of 16 (a size the launch has to ask for: not every GPU schedules it).
+  const bool may_cluster = part_rows <= 16 && splits <= (by_tma ? 16 : 8) && (splits & (splits - 1)) == 0 && !force_workspace;
   LB_CHECK_ARG(splits == 1 || may_cluster || (workspace && workspace_elems >= lb_attention_flash_workspace(num_tiles, num_kv_heads, splits, part_rows, head_dim)),
                "attention_flash: the workspace is too small for %d splits", splits);
   lb::FlashParams p;
@@ -885,20 +923,15 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   p.part_rows = part_rows;
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim; p.group = group;
   p.page_size = page_size; p.window = window; p.splits = splits;
-  p.page_shift = -1;
-  for (int b = 0; b < 31; ++b) if ((1 << b) == page_size) p.page_shift = b;
+  p.page_shift = page_shift;
   p.scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(num_tiles, num_kv_heads, splits);
   const int dp = head_dim <= 64 ? 64 : 128;
   const int smem = part_rows <= 16 ? (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2   // query tile + 3 stages
                                    : 2 * 2 * lb::FA_KEYS * dp * 2;                             // 2 stages, query tile aliased
   const bool keysplit = part_rows <= 16;      // no tile has more than 16 query rows: the warps share them
-  // Up to 8 splits (a power of two) of such tiles combine inside a thread-block cluster.
-  const bool clustered = keysplit && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && !force_workspace;
+  const bool clustered = splits > 1 && may_cluster;
   p.cluster = clustered ? splits : 0;
-  // Decoded tokens over pages of 8 to 128 keys: the kernel whose fifth warp fetches by TMA.  num_pages <= 0 keeps it off.
-  const bool by_tma = keysplit && num_pages > 0 && p.page_shift >= 3 && page_size <= 128 &&
-                      (long long)num_pages * num_kv_heads * page_size < (1ll << 31);
   if (by_tma) {
     CUtensorMap mk, mv;
     const long long pool_rows = (long long)num_pages * num_kv_heads * page_size;
@@ -911,6 +944,7 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
     static bool fd_cfg[2] = {false, false};
     void (*kern)(CUtensorMap, CUtensorMap, lb::FlashParams) = dp == 64 ? lb::flash_decode_tma_kernel<64> : lb::flash_decode_tma_kernel<128>;
     if (!fd_cfg[dp == 64]) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fd_smem);
       if (e != cudaSuccess) { lb::set_error("attention_flash: cannot reserve %d bytes of shared memory: %s", fd_smem, cudaGetErrorString(e)); return 2; }
       fd_cfg[dp == 64] = true;

@@ -263,6 +263,8 @@ def run_flash(ops, dev, st, nq, nkv, d, ps, window, seqs, splits=None, scale=Non
     (8, 2, 128, 128, 0, [(1000, 1), (130, 3), (127, 1), (128, 1)], 4),  # pages of two stages
     (8, 2, 112, 32, 50, [(1000, 2), (49, 1), (50, 1), (51, 1)], 2),     # a window over decoded tokens, head of 112
     (12, 4, 128, 16, 0, [(5000, 1)], 3),                                # three ranges: through the workspace
+    (32, 8, 128, 16, 0, [(8191, 1)], 16),                               # sixteen ranges: one cluster of 16 a kv head
+    (16, 2, 64, 32, 300, [(6000, 1), (5000, 2)], 16),
 ])
 @pytest.mark.parametrize("tma", [True, False])
 def test_attention_flash(env, nq, nkv, d, ps, window, seqs, splits, tma):
