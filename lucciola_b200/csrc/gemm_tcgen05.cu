@@ -583,6 +583,11 @@ constexpr int PF_BM = 128;       // tokens of a tile (lanes)
 constexpr int PF_BN = 256;       // the most features of a tile (columns of an accumulator)
 constexpr int PF_STAGES = 4;
 
+// The feature tiles of a launch: `cols1` columns of tiles `bn1` wide, then the features from cols1 * bn1 on in tiles
+// `bn2` wide (their weight boxes come through a second tensor map).  Tiles are numbered column by column, the token
+// tile running fastest, the second kind after the first.
+struct PrefillPlan { int bn1, cols1, bn2; };
+
 struct PrefillSmem {
   static constexpr int A_BYTES = PF_BM * BK * 2;
   static constexpr int B_BYTES = PF_BN * BK * 2;
@@ -593,8 +598,9 @@ struct PrefillSmem {
 };
 
 __global__ void __launch_bounds__(192, 1)
-gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, GemmParams p,
-                            int m_tiles, int num_tiles, int bn, int vec_store) {
+gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                            const __grid_constant__ CUtensorMap map_w2, GemmParams p, int m_tiles, int num_tiles,
+                            PrefillPlan plan, int vec_store) {
   using L = PrefillSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -609,13 +615,24 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK - 1) / BK;
-  const uint32_t stage_tx = (uint32_t)(L::A_BYTES + bn * BK * 2);       // bytes a stage receives
   const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+  const int tiles1 = plan.cols1 * m_tiles;
+  // first token, first feature and feature width of a tile; second: whether its weights come through the second map
+  auto tile_of = [&](int tile, int& m0, int& n0, int& bn) -> bool {
+    if (tile < tiles1) {
+      m0 = (tile % m_tiles) * PF_BM; n0 = (tile / m_tiles) * plan.bn1; bn = plan.bn1;
+      return false;
+    }
+    const int u = tile - tiles1;
+    m0 = (u % m_tiles) * PF_BM; n0 = plan.cols1 * plan.bn1 + (u / m_tiles) * plan.bn2; bn = plan.bn2;
+    return true;
+  };
 
   pdl_trigger();
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w2) : "memory");
     for (int s = 0; s < PF_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
     *abort_flag = 0;
@@ -636,18 +653,22 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       long long it = 0;                       // stage uses so far
       bool ok = true;
       // The weights of the first tile do not depend on the kernel before this one.
-      const int first = blockIdx.x;
       const int early = num_kb < PF_STAGES ? num_kb : PF_STAGES;
-      for (int i = 0; i < early; ++i) {
-        mbar_expect_tx(full_bar(i), stage_tx);
-        tma_load_2d(smem_base + i * L::STAGE_BYTES + L::A_BYTES, &map_w, i * BK, (first / m_tiles) * bn, full_bar(i));
+      {
+        int m0, n0, bn;
+        const CUtensorMap* mw = tile_of(blockIdx.x, m0, n0, bn) ? &map_w2 : &map_w;
+        for (int i = 0; i < early; ++i) {
+          mbar_expect_tx(full_bar(i), (uint32_t)(L::A_BYTES + bn * BK * 2));
+          tma_load_2d(smem_base + i * L::STAGE_BYTES + L::A_BYTES, mw, i * BK, n0, full_bar(i));
+        }
+        pdl_wait();
+        for (int i = 0; i < early; ++i)
+          tma_load_2d(smem_base + i * L::STAGE_BYTES, &map_x, i * BK, m0, full_bar(i));
       }
-      pdl_wait();
-      for (int i = 0; i < early; ++i)
-        tma_load_2d(smem_base + i * L::STAGE_BYTES, &map_x, i * BK, (first % m_tiles) * PF_BM, full_bar(i));
       for (int t = 0; t < my_tiles && ok; ++t) {
-        const int tile = blockIdx.x + t * gridDim.x;
-        const int m0 = (tile % m_tiles) * PF_BM, n0 = (tile / m_tiles) * bn;
+        int m0, n0, bn;
+        const CUtensorMap* mw = tile_of(blockIdx.x + t * gridDim.x, m0, n0, bn) ? &map_w2 : &map_w;
+        const uint32_t stage_tx = (uint32_t)(L::A_BYTES + bn * BK * 2);       // bytes a stage receives
         for (int kb = (t == 0 ? early : 0); kb < num_kb; ++kb) {
           const long long use = (long long)t * num_kb + kb;
           const int s = (int)(use % PF_STAGES);
@@ -656,7 +677,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
           mbar_expect_tx(full_bar(s), stage_tx);
           const uint32_t dst = smem_base + s * L::STAGE_BYTES;
           tma_load_2d(dst, &map_x, kb * BK, m0, full_bar(s));
-          tma_load_2d(dst + L::A_BYTES, &map_w, kb * BK, n0, full_bar(s));
+          tma_load_2d(dst + L::A_BYTES, mw, kb * BK, n0, full_bar(s));
           it = use + 1;
         }
         if (t == 0 && it < early) it = early;
@@ -672,10 +693,12 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   } else if (warp == 1) {
     // ---- tensor-core issue -----------------------------------------------------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(bn);
       bool ok = true;
       for (int t = 0; t < my_tiles && ok; ++t) {
         const int b = t & 1;
+        int m0, n0, bn;
+        tile_of(blockIdx.x + t * gridDim.x, m0, n0, bn);
+        const uint32_t idesc = umma_idesc(bn);
         // the epilogue has drained this accumulator (its use two tiles ago)
         ok = mbar_wait(acc_empty(b), (uint32_t)((t >> 1) & 1) ^ 1u, abort_flag, ERR_ACCUM_WAIT);
         if (!ok) break;
@@ -701,9 +724,9 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
     const int quarter = warp & 3;
     bool ok = true;
     for (int t = 0; t < my_tiles && ok; ++t) {
-      const int tile = blockIdx.x + t * gridDim.x;
-      const int m = (tile % m_tiles) * PF_BM + quarter * 32 + lane;
-      const int n0 = (tile / m_tiles) * bn;
+      int m0, n0, bn;
+      tile_of(blockIdx.x + t * gridDim.x, m0, n0, bn);
+      const int m = m0 + quarter * 32 + lane;
       const int b = t & 1;
       ok = mbar_wait(acc_full(b), (uint32_t)((t >> 1) & 1), abort_flag, ERR_ACCUM_WAIT);
       ok = __all_sync(0xffffffffu, ok);
@@ -802,21 +825,68 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   }
 }
 
-// The feature width of the tiles: 256 unless a narrower multiple of 16 (of 128 with the fused SwiGLU, whose gate and
-// up rows come in blocks of 64) needs clearly less waves x (width + 64); the 64 stand for what a tile costs whatever
-// its width (its token tile is loaded again for every feature tile, and narrow MMAs use the tensor cores less well).
+// The feature tiles of a launch.  CTA i of G = min(tiles, SMs) takes tiles i, i + G, ...; a tile costs its width + 64
+// (the 64 stand for what a tile costs whatever its width: its token tile is loaded again for every feature tile, and
+// narrow MMAs use the tensor cores less well), and the launch takes as long as its busiest CTA.  Candidates: one width
+// for all tiles (256, or a narrower multiple of 16, of 128 with the fused SwiGLU, whose gate and up rows come in blocks
+// of 64), or columns of 256 followed by narrower tiles for the rest, so that the last round of tiles fits the SMs (2048
+// tokens x 4096 features: 9 columns of 256 and 9 of 208 are two rounds of 144 tiles instead of 148 + 108 tiles of 256).
 // Measured at 8B sizes: 512 x 4096 x 4096 27.6 -> 23.4 us (width 144), 2048 x 6144 x 4096 81.3 -> 80.0 (240); with
-// ten waves and more a narrower tile only lost (2048 x 24576 x 4096, width 224: 305 -> 314 us), hence the margin.
-static int prefill_tile_width(int m_tiles, int N, int swiglu, int num_sms) {
-  auto cost = [&](int bn) {
-    const long long tiles = (long long)m_tiles * ((N + bn - 1) / bn);
-    return ((tiles + num_sms - 1) / num_sms) * (long long)(bn + 64);
-  };
-  int best = PF_BN;
-  long long best_cost = cost(PF_BN) * 93 / 100;          // a narrower tile has to win by 7 %
-  for (int bn = PF_BN - (swiglu ? 128 : 16); bn >= 64; bn -= swiglu ? 128 : 16) {
-    const long long c = cost(bn);
-    if (c < best_cost) { best = bn; best_cost = c; }
+// ten waves and more a narrower tile for all only lost (2048 x 24576 x 4096, width 224: 305 -> 314 us), hence the margin
+// a narrower plan has to win by.
+static long long prefill_plan_cost(const PrefillPlan& pl, int m_tiles, int N, int num_sms) {
+  const long long t1 = (long long)pl.cols1 * m_tiles;
+  const int rest = N - pl.cols1 * pl.bn1;
+  const long long t2 = rest > 0 ? (long long)m_tiles * ((rest + pl.bn2 - 1) / pl.bn2) : 0;
+  const long long tiles = t1 + t2;
+  const long long G = tiles < num_sms ? tiles : num_sms;
+  if (G <= 0) return 0;
+  // CTA 0 takes the most tiles; CTA i's tiles i, i + G, ... of the first kind number ceil((t1 - i) / G)
+  long long worst = 0;
+  for (long long i = 0; i < G; ++i) {
+    const long long n1 = i < t1 ? (t1 - 1 - i) / G + 1 : 0;
+    const long long first2 = t1 + ((i - t1) % G + G) % G;                  // its first tile index >= t1
+    const long long n2 = first2 < tiles ? (tiles - 1 - first2) / G + 1 : 0;
+    const long long c = n1 * (pl.bn1 + 64) + n2 * (pl.bn2 + 64);
+    if (c > worst) worst = c;
+  }
+  return worst;
+}
+
+static PrefillPlan prefill_plan_search(int m_tiles, int N, int swiglu, int num_sms);
+
+// The search costs a few hundred microseconds: its result is kept per (token tiles, features, SwiGLU, SMs).
+static PrefillPlan prefill_plan(int m_tiles, int N, int swiglu, int num_sms) {
+  static std::unordered_map<unsigned long long, PrefillPlan> cache;
+  static std::mutex mu;
+  const unsigned long long key = ((unsigned long long)m_tiles << 40) ^ ((unsigned long long)N << 12) ^ ((unsigned long long)num_sms << 1) ^ (unsigned long long)(swiglu != 0);
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 4096) cache.clear();
+  const PrefillPlan pl = prefill_plan_search(m_tiles, N, swiglu, num_sms);
+  cache.emplace(key, pl);
+  return pl;
+}
+
+static PrefillPlan prefill_plan_search(int m_tiles, int N, int swiglu, int num_sms) {
+  const int step = swiglu ? 128 : 16;
+  const int full_cols = (N + PF_BN - 1) / PF_BN;
+  PrefillPlan best{PF_BN, full_cols, PF_BN};
+  const long long base = prefill_plan_cost(best, m_tiles, N, num_sms);
+  long long best_cost = base * 93 / 100;                   // one narrower width for all has to win by 7 %
+  for (int bn = PF_BN - step; bn >= 64; bn -= step) {
+    PrefillPlan pl{bn, (N + bn - 1) / bn, bn};
+    const long long c = prefill_plan_cost(pl, m_tiles, N, num_sms);
+    if (c < best_cost) { best = pl; best_cost = c; }
+  }
+  if (best.bn1 == PF_BN) best_cost = base * 97 / 100;      // columns of 256 and a narrower rest: by 3 %
+  for (int cols1 = N / PF_BN - 1; cols1 >= 0 && cols1 >= N / PF_BN - 24; --cols1) {
+    for (int bn2 = PF_BN - step; bn2 >= 64; bn2 -= step) {
+      PrefillPlan pl{PF_BN, cols1, bn2};
+      const long long c = prefill_plan_cost(pl, m_tiles, N, num_sms);
+      if (c < best_cost) { best = pl; best_cost = c; }
+    }
   }
   return best;
 }
@@ -832,17 +902,21 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
     if (num_sms <= 0) num_sms = 148;
   }
   const int m_tiles = (M + PF_BM - 1) / PF_BM;
-  const int bn = force_bn ? force_bn : prefill_tile_width(m_tiles, N, swiglu, num_sms);
-  CUtensorMap mx, mw;
-  if (!cached_map(&mx, x, M, K, ldx, PF_BM) || !cached_map(&mw, w, N, K, K, bn)) {
+  PrefillPlan plan;
+  if (force_bn > 0) plan = PrefillPlan{force_bn, (N + force_bn - 1) / force_bn, force_bn};
+  else if (force_bn < 0) plan = PrefillPlan{PF_BN, (-force_bn) >> 10, (-force_bn) & 1023};   // tests: columns of 256, then a width
+  else plan = prefill_plan(m_tiles, N, swiglu, num_sms);
+  if (plan.cols1 * plan.bn1 >= N) plan = PrefillPlan{plan.bn1, (N + plan.bn1 - 1) / plan.bn1, plan.bn1};
+  CUtensorMap mx, mw, mw2;
+  if (!cached_map(&mx, x, M, K, ldx, PF_BM) || !cached_map(&mw, w, N, K, K, plan.bn1) || !cached_map(&mw2, w, N, K, K, plan.bn2)) {
     set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);
     return 3;
   }
   GemmParams p;
   p.y = const_cast<void*>(y); p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = ldy;
   p.out_dtype = y_dtype; p.cluster = 0; p.swiglu = swiglu;
-  const int n_tiles = (N + bn - 1) / bn;
-  const int num_tiles = m_tiles * n_tiles;
+  const int rest = N - plan.cols1 * plan.bn1;
+  const int num_tiles = m_tiles * (plan.cols1 + (rest > 0 ? (rest + plan.bn2 - 1) / plan.bn2 : 0));
   const int el = y_dtype == LB_F32 ? 4 : 2;
   const int vec_store = ((uintptr_t)y % 16 == 0) && ((ldy * el) % 16 == 0);
   const int smem = PrefillSmem::TOTAL + 1024;
@@ -853,7 +927,7 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
     configured = true;
   }
   const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-  launch(gemm_tcgen05_prefill_kernel, dim3(grid), dim3(192), smem, stream, mx, mw, p, m_tiles, num_tiles, bn, vec_store);
+  launch(gemm_tcgen05_prefill_kernel, dim3(grid), dim3(192), smem, stream, mx, mw, mw2, p, m_tiles, num_tiles, plan, vec_store);
   return 0;
 }
 
@@ -871,6 +945,13 @@ static int launch_for_tile(int bt, const CUtensorMap& mw, const CUtensorMap& mx,
 }
 
 }  // namespace lb
+
+// The feature tiles the many-token kernel would use for M tokens and N features: out[0] columns of tiles out[1] wide,
+// then tiles out[2] wide (out[0] * out[1] >= N: one width for all).
+LB_EXPORT void lb_gemm_tcgen05_prefill_plan(int M, int N, int swiglu, int num_sms, int* out) {
+  const lb::PrefillPlan pl = lb::prefill_plan((M + lb::PF_BM - 1) / lb::PF_BM, N, swiglu, num_sms > 0 ? num_sms : 148);
+  out[0] = pl.cols1; out[1] = pl.bn1; out[2] = pl.bn2;
+}
 
 // Which (token tile, splits) the launcher would choose; exposed so that callers can size the workspace
 // and tests can force a choice.  Returns splits; *bt receives the token tile.
@@ -910,10 +991,11 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   LB_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
   if (M == 0) return 0;
   if (M > 256 && force_bt == 0) {
-    // with many tokens force_splits stands for the feature width of the tiles (0: choose)
-    LB_CHECK_ARG(force_splits == 0 || (force_splits >= 16 && force_splits <= lb::PF_BN && force_splits % 16 == 0 &&
-                                       (!swiglu || force_splits % 128 == 0)),
-                 "gemm_tcgen05: tile width %d is no multiple of 16 (128 with SwiGLU) up to 256", force_splits);
+    // with many tokens force_splits stands for the feature width of the tiles (0: choose; -(c * 1024 + w): c columns of
+    // tiles 256 wide, then tiles w wide)
+    const int fw = force_splits < 0 ? (-force_splits) & 1023 : force_splits;
+    LB_CHECK_ARG(force_splits == 0 || (fw >= 16 && fw <= lb::PF_BN && fw % 16 == 0 && (!swiglu || fw % 128 == 0)),
+                 "gemm_tcgen05: tile width %d is no multiple of 16 (128 with SwiGLU) up to 256", fw);
     if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, force_splits, stream)) return rc;
     LB_CHECK_LAUNCH("gemm_tcgen05 (many tokens)");
     return 0;

@@ -463,6 +463,10 @@ def test_gemm_plain_is_true_32_bit(env):
     # the same with a given feature width of the tiles (here `splits` stands for it): narrow, odd multiples of 16, the widest
     (2048, 512, 4096, 0, 128), (384, 4096, 1024, 0, 144), (1000, 300, 136, 0, 64), (640, 1030, 1024, 0, 240), (512, 4096, 512, 0, 16),
     (576, 4096, 1024, 0, 0), (512, 1000, 2048, 0, 256),
+    # columns of tiles 256 wide, then narrower tiles for the rest of the features (-(columns * 1024 + width)); the last two
+    # are sizes for which the kernel chooses such a plan itself
+    (2048, 4096, 256, 0, -(9 * 1024 + 208)), (1024, 1030, 512, 0, -(2 * 1024 + 64)), (512, 700, 256, 0, -(0 * 1024 + 176)),
+    (300, 2000, 128, 0, -(7 * 1024 + 16)), (2048, 6144, 128, 0, 0), (2048, 4096, 192, 0, 0),
 ])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
@@ -483,7 +487,8 @@ def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
 
 @pytest.mark.parametrize("M,I,K,bt,splits", [(5, 128, 96, 0, 0), (16, 256, 1024, 16, 4), (40, 640, 512, 64, 1), (8, 12288, 512, 0, 0),
                                              (64, 192, 2048, 0, 0), (300, 320, 264, 0, 0), (2048, 1024, 256, 0, 0), (700, 64, 4096, 0, 0),
-                                             (700, 1024, 2048, 0, 128), (512, 2048, 512, 0, 0)])
+                                             (700, 1024, 2048, 0, 128), (512, 2048, 512, 0, 0),
+                                             (1024, 1536, 512, 0, -(8 * 1024 + 128)), (2048, 12288, 64, 0, 0)])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05_with_swiglu_epilogue(env, M, I, K, bt, splits, ty):
     """gate and up rows interleaved in blocks of 64; the product's epilogue forms silu(gate) * up."""
