@@ -255,3 +255,28 @@ def test_a_decoding_batch_with_pages_to_spare_is_planned_as_it_stands():
     assert [(e.request.rid, e.start, e.num_tokens, e.sample) for e in plan2] == \
         [(e.request.rid, e.request.num_computed - 1, 1, True) for e in plan2]
     assert [e.request.rid for e in plan2] == [1, 2, 3]
+
+
+def test_attention_split_counts_are_valid_and_hit_the_measured_points():
+    """How many key ranges a decode attention launch is cut into is a plan made on the host: every answer must be
+    launchable (a range has at least 256 keys, at most 64 ranges, powers of two where a cluster combines them), and the
+    points that were measured keep their answers."""
+    from lucciola_b200.ops import attention_splits
+    for tiles in (1, 2, 3, 8, 12, 24, 37, 40, 48, 64, 96, 128, 500):
+        for heads in (1, 2, 8):
+            for span in (1, 100, 256, 1000, 4096, 8192, 32768, 131072):
+                for rows in (1, 4, 16, 17, 64):
+                    for wide in (0, 14):
+                        s = attention_splits(tiles, heads, span, rows, wide_clusters=wide)
+                        assert 1 <= s <= 64, (tiles, heads, span, rows, s)
+                        assert s == 1 or span // s >= 256, (tiles, heads, span, rows, s)
+                        if rows <= 16 and tiles * heads <= 296 and s < 16:
+                            assert s & (s - 1) == 0, (tiles, heads, span, rows, s)
+                        if rows > 16 and tiles * heads >= 148:
+                            assert s == 1
+    assert attention_splits(8, 8, 8192, 4) == 4            # batch 8: one wave of 256 CTAs
+    assert attention_splits(64, 8, 8192, 4) == 1           # two waves that are full enough: no cutting
+    assert attention_splits(40, 8, 8192, 4) == 4           # 320 tiles: a last wave of 24 CTAs would cost more than the cuts
+    assert attention_splits(1, 8, 8192, 4, wide_clusters=14) == 16      # one request: 16 ranges in clusters of 16
+    assert attention_splits(1, 8, 32768, 4, wide_clusters=14) > 16      # very long: more ranges through the workspace
+    assert attention_splits(2, 8, 8192, 4, wide_clusters=14) == 18      # 16 clusters of 16 would not fit at once
