@@ -47,6 +47,9 @@ SHAPES = {
     "8b": ("Qwen3-8B shape", QWEN3_8B),
     "14b": ("Qwen3-14B shape", dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)),
     "32b": ("Qwen3-32B shape", dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)),
+    # the size lucciola's own benchmark programs load (benchmarks/basic_bench.cc:13)
+    "0.6b": ("Qwen3-0.6B shape", dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, intermediate_size=3072,
+                                      tie_word_embeddings=True)),
 }
 
 
@@ -309,8 +312,9 @@ def main() -> int:
         "ms_per_step": round(main_r["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0, 0.02)", "impl": "ours",
         "config": {"model": shape_name, "layers": args.layers, "layers_of_configuration": full_layers,
-                   "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
-                   "intermediate_size": 12288, "vocab_size": 151936, "global_batch": args.batch, "seq_len": ctx,
+                   "hidden_size": cfg["hidden_size"], "num_attention_heads": cfg["num_attention_heads"],
+                   "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"], "global_batch": args.batch, "seq_len": ctx,
                    "context_len": main_r["final_context"], "page_size": page, "parallelism": "single GPU",
                    "cuda_graph": bool(options.use_cuda_graph), "l2": "inputs larger than L2 (%.0f GB of weights a step)" % (weight_bytes / 1e9),
                    "prefill_tokens": T, "peaks": pk["source"]},
