@@ -31,6 +31,11 @@ _BIG_PORTION = 16
 
 # Batch sizes for which decode-only steps are recorded as CUDA graphs; a batch is padded to the next one.
 _GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+# A step that is one short portion of one request (a short prompt, the end of a long one) is recorded too, per number of
+# tokens, from the second time that number is seen: such a step is a few hundred launches of a few microseconds, and
+# launching them one by one takes the host longer than the GPU needs to run them.
+_SHORT_PORTION = 64
+_SHORT_GRAPHS = 48                       # recordings of that kind kept at a time
 
 
 class OutOfPages(RuntimeError):
@@ -107,6 +112,7 @@ class ModelRunner:
         self._table_rows: dict[tuple[Hashable, int], tuple[int, np.ndarray]] = {}
         self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._graph_inputs: dict[tuple[int, int], torch.Tensor] = {}
+        self._short_seen: dict[tuple[int, int], int] = {}       # how often a short portion of this size has come
         self._graph_launches = 0           # kernels replayed from CUDA graphs so far
 
     # ---- what a batch builder may ask ------------------------------------
@@ -148,9 +154,9 @@ class ModelRunner:
         return self._staging
 
     def _run_graph(self, key: tuple[int, int], d_tok: torch.Tensor, step: StepContext, d_rows: torch.Tensor) -> torch.Tensor:
-        """Decode-only step of a fixed batch size: the first time it runs as usual and is then recorded
-        (launches into a capturing stream are not executed); later steps replay the recording.  The
-        result lives in the graph's memory and is valid until the next step."""
+        """A step of a fixed shape (decoded tokens of a batch bucket, or one short portion of a given size): the first
+        time it runs as usual and is then recorded (launches into a capturing stream are not executed); later steps replay
+        the recording.  The result lives in the graph's memory and is valid until the next step."""
         from .. import ops
         hit = self._graphs.get(key)
         if hit is not None:
@@ -245,6 +251,20 @@ class ModelRunner:
             graph_key = (S, span_hint)
             q_lens = q_lens + [1] * (S - S_real)
             starts = starts + [0] * (S - S_real)
+        elif (self.options.use_cuda_graph and self.rt.fast_kernels and not self.cache.states and S_real == 1
+              and 2 <= q_lens[0] <= _SHORT_PORTION):
+            key = (-q_lens[0], max(256, 1 << (max_ctx - 1).bit_length()))       # a negative first number: this kind
+            if key in self._graphs:
+                graph_key = key
+            else:
+                seen = self._short_seen[key] = self._short_seen.get(key, 0) + 1
+                if seen >= 2:
+                    short = [k for k in self._graphs if k[0] < 0]
+                    if len(short) >= _SHORT_GRAPHS:                             # the oldest recording makes room
+                        self._graphs.pop(short[0])
+                        self._graph_inputs.pop(short[0], None)
+                    graph_key = key
+        decode_graph = graph_key is not None and graph_key[0] > 0
         S, T = len(q_lens), sum(q_lens)
         R = T if graph_key else sum(len(e.want) for e in entries)
         G, P = len(self.groups), self.max_pages_per_seq
@@ -259,7 +279,7 @@ class ModelRunner:
         for i in range(1, S):
             first_token[i] = first_token[i - 1] + q_lens[i - 1]
         for g in self.tile_groups:
-            if graph_key:                         # one token each: the same tiles for every step of this size
+            if decode_graph:                      # one token each: the same tiles for every step of this size
                 tile_lists[(g, "all")] = self._decode_tiles.get(S) or self._decode_tiles.setdefault(S, self._tiles(q_lens, g, 64))
                 continue
             tile_lists[(g, "all")] = self._tiles(q_lens, g, 64)
@@ -292,14 +312,14 @@ class ModelRunner:
         tables = [take(S * P).reshape(S, P) for _ in range(G)]
         for tl in tile_lists.values():
             o = (o + 3) & ~3                      # the kernel reads a tile as one 16-byte word
-            flat = self._decode_tiles_flat.get(len(tl)) if graph_key else None
+            flat = self._decode_tiles_flat.get(len(tl)) if decode_graph else None
             if flat is None:
                 flat = np.asarray(tl, dtype=np.int32).reshape(-1)
-                if graph_key:
+                if decode_graph:
                     self._decode_tiles_flat[len(tl)] = flat
             take(4 * len(tl))[:] = flat
         wanted_rows: list[int] = []
-        if graph_key:
+        if decode_graph:
             # One token each: everything but the tables is a handful of whole-array assignments.
             ar = self._arange(S + 1)
             tok[:S_real] = token_arrays
@@ -335,6 +355,8 @@ class ModelRunner:
                 ctx[i] = starts[i] + n
         if graph_key is None:
             rows[:] = np.asarray(wanted_rows, dtype=np.int32)
+        elif not decode_graph:
+            rows[:] = self._arange(T)            # a recording computes the logits of every token
         dev = self._graph_inputs.get(graph_key) if graph_key else None
         if graph_key and dev is None:
             dev = self._graph_inputs[graph_key] = torch.empty(total, dtype=torch.int32, device=self.device)

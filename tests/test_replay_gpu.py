@@ -151,3 +151,31 @@ def test_step_refuses_bad_input(tiny_models):
         runner.step([StepEntry("x", [1] * 65, [])])
     assert runner.manager.num_requests() == 0 and runner.manager.pools[0].num_free == 4     # nothing was taken
     assert runner.step([StepEntry("x", [1] * 64, [])]) is None
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_short_portions_replayed_from_recordings(tiny_models, name):
+    """A step that is one short portion of one request is recorded as a CUDA graph the second time its size comes: whole
+    short prompts of one length and ends of longer prompts, each against the plain implementation; the later ones are replays
+    (other requests, other pages, other positions than the step that was recorded)."""
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.load import build_runner
+
+    page = TINY[name][4]
+    runner = build_runner(tiny_models[name], EngineOptions(dtype="bfloat16", block_size=page, max_blocks=64, max_num_seqs=8,
+                                                           use_cuda_graph=True), num_pages=64)
+    reqs = {f"s{i}": tokens_for(name, 17, salt=20 + i) for i in range(4)}
+    steps = ru.whole(reqs)
+    # longer prompts in portions of 60 and 9 tokens (and a rest of 0, 1 or 2): the same sizes at other positions
+    longer = {f"l{i}": tokens_for(name, 69 + i, salt=30 + i) for i in range(3)}
+    for rid, ids in longer.items():
+        n = len(steps)
+        steps.append({"step": n, "entries": [{"id": rid, "tokens": ids[:60], "want": [59]}], "end": []})
+        steps.append({"step": n + 1, "entries": [{"id": rid, "tokens": ids[60:69], "want": list(range(9))}], "end": []})
+        if len(ids) > 69:
+            steps.append({"step": n + 2, "entries": [{"id": rid, "tokens": ids[69:], "want": list(range(len(ids) - 69))}], "end": []})
+        steps[-1]["end"] = [rid]
+    got = ru.replay(runner, steps)
+    ru.compare(got, tiny_models[name], {**reqs, **longer}, "bfloat16")
+    short = [k for k in runner._graphs if k[0] < 0]
+    assert (-17, 256) in short and (-9, 256) in short and (-60, 256) in short, short

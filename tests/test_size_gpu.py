@@ -67,6 +67,20 @@ def test_bfloat16_engine_against_float32_engine_at_real_layer_sizes(runners):
     assert len(runners["bfloat16"]._graphs) > 0
 
 
+def test_short_prompts_replayed_from_recordings_at_real_layer_sizes(runners):
+    """Three prompts of 36 tokens one after the other: the second is recorded as a CUDA graph (q|k|v product, rotation,
+    tensor-memory attention and all), the third replays it with other tokens and other pages."""
+    g = torch.Generator().manual_seed(5)
+    before = len([k for k in runners["bfloat16"]._graphs if k[0] < 0])
+    for _ in range(3):
+        ids = torch.randint(0, CFG["vocab_size"], (36,), generator=g).tolist()
+        ref = logits_of(runners["float32"], ids, [36])
+        got = logits_of(runners["bfloat16"], ids, [36])
+        err = ((got - ref).abs().max() / ref.abs().max()).item()
+        assert torch.isfinite(got).all() and err < 3e-2, err
+    assert len([k for k in runners["bfloat16"]._graphs if k[0] < 0]) == before + 1
+
+
 def test_mixed_batch_at_real_layer_sizes(runners):
     """Up to five live requests: long portions, portions of a few tokens and decoded tokens side by side (each kind
     goes to its own attention launch), long contexts beside short ones."""
