@@ -153,7 +153,7 @@ class ModelRunner:
             self._staging = _Staging(self.device, max(n, 4096) * 2)
         return self._staging
 
-    def _run_graph(self, key: tuple[int, int], d_tok: torch.Tensor, step: StepContext, d_rows: torch.Tensor) -> torch.Tensor:
+    def _run_graph(self, key: tuple, d_tok: torch.Tensor, step: StepContext, d_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """A step of a fixed shape (decoded tokens of a batch bucket, or one short portion of a given size): the first
         time it runs as usual and is then recorded (launches into a capturing stream are not executed); later steps replay
         the recording.  The result lives in the graph's memory and is valid until the next step."""
@@ -253,7 +253,10 @@ class ModelRunner:
             starts = starts + [0] * (S - S_real)
         elif (self.options.use_cuda_graph and self.rt.fast_kernels and not self.cache.states and S_real == 1
               and 2 <= q_lens[0] <= _SHORT_PORTION):
-            key = (-q_lens[0], max(256, 1 << (max_ctx - 1).bit_length()))       # a negative first number: this kind
+            want = tuple(entries[0].want)
+            # which logits the recording computes: those of the last token, none, or all of them
+            rows_kind = "last" if want == (q_lens[0] - 1,) else "none" if not want else "all"
+            key = (-q_lens[0], max(256, 1 << (max_ctx - 1).bit_length()), rows_kind)   # a negative first number: this kind
             if key in self._graphs:
                 graph_key = key
             else:
@@ -267,6 +270,8 @@ class ModelRunner:
         decode_graph = graph_key is not None and graph_key[0] > 0
         S, T = len(q_lens), sum(q_lens)
         R = T if graph_key else sum(len(e.want) for e in entries)
+        if graph_key and not decode_graph and graph_key[2] != "all":
+            R = 1 if graph_key[2] == "last" else 0
         G, P = len(self.groups), self.max_pages_per_seq
         # Work items of the attention kernels, per group size: "all" = every entry in tiles of up to 64 query
         # rows; when the step holds portions of prompts, also "big" = those portions in work items of up to 256
@@ -356,7 +361,11 @@ class ModelRunner:
         if graph_key is None:
             rows[:] = np.asarray(wanted_rows, dtype=np.int32)
         elif not decode_graph:
-            rows[:] = self._arange(T)            # a recording computes the logits of every token
+            if graph_key[2] == "all":
+                rows[:] = self._arange(T)        # the recording computes the logits of every token
+            elif graph_key[2] == "last":
+                rows[0] = T - 1
+                wanted_rows = [0]
         dev = self._graph_inputs.get(graph_key) if graph_key else None
         if graph_key and dev is None:
             dev = self._graph_inputs[graph_key] = torch.empty(total, dtype=torch.int32, device=self.device)
@@ -396,7 +405,7 @@ class ModelRunner:
             logits = self.model.forward(d_tok, step, self.cache.views, d_rows if R else None)
         else:
             step.plans["span_hint"] = graph_key[1]
-            logits = self._wanted(self._run_graph(graph_key, d_tok, step, d_rows), wanted_rows)
+            logits = self._wanted(self._run_graph(graph_key, d_tok, step, d_rows if R else None), wanted_rows)
         return self._after_step(entries, T, logits)
 
     def _table_row(self, rid: Hashable, g: int) -> np.ndarray:

@@ -175,7 +175,13 @@ def test_short_portions_replayed_from_recordings(tiny_models, name):
         if len(ids) > 69:
             steps.append({"step": n + 2, "entries": [{"id": rid, "tokens": ids[69:], "want": list(range(len(ids) - 69))}], "end": []})
         steps[-1]["end"] = [rid]
+    # a portion of which no logits are wanted, then the rest
+    quiet = {f"q{i}": tokens_for(name, 45, salt=40 + i) for i in range(3)}
+    for rid, ids in quiet.items():
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": ids[:30], "want": []}], "end": []})
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": ids[30:], "want": list(range(15))}], "end": [rid]})
     got = ru.replay(runner, steps)
-    ru.compare(got, tiny_models[name], {**reqs, **longer}, "bfloat16")
+    ru.compare(got, tiny_models[name], {**reqs, **longer, **quiet}, "bfloat16")
     short = [k for k in runner._graphs if k[0] < 0]
-    assert (-17, 256) in short and (-9, 256) in short and (-60, 256) in short, short
+    assert (-30, 256, "none") in short and (-15, 256, "all") in short, short
+    assert (-17, 256, "all") in short and (-9, 256, "all") in short and (-60, 256, "last") in short, short
