@@ -79,6 +79,14 @@ def test_short_prompts_replayed_from_recordings_at_real_layer_sizes(runners):
         err = ((got - ref).abs().max() / ref.abs().max()).item()
         assert torch.isfinite(got).all() and err < 3e-2, err
     assert len([k for k in runners["bfloat16"]._graphs if k[0] < 0]) == before + 1
+    # 300 tokens: the many-token product kernel and several attention work items in a recording
+    for _ in range(3):
+        ids = torch.randint(0, CFG["vocab_size"], (300,), generator=g).tolist()
+        ref = logits_of(runners["float32"], ids, [300])
+        got = logits_of(runners["bfloat16"], ids, [300])
+        err = ((got - ref).abs().max() / ref.abs().max()).item()
+        assert torch.isfinite(got).all() and err < 3e-2, err
+    assert (-300, 512, "all") in runners["bfloat16"]._graphs
 
 
 def test_mixed_batch_at_real_layer_sizes(runners):
