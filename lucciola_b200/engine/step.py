@@ -35,7 +35,7 @@ _GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 # tokens, from the second time that number is seen: such a step is a few hundred launches, and launching them one by one
 # takes the host longer than the GPU needs to run them (3.4 ms for 28 layers whether the portion has 36 or 512 tokens).
 _SHORT_PORTION = 512
-_SHORT_GRAPHS = 48                       # recordings of that kind kept at a time
+_SHORT_GRAPHS = 16                       # recordings of that kind kept at a time
 
 
 class OutOfPages(RuntimeError):
