@@ -561,3 +561,36 @@ def test_temperature_sampler_equals_its_plain_restatement(env):
     p = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]) / 0.8, 0)
     freq = torch.bincount(o4.cpu().long(), minlength=4).float() / 4000
     assert (freq - p).abs().max() < 0.03
+
+
+@pytest.mark.gpu
+def test_feature_tiles_of_the_many_token_product_cover_every_feature_once():
+    """The plan of the many-token product (columns of tiles of one width, then tiles of a second width) is searched on
+    the host: whatever it finds has to be launchable and must never cost more, by its own measure, than tiles of 256."""
+    import ctypes
+    from lucciola_b200.csrc import library
+    lib = library()
+    out = (ctypes.c_int * 3)()
+    sms = 148
+
+    def busiest(cols1, bn1, bn2, m_tiles, N):
+        t1 = cols1 * m_tiles
+        rest = N - cols1 * bn1
+        tiles = t1 + (m_tiles * -(-rest // bn2) if rest > 0 else 0)
+        G = min(tiles, sms)
+        load = [0] * G
+        for j in range(tiles):
+            load[j % G] += (bn1 if j < t1 else bn2) + 64
+        return max(load)
+
+    for M in (257, 300, 512, 544, 1000, 2048, 4096, 5000, 16384):
+        for N, swiglu in ((16, 0), (300, 0), (1024, 0), (4096, 0), (5120, 0), (6144, 0), (7168, 0), (151936, 0),
+                          (128, 1), (2048, 1), (24576, 1), (34816, 1)):
+            lib.lb_gemm_tcgen05_prefill_plan(M, N, swiglu, sms, out)
+            cols1, bn1, bn2 = out[0], out[1], out[2]
+            step = 128 if swiglu else 16
+            assert cols1 >= 0 and 16 <= bn1 <= 256 and 16 <= bn2 <= 256 and bn1 % step == 0 and bn2 % step == 0, (M, N, list(out))
+            if cols1 * bn1 < N:
+                assert bn1 == 256, (M, N, list(out))          # a second width only behind columns of 256
+            m_tiles = -(-M // 128)
+            assert busiest(cols1, bn1, bn2, m_tiles, N) <= busiest(-(-N // 256), 256, 256, m_tiles, N), (M, N, list(out))
