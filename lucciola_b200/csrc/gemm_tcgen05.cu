@@ -91,6 +91,25 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// The same from a CTA of a pair (cta_group::2): the barrier may lie in the other CTA of the pair (a shared::cluster
+// address), which is how both CTAs' bytes are counted on the barrier of the CTA that issues the pair's MMAs.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, groups
 // of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -114,6 +133,23 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// One MMA of a CTA pair: 256 rows (128 from each CTA's shared memory), n columns (half of the B rows from each CTA).
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The commit of a pair arrives on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
@@ -180,7 +216,8 @@ struct GemmParams {
                         // features; the output has N/2 columns and holds silu(gate) * up (computed in 32-bit)
 };
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+// silu(g) * u; the quotient by the fast division (2 ulp), the result is rounded to bfloat16 or summed with like terms afterwards
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 template <int BT>
 __host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
@@ -588,20 +625,32 @@ constexpr int PF_STAGES = 4;
 // tile running fastest, the second kind after the first.
 struct PrefillPlan { int bn1, cols1, bn2; };
 
-struct PrefillSmem {
+// PAIR: two CTAs of a cluster work on one tile of 256 tokens x up to 256 features (tcgen05 cta_group::2): each holds its
+// own 128 tokens and half of the tile's weight rows in shared memory (two thirds of the bytes a stage of one CTA holds:
+// six stages instead of four), the first CTA of the pair issues the MMAs for both, and each CTA finds its 128 tokens x
+// all features of the tile in its own tensor memory.
+template <bool PAIR>
+struct PrefillSmemT {
+  static constexpr int STAGES = PAIR ? 6 : PF_STAGES;
   static constexpr int A_BYTES = PF_BM * BK * 2;
-  static constexpr int B_BYTES = PF_BN * BK * 2;
+  static constexpr int B_BYTES = (PAIR ? PF_BN / 2 : PF_BN) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = PF_STAGES * STAGE_BYTES;
-  static constexpr int NUM_BARS = 2 * PF_STAGES + 4;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
 };
+using PrefillSmem = PrefillSmemT<false>;
 
+// With PAIR, m_tiles counts pairs of token tiles, num_tiles tiles of 256 tokens, and the grid holds two CTAs a tile slot.
+template <bool PAIR>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                             const __grid_constant__ CUtensorMap map_w2, GemmParams p, int m_tiles, int num_tiles,
                             PrefillPlan plan, int vec_store) {
-  using L = PrefillSmem;
+  using L = PrefillSmemT<PAIR>;
+  constexpr int PF_STAGES = L::STAGES;
+  const uint32_t rank = PAIR ? cluster_rank() : 0u;          // 0: the CTA that issues the pair's MMAs
+  const int slot_id = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, num_slots = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
@@ -615,17 +664,25 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+  const int my_tiles = slot_id < num_tiles ? (num_tiles - 1 - slot_id) / num_slots + 1 : 0;
   const int tiles1 = plan.cols1 * m_tiles;
-  // first token, first feature and feature width of a tile; second: whether its weights come through the second map
+  constexpr int M_STEP = PAIR ? 2 * PF_BM : PF_BM;
+  // first token (of this CTA), first feature and feature width of a tile; second: whether its weights come through the second map
   auto tile_of = [&](int tile, int& m0, int& n0, int& bn) -> bool {
     if (tile < tiles1) {
-      m0 = (tile % m_tiles) * PF_BM; n0 = (tile / m_tiles) * plan.bn1; bn = plan.bn1;
+      m0 = (tile % m_tiles) * M_STEP + (int)rank * PF_BM; n0 = (tile / m_tiles) * plan.bn1; bn = plan.bn1;
       return false;
     }
     const int u = tile - tiles1;
-    m0 = (u % m_tiles) * PF_BM; n0 = plan.cols1 * plan.bn1 + (u / m_tiles) * plan.bn2; bn = plan.bn2;
+    m0 = (u % m_tiles) * M_STEP + (int)rank * PF_BM; n0 = plan.cols1 * plan.bn1 + (u / m_tiles) * plan.bn2; bn = plan.bn2;
     return true;
+  };
+  // bytes a stage's barrier expects (of a pair: both CTAs' bytes on the first CTA's barrier), the first weight row this CTA loads
+  auto stage_bytes = [&](int bn) { return (uint32_t)(PAIR ? 2 * (L::A_BYTES + (bn / 2) * BK * 2) : L::A_BYTES + bn * BK * 2); };
+  auto w_row = [&](int n0, int bn) { return PAIR ? n0 + (int)rank * (bn / 2) : n0; };
+  auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    if (PAIR) tma_load_2d_pair(dst, map, x, y, map_to_rank(bar, 0));
+    else tma_load_2d(dst, map, x, y, bar);
   };
 
   pdl_trigger();
@@ -634,16 +691,23 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w2) : "memory");
     for (int s = 0; s < PF_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+    // an accumulator is free again when the four epilogue warps (of both CTAs of a pair) have read it
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), PAIR ? 8 : 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync_all();          // the other CTA's barriers are set up before anything of this CTA signals them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
@@ -656,28 +720,28 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       const int early = num_kb < PF_STAGES ? num_kb : PF_STAGES;
       {
         int m0, n0, bn;
-        const CUtensorMap* mw = tile_of(blockIdx.x, m0, n0, bn) ? &map_w2 : &map_w;
+        const CUtensorMap* mw = tile_of(slot_id, m0, n0, bn) ? &map_w2 : &map_w;
         for (int i = 0; i < early; ++i) {
-          mbar_expect_tx(full_bar(i), (uint32_t)(L::A_BYTES + bn * BK * 2));
-          tma_load_2d(smem_base + i * L::STAGE_BYTES + L::A_BYTES, mw, i * BK, n0, full_bar(i));
+          if (rank == 0) mbar_expect_tx(full_bar(i), stage_bytes(bn));
+          load(smem_base + i * L::STAGE_BYTES + L::A_BYTES, mw, i * BK, w_row(n0, bn), full_bar(i));
         }
         pdl_wait();
         for (int i = 0; i < early; ++i)
-          tma_load_2d(smem_base + i * L::STAGE_BYTES, &map_x, i * BK, m0, full_bar(i));
+          load(smem_base + i * L::STAGE_BYTES, &map_x, i * BK, m0, full_bar(i));
       }
       for (int t = 0; t < my_tiles && ok; ++t) {
         int m0, n0, bn;
-        const CUtensorMap* mw = tile_of(blockIdx.x + t * gridDim.x, m0, n0, bn) ? &map_w2 : &map_w;
-        const uint32_t stage_tx = (uint32_t)(L::A_BYTES + bn * BK * 2);       // bytes a stage receives
+        const CUtensorMap* mw = tile_of(slot_id + t * num_slots, m0, n0, bn) ? &map_w2 : &map_w;
+        const uint32_t stage_tx = stage_bytes(bn);
         for (int kb = (t == 0 ? early : 0); kb < num_kb; ++kb) {
           const long long use = (long long)t * num_kb + kb;
           const int s = (int)(use % PF_STAGES);
           const uint32_t parity = (uint32_t)((use / PF_STAGES) & 1) ^ 1u;
           if (!mbar_wait(empty_bar(s), parity, abort_flag, ERR_EMPTY_WAIT)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), stage_tx);
+          if (rank == 0) mbar_expect_tx(full_bar(s), stage_tx);
           const uint32_t dst = smem_base + s * L::STAGE_BYTES;
-          tma_load_2d(dst, &map_x, kb * BK, m0, full_bar(s));
-          tma_load_2d(dst + L::A_BYTES, mw, kb * BK, n0, full_bar(s));
+          load(dst, &map_x, kb * BK, m0, full_bar(s));
+          load(dst + L::A_BYTES, mw, kb * BK, w_row(n0, bn), full_bar(s));
           it = use + 1;
         }
         if (t == 0 && it < early) it = early;
@@ -692,13 +756,13 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
     }
   } else if (warp == 1) {
     // ---- tensor-core issue -----------------------------------------------------------------------------------
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       bool ok = true;
       for (int t = 0; t < my_tiles && ok; ++t) {
         const int b = t & 1;
         int m0, n0, bn;
-        tile_of(blockIdx.x + t * gridDim.x, m0, n0, bn);
-        const uint32_t idesc = umma_idesc(bn);
+        tile_of(slot_id + t * num_slots, m0, n0, bn);
+        const uint32_t idesc = PAIR ? umma_idesc_pair(bn) : umma_idesc(bn);
         // the epilogue has drained this accumulator (its use two tiles ago)
         ok = mbar_wait(acc_empty(b), (uint32_t)((t >> 1) & 1) ^ 1u, abort_flag, ERR_ACCUM_WAIT);
         if (!ok) break;
@@ -713,10 +777,13 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
           const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
           const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + L::A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) umma_f16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
-          umma_commit(empty_bar(s));
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            if (PAIR) umma_f16_pair(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+            else umma_f16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          }
+          if (PAIR) umma_commit_pair(empty_bar(s)); else umma_commit(empty_bar(s));
         }
-        if (ok) umma_commit(acc_full(b));
+        if (ok) { if (PAIR) umma_commit_pair(acc_full(b)); else umma_commit(acc_full(b)); }
       }
     }
   } else {
@@ -725,7 +792,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
     bool ok = true;
     for (int t = 0; t < my_tiles && ok; ++t) {
       int m0, n0, bn;
-      tile_of(blockIdx.x + t * gridDim.x, m0, n0, bn);
+      tile_of(slot_id + t * num_slots, m0, n0, bn);
       const int m = m0 + quarter * 32 + lane;
       const int b = t & 1;
       ok = mbar_wait(acc_full(b), (uint32_t)((t >> 1) & 1), abort_flag, ERR_ACCUM_WAIT);
@@ -814,14 +881,19 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       // this accumulator may be overwritten: one arrival per epilogue warp
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
+      if (lane == 0) {
+        if (PAIR) asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(map_to_rank(acc_empty(b), 0)) : "memory");
+        else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync_all();          // nothing of the other CTA is on its way to this CTA's barriers or tensor memory any more
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
 }
 
@@ -853,24 +925,24 @@ static long long prefill_plan_cost(const PrefillPlan& pl, int m_tiles, int N, in
   return worst;
 }
 
-static PrefillPlan prefill_plan_search(int m_tiles, int N, int swiglu, int num_sms);
+static PrefillPlan prefill_plan_search(int m_tiles, int N, int step, int num_sms);
 
-// The search costs a few hundred microseconds: its result is kept per (token tiles, features, SwiGLU, SMs).
-static PrefillPlan prefill_plan(int m_tiles, int N, int swiglu, int num_sms) {
+// The search costs a few hundred microseconds: its result is kept per (token tiles, features, step of the widths, SMs).
+// step: 16, 32 for CTA pairs (each CTA loads half of a tile's weight rows), 128 with the fused SwiGLU.
+static PrefillPlan prefill_plan(int m_tiles, int N, int step, int num_sms) {
   static std::unordered_map<unsigned long long, PrefillPlan> cache;
   static std::mutex mu;
-  const unsigned long long key = ((unsigned long long)m_tiles << 40) ^ ((unsigned long long)N << 12) ^ ((unsigned long long)num_sms << 1) ^ (unsigned long long)(swiglu != 0);
+  const unsigned long long key = ((unsigned long long)m_tiles << 44) ^ ((unsigned long long)N << 20) ^ ((unsigned long long)num_sms << 8) ^ (unsigned long long)step;
   std::lock_guard<std::mutex> g(mu);
   auto it = cache.find(key);
   if (it != cache.end()) return it->second;
   if (cache.size() > 4096) cache.clear();
-  const PrefillPlan pl = prefill_plan_search(m_tiles, N, swiglu, num_sms);
+  const PrefillPlan pl = prefill_plan_search(m_tiles, N, step, num_sms);
   cache.emplace(key, pl);
   return pl;
 }
 
-static PrefillPlan prefill_plan_search(int m_tiles, int N, int swiglu, int num_sms) {
-  const int step = swiglu ? 128 : 16;
+static PrefillPlan prefill_plan_search(int m_tiles, int N, int step, int num_sms) {
   const int full_cols = (N + PF_BN - 1) / PF_BN;
   PrefillPlan best{PF_BN, full_cols, PF_BN};
   const long long base = prefill_plan_cost(best, m_tiles, N, num_sms);
@@ -893,7 +965,7 @@ static PrefillPlan prefill_plan_search(int m_tiles, int N, int swiglu, int num_s
 
 // force_bn: 0 choose, else the feature width of the tiles (tests).
 static int launch_prefill(const void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
-                          long long ldy, int swiglu, int force_bn, cudaStream_t stream) {
+                          long long ldy, int swiglu, int force_bn, int pair, cudaStream_t stream) {
   static int num_sms = 0;
   if (num_sms == 0) {
     int dev = 0;
@@ -901,14 +973,26 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     if (num_sms <= 0) num_sms = 148;
   }
-  const int m_tiles = (M + PF_BM - 1) / PF_BM;
+  // Pairs of CTAs on tiles of 256 tokens when there are at least two token tiles (pair: 0 choose, 1 never, 2 always);
+  // their widths are multiples of 32, each CTA loading half of a tile's weight rows.
+  int forced_width = force_bn < 0 ? (-force_bn) & 1023 : force_bn;
+  // Measured at 8B sizes: pairs are 3 to 8 % faster from 1024 tokens on (2048 x 4096 x 12288: 155.7 -> 147.3 us; with
+  // SwiGLU 2048 x 24576 x 4096: 293.6 -> 275.9 us; whole steps of 2048 tokens, many in a row: 28.3 -> 27.3 ms); they
+  // compute whole tiles of 256 tokens, so they are left alone where that adds more than 4 % of rows.
+  const int rows_pair = (M + 2 * PF_BM - 1) / (2 * PF_BM) * 2 * PF_BM, rows_single = (M + PF_BM - 1) / PF_BM * PF_BM;
+  const bool use_pair = pair == 2 || (pair == 0 && M >= 1024 && rows_pair * 100 <= rows_single * 104 && num_sms >= 2 &&
+                                      (forced_width % 32) == 0);
+  const int m_tiles = use_pair ? (M + 2 * PF_BM - 1) / (2 * PF_BM) : (M + PF_BM - 1) / PF_BM;
+  const int slots = use_pair ? num_sms / 2 : num_sms;
   PrefillPlan plan;
   if (force_bn > 0) plan = PrefillPlan{force_bn, (N + force_bn - 1) / force_bn, force_bn};
   else if (force_bn < 0) plan = PrefillPlan{PF_BN, (-force_bn) >> 10, (-force_bn) & 1023};   // tests: columns of 256, then a width
-  else plan = prefill_plan(m_tiles, N, swiglu, num_sms);
+  else plan = prefill_plan(m_tiles, N, swiglu ? 128 : use_pair ? 32 : 16, slots);
   if (plan.cols1 * plan.bn1 >= N) plan = PrefillPlan{plan.bn1, (N + plan.bn1 - 1) / plan.bn1, plan.bn1};
+  if (use_pair && (plan.bn1 % 32 || plan.bn2 % 32)) { set_error("gemm_tcgen05: pairs of CTAs take tile widths that are multiples of 32"); return 1; }
+  const int box1 = use_pair ? plan.bn1 / 2 : plan.bn1, box2 = use_pair ? plan.bn2 / 2 : plan.bn2;
   CUtensorMap mx, mw, mw2;
-  if (!cached_map(&mx, x, M, K, ldx, PF_BM) || !cached_map(&mw, w, N, K, K, plan.bn1) || !cached_map(&mw2, w, N, K, K, plan.bn2)) {
+  if (!cached_map(&mx, x, M, K, ldx, PF_BM) || !cached_map(&mw, w, N, K, K, box1) || !cached_map(&mw2, w, N, K, K, box2)) {
     set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);
     return 3;
   }
@@ -919,15 +1003,28 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
   const int num_tiles = m_tiles * (plan.cols1 + (rest > 0 ? (rest + plan.bn2 - 1) / plan.bn2 : 0));
   const int el = y_dtype == LB_F32 ? 4 : 2;
   const int vec_store = ((uintptr_t)y % 16 == 0) && ((ldy * el) % 16 == 0);
-  const int smem = PrefillSmem::TOTAL + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  const int smem = (use_pair ? PrefillSmemT<true>::TOTAL : PrefillSmemT<false>::TOTAL) + 1024;
+  static bool configured[2] = {false, false};
+  if (!configured[use_pair]) {
+    cudaError_t e = use_pair ? cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                             : cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) { set_error("gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e)); return 2; }
-    configured = true;
+    configured[use_pair] = true;
   }
-  const int grid = num_tiles < num_sms ? num_tiles : num_sms;
-  launch(gemm_tcgen05_prefill_kernel, dim3(grid), dim3(192), smem, stream, mx, mw, mw2, p, m_tiles, num_tiles, plan, vec_store);
+  const int grid = num_tiles < slots ? num_tiles : slots;
+  if (!use_pair) {
+    launch(gemm_tcgen05_prefill_kernel<false>, dim3(grid), dim3(192), smem, stream, mx, mw, mw2, p, m_tiles, num_tiles, plan, vec_store);
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * grid); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = g_pdl_enabled ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, gemm_tcgen05_prefill_kernel<true>, mx, mw, mw2, p, m_tiles, num_tiles, plan, vec_store);
   return 0;
 }
 
@@ -949,7 +1046,7 @@ static int launch_for_tile(int bt, const CUtensorMap& mw, const CUtensorMap& mx,
 // The feature tiles the many-token kernel would use for M tokens and N features: out[0] columns of tiles out[1] wide,
 // then tiles out[2] wide (out[0] * out[1] >= N: one width for all).
 LB_EXPORT void lb_gemm_tcgen05_prefill_plan(int M, int N, int swiglu, int num_sms, int* out) {
-  const lb::PrefillPlan pl = lb::prefill_plan((M + lb::PF_BM - 1) / lb::PF_BM, N, swiglu, num_sms > 0 ? num_sms : 148);
+  const lb::PrefillPlan pl = lb::prefill_plan((M + lb::PF_BM - 1) / lb::PF_BM, N, swiglu ? 128 : 16, num_sms > 0 ? num_sms : 148);
   out[0] = pl.cols1; out[1] = pl.bn1; out[2] = pl.bn2;
 }
 
@@ -990,13 +1087,16 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   LB_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0, "gemm_tcgen05: K=%d and the row stride %lld must be multiples of 8 (TMA strides are multiples of 16 bytes)", K, ldx);
   LB_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
   if (M == 0) return 0;
-  if (M > 256 && force_bt == 0) {
+  if (M > 256 && force_bt <= 0) {
+    // force_bt: 0 chooses between one CTA a tile of 128 tokens and a pair of CTAs a tile of 256, -1 asks for the former,
+    // -2 for the latter
     // with many tokens force_splits stands for the feature width of the tiles (0: choose; -(c * 1024 + w): c columns of
     // tiles 256 wide, then tiles w wide)
     const int fw = force_splits < 0 ? (-force_splits) & 1023 : force_splits;
     LB_CHECK_ARG(force_splits == 0 || (fw >= 16 && fw <= lb::PF_BN && fw % 16 == 0 && (!swiglu || fw % 128 == 0)),
                  "gemm_tcgen05: tile width %d is no multiple of 16 (128 with SwiGLU) up to 256", fw);
-    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, force_splits, stream)) return rc;
+    LB_CHECK_ARG(force_bt >= -2, "gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", force_bt);
+    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, force_splits, -force_bt, stream)) return rc;
     LB_CHECK_LAUNCH("gemm_tcgen05 (many tokens)");
     return 0;
   }

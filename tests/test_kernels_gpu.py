@@ -467,6 +467,10 @@ def test_gemm_plain_is_true_32_bit(env):
     # are sizes for which the kernel chooses such a plan itself
     (2048, 4096, 256, 0, -(9 * 1024 + 208)), (1024, 1030, 512, 0, -(2 * 1024 + 64)), (512, 700, 256, 0, -(0 * 1024 + 176)),
     (300, 2000, 128, 0, -(7 * 1024 + 16)), (2048, 6144, 128, 0, 0), (2048, 4096, 192, 0, 0),
+    # pairs of CTAs on tiles of 256 tokens (bt -2; -1: one CTA a tile of 128 tokens): a token count that leaves the second
+    # CTA of the last pair without tokens, partial tiles in both directions, given widths, the sizes that choose pairs themselves
+    (512, 256, 64, -2, 0), (300, 1000, 136, -2, 0), (1000, 300, 520, -2, 64), (640, 1030, 1024, -2, 224),
+    (2048, 4096, 256, -2, -(9 * 1024 + 192)), (1300, 520, 4096, -2, 0), (1024, 6144, 512, 0, 0), (1024, 6144, 512, -1, 0),
 ])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
@@ -488,7 +492,8 @@ def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
 @pytest.mark.parametrize("M,I,K,bt,splits", [(5, 128, 96, 0, 0), (16, 256, 1024, 16, 4), (40, 640, 512, 64, 1), (8, 12288, 512, 0, 0),
                                              (64, 192, 2048, 0, 0), (300, 320, 264, 0, 0), (2048, 1024, 256, 0, 0), (700, 64, 4096, 0, 0),
                                              (700, 1024, 2048, 0, 128), (512, 2048, 512, 0, 0),
-                                             (1024, 1536, 512, 0, -(8 * 1024 + 128)), (2048, 12288, 64, 0, 0)])
+                                             (1024, 1536, 512, 0, -(8 * 1024 + 128)), (2048, 12288, 64, 0, 0),
+                                             (1024, 1536, 512, -2, 0), (700, 512, 2048, -2, 128), (1100, 640, 256, -1, 0)])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05_with_swiglu_epilogue(env, M, I, K, bt, splits, ty):
     """gate and up rows interleaved in blocks of 64; the product's epilogue forms silu(gate) * up."""
