@@ -963,6 +963,8 @@ static PrefillPlan prefill_plan_search(int m_tiles, int N, int step, int num_sms
   return best;
 }
 
+static int g_pair_slots_seen = -1;
+
 // force_bn: 0 choose, else the feature width of the tiles (tests).
 static int launch_prefill(const void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
                           long long ldy, int swiglu, int force_bn, int pair, cudaStream_t stream) {
@@ -983,7 +985,25 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
   const bool use_pair = pair == 2 || (pair == 0 && M >= 1024 && rows_pair * 100 <= rows_single * 104 && num_sms >= 2 &&
                                       (forced_width % 32) == 0);
   const int m_tiles = use_pair ? (M + 2 * PF_BM - 1) / (2 * PF_BM) : (M + PF_BM - 1) / PF_BM;
-  const int slots = use_pair ? num_sms / 2 : num_sms;
+  // The pairs of a launch all have to be resident at once (each walks its own list of tiles): as many as the GPU takes.
+  static int pair_slots = -1;
+  if (use_pair && pair_slots < 0) {
+    const int smem_pair = PrefillSmemT<true>::TOTAL + 1024;
+    pair_slots = num_sms / 2;
+    if (cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair) == cudaSuccess) {
+      cudaLaunchConfig_t qc = {};
+      qc.gridDim = dim3(2 * (num_sms / 2)); qc.blockDim = dim3(192); qc.dynamicSmemBytes = smem_pair;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      qc.attrs = qa; qc.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_prefill_kernel<true>, &qc) == cudaSuccess && n > 0 && n < pair_slots) pair_slots = n;
+    }
+    cudaGetLastError();
+  }
+  if (use_pair) g_pair_slots_seen = pair_slots;
+  const int slots = use_pair ? pair_slots : num_sms;
   PrefillPlan plan;
   if (force_bn > 0) plan = PrefillPlan{force_bn, (N + force_bn - 1) / force_bn, force_bn};
   else if (force_bn < 0) plan = PrefillPlan{PF_BN, (-force_bn) >> 10, (-force_bn) & 1023};   // tests: columns of 256, then a width
@@ -1042,6 +1062,9 @@ static int launch_for_tile(int bt, const CUtensorMap& mw, const CUtensorMap& mx,
 }
 
 }  // namespace lb
+
+// How many pairs of CTAs of the many-token kernel run at a time (-1: no launch has asked yet).
+LB_EXPORT int lb_gemm_tcgen05_pair_slots() { return lb::g_pair_slots_seen; }
 
 // The feature tiles the many-token kernel would use for M tokens and N features: out[0] columns of tiles out[1] wide,
 // then tiles out[2] wide (out[0] * out[1] >= N: one width for all).
