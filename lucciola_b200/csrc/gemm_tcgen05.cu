@@ -21,6 +21,11 @@
 // to) the partials go through a workspace in global memory and the CTA that finishes last for a
 // tile adds them, again in the order of the splits.  Either way the result does not depend on timing.
 //
+// With more than 256 tokens a second kernel takes over (gemm_tcgen05_prefill_kernel): tokens on the lanes, features on
+// the columns, persistent CTAs over tiles of 128 tokens x up to 256 features with two accumulators, so that the epilogue
+// of a tile runs under the MMAs of the next; from 1024 tokens on as pairs of CTAs on tiles of 256 x 256 (tcgen05
+// cta_group::2: each CTA stages its 128 tokens and half of the weight rows, the first CTA issues the MMAs for both).
+//
 // Every wait on an mbarrier is bounded: when a wait gives up the CTA records a code in a device
 // flag, stops, waits (bounded) for its loads in flight, frees its tensor memory and returns.
 // K must be a multiple of 8 and X, W 16-byte aligned (TMA strides); M, N, K tails are handled by
