@@ -628,7 +628,7 @@ constexpr int PF_STAGES = 4;
 // The feature tiles of a launch: `cols1` columns of tiles `bn1` wide, then the features from cols1 * bn1 on in tiles
 // `bn2` wide (their weight boxes come through a second tensor map).  Tiles are numbered column by column, the token
 // tile running fastest, the second kind after the first.
-struct PrefillPlan { int bn1, cols1, bn2; };
+struct PrefillPlan { int bn1, cols1, bn2; int mb = 16; };     // mb: token tiles of a block (the order of the tiles, see tile_of)
 
 // PAIR: two CTAs of a cluster work on one tile of 256 tokens x up to 256 features (tcgen05 cta_group::2): each holds its
 // own 128 tokens and half of the tile's weight rows in shared memory (two thirds of the bytes a stage of one CTA holds:
@@ -673,13 +673,28 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   const int tiles1 = plan.cols1 * m_tiles;
   constexpr int M_STEP = PAIR ? 2 * PF_BM : PF_BM;
   // first token (of this CTA), first feature and feature width of a tile; second: whether its weights come through the second map
+  // Inside a kind of tiles the token tiles run fastest, in blocks of MB token tiles: the tiles that are worked on at a time
+  // (one a CTA or pair) then share MB token tiles and slots / MB feature tiles, which is what L2 has to hold; with all token
+  // tiles in one block, 8192 tokens x 4096 are 67 MB of tokens read again for every two columns of feature tiles.  The
+  // launcher sizes a block to about 24 MB of tokens (at most 8 pairs or 16 single token tiles, at least 2).
+  const int MB = plan.mb;
+  auto place = [&](int idx, int cols, int& mt, int& col) {
+    const int per_block = MB * cols;
+    const int b = idx / per_block, r = idx - b * per_block;
+    const int mb = min(MB, m_tiles - b * MB);
+    col = r / mb;
+    mt = b * MB + (r - col * mb);
+  };
   auto tile_of = [&](int tile, int& m0, int& n0, int& bn) -> bool {
+    int mt, col;
     if (tile < tiles1) {
-      m0 = (tile % m_tiles) * M_STEP + (int)rank * PF_BM; n0 = (tile / m_tiles) * plan.bn1; bn = plan.bn1;
+      place(tile, plan.cols1, mt, col);
+      m0 = mt * M_STEP + (int)rank * PF_BM; n0 = col * plan.bn1; bn = plan.bn1;
       return false;
     }
-    const int u = tile - tiles1;
-    m0 = (u % m_tiles) * M_STEP + (int)rank * PF_BM; n0 = plan.cols1 * plan.bn1 + (u / m_tiles) * plan.bn2; bn = plan.bn2;
+    const int cols2 = (p.N - plan.cols1 * plan.bn1 + plan.bn2 - 1) / plan.bn2;
+    place(tile - tiles1, cols2, mt, col);
+    m0 = mt * M_STEP + (int)rank * PF_BM; n0 = plan.cols1 * plan.bn1 + col * plan.bn2; bn = plan.bn2;
     return true;
   };
   // bytes a stage's barrier expects (of a pair: both CTAs' bytes on the first CTA's barrier), the first weight row this CTA loads
@@ -1017,6 +1032,12 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
   else if (force_bn < 0) plan = PrefillPlan{PF_BN, (-force_bn) >> 10, (-force_bn) & 1023};   // tests: columns of 256, then a width
   else plan = prefill_plan(m_tiles, N, swiglu ? 128 : use_pair ? 32 : 16, slots);
   if (plan.cols1 * plan.bn1 >= N) plan = PrefillPlan{plan.bn1, (N + plan.bn1 - 1) / plan.bn1, plan.bn1};
+  {
+    const long long tile_bytes = (long long)(use_pair ? 2 * PF_BM : PF_BM) * K * 2;
+    long long mb = (24ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
+    const int top = use_pair ? 8 : 16;
+    plan.mb = (int)(mb < 2 ? 2 : mb > top ? top : mb);
+  }
   if (use_pair && (plan.bn1 % 32 || plan.bn2 % 32)) { set_error("gemm_tcgen05: pairs of CTAs take tile widths that are multiples of 32"); return 1; }
   const int box1 = use_pair ? plan.bn1 / 2 : plan.bn1, box2 = use_pair ? plan.bn2 / 2 : plan.bn2;
   CUtensorMap mx, mw, mw2;
