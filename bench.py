@@ -14,7 +14,14 @@ decode step of the whole batch.  The line printed at the end is one JSON object:
   prefill     one step over a prompt of 2048 tokens: tokens a second, and its FLOPs / time / peak
   roofline    bytes a decode step must read (every weight once, the cache of the live requests)
               / time, against the measured copy bandwidth
-  points      decode at batch 1 and 64, same context
+  points      decode at batch 1 and 64, same context; and the other workloads this engine is specified on, each through
+              Engine.step with host tokens in and out, with its share of the roofline and step latencies (p50/p90/p99):
+                decode_bN_ctx768   the 8B shape, N = 1, 8, 64 requests, prompts of 512 tokens, 256 new tokens each
+                mixed14b           the 14B shape: every step 32 decoding requests and one 512-token portion of a
+                                   2048-token prompt (compute-bound: FLOPs / time / peak)
+                pressure32b        the 32B shape: 64 requests with prompts of 4096 tokens and 256 new tokens each, in a
+                                   pool with fewer pages than they need together, so that the scheduler preempts
+              (--no-points skips them; --only-points runs nothing else)
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures 6650 GB/s and 1590 TFLOP/s.  The timed work reads far more than the 126 MB of L2
@@ -132,6 +139,152 @@ def prefill_flops(cfg: dict, layers: int, T: int) -> float:
     return linear + attention + 2.0 * V * H                                        # the output head on one row
 
 
+def percentiles(ms: list[float]) -> dict:
+    q = statistics.quantiles(ms, n=100, method="inclusive") if len(ms) > 1 else [ms[0]] * 99
+    return {"p50_ms": round(q[49], 3), "p90_ms": round(q[89], 3), "p99_ms": round(q[98], 3)}
+
+
+def timed_steps(engine, torch, keep_going) -> list[float]:
+    """Engine.step until keep_going() says no; wall-clock milliseconds of each step (a step ends with the sampled
+    tokens on the host, so the device has finished it)."""
+    out = []
+    while keep_going():
+        t0 = time.perf_counter()
+        engine.step()
+        out.append((time.perf_counter() - t0) * 1e3)
+    return out
+
+
+def run_ctx768(engine, cfg, layers, rng, pk, batches=(64, 8, 1)) -> dict:
+    """Decode at the lengths lucciola's own benchmark uses: prompts of 512 tokens, 256 new tokens, so the context
+    grows from 512 to 768."""
+    import torch
+    from lucciola_b200.sampling.params import SamplingParams
+    V = cfg["vocab_size"]
+    _, weight_bytes, kv_per_token = model_bytes_and_flops(cfg, layers)
+    out = {}
+    for B in batches:
+        params = SamplingParams(max_new_tokens=400, temperature=0.0, ignore_eos=True)
+        reqs = [engine.add_request(rng.integers(0, V, size=512).tolist(), params) for _ in range(B)]
+        while any(not r.output for r in reqs):                       # the prompts, untimed
+            engine.step()
+        for _ in range(3):                                           # warm-up: the recording of this batch size
+            engine.step()
+        torch.cuda.synchronize()
+        cached0 = sum(r.num_computed for r in reqs)
+        left = [256]
+        def more():
+            left[0] -= 1
+            return left[0] >= 0
+        ms = timed_steps(engine, torch, more)
+        mean_ctx = (cached0 + sum(r.num_computed for r in reqs)) / 2 / B
+        for r in reqs:
+            engine.abort(r.rid)
+        steps, total = len(ms), sum(ms)
+        frac = (weight_bytes + B * mean_ctx * kv_per_token) / (total / steps * 1e-3) / 1e9 / pk["hbm_gbs"]
+        key = f"decode_b{B}_ctx768"
+        out[key] = round(B * steps / total * 1e3, 1)
+        out[key + "_hbm_frac"] = round(frac, 4)
+        out[key + "_mean_ctx"] = round(mean_ctx, 1)
+        out.update({f"{key}_{k}": v for k, v in percentiles(ms).items()})
+    return out
+
+
+def run_mixed14b(rng, pk, layers=0, steps=40) -> dict:
+    """32 requests decode while prompts of 2048 tokens are read in portions of 512: every timed step holds 32 single
+    tokens and one portion (lucciola's schedule: all running requests, then one portion, src/scheduler.cc:51-120)."""
+    import torch
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.llm import Engine
+    from lucciola_b200.sampling.params import SamplingParams
+    name, shape = SHAPES["14b"]
+    layers = layers or shape["num_hidden_layers"]
+    cfg = dict(shape, num_hidden_layers=layers)
+    V, D, chunk, prompt = cfg["vocab_size"], 32, 512, 2048
+    pages = D * (4096 // 16) + 4 * (prompt // 16) + 64
+    options = EngineOptions(dtype="bfloat16", block_size=16, max_blocks=pages, max_num_seqs=D + 4, max_tokens_per_step=D + chunk,
+                            prefill_chunk=chunk, max_model_len=8192)
+    engine = Engine.from_random(cfg, seed=0, options=options)
+    decoders = [engine.add_request(rng.integers(0, V, size=1024).tolist(), SamplingParams(max_new_tokens=2000, ignore_eos=True))
+                for _ in range(D)]
+    while any(not r.output for r in decoders):
+        engine.step()
+    one = SamplingParams(max_new_tokens=1, ignore_eos=True)          # a prompt leaves when it has been read
+    warm = 12
+    for _ in range((warm + steps) // 4 + 2):
+        engine.add_request(rng.integers(0, V, size=prompt).tolist(), one)
+    for _ in range(warm):
+        engine.step()
+    torch.cuda.synchronize()
+    tokens0, launches0 = engine.runner.tokens_run, engine.runner.kernel_launches()
+    replays0 = engine.runner.graph_replays
+    left = [steps]
+    def more():
+        left[0] -= 1
+        return left[0] >= 0
+    ms = timed_steps(engine, torch, more)
+    tokens = engine.runner.tokens_run - tokens0
+    per_layer, _, _ = model_bytes_and_flops(cfg, layers)
+    nq, d, H = cfg["num_attention_heads"], cfg["head_dim"], cfg["hidden_size"]
+    ctx_decode = sum(r.num_computed for r in decoders) / D
+    flops_step = (2.0 * (D + chunk) * per_layer * layers                                   # every product of the layers
+                  + layers * nq * 4.0 * d * (D * ctx_decode + chunk * (prompt / 2))       # attention: decoded rows, mean portion
+                  + 2.0 * (D + 1) * V * H)                                                # the output head on 33 rows
+    mean_ms = sum(ms) / len(ms)
+    out = {"mixed14b_tokens_per_s": round(tokens / sum(ms) * 1e3, 1), "mixed14b_tokens_per_step": round(tokens / len(ms), 1),
+           "mixed14b_frac": round(flops_step / (mean_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+           "mixed14b_layers": layers, "mixed14b_replayed_steps": engine.runner.graph_replays - replays0,
+           "mixed14b_launches_per_step": round((engine.runner.kernel_launches() - launches0) / len(ms), 1)}
+    out.update({f"mixed14b_{k}": v for k, v in percentiles(ms).items()})
+    return out
+
+
+def run_pressure32b(rng, pk, layers=0, B=64, prompt=4096, new=256) -> dict:
+    """64 requests with prompts of 4096 tokens generate 256 tokens each from a pool that holds fewer pages than they
+    need together (64 x 272): the scheduler preempts the request admitted last and recomputes it later; every request
+    must finish."""
+    import torch
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.llm import Engine
+    from lucciola_b200.sampling.params import SamplingParams
+    name, shape = SHAPES["32b"]
+    layers = layers or shape["num_hidden_layers"]
+    cfg = dict(shape, num_hidden_layers=layers)
+    V = cfg["vocab_size"]
+    pages = B * (prompt // 16) + B * 4                               # the prompts fit; 64 more tokens each, not 256
+    options = EngineOptions(dtype="bfloat16", block_size=16, max_blocks=pages, max_num_seqs=B, max_tokens_per_step=2048 + B,
+                            max_model_len=16384)
+    engine = Engine.from_random(cfg, seed=0, options=options)
+    _, weight_bytes, kv_per_token = model_bytes_and_flops(cfg, layers)
+    reqs = [engine.add_request(rng.integers(0, V, size=prompt).tolist(), SamplingParams(max_new_tokens=new, ignore_eos=True))
+            for _ in range(B)]
+    torch.cuda.synchronize()
+    ms, decode_ms, decode_bytes = [], 0.0, 0.0
+    t_all = time.perf_counter()
+    while engine.has_unfinished():
+        cached = sum(r.num_computed for r in engine.scheduler.running)
+        tokens0 = engine.runner.tokens_run
+        t0 = time.perf_counter()
+        events = engine.step()
+        dt = (time.perf_counter() - t0) * 1e3
+        ms.append(dt)
+        if events and engine.runner.tokens_run - tokens0 == len(events):      # single tokens only: a decode step
+            decode_ms += dt
+            decode_bytes += weight_bytes + cached * kv_per_token
+    total_s = time.perf_counter() - t_all
+    generated = sum(len(r.output) for r in reqs)
+    st = engine.stats()
+    out = {"pressure32b_tokens_per_s": round(generated / total_s, 1),
+           "pressure32b_processed_tokens_per_s": round(engine.runner.tokens_run / total_s, 1),
+           "pressure32b_preemptions": st["preemptions"],
+           "pressure32b_finished": sum(len(r.output) == new for r in reqs), "pressure32b_requests": B,
+           "pressure32b_pages": pages, "pressure32b_pages_for_all": B * -(-(prompt + new) // 16),
+           "pressure32b_decode_hbm_frac": round(decode_bytes / max(decode_ms, 1e-9) / 1e6 / pk["hbm_gbs"], 4),
+           "pressure32b_layers": layers, "pressure32b_steps": len(ms), "pressure32b_seconds": round(total_s, 2)}
+    out.update({f"pressure32b_{k}": v for k, v in percentiles(ms).items()})
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -143,7 +296,11 @@ def main() -> int:
     ap.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes: the default Qwen3-8B shape or another of the family")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 and the other workloads")
+    ap.add_argument("--workloads", default="ctx768,mixed14b,pressure32b",
+                    help="which of the other workloads run (comma-separated; empty: none)")
+    ap.add_argument("--workload-layers", type=int, default=0,
+                    help="fewer layers for the 14B and 32B workloads than their configurations have (reported with them)")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps from CUDA graphs")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off)")
@@ -297,14 +454,37 @@ def main() -> int:
         out.update({"value": B * K / ms * 1e3, "ms_per_step": ms / K, "launches": launches, "clocks": clocks.summary(),
                     "bytes": step_bytes, "gbs": step_bytes / (ms / K * 1e-3) / 1e9, "final_context": final_ctx})
         for r in reqs:
-            engine.scheduler.abort(r.rid)
+            engine.abort(r.rid)
         return out
 
     results = {}
     for B in sorted(batches, reverse=True):
         results[B] = decode_point(B, with_e2e=(B == args.batch))
     main_r = results[args.batch]
+    # The other workloads: each on its own; a failure of one is recorded, not fatal to the line.
+    extra: dict = {}
+    workloads = [] if args.no_points else [w for w in args.workloads.split(",") if w]
+    if "ctx768" in workloads:
+        try:
+            extra.update(run_ctx768(engine, cfg, args.layers, rng, pk))
+        except Exception as e:                                       # noqa: BLE001
+            extra["ctx768_error"] = f"{type(e).__name__}: {e}"[:200]
     err = ops.device_error()
+    if any(w in workloads for w in ("mixed14b", "pressure32b")):
+        import gc
+        del engine, runner, logits
+        gc.collect()
+        torch.cuda.empty_cache()
+        for w, fn in (("mixed14b", run_mixed14b), ("pressure32b", run_pressure32b)):
+            if w not in workloads:
+                continue
+            try:
+                extra.update(fn(rng, pk, args.workload_layers))
+            except Exception as e:                                   # noqa: BLE001
+                extra[w + "_error"] = f"{type(e).__name__}: {e}"[:200]
+            gc.collect()
+            torch.cuda.empty_cache()
+        err = err or ops.device_error()
 
     line = {
         "metric": "decode tokens/s (%s, bf16, batch %d, context %d)" % (shape_name, args.batch, ctx),
@@ -324,7 +504,7 @@ def main() -> int:
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(main_r["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(main_r["gbs"] / pk["hbm_gbs"], 4)},
-        "points": {f"decode_b{B}": round(r["value"], 2) for B, r in results.items() if B != args.batch},
+        "points": {**{f"decode_b{B}": round(r["value"], 2) for B, r in results.items() if B != args.batch}, **extra},
         "points_roofline_frac": {f"decode_b{B}": round(r["gbs"] / pk["hbm_gbs"], 4) for B, r in results.items()},
         "device_error": err, "build_s": round(build_s, 1),
     }

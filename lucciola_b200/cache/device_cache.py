@@ -1,4 +1,4 @@
-"""Device memory of the caches: one tensor of pages per group, one tensor of slots per state cache.
+"""Device memory of the caches: one tensor of pages per group, one tensor of slots (and a spare row) per state cache.
 
 Pages of a group: [layer in group][k|v][page][kv head][slot in page][head_dim], so that the keys
 (or values) of one page and kv head are one contiguous box of page_size x head_dim elements.
@@ -46,14 +46,18 @@ class DeviceCache:
         self.states: dict[int, torch.Tensor] = {}
         for cid, r in enumerate(requests):
             if isinstance(r, StateSlot):
-                st = torch.zeros((num_slots, *r.shape), dtype=r.dtype, device=device)
+                # one row more than there are slots: row `num_slots` belongs to no request; the entries that pad a
+                # recorded step read and write it
+                st = torch.zeros((num_slots + 1, *r.shape), dtype=r.dtype, device=device)
                 self.states[cid] = st
                 self.views[cid] = StateCacheView(st)
 
-    def zero_slots(self, slots: torch.Tensor) -> None:
-        """Clear the state rows of newly admitted requests."""
+    def zero_slots(self, slots: torch.Tensor, stream: int) -> None:
+        """Clear the state rows of newly admitted requests.  `slots`: int32 on the device, negative entries name
+        no row (the list has a fixed length so that the launch can be part of a recorded step)."""
+        from .. import ops
         for st in self.states.values():
-            st.index_fill_(0, slots, 0)
+            ops.zero_rows(st, slots, stream)
 
     def poison_pages(self, group: int, pages: Sequence[int], value: float = float("nan")) -> None:
         """Fill pages with a value that would show in any sum (for tests of page reuse)."""

@@ -21,7 +21,9 @@ class EngineOptions:
     prefill_chunk: int = 0             # largest portion of one prompt in a step; 0 = the budget
     max_num_seqs: int = 256            # most requests that run at a time
     max_model_len: int = 0             # longest sequence; 0 = max_position_embeddings
-    use_cuda_graph: bool = True        # replay decode-only steps from CUDA graphs
+    use_cuda_graph: bool = True        # record steps whose shape comes again as CUDA graphs and replay them
+    graph_after: int = 2               # a step with portions of prompts is recorded when its shape has come this often
+    max_shape_graphs: int = 32         # recordings of steps with portions kept at a time (least recently used goes)
     device: str = "cuda:0"
 
     def validate(self) -> None:
@@ -35,5 +37,7 @@ class EngineOptions:
             raise ValueError(f"mem_fraction must be in (0, 1], got {self.mem_fraction}")
         if self.max_tokens_per_step <= 0 or self.max_num_seqs <= 0:
             raise ValueError("max_tokens_per_step and max_num_seqs must be positive")
+        if self.graph_after < 1 or self.max_shape_graphs < 1:
+            raise ValueError("graph_after and max_shape_graphs must be at least 1")
         if self.prefill_chunk < 0 or self.max_model_len < 0:
             raise ValueError("prefill_chunk and max_model_len must not be negative")

@@ -23,6 +23,11 @@
 // LB_STATIC_SCRATCH_COUNTERS counters; a larger request is refused with a message that names the
 // limit, and nothing is launched.  Products that are not split use no scratch and have no such limit.
 //
+// Which kernel runs.  Every size goes to the few-token kernel (weight rows on the tensor core's 128 lanes,
+// up to 256 tokens a tile).  The result is right for any M, but a product of many tokens (M > 256), which
+// lb_gemm_tcgen05 sends to its persistent many-token kernel, runs slower here: this entry point is meant
+// for the few-token products that need scratch at all.
+//
 // First call on a device.  The array's name is a host-side handle, not a device address.  The first
 // call on each device, made with that device current, asks the runtime for the array's address on that
 // device (cudaGetSymbolAddress) and keeps it; that first call should come before any stream capture

@@ -18,12 +18,19 @@ __host__ __device__ __forceinline__ unsigned long long mix64(unsigned long long 
   return x;
 }
 
-// Uniform in (0, 1) with 24 bits.
+// The top 23 bits of a hash as a number strictly inside (0, 1): (b + 0.5) / 2^23.  b + 0.5 has at most 24
+// significant bits, so every value is exact in float32; the smallest is 2^-24 and the largest 1 - 2^-24.  (With
+// 24 bits the largest sum, 16777215.5, would round to 2^24 and give exactly 1, whose score is +infinity.)
+__host__ __device__ __forceinline__ float bits_to_uniform(unsigned int bits23) {
+  return ((float)bits23 + 0.5f) * (1.0f / 8388608.0f);
+}
+
+// Uniform in (0, 1) with 23 bits.
 __host__ __device__ __forceinline__ float hash_uniform(unsigned long long key, unsigned int counter,
                                                        unsigned int i) {
   unsigned long long x = mix64(key + 0x9E3779B97F4A7C15ull * (unsigned long long)(counter + 1u));
   x = mix64(x ^ (0xD6E8FEB86659FD93ull * (unsigned long long)(i + 1u)));
-  return ((float)(unsigned int)(x >> 40) + 0.5f) * (1.0f / 16777216.0f);
+  return bits_to_uniform((unsigned int)(x >> 41));
 }
 
 __global__ void sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits,
@@ -91,3 +98,5 @@ LB_EXPORT int lb_sample(int* tokens, const float* logits, const float* temperatu
 LB_EXPORT float lb_hash_uniform(unsigned long long key, unsigned int counter, unsigned int i) {
   return lb::hash_uniform(key, counter, i);
 }
+
+LB_EXPORT float lb_bits_to_uniform(unsigned int bits23) { return lb::bits_to_uniform(bits23 & 0x7FFFFFu); }

@@ -21,7 +21,7 @@ from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass
-from typing import Iterable, Optional, Sequence
+from typing import Callable, Hashable, Iterable, Optional, Sequence
 
 from ..cache.manager import CacheManager
 from .request import Request, Status
@@ -37,8 +37,12 @@ class Scheduled:
 
 class Scheduler:
     def __init__(self, manager: CacheManager, max_tokens_per_step: int, max_num_seqs: int, max_model_len: int,
-                 prefill_chunk: int = 0, eos_token_ids: Iterable[int] = ()):
+                 prefill_chunk: int = 0, eos_token_ids: Iterable[int] = (),
+                 release: Optional[Callable[[Hashable], None]] = None):
+        """`release(rid)` gives back all that a request holds; whoever keeps more per request than the cache
+        manager does (the runner's converted block tables) passes its own."""
         self.manager = manager
+        self._release_fn = release
         self.max_tokens_per_step = max_tokens_per_step
         self.max_num_seqs = min(max_num_seqs, manager.num_slots)
         self.max_model_len = max_model_len
@@ -102,9 +106,14 @@ class Scheduler:
             best = min(best, (have + p.num_free - reserved[g]) * ps)
         return best
 
+    def _release(self, rid: Hashable) -> None:
+        if self._release_fn is not None:
+            self._release_fn(rid)
+        elif self.manager.has_request(rid):
+            self.manager.release(rid)
+
     def _preempt(self, r: Request) -> None:
-        if self.manager.has_request(r.rid):
-            self.manager.release(r.rid)
+        self._release(r.rid)
         self.running.remove(r)
         r.status = Status.WAITING
         r.num_computed = 0
@@ -113,8 +122,7 @@ class Scheduler:
         self.waiting.appendleft(r)
 
     def _finish(self, r: Request, reason: str) -> None:
-        if self.manager.has_request(r.rid):
-            self.manager.release(r.rid)
+        self._release(r.rid)
         if r in self.running:
             self.running.remove(r)
         r.status, r.finish_reason = Status.FINISHED, reason

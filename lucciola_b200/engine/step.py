@@ -10,10 +10,24 @@ are computed for the wanted rows only, and sampling happens above.
 The runner owns the model, the cache manager and the device memory of the caches.  Pages are
 taken here, at the start of a step, for exactly the tokens of the step; whoever builds batches
 (the scheduler, the trace replay) asks `can_run` first and decides what to do when pages are short.
+
+What the runner knows of the model is its interfaces: the cache each layer asks for, and the plans
+that parts make for a step on the host (`Mixer.plan`), which it carries to the device with its own
+integers.  How a part cuts its work into launches is the part's business.
+
+Steps of a shape that comes again are recorded as CUDA graphs and replayed: a step is a few hundred
+launches, and launching them one by one takes the host longer than the GPU needs to run them when the
+step has few tokens.  The shape of a step is (how many single tokens lead it, the lengths of the
+portions that follow, a bound on the context length): steps of single tokens only are padded to a
+bucket and recorded the first time, steps with portions (lucciola's usual step while a prompt is
+being read: every running request, then a portion, src/scheduler.cc:51-120) when their shape has come
+`graph_after` times.  A recording reads everything that differs between steps of its shape (tokens,
+positions, block tables, plans, new state slots) from one device buffer that is filled before each replay.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from collections import OrderedDict
+from dataclasses import dataclass
 from typing import Hashable, Optional, Sequence
 
 import numpy as np
@@ -23,19 +37,18 @@ from ..cache.device_cache import DeviceCache, pages_that_fit
 from ..cache.manager import NO_PAGE, CacheManager, plan_groups
 from ..config.engine_options import EngineOptions
 from ..models.decoder import DecoderModel
-from ..parts.base import Runtime, StepContext
+from ..parts.base import BatchShape, PlanView, Runtime, StepContext, StepPlan
 
 
-# Entries with at least this many tokens in a step go to the tensor-memory attention kernel (128-row tiles).
-_BIG_PORTION = 16
-
-# Batch sizes for which decode-only steps are recorded as CUDA graphs; a batch is padded to the next one.
+# Numbers of leading single tokens for which steps are recorded; a step is padded to the next one.
 _GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
-# A step that is one short portion of one request (a short prompt, the end of a long one) is recorded too, per number of
-# tokens, from the second time that number is seen: such a step is a few hundred launches, and launching them one by one
-# takes the host longer than the GPU needs to run them (3.4 ms for 28 layers whether the portion has 36 or 512 tokens).
-_SHORT_PORTION = 512
-_SHORT_GRAPHS = 16                       # recordings of that kind kept at a time
+# Steps with portions are recorded up to this many tokens and this many portions: beyond, the GPU needs longer
+# for a step than the host needs to launch it.
+_RECORD_TOKENS = 1024
+_RECORD_PORTIONS = 4
+# A recording of a portion of which some logits are wanted computes those of all its tokens; not worth it for
+# a long portion of which few are wanted.
+_ALL_ROWS = 64
 
 
 class OutOfPages(RuntimeError):
@@ -76,6 +89,13 @@ class _Staging:
         self.recorded[i] = True
 
 
+@dataclass
+class _Recording:
+    graph: object                        # a torch.cuda.CUDAGraph: replay() runs the recorded step again
+    logits: Optional[torch.Tensor]       # lives in the graph's memory; valid until the next step
+    kernels: int                         # kernel nodes, for the launch count
+
+
 class ModelRunner:
     def __init__(self, model: DecoderModel, rt: Runtime, options: EngineOptions, num_pages: Optional[int] = None):
         options.validate()
@@ -100,20 +120,25 @@ class ModelRunner:
         self.max_pages_per_seq = -(-self.max_model_len // self.page_size)
         self._any_window = any(g.window > 0 for g in self.groups)
         self._arange_cache = np.arange(512, dtype=np.int32)
-        self._decode_tiles: dict[int, list] = {}               # tiles of a decode-only step, by its (padded) size
-        self._decode_tiles_flat: dict[int, np.ndarray] = {}
-        # Group sizes for which a step carries tiles of the tensor-core attention kernel.
-        self.tile_groups = sorted({g for b in model.blocks if (g := b.mixer.query_group_size()) and g <= 64}) \
-            if rt.fast_kernels else []
+        # The parts that plan work on the host for every step: one for each distinct key.
+        self._planners: dict[Hashable, object] = {}
+        for block in model.blocks:
+            key = block.mixer.plan_key()
+            if key is not None and key not in self._planners:
+                self._planners[key] = block.mixer
+        # Steps are recorded only when every part of the model says its forward() can be.
+        self._can_record = bool(options.use_cuda_graph and rt.fast_kernels and all(p.recordable for p in model.all_parts()))
         self._staging: Optional[_Staging] = None
         self.steps_run = 0
         self.tokens_run = 0
         self.h2d_bytes = 0                 # bytes of step inputs copied from pinned host memory so far
         self._table_rows: dict[tuple[Hashable, int], tuple[int, np.ndarray]] = {}
-        self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
-        self._graph_inputs: dict[tuple[int, int], torch.Tensor] = {}
-        self._short_seen: dict[tuple[int, int], int] = {}       # how often a short portion of this size has come
+        self._graphs: "OrderedDict[tuple, _Recording]" = OrderedDict()         # by shape, least recently used first
+        self._graph_inputs: dict[tuple, torch.Tensor] = {}
+        self._graph_pool = None            # the recordings replay one at a time and share their memory
+        self._shape_seen: dict[tuple, int] = {}      # how often a shape with portions has come
         self._graph_launches = 0           # kernels replayed from CUDA graphs so far
+        self.graph_replays = 0
 
     # ---- what a batch builder may ask ------------------------------------
     def length(self, rid: Hashable) -> int:
@@ -146,57 +171,101 @@ class ModelRunner:
         for g in range(len(self.groups)):
             self._table_rows.pop((rid, g), None)
 
+    # ---- recordings ----------------------------------------------------------------
+    def _shape_of(self, entries: Sequence[StepEntry], q_lens: Sequence[int], max_ctx: int) -> Optional[tuple]:
+        """The shape under which this step may be recorded and replayed, or None: (single tokens that lead it,
+        padded to a bucket; lengths of the portions behind them; bound on the context length; which logits of
+        each portion a recording computes: "last", "none" or "all")."""
+        if not self._can_record:
+            return None
+        lead = 0
+        while lead < len(q_lens) and q_lens[lead] == 1:
+            lead += 1
+        portions = tuple(q_lens[lead:])
+        if lead > _GRAPH_BUCKETS[-1] or len(portions) > _RECORD_PORTIONS:
+            return None
+        padded = next(b for b in _GRAPH_BUCKETS if b >= lead) if lead else 0
+        if portions and padded + sum(portions) > _RECORD_TOKENS:
+            return None
+        kinds = []
+        for e, n in zip(entries[lead:], portions):
+            want = tuple(e.want)
+            if want == (n - 1,):
+                kinds.append("last")
+            elif not want:
+                kinds.append("none")
+            elif n <= _ALL_ROWS or 2 * len(want) >= n:
+                kinds.append("all")
+            else:
+                return None
+        span = max(256, 1 << (max_ctx - 1).bit_length())
+        return (padded, portions, span, tuple(kinds))
+
+    def _record_now(self, shape: tuple) -> bool:
+        """Steps of single tokens are recorded at once; shapes with portions when they have come often enough."""
+        if shape in self._graphs or not shape[1]:
+            return True
+        seen = self._shape_seen[shape] = self._shape_seen.get(shape, 0) + 1
+        if seen < self.options.graph_after:
+            return False
+        if len(self._shape_seen) > 4096:                                     # shapes that never came again
+            self._shape_seen = {k: v for k, v in self._shape_seen.items() if v > 1}
+        kept = [k for k in self._graphs if k[1]]
+        if len(kept) >= self.options.max_shape_graphs:                       # the one not used for longest makes room
+            del self._graphs[kept[0]]
+            self._graph_inputs.pop(kept[0], None)
+        return True
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _sync(self) -> None:
+        torch.cuda.current_stream(self.device).synchronize()
+
+    def _forward(self, d_tok: torch.Tensor, step: StepContext, d_rows: Optional[torch.Tensor],
+                 d_fresh: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        if d_fresh is not None:
+            self.cache.zero_slots(d_fresh, self.rt.stream)     # state of the requests this step admits
+        return self.model.forward(d_tok, step, self.cache.views, d_rows)
+
+    def _run_and_record(self, shape: tuple, d_tok: torch.Tensor, step: StepContext, d_rows: Optional[torch.Tensor],
+                        d_fresh: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """The first step of a shape that is to be recorded: it runs as usual (which also warms every lazy set-up)
+        and is then recorded; launches into a capturing stream are not executed.  Later steps replay the recording."""
+        from .. import ops
+        logits = self._forward(d_tok, step, d_rows, d_fresh)
+        self._sync()
+        before = ops.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        outer = self.rt.stream
+        try:
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                self.rt.stream = torch.cuda.current_stream(self.device).cuda_stream
+                static_logits = self._forward(d_tok, step, d_rows, d_fresh)
+        finally:
+            self.rt.stream = outer
+        self._graphs[shape] = _Recording(graph, static_logits, ops.launch_count() - before)
+        return logits
+
     # ---- the step ----------------------------------------------------------
     def _staging_for(self, n: int) -> _Staging:
         if self._staging is None or self._staging.capacity < n:
-            torch.cuda.current_stream(self.device).synchronize()
+            if self._staging is not None:
+                self._sync()                    # a copy out of the old buffers may still be under way
             self._staging = _Staging(self.device, max(n, 4096) * 2)
         return self._staging
 
-    def _run_graph(self, key: tuple, d_tok: torch.Tensor, step: StepContext, d_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-        """A step of a fixed shape (decoded tokens of a batch bucket, or one short portion of a given size): the first
-        time it runs as usual and is then recorded (launches into a capturing stream are not executed); later steps replay
-        the recording.  The result lives in the graph's memory and is valid until the next step."""
-        from .. import ops
-        hit = self._graphs.get(key)
-        if hit is not None:
-            graph, logits, kernels = hit
-            graph.replay()
-            self._graph_launches += kernels
-            return logits
-        logits = self.model.forward(d_tok, step, self.cache.views, d_rows)      # also warms every lazy set-up
-        torch.cuda.current_stream(self.device).synchronize()
-        before = ops.launch_count()
-        graph = torch.cuda.CUDAGraph()
-        outer = self.rt.stream
-        with torch.cuda.graph(graph):
-            self.rt.stream = torch.cuda.current_stream(self.device).cuda_stream
-            static_logits = self.model.forward(d_tok, step, self.cache.views, d_rows)
-        self.rt.stream = outer
-        self._graphs[key] = (graph, static_logits, ops.launch_count() - before)
-        return logits
-
-    @staticmethod
-    def _tiles(q_lens: Sequence[int], group: int, rows: int = 64, take=None) -> list[tuple[int, int, int, int]]:
-        """Runs of up to rows // group consecutive tokens of one request: (first token, tokens, request, 0),
-        for the requests whose number of tokens passes `take`."""
-        per = rows // group
-        tiles, t = [], 0
-        for i, n in enumerate(q_lens):
-            if take is None or take(n):
-                for off in range(0, n, per):
-                    tiles.append((t + off, min(per, n - off), i, 0))
-            t += n
-        return tiles
-
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run the entries as one batch.  Returns logits [wanted, vocab] (float32, on the device) in the
-        order of the entries and of their `want`, or None when nothing is wanted."""
+        order of the entries and of their `want`, or None when nothing is wanted.  The tensor is valid until
+        the next step."""
         if not entries:
             return None
         vocab = self.model.vocab_size
         seen: set[Hashable] = set()
-        token_arrays: list[np.ndarray] = []
+        token_arrays: list = []
         for e in entries:
             if e.rid in seen:
                 raise ValueError(f"request {e.rid!r} appears twice in one step")
@@ -219,7 +288,7 @@ class ModelRunner:
             if lo < 0 or hi >= vocab:
                 raise ValueError(f"request {e.rid!r}: token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab}")
         # Take pages; collect the batch on the host.
-        new_slots: list[int] = []
+        new_slots: list[tuple[int, int]] = []           # (entry, slot) of the requests this step admits
         starts, q_lens = [], []
         if all(isinstance(a, int) for a in token_arrays) and all(self.manager.has_request(e.rid) for e in entries):
             # every entry is one more token of a request that is under way: one pass over the page tables
@@ -230,9 +299,9 @@ class ModelRunner:
         else:
             if not self.can_run(entries):
                 raise OutOfPages(f"the step needs more pages or slots than are free ({[p.num_free for p in self.manager.pools]} pages free)")
-            for e in entries:
+            for i, e in enumerate(entries):
                 if not self.manager.has_request(e.rid):
-                    new_slots.append(self.manager.admit(e.rid))
+                    new_slots.append((i, self.manager.admit(e.rid)))
                 start = self.manager.length(e.rid)
                 if not self.manager.extend(e.rid, start + len(e.tokens)):
                     raise OutOfPages("pages ran out while a step was being prepared")   # can_run() said yes
@@ -241,68 +310,42 @@ class ModelRunner:
 
         S_real = len(entries)
         max_ctx = max(s + n for s, n in zip(starts, q_lens))
-        # Decode-only steps replay a CUDA graph: the batch is padded to a bucket with entries that
-        # own no page (their keys and values are written nowhere and they attend to nothing).
-        graph_key = None
-        if (self.options.use_cuda_graph and self.rt.fast_kernels and not self.cache.states and max(q_lens) == 1
-                and S_real <= _GRAPH_BUCKETS[-1]):
-            S = next(b for b in _GRAPH_BUCKETS if b >= S_real)
-            span_hint = max(256, 1 << (max_ctx - 1).bit_length())
-            graph_key = (S, span_hint)
-            q_lens = q_lens + [1] * (S - S_real)
-            starts = starts + [0] * (S - S_real)
-        elif (self.options.use_cuda_graph and self.rt.fast_kernels and not self.cache.states and S_real == 1
-              and 2 <= q_lens[0] <= _SHORT_PORTION):
-            want = tuple(entries[0].want)
-            # which logits the recording computes: those of the last token, none, or all of them
-            rows_kind = "last" if want == (q_lens[0] - 1,) else "none" if not want else "all"
-            key = (-q_lens[0], max(256, 1 << (max_ctx - 1).bit_length()), rows_kind)   # a negative first number: this kind
-            if key in self._graphs:
-                graph_key = key
-            else:
-                seen = self._short_seen[key] = self._short_seen.get(key, 0) + 1
-                if seen >= 2:
-                    short = [k for k in self._graphs if k[0] < 0]
-                    if len(short) >= _SHORT_GRAPHS:                             # the oldest recording makes room
-                        self._graphs.pop(short[0])
-                        self._graph_inputs.pop(short[0], None)
-                    graph_key = key
-        decode_graph = graph_key is not None and graph_key[0] > 0
+        # A step that is recorded, or replayed from a recording, is padded: behind its leading single tokens come
+        # entries that own no page (their keys and values are written nowhere and they attend to nothing).
+        shape = self._shape_of(entries, q_lens, max_ctx)
+        if shape is not None and not self._record_now(shape):
+            shape = None
+        lead = pad = 0
+        if shape is not None:
+            lead = S_real - len(shape[1])
+            pad = shape[0] - lead
+            if pad:
+                q_lens = q_lens[:lead] + [1] * pad + q_lens[lead:]
+                starts = starts[:lead] + [0] * pad + starts[lead:]
         S, T = len(q_lens), sum(q_lens)
-        R = T if graph_key else sum(len(e.want) for e in entries)
-        if graph_key and not decode_graph and graph_key[2] != "all":
-            R = 1 if graph_key[2] == "last" else 0
+        place = lambda i: i if i < lead else i + pad          # where entry i sits among the padded ones
+        # Which rows the output head computes, and which of them are handed out.
+        if shape is None:
+            R = sum(len(e.want) for e in entries)
+            wanted_rows = list(range(R))
+        else:
+            R, wanted_rows = shape[0], [i for i in range(lead) if entries[i].want]
+            for e, n, kind in zip(entries[lead:], shape[1], shape[3]):
+                if kind == "last":
+                    wanted_rows.append(R)
+                    R += 1
+                elif kind == "all":
+                    wanted_rows += [R + w for w in e.want]
+                    R += n
         G, P = len(self.groups), self.max_pages_per_seq
-        # Work items of the attention kernels, per group size: "all" = every entry in tiles of up to 64 query
-        # rows; when the step holds portions of prompts, also "big" = those portions in work items of up to 256
-        # rows (for the tcgen05 kernel) and "rest" = the other entries in 64-row tiles; and when the entries that are
-        # not "big" mix tiles of at most 16 query rows (decoded tokens) with larger ones (a few tokens of a prompt),
-        # "one" = the former and "rest" = the latter: tiles of at most 16 rows have a kernel of their own, which a
-        # launch uses only if all of its tiles are such.
-        tile_lists: dict[tuple[int, str], list] = {}
-        first_token = [0] * S
-        for i in range(1, S):
-            first_token[i] = first_token[i - 1] + q_lens[i - 1]
-        for g in self.tile_groups:
-            if decode_graph:                      # one token each: the same tiles for every step of this size
-                tile_lists[(g, "all")] = self._decode_tiles.get(S) or self._decode_tiles.setdefault(S, self._tiles(q_lens, g, 64))
-                continue
-            tile_lists[(g, "all")] = self._tiles(q_lens, g, 64)
-            has_big = max(q_lens) >= _BIG_PORTION
-            if has_big:
-                # two tiles of floor(128 / g) tokens each
-                big = self._tiles(q_lens, g, 2 * (128 // g) * g, lambda n: n >= _BIG_PORTION)
-                # tiles that see the most keys first: the short ones then fill the end of the last wave
-                big.sort(key=lambda tl: -(starts[tl[2]] + (tl[0] - first_token[tl[2]]) + tl[1]))
-                tile_lists[(g, "big")] = big
-            others = [n for n in q_lens if n < _BIG_PORTION]
-            mixed = any(n * g <= 16 for n in others) and any(n * g > 16 for n in others)
-            if mixed:
-                tile_lists[(g, "rest")] = self._tiles(q_lens, g, 64, lambda n: n < _BIG_PORTION and n * g > 16)
-                tile_lists[(g, "one")] = self._tiles(q_lens, g, 64, lambda n: n * g <= 16)
-            elif has_big and others:
-                tile_lists[(g, "rest")] = self._tiles(q_lens, g, 64, lambda n: n < _BIG_PORTION)
-        total = 3 * T + (S + 1) + 2 * S + R + G * S * P + sum(4 * len(t) + 3 for t in tile_lists.values())
+        batch = BatchShape(q_lens, starts, max(q_lens), max_ctx, shape[2] if shape is not None else max_ctx, shape is not None)
+        made: dict[Hashable, StepPlan] = {}
+        for key, part in self._planners.items():
+            plan = part.plan(batch)
+            if plan is not None:
+                made[key] = plan
+        has_state = bool(self.cache.states)
+        total = 3 * T + (S + 1) + 3 * S + R + G * S * P + sum(a.size + 3 for p in made.values() for a in p.arrays.values())
         st = self._staging_for(total)
         hi, _ = st.next_host()
         h = st.host_np[hi]
@@ -313,18 +356,16 @@ class ModelRunner:
             o += n
             return v
         tok, pos, seq = take(T), take(T), take(T)
-        cu, ctx, slots, rows = take(S + 1), take(S), take(S), take(R)
+        cu, ctx, slots, fresh, rows = take(S + 1), take(S), take(S), take(S), take(R)
         tables = [take(S * P).reshape(S, P) for _ in range(G)]
-        for tl in tile_lists.values():
-            o = (o + 3) & ~3                      # the kernel reads a tile as one 16-byte word
-            flat = self._decode_tiles_flat.get(len(tl)) if decode_graph else None
-            if flat is None:
-                flat = np.asarray(tl, dtype=np.int32).reshape(-1)
-                if decode_graph:
-                    self._decode_tiles_flat[len(tl)] = flat
-            take(4 * len(tl))[:] = flat
-        wanted_rows: list[int] = []
-        if decode_graph:
+        for plan in made.values():
+            for a in plan.arrays.values():
+                o = (o + 3) & ~3                      # kernels read a work item as one 16-byte word
+                take(a.size)[:] = a.reshape(-1)
+        fresh[:] = -1
+        for i, slot in new_slots:
+            fresh[place(i)] = slot
+        if batch.max_q_len == 1:
             # One token each: everything but the tables is a handful of whole-array assignments.
             ar = self._arange(S + 1)
             tok[:S_real] = token_arrays
@@ -333,51 +374,69 @@ class ModelRunner:
             seq[:] = ar[:S]
             cu[:] = ar
             ctx[:] = pos + 1
-            rows[:] = ar[:T]
-            slots[S_real:] = 0
+            slots[S_real:] = self.manager.num_slots            # the spare state row
             for g in range(G):
                 tables[g][S_real:] = NO_PAGE
             for i, e in enumerate(entries):
                 slots[i] = self.manager.slot(e.rid)
                 for g in range(G):
                     tables[g][i] = self._table_row(e.rid, g)
-                if e.want:
-                    wanted_rows.append(i)
+            if shape is None:
+                rows[:] = [i for i, e in enumerate(entries) for _ in e.want]
+            else:
+                rows[:] = ar[:R]
         else:
-            t = 0
-            cu[0] = 0
-            for i, e in enumerate(entries):
-                n = q_lens[i]
-                tok[t:t + n] = token_arrays[i]
-                slots[i] = self.manager.slot(e.rid)
+            if pad:
+                tok[lead:lead + pad] = 0
+                pos[lead:lead + pad] = 0
+                slots[lead:lead + pad] = self.manager.num_slots     # the spare state row
                 for g in range(G):
-                    tables[g][i] = self._table_row(e.rid, g)
-                wanted_rows += [t + w for w in e.want]
-                pos[t:t + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
-                seq[t:t + n] = i
+                    tables[g][lead:lead + pad] = NO_PAGE
+            t, r = 0, 0
+            cu[0] = 0
+            for j in range(S):
+                n = q_lens[j]
+                seq[t:t + n] = j
+                ctx[j] = starts[j] + n
+                cu[j + 1] = t + n
                 t += n
-                cu[i + 1] = t
-                ctx[i] = starts[i] + n
-        if graph_key is None:
-            rows[:] = np.asarray(wanted_rows, dtype=np.int32)
-        elif not decode_graph:
-            if graph_key[2] == "all":
-                rows[:] = self._arange(T)        # the recording computes the logits of every token
-            elif graph_key[2] == "last":
-                rows[0] = T - 1
-                wanted_rows = [0]
-        dev = self._graph_inputs.get(graph_key) if graph_key else None
-        if graph_key and dev is None:
-            dev = self._graph_inputs[graph_key] = torch.empty(total, dtype=torch.int32, device=self.device)
+            for i, e in enumerate(entries):
+                j = place(i)
+                t, n = int(cu[j]), q_lens[j]
+                tok[t:t + n] = token_arrays[i]
+                pos[t:t + n] = np.arange(starts[j], starts[j] + n, dtype=np.int32)
+                slots[j] = self.manager.slot(e.rid)
+                for g in range(G):
+                    tables[g][j] = self._table_row(e.rid, g)
+                if shape is None:
+                    for w in e.want:
+                        rows[r] = t + w
+                        r += 1
+            if shape is not None:
+                rows[:shape[0]] = self._arange(shape[0])           # the leading single tokens, padding included
+                r = shape[0]
+                for j, (n, kind) in enumerate(zip(shape[1], shape[3])):
+                    t = int(cu[shape[0] + j])
+                    if kind == "last":
+                        rows[r] = t + n - 1
+                        r += 1
+                    elif kind == "all":
+                        rows[r:r + n] = np.arange(t, t + n, dtype=np.int32)
+                        r += n
+        dev = self._graph_inputs.get(shape) if shape is not None else None
+        if shape is not None and dev is None:
+            dev = self._graph_inputs[shape] = torch.empty(total, dtype=torch.int32, device=self.device)
         st.upload(hi, total, dev)
         self.h2d_bytes += 4 * total
 
-        if graph_key and graph_key in self._graphs:
+        if shape is not None and shape in self._graphs:
             # The recording reads its inputs from the buffer just filled: nothing else to set up.
-            graph, logits, kernels = self._graphs[graph_key]
-            graph.replay()
-            self._graph_launches += kernels
-            return self._after_step(entries, T, self._wanted(logits, wanted_rows))
+            rec = self._graphs[shape]
+            self._graphs.move_to_end(shape)
+            rec.graph.replay()
+            self._graph_launches += rec.kernels
+            self.graph_replays += 1
+            return self._after_step(entries, T, self._wanted(rec.logits, wanted_rows, R))
 
         d = st.dev if dev is None else dev
         o = 0
@@ -387,25 +446,27 @@ class ModelRunner:
             o += n
             return v
         d_tok, d_pos, d_seq = view(T), view(T), view(T)
-        d_cu, d_ctx, d_slots, d_rows = view(S + 1), view(S), view(S), view(R)
+        d_cu, d_ctx, d_slots, d_fresh, d_rows = view(S + 1), view(S), view(S), view(S), view(R)
         d_tables = [view(S * P).view(S, P) for _ in range(G)]
-        attn_meta: dict[int, dict] = {}
-        for (g, kind), tl in tile_lists.items():
-            o = (o + 3) & ~3
-            attn_meta.setdefault(g, {})[kind] = (view(4 * len(tl)).view(len(tl), 4), max(n for _, n, _, _ in tl) * g)
+        plans: dict[Hashable, PlanView] = {}
+        for key, plan in made.items():
+            arrays = {}
+            for name, a in plan.arrays.items():
+                o = (o + 3) & ~3
+                arrays[name] = view(a.size).view(a.shape)
+            plans[key] = PlanView(arrays, plan.host)
 
         step = StepContext(
             num_tokens=T, num_seqs=S, positions=d_pos, token_seq=d_seq, cu_tokens=d_cu, context_lens=d_ctx,
             block_tables=d_tables, state_slots=d_slots, q_lens=q_lens, start_positions=starts,
-            max_q_len=max(q_lens), max_context_len=max_ctx, attn_meta=attn_meta)
-        self.rt.stream = torch.cuda.current_stream(self.device).cuda_stream
-        if new_slots and self.cache.states:
-            self.cache.zero_slots(torch.tensor(new_slots, dtype=torch.long, device=self.device))
-        if graph_key is None:
-            logits = self.model.forward(d_tok, step, self.cache.views, d_rows if R else None)
+            max_q_len=batch.max_q_len, max_context_len=max_ctx, span_hint=batch.span_hint, plans=plans)
+        self.rt.stream = self._stream()
+        d_rows = d_rows if R else None
+        d_fresh = d_fresh if has_state and (new_slots or shape is not None) else None
+        if shape is None:
+            logits = self._forward(d_tok, step, d_rows, d_fresh)
         else:
-            step.plans["span_hint"] = graph_key[1]
-            logits = self._wanted(self._run_graph(graph_key, d_tok, step, d_rows if R else None), wanted_rows)
+            logits = self._wanted(self._run_and_record(shape, d_tok, step, d_rows, d_fresh), wanted_rows, R)
         return self._after_step(entries, T, logits)
 
     def _table_row(self, rid: Hashable, g: int) -> np.ndarray:
@@ -425,12 +486,13 @@ class ModelRunner:
             self._arange_cache = np.arange(max(n, 512), dtype=np.int32)
         return self._arange_cache[:n]
 
-    def _wanted(self, logits: torch.Tensor, wanted_rows: list[int]) -> Optional[torch.Tensor]:
-        """The wanted rows of a recording's logits (it computes one row per token)."""
-        if not wanted_rows:
+    def _wanted(self, logits: Optional[torch.Tensor], wanted_rows: list[int], computed: int) -> Optional[torch.Tensor]:
+        """The wanted rows among those a recording computes."""
+        if not wanted_rows or logits is None:
             return None
-        if wanted_rows == list(range(len(wanted_rows))):
-            return logits[:len(wanted_rows)]
+        first, n = wanted_rows[0], len(wanted_rows)
+        if wanted_rows[-1] == first + n - 1 and wanted_rows == list(range(first, first + n)):
+            return logits if n == computed else logits[first:first + n]
         return logits.index_select(0, torch.tensor(wanted_rows, dtype=torch.long, device=self.device))
 
     def _after_step(self, entries: Sequence[StepEntry], T: int, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:

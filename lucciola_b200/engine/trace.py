@@ -29,6 +29,9 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each request rounded up to 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens in a cache page (must divide 64)")
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="record every step whose shape allows it as a CUDA graph when the shape first comes, and replay "
+                         "the recording for later steps of that shape (bfloat16 only; off: every step launches its kernels)")
     args = ap.parse_args(argv)
     if args.max_tokens <= 0:
         ap.error("--max-tokens must be positive")
@@ -43,7 +46,7 @@ def main(argv: list[str] | None = None) -> int:
     out.mkdir(parents=True, exist_ok=True)
     pages = -(-args.max_tokens // args.block_size)
     options = EngineOptions(dtype=args.dtype, block_size=args.block_size, max_blocks=pages, max_num_seqs=8,
-                            use_cuda_graph=False)
+                            use_cuda_graph=args.cuda_graph, graph_after=1, max_shape_graphs=256)
     runner = build_runner(args.model, options, num_pages=pages)
 
     for line in sys.stdin:

@@ -23,6 +23,8 @@ class LayerCall:
 
 
 class DecoderModel(Part):
+    recordable = True
+
     def __init__(self, rt: Runtime, embedding: TokenEmbedding, blocks: Sequence[Block], calls: Sequence[LayerCall],
                  final_norm: Norm, head: OutputHead, vocab_size: int, max_positions: int, eos_token_ids: Sequence[int] = ()):
         self.rt = rt

@@ -43,6 +43,7 @@ _SIGNATURES = {
     "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
                         c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "lb_upload": [c_void_p, c_void_p, c_longlong, c_void_p],
+    "lb_zero_rows": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p],
     "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
@@ -286,6 +287,13 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
+def zero_rows(state: torch.Tensor, slots: torch.Tensor, stream: int) -> None:
+    """state[slots[i]] = 0 for every non-negative entry of slots (int32, on the device)."""
+    _check(state, "state"); _check(slots, "slot list", torch.int32)
+    row_bytes = state[0].numel() * state.element_size()
+    _call("lb_zero_rows", state.data_ptr(), row_bytes, state.shape[0], slots.data_ptr(), slots.shape[0], stream)
+
+
 def upload(dst_ptr: int, src_ptr: int, nbytes: int, stream: int) -> None:
     """One asynchronous copy from pinned host memory to the device, in the order of `stream`."""
     _call("lb_upload", dst_ptr, src_ptr, nbytes, stream)
@@ -318,16 +326,24 @@ def linear(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, fast:
 
 
 _attn_ws: dict[int, torch.Tensor] = {}
+_attn_ws_retired: list[torch.Tensor] = []
 
 
 def _attention_workspace(device: torch.device, elems: int) -> torch.Tensor:
-    """Per device: float32 scratch for the partial results of split attention; grows on demand."""
+    """Per device: float32 scratch for the partial results of split attention; grows on demand.
+
+    A recorded CUDA graph keeps the address of the workspace it was recorded with, so a workspace that has
+    been handed out is never freed: when a larger one is needed the old one is retired, not released (it stays
+    valid for the recordings that name it; launches are ordered on one stream, so sharing it is safe).  Sizes at
+    least double, which bounds what the retired ones hold to the size of the current one."""
     key = device.index if device.index is not None else torch.cuda.current_device()
     ws = _attn_ws.get(key)
     if ws is None or ws.numel() < elems:
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("the attention workspace cannot grow while a CUDA graph is captured; run the step once before")
-        ws = torch.empty(max(elems, 1 << 20), dtype=torch.float32, device=device)
+        if ws is not None:
+            _attn_ws_retired.append(ws)
+        ws = torch.empty(max(elems, 1 << 20, 2 * ws.numel() if ws is not None else 0), dtype=torch.float32, device=device)
         _attn_ws[key] = ws
     return ws
 
@@ -440,31 +456,30 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
               num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-              stream: int, fast: bool) -> None:
-    """Causal attention of this step's queries over the pages of their requests.  `fast` allows the
-    tensor-core kernels where their conditions hold and the step carries tiles for this group size:
+              stream: int, plan=None) -> None:
+    """Causal attention of this step's queries over the pages of their requests.  With a `plan` (tile lists
+    by kind on the device, see parts/attention.py) the tensor-core kernels run where their conditions hold:
     portions of prompts go to the tcgen05 kernel, the rest (decoded tokens, short portions, other head
-    sizes) to the mma.sync kernels, decoded tokens in a launch of their own when the step lists them apart
-    ("one"); everything else to the plain kernel."""
-    G = num_q_heads // num_kv_heads
-    meta = step.attn_meta.get(G) if fast else None
-    if meta is None or not attention_flash_ok(q, num_q_heads, num_kv_heads, head_dim):
+    sizes) to the mma.sync kernels, decoded tokens in a launch of their own when the plan lists them apart
+    ("one"); everything else, and every step without a plan, goes to the plain kernel."""
+    if plan is None or not attention_flash_ok(q, num_q_heads, num_kv_heads, head_dim):
         attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
                         num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
         return
-    longest = step.plans.get("span_hint", step.max_context_len)      # a recorded step plans for a bucket of lengths
+    meta, most_rows = plan.arrays, plan.host["rows"]
+    longest = step.span_hint or step.max_context_len                 # a recorded step plans for a bucket of lengths
     span = min(longest, window + step.max_q_len) if window > 0 else longest
     kinds = ["all"]
     if "big" in meta and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size,
                                               step.block_tables[group].shape[1]):
-        attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"][0],
+        attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"],
                           num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
         kinds = [k for k in ("rest", "one") if k in meta]
     elif "big" not in meta and "one" in meta:
         kinds = ["rest", "one"]          # decoded tokens beside a few tokens of a prompt: a launch for each
     for kind in kinds:
-        tiles, rows = meta[kind]
-        rows = min(rows, 64)
+        tiles = meta[kind]
+        rows = min(most_rows[kind], 64)
         wide = attention_wide_clusters(head_dim) if rows <= 16 and page_size in (8, 16, 32, 64, 128) else 0
         splits = attention_splits(tiles.shape[0], num_kv_heads, span, rows, wide_clusters=wide)
         attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, rows,

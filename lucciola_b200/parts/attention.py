@@ -6,20 +6,75 @@ before the rotation; rotary position encoding of q and k; k and v written to the
 token's position; causal attention of every query head h over the keys of kv head
 h / (nq / nkv) with scale 1/sqrt(head_dim) unless another scale is given; output projection.
 A window W, which lucciola does not have, limits a query at position p to keys p-W+1 .. p.
+
+The attention kernels take their work from lists of tiles that this part makes on the host before a step runs
+(`plan`): which tokens of which request form a tile, how many rows a tile has, which tiles go to which kernel.
 """
 from __future__ import annotations
 
 import math
-from typing import Callable, Optional
+from typing import Callable, Hashable, Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import ops
-from .base import KVCacheView, KVPages, Mixer, ParamSpec, Part, PositionEncoding, Runtime, StepContext
+from .base import (BatchShape, KVCacheView, KVPages, Mixer, ParamSpec, Part, PositionEncoding, Runtime, StepContext,
+                   StepPlan)
 from .linear import Linear
+
+# Entries with at least this many tokens in a step go to the tensor-memory attention kernel (128-row tiles).
+BIG_PORTION = 16
+# Query rows (heads of a group x tokens) of a tile of the mma.sync kernels; tiles of at most DECODE_ROWS rows have
+# a kernel of their own, which a launch uses only if all of its tiles are such.
+TILE_ROWS, DECODE_ROWS = 64, 16
+
+
+def tiles_of(q_lens: Sequence[int], group: int, rows: int, take=None) -> list[tuple[int, int, int, int]]:
+    """Runs of up to rows // group consecutive tokens of one request: (first token, tokens, request, 0),
+    for the requests whose number of tokens passes `take`."""
+    per = rows // group
+    tiles, t = [], 0
+    for i, n in enumerate(q_lens):
+        if take is None or take(n):
+            for off in range(0, n, per):
+                tiles.append((t + off, min(per, n - off), i, 0))
+        t += n
+    return tiles
+
+
+def plan_tiles(batch: BatchShape, group: int) -> StepPlan:
+    """The tile lists of one step for query groups of `group` heads.  Kinds: "all" = every entry in tiles of up
+    to 64 query rows; when the step holds portions of prompts, also "big" = those portions in work items of up to
+    256 rows (two tiles of floor(128 / group) tokens, for the tensor-memory kernel) and "rest" = the other entries
+    in 64-row tiles; and when the entries that are not "big" mix tiles of at most 16 query rows (decoded tokens)
+    with larger ones (a few tokens of a prompt), "one" = the former and "rest" = the latter.  Each array is
+    int32 [n, 4]; host["rows"][kind] is the most query rows of a tile of that kind."""
+    q_lens, starts, g = batch.q_lens, batch.start_positions, group
+    lists: dict[str, list] = {"all": tiles_of(q_lens, g, TILE_ROWS)}
+    if batch.max_q_len > 1:
+        has_big = batch.max_q_len >= BIG_PORTION
+        if has_big:
+            first_token = np.concatenate(([0], np.cumsum(q_lens)[:-1])).tolist()
+            big = tiles_of(q_lens, g, 2 * (128 // g) * g, lambda n: n >= BIG_PORTION)
+            # tiles that see the most keys first: the short ones then fill the end of the last wave
+            big.sort(key=lambda tl: -(starts[tl[2]] + (tl[0] - first_token[tl[2]]) + tl[1]))
+            lists["big"] = big
+        others = [n for n in q_lens if n < BIG_PORTION]
+        mixed = any(n * g <= DECODE_ROWS for n in others) and any(n * g > DECODE_ROWS for n in others)
+        if mixed:
+            lists["rest"] = tiles_of(q_lens, g, TILE_ROWS, lambda n: n < BIG_PORTION and n * g > DECODE_ROWS)
+            lists["one"] = tiles_of(q_lens, g, TILE_ROWS, lambda n: n * g <= DECODE_ROWS)
+        elif has_big and others:
+            lists["rest"] = tiles_of(q_lens, g, TILE_ROWS, lambda n: n < BIG_PORTION)
+    return StepPlan({k: np.asarray(tl, dtype=np.int32).reshape(len(tl), 4) for k, tl in lists.items()},
+                    {"rows": {k: max(n for _, n, _, _ in tl) * g for k, tl in lists.items()}})
+
 
 
 class GQAttention(Mixer):
+    _decode_plans: dict[tuple[int, int], StepPlan] = {}      # (group size, batch size) -> plan of a step of single tokens
+
     def __init__(self, rt: Runtime, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PositionEncoding], qk_norm_eps: Optional[float], window: int = 0,
                  scale: Optional[float] = None):
@@ -41,6 +96,11 @@ class GQAttention(Mixer):
     def children(self) -> list[Part]:
         return [self.qkv, self.o]
 
+    @property
+    def recordable(self) -> bool:
+        """This part only launches kernels; a position encoding of its own kind has its own say."""
+        return self.position_encoding is None or self.position_encoding.recordable
+
     def param_specs(self) -> list[ParamSpec]:
         if self.qk_norm_eps is None:
             return []
@@ -52,8 +112,21 @@ class GQAttention(Mixer):
             self.q_norm_w = get(f"{self.prefix}.q_norm.weight").to(torch.float32).contiguous()
             self.k_norm_w = get(f"{self.prefix}.k_norm.weight").to(torch.float32).contiguous()
 
-    def query_group_size(self) -> int:
-        return self.num_heads // self.num_kv_heads
+    def plan_key(self) -> Optional[Hashable]:
+        """The tensor-core kernels run on the bfloat16 path for groups of up to 64 query heads; the tile lists
+        depend on the group size alone, so all such layers of a model share them."""
+        g = self.num_heads // self.num_kv_heads
+        return ("attention tiles", g) if self.rt.fast_kernels and g <= TILE_ROWS else None
+
+    def plan(self, batch: BatchShape) -> Optional[StepPlan]:
+        g = self.num_heads // self.num_kv_heads
+        if batch.max_q_len == 1:                    # one token each: the same tiles for every step of this size
+            key = (g, len(batch.q_lens))
+            hit = self._decode_plans.get(key)
+            if hit is None:
+                hit = self._decode_plans[key] = plan_tiles(batch, g)
+            return hit
+        return plan_tiles(batch, g)
 
     def cache_request(self) -> KVPages:
         return KVPages(self.num_kv_heads, self.head_dim, self.window)
@@ -75,7 +148,7 @@ class GQAttention(Mixer):
                                    inv_freq=rotary[0] if rotary is not None else None)
             out = rt.empty((T, nq, d))
             ops.attention(q, out, cache.k, cache.v, step, cache.group, nq, nkv, d, cache.page_size, self.window,
-                          self.scale, rt.stream, fast=rt.fast_kernels)
+                          self.scale, rt.stream, plan=step.plans.get(self.plan_key()))
             return self.o.forward(out.view(T, self.q_size))
         if write_cache:
             qkv = self.qkv.forward(h)
@@ -105,5 +178,5 @@ class GQAttention(Mixer):
                             page_size=cache.page_size)
         out = rt.empty((T, nq, d))
         ops.attention(q, out, cache.k, cache.v, step, cache.group, nq, nkv, d, cache.page_size, self.window,
-                      self.scale, rt.stream, fast=rt.fast_kernels)
+                      self.scale, rt.stream, plan=step.plans.get(self.plan_key()))
         return self.o.forward(out.view(T, self.q_size))

@@ -10,12 +10,14 @@ What a part must provide:
 
 Part (all)        param_specs() -> [ParamSpec]    tensors wanted, by full name
                   bind(get)                        take them: get(name) -> tensor on the device
+                  recordable                       True if forward() may be recorded into a CUDA graph
 Norm              forward(x, out_dtype)            -> normed copy
                   add_forward(residual, delta, out_dtype, rows=None)
                                                    residual += delta; -> norm(residual) [on rows]
 PositionEncoding  rotary_table() / apply(q, k, positions)
 Mixer             cache_request() -> KVPages | StateSlot | None
                   forward(h, step, cache) -> [T, hidden] in the activation type
+                  plan_key(), plan(batch) -> StepPlan   optional: work lists its kernels read on the device
 FeedForward       forward(h, step) -> [T, hidden]
 Block             mixer, forward(residual, delta, step, cache) -> (residual, delta)
 
@@ -24,8 +26,9 @@ Block             mixer, forward(residual, delta, step, cache) -> (residual, del
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Callable, Optional, Sequence
+from typing import Any, Callable, Hashable, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -76,8 +79,42 @@ class KVCacheView:
 
 @dataclass
 class StateCacheView:
-    """One cache layer of per-request state: row `slot` belongs to the request in that slot."""
-    state: torch.Tensor             # [slots, *shape]
+    """One cache layer of per-request state: row `slot` belongs to the request in that slot.  The last row belongs
+    to no request: the entries that pad a recorded step name it in `state_slots`, so that a mixer may treat them
+    like any other entry."""
+    state: torch.Tensor             # [slots + 1, *shape]
+
+
+@dataclass
+class BatchShape:
+    """The batch of one step as the host knows it, for parts that plan work before the step runs.
+
+    When the step is recorded as a CUDA graph, the recording is replayed for every later step with the same
+    `q_lens`; `start_positions` and `max_context_len` are then those of the step at hand only, and `span_hint` is
+    the bound on the context length that every step of the recording keeps (a power of two).  A plan's arrays may
+    depend on all of these (they are refilled for every step); their shapes, and whatever a part's forward() takes
+    from the host, may depend on `q_lens` and `span_hint` only."""
+    q_lens: list[int]
+    start_positions: list[int]
+    max_q_len: int
+    max_context_len: int
+    span_hint: int
+    recorded: bool = False
+
+
+@dataclass
+class StepPlan:
+    """What a part's plan() returns: int32 arrays that travel to the device with the step's own integers, and
+    what the part wants to keep on the host beside them (sizes its launches need)."""
+    arrays: dict[str, np.ndarray]
+    host: dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass
+class PlanView:
+    """A StepPlan as forward() sees it: the arrays as int32 tensors on the device, in the plan's shapes."""
+    arrays: dict[str, torch.Tensor]
+    host: dict[str, Any]
 
 
 @dataclass
@@ -99,17 +136,18 @@ class StepContext:
     start_positions: list[int] = field(default_factory=list)
     max_q_len: int = 0
     max_context_len: int = 0
-    # Per step scratch that parts of the same kind may share (plans of the attention kernels).
-    plans: dict = field(default_factory=dict)
-    # Work items of the tensor-core attention kernels, by query-group size G: a dict of kind ->
-    # (tiles int32 [n, 4] of (first token, tokens, request index, 0) on the device, most query rows of a tile).
-    # Kinds: "all" every entry in tiles of up to 64 rows; "big" the long portions in work items of up to 256
-    # rows; "rest" what "big" leaves out, in 64-row tiles; "one" the tiles of at most 16 rows (decoded tokens),
-    # listed apart from "rest" when a step mixes them with larger tiles.
-    attn_meta: dict = field(default_factory=dict)
+    span_hint: int = 0                          # bound on the context lengths to plan launches for (see BatchShape)
+    # What the parts planned for this step, by their plan_key().
+    plans: dict[Hashable, PlanView] = field(default_factory=dict)
 
 
 class Part:
+    # True when forward() only launches work on the step's stream and takes nothing from the host that changes
+    # between steps of the same shape (see BatchShape): then a step through it may be recorded as a CUDA graph.
+    # A part that reads device values on the host, synchronises or branches on positions leaves it False, and
+    # models that hold such a part run every step launch by launch.
+    recordable = False
+
     def param_specs(self) -> list[ParamSpec]:
         return []
 
@@ -129,6 +167,12 @@ class Part:
         self.bind(get)
         for c in self.children():
             c.bind_all(get)
+
+    def all_parts(self) -> list["Part"]:
+        out: list[Part] = [self]
+        for c in self.children():
+            out += c.all_parts()
+        return out
 
 
 class Norm(Part):
@@ -154,8 +198,13 @@ class Mixer(Part):
     def cache_request(self) -> KVPages | StateSlot | None:
         return None
 
-    def query_group_size(self) -> Optional[int]:
-        """Query heads per kv head, if this mixer wants the step to carry attention tiles for it."""
+    def plan_key(self) -> Optional[Hashable]:
+        """Not None: this mixer wants plan() called once a step; mixers with equal keys share one plan."""
+        return None
+
+    def plan(self, batch: BatchShape) -> Optional[StepPlan]:
+        """Work lists for this step's kernels, made on the host before the step runs.  forward() finds them in
+        `step.plans[self.plan_key()]` as a PlanView."""
         return None
 
     def forward(self, h: torch.Tensor, step: StepContext, cache, write_cache: bool = True) -> torch.Tensor:

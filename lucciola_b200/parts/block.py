@@ -13,6 +13,8 @@ from .base import Block, FeedForward, Mixer, Norm, Part, StepContext
 
 
 class PreNormBlock(Block):
+    recordable = True
+
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm, act_dtype: torch.dtype):
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm

@@ -12,6 +12,8 @@ from .linear import Linear
 
 class TokenEmbedding(Part):
     """residual[t, :] = table[id_t, :], unscaled (src/kernels/embedding.cu:22-38 of lucciola), as float32."""
+    recordable = True
+
 
     def __init__(self, rt: Runtime, name: str, vocab_size: int, hidden_size: int):
         self.rt, self.name, self.vocab_size, self.hidden_size = rt, name, vocab_size, hidden_size
@@ -32,6 +34,8 @@ class TokenEmbedding(Part):
 class OutputHead(Part):
     """logits = h . W^T in float32; W is its own tensor or the embedding table when tied
     (src/qwen.cc:80-84 of lucciola falls back to a second copy of the table; here the table is shared)."""
+    recordable = True
+
 
     def __init__(self, rt: Runtime, name: str, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None):
         self.rt, self.name, self.tied_to = rt, name, tied_to

@@ -15,6 +15,8 @@ from .base import ParamSpec, Part, Runtime
 
 
 class Linear(Part):
+    recordable = True
+
     def __init__(self, rt: Runtime, names: str | Sequence[str], in_features: int, out_features: int | Sequence[int],
                  init: str = "linear"):
         self.rt = rt

@@ -12,6 +12,8 @@ from .linear import Linear
 
 
 class SwiGLUFeedForward(FeedForward):
+    recordable = True
+
     def __init__(self, rt: Runtime, prefix: str, hidden_size: int, intermediate_size: int):
         self.rt = rt
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size

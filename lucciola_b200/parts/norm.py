@@ -11,6 +11,8 @@ from .base import Norm, ParamSpec, Runtime
 
 
 class RMSNorm(Norm):
+    recordable = True
+
     def __init__(self, rt: Runtime, name: str, size: int, eps: float):
         self.rt, self.name, self.size, self.eps = rt, name, size, float(eps)
         self.weight: torch.Tensor | None = None     # float32 on the device

@@ -12,6 +12,8 @@ from .base import PositionEncoding, Runtime
 
 
 class RotaryEmbedding(PositionEncoding):
+    recordable = True
+
     def __init__(self, rt: Runtime, head_dim: int, theta: float, rot_dim: int | None = None):
         self.rt = rt
         self.head_dim = head_dim

@@ -182,11 +182,16 @@ def _mix64(x: int) -> int:
     return x
 
 
+def bits_to_uniform(bits23):
+    """(b + 0.5) / 2^23 in float32 for 23-bit b (a number or an array): exact, and strictly inside (0, 1)."""
+    return (np.asarray(bits23, dtype=np.float32) + np.float32(0.5)) * np.float32(1.0 / 8388608.0)
+
+
 def hash_uniform(key: int, counter: int, i: int) -> np.float32:
     """The uniform number in (0, 1) that the temperature sampler uses for vocabulary index i."""
     x = _mix64((key + 0x9E3779B97F4A7C15 * (counter + 1)) & _M64)
     x = _mix64(x ^ ((0xD6E8FEB86659FD93 * (i + 1)) & _M64))
-    return np.float32((np.float32(x >> 40) + np.float32(0.5)) * np.float32(1.0 / 16777216.0))
+    return np.float32(bits_to_uniform(x >> 41))
 
 
 def request_key(seed: int, request_index: int) -> int:

@@ -12,8 +12,9 @@ import plain_qwen3 as plain
 
 # Largest allowed |engine - plain| as a fraction of the largest |logit| of the sequence.  float32: a
 # few units of its rounding (2^-24 = 6e-8) times the length of the sums; bfloat16: activations are
-# rounded to 8 bits (2^-9 = 2e-3 each) between all kernels of up to four layers.
-TOL = {"float32": 1e-5, "bfloat16": 3e-2}
+# rounded to 8 bits (2^-9 = 2e-3 each) between all kernels of up to four layers; the largest error these tests
+# have measured is 1e-2, and the bound is twice that.
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
 
 
 def ceil64(n: int) -> int:
@@ -54,9 +55,10 @@ def portions(reqs: dict[str, list[int]], sizes=(7, 2, 13, 3, 2, 31, 1, 16, 2, 17
     return steps
 
 
-def mixed(reqs: dict[str, list[int]], seed: int = 0, max_live: int = 4) -> list[dict]:
+def mixed(reqs: dict[str, list[int]], seed: int = 0, max_live: int = 4, decodes_first: bool = False) -> list[dict]:
     """Up to four live requests: portions of some beside single tokens of others; requests start while
-    others run, may sit out a step, and end at different times, so that their pages are used again."""
+    others run, may sit out a step, and end at different times, so that their pages are used again.
+    `decodes_first` lists a step's single tokens before its portions, as a scheduler does."""
     rng = random.Random(seed)
     queue = list(reqs)
     pos: dict[str, int] = {}
@@ -81,6 +83,8 @@ def mixed(reqs: dict[str, list[int]], seed: int = 0, max_live: int = 4) -> list[
                 end.append(rid)
         for rid in end:
             del pos[rid]
+        if decodes_first:
+            entries.sort(key=lambda e: len(e["tokens"]) > 1)
         steps.append({"step": len(steps), "entries": entries, "end": end})
     return steps
 

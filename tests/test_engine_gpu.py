@@ -165,6 +165,78 @@ def test_async_engine_streams_tokens_and_stops(tiny_models):
         eng.generate_async([1], 1)
 
 
+def test_abort_wherever_a_request_is(tiny_models):
+    """Engine.abort on a request that waits, one in the middle of its prompt and one that decodes: each gives back all
+    it holds at once, the others go on and generate what they generate alone; nothing is kept per request afterwards."""
+    from lucciola_b200 import SamplingParams
+    name = "A"
+    eng = make_engine(tiny_models[name], name, "float32", max_tokens_per_step=16, max_blocks=24, max_num_seqs=3)
+    params = SamplingParams(max_new_tokens=12, ignore_eos=True)
+    prompts = [tokens_for(name, n, salt=21) for n in (9, 70, 40, 30)]
+    reqs = [eng.add_request(p, params) for p in prompts]
+    for _ in range(3):
+        eng.step()
+    decoding, mid_prompt, waiting = reqs[0], reqs[1], reqs[3]
+    assert decoding.output and 0 < mid_prompt.num_computed < 70 and not mid_prompt.output
+    assert waiting.status.value == "waiting"
+    held = eng.runner.manager.pools[0].num_pages - eng.runner.manager.pools[0].num_free
+    assert held > 0
+    for r in (mid_prompt, waiting, decoding):
+        assert eng.abort(r.rid) is r and r.finish_reason == "abort"
+        assert eng.abort(r.rid) is None                   # a second time: nothing to do
+        eng.runner.manager.check_invariants()
+    assert eng.abort(12345) is None
+    while eng.has_unfinished():
+        eng.step()
+    cfg, w = plain.read_model(tiny_models[name])
+    assert reqs[2].output == plain.generate(cfg, w, prompts[2], 12)
+    assert len(decoding.output) < 12
+    assert eng.runner.manager.num_requests() == 0 and all(p.num_free == p.num_pages for p in eng.runner.manager.pools)
+    assert not eng.runner._table_rows and not eng._live      # nothing is kept for requests that are gone
+    st = eng.stats()
+    assert st["waiting"] == 0 and st["running"] == 0 and st["free_pages"] == 24
+
+
+def test_async_engine_abort_stats_and_a_callback_that_raises(tiny_models):
+    from lucciola_b200 import AsyncEngine
+    name = "A"
+    eng = AsyncEngine(tiny_models[name], max_blocks=32, block_size=16, dtype="float32", max_tokens_per_step=8)
+    got: dict[str, list[tuple[int, bool]]] = {k: [] for k in "abcd"}
+    done = {k: threading.Event() for k in "abcd"}
+    ids: dict[str, int] = {}
+
+    def cb(k):
+        def f(token, finished):
+            got[k].append((token, finished))
+            if k == "b" and len(got[k]) == 3:
+                eng.abort(ids["b"])                          # from the engine's own thread, while it decodes
+            if k == "d" and len(got[k]) == 2:
+                raise RuntimeError("the listener broke")
+            if finished:
+                done[k].set()
+        return f
+
+    prompts = {k: tokens_for(name, n, salt=31) for k, n in (("a", 20), ("b", 11), ("c", 90), ("d", 7))}
+    for k in "abcd":
+        ids[k] = eng.generate_async(prompts[k], 10, cb(k), ignore_eos=True)
+    eng.abort(ids["c"])                                      # at once: it still waits, or is in the middle of its prompt
+    for k in "abc":
+        assert done[k].wait(120), k
+    eng.stop()                                               # the broken listener does not surface here
+    cfg, w = plain.read_model(tiny_models[name])
+    assert [t for t, _ in got["a"]] == plain.generate(cfg, w, prompts["a"], 10) and got["a"][-1][1]
+    assert got["b"][:3] == [(t, False) for t in plain.generate(cfg, w, prompts["b"], 3)] and got["b"][-1] == (-1, True)
+    assert len(got["b"]) <= 5                                # at most one more token before the abort took effect
+    assert got["c"] == [(-1, True)]
+    assert len(got["d"]) == 2 and [rid for rid, _ in eng.callback_errors] == [ids["d"]]
+    st = eng.stats()
+    assert st["submitted"] == 4 and st["aborted"] == 3 and st["callback_errors"] == 1 and st["queued"] == 0
+    assert st["running"] == 0 and st["waiting"] == 0 and st["free_pages"] == 32
+    # the id handed out is the request's id in the engine
+    assert eng.engine._next_id == max(ids.values()) + 1
+    assert not eng.engine.runner._table_rows
+
+
 def test_command_line(tiny_models):
     name = "A"
     prompt = tokens_for(name, 9, salt=12)

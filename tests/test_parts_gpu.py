@@ -52,16 +52,17 @@ def one_request_step(rt, T, page, nkv, d, start=0, window=0, group=None):
     bt[0, :-(-L // page)] = torch.randperm(-(-L // page) + 2)[:-(-L // page)].int()
     pool = torch.full((2, P + 2, nkv, page, d), float("nan"), dtype=rt.act_dtype, device=dev)
     pos = torch.arange(start, L, dtype=torch.int32, device=dev)
-    meta = {}
-    if group and rt.fast_kernels:
-        per = 64 // group
-        tiles = [(o, min(per, T - o), 0, 0) for o in range(0, T, per)]
-        meta[group] = {"all": (torch.tensor(tiles, dtype=torch.int32, device=dev), max(t[1] for t in tiles) * group)}
+    plans = {}
+    if group and rt.fast_kernels:                 # the tile lists that the attention part plans for such a step
+        from lucciola_b200.parts.attention import plan_tiles
+        from lucciola_b200.parts.base import BatchShape, PlanView
+        made = plan_tiles(BatchShape([T], [start], T, L, L), group)
+        plans[("attention tiles", group)] = PlanView({k: torch.from_numpy(a).to(dev) for k, a in made.arrays.items()}, made.host)
     step = StepContext(num_tokens=T, num_seqs=1, positions=pos, token_seq=torch.zeros(T, dtype=torch.int32, device=dev),
                        cu_tokens=torch.tensor([0, T], dtype=torch.int32, device=dev),
                        context_lens=torch.tensor([L], dtype=torch.int32, device=dev), block_tables=[bt.to(dev)],
                        state_slots=torch.zeros(1, dtype=torch.int32, device=dev), q_lens=[T], start_positions=[start],
-                       max_q_len=T, max_context_len=L, attn_meta=meta)
+                       max_q_len=T, max_context_len=L, plans=plans)
     return step, KVCacheView(pool[0], pool[1], 0, page)
 
 
@@ -211,18 +212,55 @@ def test_order_of_layers_is_data(tiny_models, dtype):
         assert ((got2 - want).abs().max() / scale).item() < ru.TOL[dtype]
 
 
+def toy_running_mean_model(tmp_path, mixer_class):
+    """An architecture defined here around `mixer_class` (a mixer with a fixed-size state per request: a running mean
+    of what it has seen): registered, written as config.json + safetensors.  Returns (config, plain forward)."""
+    from lucciola_b200.config import register_architecture
+    from lucciola_b200.models import DecoderModel, LayerCall
+    from lucciola_b200.parts import OutputHead, PreNormBlock, RMSNorm, Runtime, SwiGLUFeedForward, TokenEmbedding
+    from lucciola_b200.weights import write_safetensors
+    from lucciola_b200.weights.random_init import RandomWeights
+
+    def build(cfg, rt):
+        H, V = cfg["hidden_size"], cfg["vocab_size"]
+        emb = TokenEmbedding(rt, "emb.weight", V, H)
+        blocks = [PreNormBlock(mixer_class(rt, f"l{i}.mix", H), SwiGLUFeedForward(rt, f"l{i}.mlp", H, cfg["inner"]),
+                               RMSNorm(rt, f"l{i}.n1.weight", H, cfg["eps"]), RMSNorm(rt, f"l{i}.n2.weight", H, cfg["eps"]),
+                               rt.act_dtype) for i in range(cfg["layers"])]
+        return DecoderModel(rt, emb, blocks, [LayerCall(i, i) for i in range(cfg["layers"])],
+                            RMSNorm(rt, "norm.weight", H, cfg["eps"]), OutputHead(rt, "head.weight", V, H, None), V, cfg["max_len"])
+
+    register_architecture("ToyRunningMeanLM", dict, build, replace=True)
+    cfg = {"architectures": ["ToyRunningMeanLM"], "hidden_size": 40, "vocab_size": 61, "inner": 72, "layers": 2,
+           "eps": 1e-5, "max_len": 64}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    specs = build(cfg, Runtime("cpu", torch.float32)).all_param_specs()
+    src = RandomWeights(specs, 3, std=0.2, norm_std=0.1)
+    weights = {n: src.get(n) for n in src.names()}
+    write_safetensors(tmp_path / "model.safetensors", weights)
+
+    def plain_forward(ids):
+        w = {k: v.double() for k, v in weights.items()}
+        x = w["emb.weight"][torch.tensor(ids)]
+        for i in range(cfg["layers"]):
+            h = plain.rms_norm(x, w[f"l{i}.n1.weight"], cfg["eps"])
+            mean = torch.cumsum(h, 0) / torch.arange(1, len(ids) + 1, dtype=torch.float64)[:, None]
+            x = x + plain.linear(mean, w[f"l{i}.mix.proj.weight"])
+            h = plain.rms_norm(x, w[f"l{i}.n2.weight"], cfg["eps"])
+            x = x + plain.feed_forward(h, {k.replace(f"l{i}.mlp.", "m."): v for k, v in w.items()}, "m")
+        return plain.linear(plain.rms_norm(x, w["norm.weight"], cfg["eps"]), w["head.weight"])
+
+    return cfg, plain_forward
+
+
 def test_toy_mixer_with_state_of_its_own(tmp_path):
     """A mixer defined here, with a fixed-size state per request (a running mean of what it has seen),
     inside an architecture defined here: registered, built from a config.json, loaded from safetensors
     and stepped by the framework's runner, whole and in portions, mixed with a second request."""
-    from lucciola_b200.config import EngineOptions, register_architecture
+    from lucciola_b200.config import EngineOptions
     from lucciola_b200.engine.load import build_runner
     from lucciola_b200.engine.step import StepEntry
-    from lucciola_b200.models import DecoderModel, LayerCall
-    from lucciola_b200.parts import (Linear, Mixer, OutputHead, PreNormBlock, RMSNorm, StateSlot, SwiGLUFeedForward,
-                                     TokenEmbedding)
-    from lucciola_b200.weights import write_safetensors
-    from lucciola_b200.weights.random_init import RandomWeights
+    from lucciola_b200.parts import Linear, Mixer, StateSlot
 
     class RunningMean(Mixer):
         """out_t = W . mean(h_0 .. h_t).  State per request: the sum so far and the count."""
@@ -248,39 +286,7 @@ def test_toy_mixer_with_state_of_its_own(tmp_path):
                 st[:-1] = sums[-1]; st[-1] = counts[-1]
             return self.proj.forward(out)
 
-    def config_from_dict(d):
-        return dict(d)
-
-    def build(cfg, rt):
-        H, V = cfg["hidden_size"], cfg["vocab_size"]
-        emb = TokenEmbedding(rt, "emb.weight", V, H)
-        blocks = [PreNormBlock(RunningMean(rt, f"l{i}.mix", H), SwiGLUFeedForward(rt, f"l{i}.mlp", H, cfg["inner"]),
-                               RMSNorm(rt, f"l{i}.n1.weight", H, cfg["eps"]), RMSNorm(rt, f"l{i}.n2.weight", H, cfg["eps"]),
-                               rt.act_dtype) for i in range(cfg["layers"])]
-        return DecoderModel(rt, emb, blocks, [LayerCall(i, i) for i in range(cfg["layers"])],
-                            RMSNorm(rt, "norm.weight", H, cfg["eps"]), OutputHead(rt, "head.weight", V, H, None), V, cfg["max_len"])
-
-    register_architecture("ToyRunningMeanLM", config_from_dict, build, replace=True)
-    cfg = {"architectures": ["ToyRunningMeanLM"], "hidden_size": 40, "vocab_size": 61, "inner": 72, "layers": 2,
-           "eps": 1e-5, "max_len": 64}
-    (tmp_path / "config.json").write_text(json.dumps(cfg))
-    from lucciola_b200.parts import Runtime
-    specs = build(cfg, Runtime("cpu", torch.float32)).all_param_specs()
-    src = RandomWeights(specs, 3, std=0.2, norm_std=0.1)
-    weights = {n: src.get(n) for n in src.names()}
-    write_safetensors(tmp_path / "model.safetensors", weights)
-
-    def plain_forward(ids):
-        w = {k: v.double() for k, v in weights.items()}
-        x = w["emb.weight"][torch.tensor(ids)]
-        for i in range(cfg["layers"]):
-            h = plain.rms_norm(x, w[f"l{i}.n1.weight"], cfg["eps"])
-            mean = torch.cumsum(h, 0) / torch.arange(1, len(ids) + 1, dtype=torch.float64)[:, None]
-            x = x + plain.linear(mean, w[f"l{i}.mix.proj.weight"])
-            h = plain.rms_norm(x, w[f"l{i}.n2.weight"], cfg["eps"])
-            x = x + plain.feed_forward(h, {k.replace(f"l{i}.mlp.", "m."): v for k, v in w.items()}, "m")
-        return plain.linear(plain.rms_norm(x, w["norm.weight"], cfg["eps"]), w["head.weight"])
-
+    cfg, plain_forward = toy_running_mean_model(tmp_path, RunningMean)
     runner = build_runner(tmp_path, EngineOptions(dtype="float32", block_size=16, max_blocks=4, max_num_seqs=3, use_cuda_graph=False))
     assert runner.groups == [] and list(runner.cache.states) == [0, 1]          # no pages, two state caches
     a, b = [5, 9, 60, 0, 33, 7, 7, 18, 2, 41, 3], [11, 12, 13, 14, 15, 16]
@@ -295,6 +301,83 @@ def test_toy_mixer_with_state_of_its_own(tmp_path):
     got_a = torch.cat([g1[:4], g2[5:], g3]); got_b = torch.cat([g1[4:], g2[:5]])
     assert ((got_a - wa).abs().max() / wa.abs().max()) < 1e-5 and ((got_b - wb).abs().max() / wb.abs().max()) < 1e-5
     runner.finish("a"); runner.finish("b")
+    runner.manager.check_invariants()
+    # this mixer reads a device value on the host (its slot), so it does not call itself recordable, and a bfloat16
+    # runner with recordings switched on records nothing for a model that holds it
+    bf = build_runner(tmp_path, EngineOptions(dtype="bfloat16", block_size=16, max_blocks=4, max_num_seqs=3, use_cuda_graph=True, graph_after=1))
+    assert not bf._can_record
+    got = bf.step([StepEntry("a", a, list(range(len(a))))]).double().cpu()
+    assert ((got - wa).abs().max() / wa.abs().max()) < 3e-2 and not bf._graphs
+
+
+def test_toy_mixer_with_state_is_recorded_and_replayed(tmp_path):
+    """The same running mean written so that its forward() only launches work on the step's stream (the slot is used
+    as a device index): it says so (`recordable`), and the framework records its steps as CUDA graphs and replays them,
+    the clearing of a new request's slot included; single tokens of three requests replay the recording of four, whose
+    fourth entry reads and writes the spare state row."""
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.load import build_runner
+    from lucciola_b200.engine.step import StepEntry
+    from lucciola_b200.parts import Linear, Mixer, StateSlot
+
+    class RunningMean(Mixer):
+        recordable = True
+
+        def __init__(self, rt, prefix, hidden):
+            self.rt, self.hidden = rt, hidden
+            self.proj = Linear(rt, f"{prefix}.proj.weight", hidden, hidden)
+
+        def children(self):
+            return [self.proj]
+
+        def cache_request(self):
+            return StateSlot((self.hidden + 1,), torch.float32)
+
+        def forward(self, h, step, cache, write_cache=True):
+            out = torch.empty_like(h)
+            slots = step.state_slots.long()
+            t = 0
+            for i, n in enumerate(step.q_lens):                # the lengths are part of a recording's shape
+                st = cache.state.index_select(0, slots[i:i + 1])[0]
+                sums = st[:-1] + torch.cumsum(h[t:t + n].float(), dim=0)
+                counts = st[-1] + torch.arange(1, n + 1, device=h.device, dtype=torch.float32)
+                out[t:t + n] = (sums / counts[:, None]).to(h.dtype)
+                cache.state.index_copy_(0, slots[i:i + 1], torch.cat([sums[-1], counts[-1:]])[None])
+                t += n
+            return self.proj.forward(out)
+
+    cfg, plain_forward = toy_running_mean_model(tmp_path, RunningMean)
+    runner = build_runner(tmp_path, EngineOptions(dtype="bfloat16", block_size=16, max_blocks=4, max_num_seqs=4,
+                                                  use_cuda_graph=True, graph_after=1))
+    assert runner._can_record
+    seqs = {k: [(7 * i * i + 5 * i + ord(k)) % 61 for i in range(20)] for k in "abcd"}
+    want = {k: plain_forward(v) for k, v in seqs.items()}
+    got = {k: [] for k in seqs}
+
+    def run(entries):
+        out = runner.step([StepEntry(k, seqs[k][a:b], list(range(b - a))) for k, a, b in entries]).double().cpu()
+        for k, a, b in entries:
+            got[k].append(out[:b - a]); out = out[b - a:]
+
+    run([("a", 0, 11)])                                       # recorded
+    run([("b", 0, 11)])                                       # replayed: b's slot is cleared inside the recording
+    run([("c", 0, 11)])
+    assert runner.graph_replays == 2
+    for t in range(11, 17):                                   # three single tokens: the recording of four
+        run([("a", t, t + 1), ("b", t, t + 1), ("c", t, t + 1)])
+    assert (4, (), 256, ()) in runner._graphs
+    runner.finish("c")
+    got["c"] = []
+    run([("a", 17, 18), ("b", 17, 18), ("c", 0, 5)])          # single tokens beside a portion of a request that starts anew
+    run([("a", 18, 19), ("b", 18, 19), ("d", 0, 5)])          # the same shape replayed, d's slot cleared
+    run([("a", 19, 20), ("b", 19, 20), ("c", 5, 10)])
+    assert (2, (5,), 256, ("all",)) in runner._graphs and runner.graph_replays >= 2 + 5 + 2
+    for k in seqs:
+        g = torch.cat(got[k])
+        assert ((g - want[k][:g.shape[0]]).abs().max() / want[k].abs().max()) < 3e-2, k
+    assert torch.cat(got["a"]).shape[0] == 20 and torch.cat(got["c"]).shape[0] == 10
+    for k in seqs:
+        runner.finish(k)
     runner.manager.check_invariants()
 
 

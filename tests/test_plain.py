@@ -95,6 +95,24 @@ def test_greedy_tie_and_sampler_hash():
     assert abs(u.mean() - 0.5) < 0.03 and abs((u < 0.25).mean() - 0.25) < 0.03
 
 
+def test_every_hash_value_maps_strictly_inside_the_unit_interval():
+    """All 2^23 values of the hash's top bits: none maps to 0 or to 1 in float32 (u = 1 would score +infinity in
+    -log(-log u) and win whatever the logits are), the Gumbel score of each is finite, and the library's mapping of
+    the two extreme inputs is the plain one's."""
+    from lucciola_b200.csrc import library
+    import ctypes
+    u = plain.bits_to_uniform(np.arange(1 << 23, dtype=np.uint32))
+    assert u.dtype == np.float32 and u.min() > 0.0 and u.max() < 1.0
+    assert u[0] == np.float32(2.0 ** -24) and u[-1] == np.float32(1.0 - 2.0 ** -24)
+    assert (np.diff(u) > 0).all()                                       # exact: no two inputs share a value
+    score = -np.log(-np.log(u))
+    assert np.isfinite(score).all()
+    f = library().lb_bits_to_uniform
+    f.argtypes, f.restype = [ctypes.c_uint], ctypes.c_float
+    for b in (0, 1, (1 << 22), (1 << 23) - 2, (1 << 23) - 1):
+        assert f(b) == float(u[b])
+
+
 def test_temperature_sampling_follows_the_softmax():
     logits = np.array([2.0, 1.0, 0.0, -1.0], dtype=np.float32)
     T = 0.8

@@ -16,13 +16,16 @@ pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
 
 
-def make_runner(folder, name, dtype, num_pages, **kw):
+def make_runner(folder, name, dtype, num_pages, graphs=False, **kw):
+    """`graphs`: every step whose shape allows it is recorded as a CUDA graph the first time its shape comes and
+    replayed from then on."""
     from lucciola_b200.config import EngineOptions
     from lucciola_b200.engine.load import build_runner
 
     page = TINY[name][4]
     return build_runner(folder, EngineOptions(dtype=dtype, block_size=page, max_blocks=num_pages, max_num_seqs=8,
-                                              use_cuda_graph=False, **kw), num_pages=num_pages)
+                                              use_cuda_graph=graphs, graph_after=1, max_shape_graphs=1000, **kw),
+                        num_pages=num_pages)
 
 
 def requests_for(name):
@@ -63,6 +66,36 @@ def test_mixed_batches_with_reused_pages(tiny_models, name, dtype, seed):
     ru.compare(got, tiny_models[name], reqs, dtype)
     assert max(len(s["entries"]) for s in steps) >= 3
     assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"]) and any(len(e["tokens"]) > 1 for s in steps for e in s["entries"])
+
+
+@pytest.mark.parametrize("name", list(TINY))
+@pytest.mark.parametrize("cut", ["whole", "tail_decoded", "portions", "mixed", "mixed_decodes_first"])
+def test_every_cutting_through_recorded_graphs(tiny_models, name, cut):
+    """The same four families with recordings on (bfloat16; the 32-bit path records nothing): the trace runs twice
+    through one runner.  The first pass records a CUDA graph for every shape of step it meets, the second replays
+    them with other pages under the same requests; both passes are compared with the plain implementation."""
+    top = TINY[name][0]["max_position_embeddings"]
+    if cut.startswith("mixed"):
+        lengths = [n for n in (70, 9, 120, 33, 101, 2, 64, 47, 90) if n <= top]
+        reqs = {f"m{i}": tokens_for(name, n, salt=5) for i, n in enumerate(lengths)}
+        steps = ru.mixed(reqs, seed=4, decodes_first=cut.endswith("first"))
+    else:
+        reqs = requests_for(name)
+        steps = getattr(ru, cut)(reqs)
+    page = TINY[name][4]
+    runner = make_runner(tiny_models[name], name, "bfloat16", ru.max_live_tokens(steps) // page, graphs=True)
+    assert runner._can_record
+    first = ru.replay(runner, steps, poison=True)
+    ru.compare(first, tiny_models[name], reqs, "bfloat16")
+    recorded, replays = len(runner._graphs), runner.graph_replays
+    assert recorded > 0
+    second = ru.replay(runner, steps, poison=True)
+    ru.compare(second, tiny_models[name], reqs, "bfloat16")
+    assert len(runner._graphs) == recorded, "the second pass met a shape the first had not"
+    assert runner.graph_replays - replays == sum(1 for s in steps if s["entries"]), "a step of the second pass was not a replay"
+    if cut == "mixed_decodes_first":
+        assert any(k[0] and k[1] for k in runner._graphs), "no step of single tokens beside a portion"
+    assert all(p.num_free == p.num_pages for p in runner.manager.pools)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -108,15 +141,16 @@ def test_first_tokens_of_a_sequence(tiny_models, name, dtype):
             ru.compare(ru.replay(runner, steps), tiny_models[name], {"f": ids}, dtype)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_trace_run_program(tiny_models, tmp_path, dtype):
-    """The program itself, as a user runs it: steps on standard input, <step>.f32 files out."""
+@pytest.mark.parametrize("dtype,graphs", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+def test_trace_run_program(tiny_models, tmp_path, dtype, graphs):
+    """The program itself, as a user runs it: steps on standard input, <step>.f32 files out; also with --cuda-graph,
+    which records every shape of step at its first coming."""
     name = "A"
     reqs = {"a": tokens_for(name, 70), "b": tokens_for(name, 33, salt=1), "c": tokens_for(name, 90, salt=2)}
     steps = ru.mixed(reqs, seed=5, max_live=2)
     out = tmp_path / "out"
     p = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(tiny_models[name]), "--dtype", dtype,
-                        "--out", str(out), "--max-tokens", str(ru.max_live_tokens(steps))],
+                        "--out", str(out), "--max-tokens", str(ru.max_live_tokens(steps))] + (["--cuda-graph"] if graphs else []),
                        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
     assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
@@ -163,7 +197,7 @@ def test_short_portions_replayed_from_recordings(tiny_models, name):
 
     page = TINY[name][4]
     runner = build_runner(tiny_models[name], EngineOptions(dtype="bfloat16", block_size=page, max_blocks=64, max_num_seqs=8,
-                                                           use_cuda_graph=True), num_pages=64)
+                                                           use_cuda_graph=True, graph_after=2), num_pages=64)
     reqs = {f"s{i}": tokens_for(name, 17, salt=20 + i) for i in range(4)}
     steps = ru.whole(reqs)
     # longer prompts in portions of 60 and 9 tokens (and a rest of 0, 1 or 2): the same sizes at other positions
@@ -182,6 +216,6 @@ def test_short_portions_replayed_from_recordings(tiny_models, name):
         steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": ids[30:], "want": list(range(15))}], "end": [rid]})
     got = ru.replay(runner, steps)
     ru.compare(got, tiny_models[name], {**reqs, **longer, **quiet}, "bfloat16")
-    short = [k for k in runner._graphs if k[0] < 0]
-    assert (-30, 256, "none") in short and (-15, 256, "all") in short, short
-    assert (-17, 256, "all") in short and (-9, 256, "all") in short and (-60, 256, "last") in short, short
+    short = {(k[1], k[3]) for k in runner._graphs if not k[0] and k[2] == 256}
+    assert ((30,), ("none",)) in short and ((15,), ("all",)) in short, short
+    assert ((17,), ("all",)) in short and ((9,), ("all",)) in short and ((60,), ("last",)) in short, short

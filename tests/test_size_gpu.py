@@ -8,7 +8,10 @@ ranges are combined inside a cluster, CUDA graphs."""
 import pytest
 import torch
 
+import replay_util as ru
+
 pytestmark = pytest.mark.gpu
+BF16_TOL = ru.TOL["bfloat16"]
 
 CFG = {
     "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
@@ -61,7 +64,7 @@ def test_bfloat16_engine_against_float32_engine_at_real_layer_sizes(runners):
     for cuts, tail in (([700], 0), ([300, 17, 2, 198, 150], 33), ([640], 60)):
         got = logits_of(runners["bfloat16"], ids, cuts, tail)
         err = ((got - ref).abs().max() / scale).item()
-        assert torch.isfinite(got).all() and err < 3e-2, (cuts, tail, err)
+        assert torch.isfinite(got).all() and err < BF16_TOL, (cuts, tail, err)
         agree = (got.argmax(-1) == ref.argmax(-1)).float().mean().item()
         assert agree > 0.9, (cuts, tail, agree)
     assert len(runners["bfloat16"]._graphs) > 0
@@ -71,22 +74,22 @@ def test_short_prompts_replayed_from_recordings_at_real_layer_sizes(runners):
     """Three prompts of 36 tokens one after the other: the second is recorded as a CUDA graph (q|k|v product, rotation,
     tensor-memory attention and all), the third replays it with other tokens and other pages."""
     g = torch.Generator().manual_seed(5)
-    before = len([k for k in runners["bfloat16"]._graphs if k[0] < 0])
+    before = len([k for k in runners["bfloat16"]._graphs if k[1]])
     for _ in range(3):
         ids = torch.randint(0, CFG["vocab_size"], (36,), generator=g).tolist()
         ref = logits_of(runners["float32"], ids, [36])
         got = logits_of(runners["bfloat16"], ids, [36])
         err = ((got - ref).abs().max() / ref.abs().max()).item()
-        assert torch.isfinite(got).all() and err < 3e-2, err
-    assert len([k for k in runners["bfloat16"]._graphs if k[0] < 0]) == before + 1
+        assert torch.isfinite(got).all() and err < BF16_TOL, err
+    assert len([k for k in runners["bfloat16"]._graphs if k[1]]) == before + 1
     # 300 tokens: the many-token product kernel and several attention work items in a recording
     for _ in range(3):
         ids = torch.randint(0, CFG["vocab_size"], (300,), generator=g).tolist()
         ref = logits_of(runners["float32"], ids, [300])
         got = logits_of(runners["bfloat16"], ids, [300])
         err = ((got - ref).abs().max() / ref.abs().max()).item()
-        assert torch.isfinite(got).all() and err < 3e-2, err
-    assert (-300, 512, "all") in runners["bfloat16"]._graphs
+        assert torch.isfinite(got).all() and err < BF16_TOL, err
+    assert (0, (300,), 512, ("all",)) in runners["bfloat16"]._graphs
 
 
 def test_mixed_batch_at_real_layer_sizes(runners):
@@ -118,7 +121,119 @@ def test_mixed_batch_at_real_layer_sizes(runners):
         outs[dtype] = got
     for key, ref in outs["float32"].items():
         err = ((outs["bfloat16"][key] - ref).abs().max() / ref.abs().max()).item()
-        assert err < 3e-2, (key, err)
+        assert err < BF16_TOL, (key, err)
+
+
+def test_float32_engine_against_the_plain_implementation_at_real_layer_sizes(runners):
+    """The 32-bit kernels at hidden 4096, heads of 128 in groups of four: whole and in two portions against the plain
+    implementation (float32 on the CPU, the same weights drawn by name from the same seed)."""
+    import plain_qwen3 as plain
+    from lucciola_b200.weights.random_init import RandomWeights
+    r = runners["float32"]
+    src = RandomWeights(r.model.all_param_specs(), 3, 0.02, 0.05, torch.bfloat16, "cuda:0")   # as the fixture drew them
+    weights = {n: src.get(n).float().cpu() for n in src.names()}
+    assert torch.equal(weights["model.layers.1.self_attn.o_proj.weight"], r.model.blocks[1].mixer.o.weight.cpu())
+    g = torch.Generator().manual_seed(7)
+    ids = torch.randint(0, CFG["vocab_size"], (200,), generator=g).tolist()
+    want = plain.forward(CFG, weights, ids, dtype=torch.float32)
+    scale = want.abs().max().item()
+    for cuts in ([200], [131, 69]):
+        got = logits_of(r, ids, cuts)
+        err = ((got - want).abs().max() / scale).item()
+        assert err < 2e-5, (cuts, err)              # two float32 computations of sums of 12288 terms
+
+
+def test_decode_batches_that_are_no_bucket_through_recordings(runners):
+    """3 and 5 requests at different context lengths decode 20 steps: the recordings are those of 4 and 8 requests,
+    the missing ones are entries without pages (at head size 128 these pass the q|k|v product's epilogue and the
+    decode attention kernel with a page id of -1); against the float32 engine, step by step."""
+    from lucciola_b200.engine.step import StepEntry
+    g = torch.Generator().manual_seed(11)
+    for count, bucket in ((3, 4), (5, 8)):
+        lens = [37, 300, 129, 1000, 16][:count]
+        prompts = [torch.randint(0, CFG["vocab_size"], (n,), generator=g).tolist() for n in lens]
+        feed = torch.randint(0, CFG["vocab_size"], (20, count), generator=g).tolist()
+        outs = {}
+        for dtype in ("float32", "bfloat16"):
+            r = runners[dtype]
+            for i, p in enumerate(prompts):
+                r.step([StepEntry(("n", i), p, [])])
+            replays = r.graph_replays
+            rows = [r.step([StepEntry(("n", i), [feed[t][i]], [0]) for i in range(count)]).float().cpu().clone() for t in range(20)]
+            outs[dtype] = torch.stack(rows)
+            for i in range(count):
+                r.finish(("n", i))
+            if dtype == "bfloat16":
+                assert any(k[0] == bucket and not k[1] for k in r._graphs) and r.graph_replays - replays >= 18
+        ref, got = outs["float32"], outs["bfloat16"]
+        err = ((got - ref).abs().amax(dim=(1, 2)) / ref.abs().amax(dim=(1, 2))).max().item()
+        assert torch.isfinite(got).all() and err < BF16_TOL, (count, err)
+
+
+def test_generation_under_page_pressure_at_real_layer_sizes(runners):
+    """Six prompts through Engine.generate with so few pages that requests are preempted and recomputed: every
+    request finishes; the bfloat16 engine's tokens are the float32 engine's choice for the same prefix or within a
+    near-tie of it (checked with the float32 engine's logits of the bfloat16 engine's own sequence)."""
+    from lucciola_b200 import Engine, SamplingParams
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.step import ModelRunner, StepEntry
+    g = torch.Generator().manual_seed(13)
+    prompts = [torch.randint(0, CFG["vocab_size"], (n,), generator=g).tolist() for n in (90, 40, 130, 75, 20, 110)]
+    params = SamplingParams(max_new_tokens=24, ignore_eos=True)
+    base = runners["bfloat16"]
+    opts = EngineOptions(dtype="bfloat16", block_size=16, max_blocks=30, max_num_seqs=6, max_model_len=4096,
+                         max_tokens_per_step=96)
+    tight = Engine(runner=ModelRunner(base.model, base.rt, opts, 30))          # 480 tokens of cache for 465 + 144
+    outs = tight.generate(prompts, params)
+    assert all(len(o) == 24 for o in outs) and tight.stats()["preemptions"] > 0
+    tight.runner.manager.check_invariants()
+    assert all(p.num_free == p.num_pages for p in tight.runner.manager.pools) and not tight.runner._table_rows
+    ref = runners["float32"]
+    for p, o in zip(prompts, outs):
+        logits = ref.step([StepEntry("chk", p + o[:-1], list(range(len(p) - 1, len(p) + len(o) - 1)))]).float().cpu()
+        ref.finish("chk")
+        gap = logits.max(dim=-1).values - logits[torch.arange(len(o)), torch.tensor(o)]
+        # each of two logits may be off by the tolerance of the logit comparisons
+        assert gap.max().item() <= 2 * BF16_TOL * logits.abs().max().item(), (gap.max().item(), logits.abs().max().item())
+
+
+def test_a_recording_survives_growth_of_the_attention_workspace(runners):
+    """A recorded step whose attention splits its keys through the workspace (a portion of 8 tokens: 32 query rows a
+    tile, too many for the in-cluster combine) keeps the workspace's address.  A later step that needs a larger
+    workspace must not take that memory away: the old recording is replayed afterwards and must still be right."""
+    from lucciola_b200 import ops
+    from lucciola_b200.engine.step import StepEntry
+    g = torch.Generator().manual_seed(17)
+    ids = torch.randint(0, CFG["vocab_size"], (3, 3100), generator=g).tolist()
+    ref_r, r = runners["float32"], runners["bfloat16"]
+
+    def portion_of_8(runner, rid, seq, at):
+        runner.step([StepEntry(rid, seq[:at], [])])
+        out = runner.step([StepEntry(rid, seq[at:at + 8], list(range(8)))]).float().cpu().clone()
+        runner.finish(rid)
+        return out
+
+    want = [portion_of_8(ref_r, "w", ids[i], 600) for i in range(3)]
+    got0 = portion_of_8(r, "w", ids[0], 600)                  # seen once
+    got1 = portion_of_8(r, "w", ids[1], 600)                  # seen twice: recorded
+    shape = (0, (8,), 1024, ("all",))
+    assert shape in r._graphs
+    before = ops._attn_ws[r.device.index].numel()
+    # three portions of 8 tokens at 3000 tokens of context each, in one step: many more partial results
+    for i in range(3):
+        r.step([StepEntry(("big", i), ids[i][:3000], [])])
+    r.step([StepEntry(("big", i), ids[i][3000:3008], [7]) for i in range(3)])
+    for i in range(3):
+        r.finish(("big", i))
+    assert ops._attn_ws[r.device.index].numel() > before and ops._attn_ws_retired, "the step did not make the workspace grow"
+    r.step([StepEntry("w", ids[2][:600], [])])
+    replays = r.graph_replays
+    got2 = r.step([StepEntry("w", ids[2][600:608], list(range(8)))]).float().cpu().clone()     # the old recording, replayed
+    r.finish("w")
+    assert r.graph_replays == replays + 1
+    for got, ref in zip((got0, got1, got2), want):
+        err = ((got - ref).abs().max() / ref.abs().max()).item()
+        assert torch.isfinite(got).all() and err < BF16_TOL, err
 
 
 def test_sliding_window_at_the_real_head_size():
@@ -149,6 +264,6 @@ def test_sliding_window_at_the_real_head_size():
         r.finish("o")
         r.manager.check_invariants()
         err = ((got - ref).abs().max() / scale).item()
-        assert torch.isfinite(got).all() and err < 3e-2, (cuts, tail, err)
+        assert torch.isfinite(got).all() and err < BF16_TOL, (cuts, tail, err)
     sliding = [gi for gi, grp in enumerate(r.groups) if grp.window > 0]
     assert sliding and r.manager.pools[sliding[0]].high_water < 2 * (600 // 16)       # the window's group never held both requests whole
