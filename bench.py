@@ -302,8 +302,10 @@ def main() -> int:
     ap.add_argument("--workload-layers", type=int, default=0,
                     help="fewer layers for the 14B and 32B workloads than their configurations have (reported with them)")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps from CUDA graphs")
-    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
-                    help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off)")
+    ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], default=None,
+                    help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off); "
+                         "mixed: --batch decoding requests at --context and one portion of --portion tokens of a new prompt")
+    ap.add_argument("--portion", type=int, default=512, help="tokens of the portion of a --profile mixed step")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -338,7 +340,7 @@ def main() -> int:
     pages = max_b * (-(-ctx // page)) + 64
     options = EngineOptions(dtype="bfloat16", block_size=page, max_blocks=pages, max_num_seqs=max(64, max_b),
                             max_tokens_per_step=max(args.prefill_tokens, 2048) + max_b, max_model_len=max(ctx, args.prefill_tokens),
-                            use_cuda_graph=not args.no_graph)
+                            use_cuda_graph=not (args.no_graph or args.profile))
     t_build = time.time()
     engine = Engine.from_random(cfg, seed=0, options=options)
     runner = engine.runner
@@ -352,7 +354,6 @@ def main() -> int:
         return torch.cuda.Event(enable_timing=True)
 
     if args.profile:
-        options.use_cuda_graph = False
         B, T = args.batch, args.prefill_tokens
         if args.profile == "prefill":
             entries = lambda i: [StepEntry(("p", i), rng.integers(0, V, size=T).tolist(), [T - 1])]
@@ -364,9 +365,12 @@ def main() -> int:
                     runner.step([StepEntry(("d", j), rng.integers(0, V, size=n).tolist(), [])])
                     left -= n
             entries = lambda i: [StepEntry(("d", j), [int(rng.integers(0, V))], [0]) for j in range(B)]
+            if args.profile == "mixed":
+                decodes = entries
+                entries = lambda i: decodes(i) + [StepEntry(("p", i), rng.integers(0, V, size=args.portion).tolist(), [])]
         for i in range(3):
             runner.step(entries(i))
-            if args.profile == "prefill":
+            if args.profile != "decode":
                 runner.finish(("p", i))
         torch.cuda.synchronize()
         torch.cuda.profiler.start()

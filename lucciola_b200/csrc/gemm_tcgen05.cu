@@ -72,15 +72,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false when the limit passed or another role of the CTA gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+// Bounded wait.  Returns false when the limit (in clock cycles) passed or another role of the CTA gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          unsigned long long limit = WAIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (unsigned it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0u) {
       if (*abort_flag) return false;
-      if ((unsigned long long)(clock64() - t0) > WAIT_CYCLES) {
+      if ((unsigned long long)(clock64() - t0) > limit) {
         *abort_flag = code;
         atomicCAS(&g_device_error, 0, code);
         return false;
@@ -207,8 +208,54 @@ __device__ __forceinline__ float cluster_sum_f32(uint32_t addr, int splits) {
   return acc;
 }
 
+// What the epilogue of the o and down products does instead of storing their tile: the residual add and the first
+// half of the RMSNorm that follows (lucciola: add_kernel, a copy and rmsnorm_forward_kernel, src/qwen.cc:731-759).
+// residual += y; out = residual * norm_w, rounded, WITHOUT the row's factor rsqrt(mean(residual^2) + eps); and the sum
+// of squares of the new residual over this tile's features goes to sumsq[row][tile].  The product that reads `out`
+// multiplies its 32-bit sums by the row's factor (RowScale): a row's factor commutes with a linear map.
+struct AddNormEpilogue {
+  int on;
+  int tiles;                  // 128-feature tiles of a row (columns of sumsq)
+  float* residual;            // [M, N] float32
+  const float* norm_w;        // [N]
+  bf16* out;                  // [M, N]
+  float* sumsq;               // [M, tiles]
+};
+
+// The input rows of this product lack their norm's factor: row m of the result is multiplied by
+// rsqrt(sum_t sumsq[m][t] * inv_width + eps) (the tiles are added in their order).  Mirrors LbRowScale in ops.py.
+struct RowScale {
+  int on;
+  int tiles;
+  const float* sumsq;         // [M, tiles]
+  float inv_width, eps;
+};
+
+__device__ __forceinline__ float row_factor(const RowScale& rs, int m) {
+  const float* src = rs.sumsq + (size_t)m * rs.tiles;
+  float total = 0.f;
+  for (int t0 = 0; t0 < rs.tiles; t0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = t0 + u < rs.tiles ? __ldcg(src + t0 + u) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) total += v[u];
+  }
+  return rsqrtf(total * rs.inv_width + rs.eps);
+}
+
+// The same by a whole warp: lane l adds the tiles l, l + 32, ..., then the lanes add up in a fixed pattern.
+__device__ __forceinline__ float row_factor_warp(const RowScale& rs, int m, int lane) {
+  const float* src = rs.sumsq + (size_t)m * rs.tiles;
+  float part = 0.f;
+  for (int t = lane; t < rs.tiles; t += 32) part += __ldcg(src + t);
+  return rsqrtf(warp_sum(part) * rs.inv_width + rs.eps);
+}
+
 struct GemmParams {
   HeadEpilogue he = {};   // off unless a caller fills it in
+  AddNormEpilogue an = {};
+  RowScale rs = {};
   void* y;              // [M, N] output, row stride ldy
   float* workspace;     // [splits, M, N] partials (split-K only)
   int* counters;        // one per output tile, zero between launches (split-K only)
@@ -219,6 +266,8 @@ struct GemmParams {
                         // their partials through distributed shared memory (no workspace, no counters)
   int swiglu;           // 1: the weight rows alternate in blocks of 64 between "gate" and "up" rows of the same 64
                         // features; the output has N/2 columns and holds silu(gate) * up (computed in 32-bit)
+  unsigned long long wait_cycles = WAIT_CYCLES;   // after this many clock cycles a wait on a barrier gives up
+  int skip_loads = 0;   // tests of the give-up path only: the producer requests nothing, so the first wait runs out
 };
 
 // silu(g) * u; the quotient by the fast division (2 ulp), the result is rounded to bfloat16 or summed with like terms afterwards
@@ -272,7 +321,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     // This thread is also the producer.  The weights do not depend on the kernel before this one:
     // the first ring of weight tiles is requested at once, before the rest of the CTA is even set up.
-    for (int i = 0; i < early; ++i) {
+    for (int i = 0; i < early && !p.skip_loads; ++i) {
       mbar_expect_tx(full_bar(i), L::STAGE_BYTES);
       tma_load_2d(smem_base + i * L::STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, full_bar(i));
     }
@@ -285,10 +334,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_acc = *tmem_slot;
+  float an_w = 0.f, an_before[4] = {0.f, 0.f, 0.f, 0.f};       // of the epilogue that adds to the residual stream
+  float he_w = 1.f, he_freq = 0.f;                             // of the epilogue that finishes heads
 
   if (warp == 0) {
     // ---- producer --------------------------------------------------------------------------
-    if (lane == 0) {
+    if (lane == 0 && !p.skip_loads) {
       int issued = 0;
       // The token tiles follow the early weight tiles when the kernel before this one has completed.
       pdl_wait();
@@ -298,7 +349,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       for (int i = early; i < num_kb; ++i) {
         const int s = i % STAGES;
         const uint32_t parity = ((i / STAGES) & 1) ^ 1;          // the stage's earlier use has been consumed
-        if (!mbar_wait(empty_bar(s), parity, abort_flag, ERR_EMPTY_WAIT)) break;
+        if (!mbar_wait(empty_bar(s), parity, abort_flag, ERR_EMPTY_WAIT, p.wait_cycles)) break;
         mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
         const uint32_t dst = smem_base + s * L::STAGE_BYTES;
         const int k = (kb_begin + i) * BK;
@@ -322,7 +373,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       bool ok = true;
       for (int i = 0; i < num_kb && ok; ++i) {
         const int s = i % STAGES;
-        ok = mbar_wait(full_bar(s), (i / STAGES) & 1, abort_flag, ERR_FULL_WAIT);
+        ok = mbar_wait(full_bar(s), (i / STAGES) & 1, abort_flag, ERR_FULL_WAIT, p.wait_cycles);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
@@ -340,11 +391,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---- epilogue: warps 2..5, lanes (warp % 4) * 32 .. + 31 of the accumulator ----------------
     const int quarter = warp & 3;
     const int n = n0 + quarter * 32 + lane;
-    mbar_wait(accum_bar, 0, abort_flag, ERR_ACCUM_WAIT);
+    // A norm weight is read once a step: a miss all the way to memory.  Asked for here, it has arrived when the
+    // reduction at the end wants it.
+    if (p.an.on) an_w = n < p.N ? p.an.norm_w[n] : 0.f;
+    if (p.he.on) {
+      const int head = n0 / BM, nl = quarter * 32 + lane;
+      const float* w = head < p.he.num_q_heads ? p.he.q_norm_w : (head < p.he.num_q_heads + p.he.num_kv_heads ? p.he.k_norm_w : nullptr);
+      const bool rotated = head < p.he.num_q_heads + p.he.num_kv_heads;
+      he_w = w ? w[nl] : 1.f;
+      he_freq = (rotated && p.he.inv_freq) ? p.he.inv_freq[nl & 63] : 0.f;
+    }
+    // The accumulator is ready when the whole main loop is through: twice the limit of one of its waits, so that a
+    // wait of the main loop that runs out is what gets reported.
+    mbar_wait(accum_bar, 0, abort_flag, ERR_ACCUM_WAIT, 2 * p.wait_cycles);
     // All four epilogue warps take the same path: agree on the outcome before any of them goes on.
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const bool ok = (*abort_flag == 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && p.an.on && p.cluster > 0) {
+      // The residual values of the first tokens this CTA finishes, on their way while the tile goes to shared memory.
+      pdl_wait();
+      const int per = BT / p.cluster, j0 = split * per, j1 = min((split + 1) * per, p.M - m0);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        an_before[u] = (j0 + u < j1 && n < p.N) ? p.an.residual[(size_t)(m0 + j0 + u) * p.N + n] : 0.f;
+    }
     if (ok) {
       const uint32_t taddr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
       const bool direct = splits == 1;
@@ -374,12 +445,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
       if (direct && p.swiglu) {
         // gate and up of a feature sit 64 lanes apart: pair them through shared memory
+        float* row_f = part_smem + BT * BM;                        // the rows' norm factors, when the input lacks them
+        if (p.rs.on) {
+          // Eight threads a token, each adds every eighth tile (its loads are in flight together), then the eight add up
+          // in a fixed pattern: one round trip to the L2 for 16 tokens.  (Waiting for the kernel before this one any
+          // earlier, while the main loop runs, made the step slower, not faster.)
+          pdl_wait();
+          const int t = threadIdx.x - 64, sub = t & 7;
+          for (int jb = 0; jb < BT && m0 + jb < p.M; jb += 16) {
+            const int j = jb + (t >> 3);
+            float part = 0.f;
+            if (m0 + j < p.M) {
+              const float* src = p.rs.sumsq + (size_t)(m0 + j) * p.rs.tiles;
+              for (int i = sub; i < p.rs.tiles; i += 8) part += __ldcg(src + i);
+            }
+            part += __shfl_xor_sync(0xffffffffu, part, 4);
+            part += __shfl_xor_sync(0xffffffffu, part, 2);
+            part += __shfl_xor_sync(0xffffffffu, part, 1);
+            if (sub == 0 && j < BT) row_f[j] = m0 + j < p.M ? rsqrtf(part * p.rs.inv_width + p.rs.eps) : 0.f;
+          }
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int t = threadIdx.x - 64, f = t & 63;
         const int feature = (n0 >> 1) + f;
         if (feature < (p.N >> 1)) {
           for (int j = t >> 6; j < BT && m0 + j < p.M; j += 2) {
-            const float v = silu_mul(part_smem[j * BM + f], part_smem[j * BM + f + 64]);
+            const float rf = p.rs.on ? row_f[j] : 1.f;
+            const float v = silu_mul(part_smem[j * BM + f] * rf, part_smem[j * BM + f + 64] * rf);
             if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)(m0 + j) * p.ldy + feature] = v;
             else ((bf16*)p.y)[(size_t)(m0 + j) * p.ldy + feature] = __float2bfloat16_rn(v);
           }
@@ -438,13 +530,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int per = BT / p.cluster;                 // columns (tokens) of the tile this CTA adds up
       const uint32_t base = smem_base + (uint32_t)nl * 4u;
       if (p.swiglu) {
+        if (p.rs.on) pdl_wait();
         const int f = nl & 63, feature = (n0 >> 1) + f;
         if (feature < (p.N >> 1)) {
           for (int j = split * per + (nl >> 6); j < (split + 1) * per; j += 2) {
             const int m = m0 + j;
             if (m >= p.M) break;
             const uint32_t a = smem_base + (uint32_t)j * (BM * 4u) + (uint32_t)f * 4u;
-            const float g = cluster_sum_f32(a, splits), u = cluster_sum_f32(a + 256u, splits);
+            const float rf = p.rs.on ? row_factor(p.rs, m) : 1.f;
+            const float g = cluster_sum_f32(a, splits) * rf, u = cluster_sum_f32(a + 256u, splits) * rf;
             const float v = silu_mul(g, u);
             if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + feature] = v;
             else ((bf16*)p.y)[(size_t)m * p.ldy + feature] = __float2bfloat16_rn(v);
@@ -459,22 +553,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         float* scratch = reinterpret_cast<float*>(smem) + BT * BM;      // behind the partial tile: 128 values, 4 sums,
         int* tok_pos = reinterpret_cast<int*>(scratch + BM + 4);        // then position and page of this CTA's tokens
         int* tok_page = tok_pos + BT;
+        float* tok_rf = reinterpret_cast<float*>(tok_page + BT);        // and the factor its input row lacks
+        if (p.rs.on) pdl_wait();
         const float* w = kind == 0 ? he.q_norm_w : he.k_norm_w;
         // What does not depend on the sums is fetched first, all at once: the loop below then waits for nothing but
         // its own barriers.
-        const float w_n = (kind != 2 && w) ? w[nl] : 1.f;
-        const float freq = (kind != 2 && he.inv_freq) ? he.inv_freq[nl & 63] : 0.f;
+        const float w_n = he_w, freq = he_freq;                        // asked for at the kernel's start
         if (nl < per && m0 + split * per + nl < p.M) {
           const int m = m0 + split * per + nl;
           const int pos = he.positions[m];
           tok_pos[nl] = pos;
           tok_page[nl] = kind == 0 ? 0 : he.block_table[(size_t)he.token_seq[m] * he.max_pages + pos / he.page_size];
         }
+        // the factors that the input rows lack: a warp a token, a lane a tile, so that a token's loads are one round trip
+        for (int t = quarter; t < per && m0 + split * per + t < p.M; t += 4) {
+          const float f = p.rs.on ? row_factor_warp(p.rs, m0 + split * per + t, lane) : 1.f;
+          if (lane == 0) tok_rf[t] = f;
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         for (int j = split * per; j < (split + 1) * per; ++j) {
           const int m = m0 + j;
           if (m >= p.M) break;                                        // the same for every thread
-          float v = cluster_sum_f32(base + (uint32_t)j * (BM * 4u), splits);
+          float v = cluster_sum_f32(base + (uint32_t)j * (BM * 4u), splits) * tok_rf[j - split * per];
           const int pos = tok_pos[j - split * per];
           if (kind != 2) {
             if (w) {
@@ -504,6 +604,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
               pool[(((size_t)page * he.num_kv_heads + hh) * he.page_size + pos % he.page_size) * BM + nl] = __float2bfloat16_rn(v);
             }
           }
+        }
+      } else if (p.an.on) {
+        // The residual add and the first half of the norm that follows; this CTA finishes `per` tokens of the tile,
+        // four at a time so that their loads (the residual, the peers' partial sums) are in flight together.
+        const AddNormEpilogue& an = p.an;
+        float* scratch = reinterpret_cast<float*>(smem) + BT * BM;      // behind the partial tile: 4 warp sums a token
+        const float w_n = an_w;
+        const int j0 = split * per, j1 = min((split + 1) * per, p.M - m0);
+        for (int jb = j0; jb < j1; jb += 4) {
+          float before[4], acc[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            before[u] = jb == j0 ? an_before[u]
+                                 : ((jb + u < j1 && n < p.N) ? an.residual[(size_t)(m0 + jb + u) * p.N + n] : 0.f);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            acc[u] = jb + u < j1 ? cluster_sum_f32(base + (uint32_t)(jb + u) * (BM * 4u), splits) : 0.f;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (jb + u >= j1) break;                                   // the same for every thread
+            const float r = before[u] + acc[u];
+            if (n < p.N) {
+              const size_t at = (size_t)(m0 + jb + u) * p.N + n;
+              an.residual[at] = r;
+              an.out[at] = __float2bfloat16_rn(r * w_n);
+            }
+            const float sq = warp_sum(n < p.N ? r * r : 0.f);
+            if (lane == 0) scratch[(jb + u - j0) * 4 + quarter] = sq;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (nl < j1 - j0) {
+          const float* sl = scratch + nl * 4;
+          an.sumsq[(size_t)(m0 + j0 + nl) * an.tiles + blockIdx.x] = sl[0] + sl[1] + sl[2] + sl[3];
         }
       } else if (n < p.N) {
         for (int j = split * per; j < (split + 1) * per; ++j) {
@@ -1130,9 +1264,14 @@ LB_EXPORT int lb_gemm_tcgen05_plan(int M, int N, int K, int* bt) {
 // row stride ldy.  workspace (float32, workspace_elems elements) and counters (int32, zero, counters_len
 // entries) are needed when K is split; with too little of either the product runs unsplit.
 // force_bt / force_splits (0: choose) are for tests.
+// row_scale (may be null): the rows of x lack their norm's factor (see RowScale); taken by the few-token product with
+// the fused SwiGLU only.
 LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
                               long long ldy, float* workspace, long long workspace_elems, int* counters,
-                              int counters_len, int force_bt, int force_splits, int swiglu, cudaStream_t stream) {
+                              int counters_len, int force_bt, int force_splits, int swiglu, const lb::RowScale* row_scale,
+                              cudaStream_t stream) {
+  LB_CHECK_ARG(!row_scale || (swiglu && M <= 256 && row_scale->sumsq && row_scale->tiles > 0),
+               "gemm_tcgen05: a row scale is taken by the few-token product with the fused SwiGLU only (M=%d)", M);
   LB_CHECK_ARG(lb::valid_dtype(y_dtype), "gemm_tcgen05: bad output dtype %d", y_dtype);
   LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && ldx >= K && ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
   LB_CHECK_ARG(!swiglu || N % 128 == 0, "gemm_tcgen05: the fused SwiGLU needs gate and up rows in blocks of 64 (N=%d is no multiple of 128)", N);
@@ -1183,8 +1322,50 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   // (force_splits < 0 asks for -force_splits splits through the workspace).
   p.cluster = (!workspace_path && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && bt % splits == 0) ? splits : 0;
   p.swiglu = swiglu;
+  if (row_scale) { p.rs = *row_scale; p.rs.on = 1; }
   if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
   LB_CHECK_LAUNCH("gemm_tcgen05");
+  return 0;
+}
+
+// The plan of a product whose epilogue adds to the residual stream (AddNormEpilogue): token tile and splits, or 0 when
+// the sizes do not allow it.  The epilogue lives in the reduction over a cluster, so the product has to be one that is
+// split over a cluster (few tokens, fewer tiles than SMs).
+static int addnorm_plan(int M, int N, int K, int* bt) {
+  if (M <= 0 || M > 256 || K % 8) return 0;
+  int t = 16;
+  int splits = lb_gemm_tcgen05_plan(M, N, K, &t);
+  const int kb = (K + lb::BK - 1) / lb::BK;
+  if (splits > kb) splits = kb;
+  if (splits < 2 || splits > 8 || (splits & (splits - 1)) || t % splits) return 0;
+  if (bt) *bt = t;
+  return splits;
+}
+
+LB_EXPORT int lb_gemm_tcgen05_addnorm_ok(int M, int N, int K) { return addnorm_plan(M, N, K, nullptr) > 0; }
+
+// x[M,K] . w[N,K]^T added to residual [M,N] (float32, in place); out [M,N] (bfloat16) receives residual * norm_w
+// without the row's norm factor, sumsq [M, ceil(N/128)] the partial sums of squares of the new residual from which
+// the reader of `out` forms that factor (see AddNormEpilogue, RowScale).
+LB_EXPORT int lb_gemm_tcgen05_addnorm(const void* x, const void* w, int M, int N, int K, long long ldx, float* residual,
+                                      const float* norm_w, void* out, float* sumsq, cudaStream_t stream) {
+  int bt = 16;
+  const int splits = addnorm_plan(M, N, K, &bt);
+  LB_CHECK_ARG(splits > 0, "gemm_tcgen05_addnorm: sizes M=%d N=%d K=%d are not taken (a product that is split over a cluster)", M, N, K);
+  LB_CHECK_ARG(residual && norm_w && out && sumsq, "gemm_tcgen05_addnorm: null argument");
+  LB_CHECK_ARG(ldx >= K && ldx % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05_addnorm: operands must be 16-byte aligned");
+  CUtensorMap mw, mx;
+  if (!lb::cached_map(&mw, w, N, K, K, lb::BM) || !lb::cached_map(&mx, x, M, K, ldx, bt)) {
+    lb::set_error("gemm_tcgen05_addnorm: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);
+    return 3;
+  }
+  lb::GemmParams p;
+  p.an.on = 1; p.an.tiles = (N + lb::BM - 1) / lb::BM; p.an.residual = residual; p.an.norm_w = norm_w;
+  p.an.out = (lb::bf16*)out; p.an.sumsq = sumsq;
+  p.y = nullptr; p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = N; p.out_dtype = LB_BF16;
+  p.cluster = splits; p.swiglu = 0;
+  if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
+  LB_CHECK_LAUNCH("gemm_tcgen05_addnorm");
   return 0;
 }
 
@@ -1211,7 +1392,7 @@ LB_EXPORT int lb_gemm_tcgen05_heads_ok(int M, int N, int K, int head_dim) { retu
 // the heads and writes queries to he->q_out and keys and values into their cache pages (see HeadEpilogue): the
 // product's output is never stored as such.
 LB_EXPORT int lb_gemm_tcgen05_heads(const void* x, const void* w, int M, int N, int K, long long ldx, const lb::HeadEpilogue* he,
-                                    cudaStream_t stream) {
+                                    const lb::RowScale* row_scale, cudaStream_t stream) {
   int bt = 16;
   const int splits = heads_plan(M, N, K, lb::BM, &bt);
   LB_CHECK_ARG(splits > 0, "gemm_tcgen05_heads: sizes M=%d N=%d K=%d are not taken (heads of 128, up to 32 tokens, a split product)", M, N, K);
@@ -1226,10 +1407,34 @@ LB_EXPORT int lb_gemm_tcgen05_heads(const void* x, const void* w, int M, int N, 
   }
   lb::GemmParams p;
   p.he = *he; p.he.on = 1;
+  if (row_scale) { p.rs = *row_scale; p.rs.on = 1; }
   p.y = nullptr; p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = N; p.out_dtype = LB_BF16;
   p.cluster = splits; p.swiglu = 0;
   if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
   LB_CHECK_LAUNCH("gemm_tcgen05_heads");
+  return 0;
+}
+
+// For tests of the give-up path.  The smallest launch of the few-token kernel (one CTA: up to 16 tokens x up to 128
+// features, K not split, no cluster) with a producer that requests no tile at all and a wait limit of `wait_cycles`
+// clock cycles: the issuing thread's first wait runs out, it records ERR_FULL_WAIT (101) in the device error flag, the
+// other roles see the CTA's abort flag, nothing is stored to y, tensor memory is freed and the kernel returns.
+// Nothing is in flight when the wait gives up, and the context stays usable.
+LB_EXPORT int lb_gemm_tcgen05_wait_test(void* y, const void* x, const void* w, int M, int N, int K,
+                                        unsigned long long wait_cycles, cudaStream_t stream) {
+  LB_CHECK_ARG(M > 0 && M <= 16 && N > 0 && N <= lb::BM && K > 0 && K % 8 == 0, "gemm_tcgen05_wait_test: one tile only (M <= 16, N <= 128), K a multiple of 8");
+  LB_CHECK_ARG(wait_cycles > 0 && wait_cycles <= lb::WAIT_CYCLES, "gemm_tcgen05_wait_test: the limit must be positive and at most the ordinary one");
+  LB_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05_wait_test: operands must be 16-byte aligned");
+  CUtensorMap mw, mx;
+  if (!lb::make_map(&mw, w, N, K, K, lb::BM) || !lb::make_map(&mx, x, M, K, K, 16)) {
+    lb::set_error("gemm_tcgen05_wait_test: cuTensorMapEncodeTiled failed");
+    return 3;
+  }
+  lb::GemmParams p;
+  p.y = y; p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = N; p.out_dtype = LB_BF16;
+  p.cluster = 0; p.swiglu = 0; p.wait_cycles = wait_cycles; p.skip_loads = 1;
+  if (int rc = lb::launch_for_tile(16, mw, mx, p, 1, stream)) return rc;
+  LB_CHECK_LAUNCH("gemm_tcgen05_wait_test");
   return 0;
 }
 

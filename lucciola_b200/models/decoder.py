@@ -69,8 +69,15 @@ class DecoderModel(Part):
         """Run the tokens of one step; float32 logits [R, vocab] for the rows asked for (None if none)."""
         residual = self.embedding.forward(token_ids)
         delta = None
-        for c in self.calls:
-            residual, delta = self.blocks[c.block].forward(residual, delta, step, caches[c.cache], c.write_cache)
+        for i, c in enumerate(self.calls):
+            # what the call after this one offers to take over from this one's last product (see Block.entry_sink)
+            nxt = self.calls[i + 1] if i + 1 < len(self.calls) else None
+            block = self.blocks[c.block]
+            next_sink = self.blocks[nxt.block].entry_sink(residual, step.num_tokens, nxt.write_cache) if nxt is not None else None
+            if next_sink is not None and block.accepts_next_sink:
+                residual, delta = block.forward(residual, delta, step, caches[c.cache], c.write_cache, next_sink=next_sink)
+            else:
+                residual, delta = block.forward(residual, delta, step, caches[c.cache], c.write_cache)
         if logit_rows is None or logit_rows.shape[0] == 0:
             return None
         h = self.final_norm.add_forward(residual, delta, self.rt.act_dtype, rows=logit_rows)

@@ -41,10 +41,12 @@ _SIGNATURES = {
     "lb_gemm_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
                       c_longlong, c_void_p],
     "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
-                        c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                        c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "lb_gemm_tcgen05_addnorm": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p],
     "lb_upload": [c_void_p, c_void_p, c_longlong, c_void_p],
     "lb_zero_rows": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p],
-    "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p],
+    "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -219,12 +221,27 @@ def gemm_tcgen05_ok(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.data_ptr() % 16 == 0 and w.is_contiguous() and x.stride(1) == 1 and y.stride(1) == 1)
 
 
+class LbRowScale(ctypes.Structure):
+    """Mirror of RowScale in csrc/gemm_tcgen05.cu."""
+    _fields_ = [("on", c_int), ("tiles", c_int), ("sumsq", c_void_p), ("inv_width", c_float), ("eps", c_float)]
+
+
+def _row_scale(sumsq: torch.Tensor | None, width: int, eps: float):
+    """The argument for rows that lack their norm's factor: None, or a reference to an LbRowScale."""
+    if sumsq is None:
+        return None
+    _check(sumsq, "partial sums of squares", torch.float32)
+    return ctypes.byref(LbRowScale(1, sumsq.shape[1], sumsq.data_ptr(), 1.0 / width, eps))
+
+
 def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, force_bt: int = 0,
-                 force_splits: int = 0, swiglu: bool = False) -> None:
+                 force_splits: int = 0, swiglu: bool = False, sumsq: torch.Tensor | None = None, eps: float = 0.0) -> None:
     """y[M, N] = x[M, K] . w[N, K]^T on the tensor cores (tcgen05, accumulators in tensor memory).
 
     With `swiglu` the rows of w alternate in blocks of 64 between gate rows and up rows of the same 64
-    features (see interleave_gate_up), and y[M, N/2] = silu(x . gate^T) * (x . up^T), formed in the epilogue."""
+    features (see interleave_gate_up), and y[M, N/2] = silu(x . gate^T) * (x . up^T), formed in the epilogue.
+    With `sumsq` [M, tiles] the rows of x lack the factor of an RMSNorm over K values: row m of the product is
+    multiplied by rsqrt(sum(sumsq[m]) / K + eps) before the activation (see gemm_tcgen05_addnorm)."""
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or tuple(y.shape) != (M, N // 2 if swiglu else N):
@@ -234,7 +251,7 @@ def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int,
     ws, counters = _gemm_scratch(x.device)
     _call("lb_gemm_tcgen05", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), w.data_ptr(), M, N, K,
           x.stride(0) if M > 1 else K, y.stride(0) if M > 1 else y.shape[1], ws.data_ptr(), ws.numel(), counters.data_ptr(),
-          counters.numel(), force_bt, force_splits, 1 if swiglu else 0, stream)
+          counters.numel(), force_bt, force_splits, 1 if swiglu else 0, _row_scale(sumsq, K, eps), stream)
 
 
 class LbHeadEpilogue(ctypes.Structure):
@@ -243,6 +260,14 @@ class LbHeadEpilogue(ctypes.Structure):
                 ("eps", c_float), ("positions", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
                 ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("inv_freq", c_void_p), ("q_out", c_void_p),
                 ("k_cache", c_void_p), ("v_cache", c_void_p)]
+
+
+def gemm_tcgen05_heads_sizes_ok(M: int, N: int, K: int, head_dim: int) -> bool:
+    """The sizes the q|k|v product with the head epilogue takes (heads of 128, at most 32 tokens, a split product)."""
+    lib = library()
+    lib.lb_gemm_tcgen05_heads_ok.argtypes = [c_int, c_int, c_int, c_int]
+    lib.lb_gemm_tcgen05_heads_ok.restype = c_int
+    return bool(lib.lb_gemm_tcgen05_heads_ok(M, N, K, head_dim))
 
 
 def gemm_tcgen05_heads_ok(x: torch.Tensor, w: torch.Tensor, head_dim: int, rot_dim: int | None) -> bool:
@@ -257,12 +282,42 @@ def gemm_tcgen05_heads_ok(x: torch.Tensor, w: torch.Tensor, head_dim: int, rot_d
             and rot_dim in (None, head_dim) and bool(lib.lb_gemm_tcgen05_heads_ok(M, w.shape[0], K, head_dim)))
 
 
+def gemm_tcgen05_addnorm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """The conditions of the product whose epilogue adds to the residual stream: bfloat16, 16-byte alignment, and sizes
+    for which the product is split over a thread-block cluster (few tokens, fewer output tiles than SMs)."""
+    lib = library()
+    lib.lb_gemm_tcgen05_addnorm_ok.argtypes = [c_int, c_int, c_int]
+    lib.lb_gemm_tcgen05_addnorm_ok.restype = c_int
+    M, K = x.shape
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and x.stride(1) == 1
+            and (M == 1 or x.stride(0) % 8 == 0) and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and bool(lib.lb_gemm_tcgen05_addnorm_ok(M, w.shape[0], K)))
+
+
+def gemm_tcgen05_addnorm(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor, out: torch.Tensor,
+                         sumsq: torch.Tensor, stream: int) -> None:
+    """residual += x . w^T; out = (residual * norm_w) rounded to bfloat16, without the factor rsqrt(mean(residual^2) + eps)
+    of the RMSNorm; sumsq[m, t] = sum of residual[m]^2 over the t-th block of 128 features.  The product that reads
+    `out` is given `sumsq` and multiplies its sums by the row's factor (a row's factor commutes with a linear map), so
+    the add, the copy and the norm between two products cost no kernel of their own."""
+    M, K = x.shape
+    N = w.shape[0]
+    _check(w, "w", torch.bfloat16); _check(residual, "residual", torch.float32); _check(norm_w, "norm weight", torch.float32)
+    _check(out, "normed output", torch.bfloat16); _check(sumsq, "partial sums of squares", torch.float32)
+    if tuple(residual.shape) != (M, N) or tuple(out.shape) != (M, N) or tuple(sumsq.shape) != (M, -(-N // 128)) or norm_w.shape[0] != N:
+        raise KernelError(f"gemm_tcgen05_addnorm shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, residual {tuple(residual.shape)}, sumsq {tuple(sumsq.shape)}")
+    _call("lb_gemm_tcgen05_addnorm", x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0) if M > 1 else K, residual.data_ptr(),
+          norm_w.data_ptr(), out.data_ptr(), sumsq.data_ptr(), stream)
+
+
 def gemm_tcgen05_heads(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
                        block_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, num_q_heads: int,
                        num_kv_heads: int, page_size: int, eps: float, stream: int, q_norm_w: torch.Tensor | None = None,
-                       k_norm_w: torch.Tensor | None = None, inv_freq: torch.Tensor | None = None) -> None:
+                       k_norm_w: torch.Tensor | None = None, inv_freq: torch.Tensor | None = None,
+                       sumsq: torch.Tensor | None = None, row_eps: float = 0.0) -> None:
     """x . w^T for w = [q | k | v] rows with heads of 128, finished per head in the product's epilogue: RMSNorm of
-    query and key heads, rotation, queries to q_out [M, nq, 128], keys and values into their cache pages."""
+    query and key heads, rotation, queries to q_out [M, nq, 128], keys and values into their cache pages.
+    `sumsq`, `row_eps`: the rows of x lack their norm's factor (see gemm_tcgen05)."""
     M, K = x.shape
     _check(x, "x", torch.bfloat16); _check(w, "w", torch.bfloat16); _check(q_out, "q output", torch.bfloat16)
     _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
@@ -275,7 +330,7 @@ def gemm_tcgen05_heads(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, po
                         token_seq.data_ptr(), block_table.data_ptr(), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
                         q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr())
     _call("lb_gemm_tcgen05_heads", x.data_ptr(), w.data_ptr(), M, w.shape[0], K, x.stride(0) if M > 1 else K,
-          ctypes.byref(he), stream)
+          ctypes.byref(he), _row_scale(sumsq, K, row_eps), stream)
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -460,8 +515,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     """Causal attention of this step's queries over the pages of their requests.  With a `plan` (tile lists
     by kind on the device, see parts/attention.py) the tensor-core kernels run where their conditions hold:
     portions of prompts go to the tcgen05 kernel, the rest (decoded tokens, short portions, other head
-    sizes) to the mma.sync kernels, decoded tokens in a launch of their own when the plan lists them apart
-    ("one"); everything else, and every step without a plan, goes to the plain kernel."""
+    sizes) to the mma.sync kernels; everything else, and every step without a plan, goes to the plain kernel."""
     if plan is None or not attention_flash_ok(q, num_q_heads, num_kv_heads, head_dim):
         attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
                         num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
@@ -474,9 +528,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                                               step.block_tables[group].shape[1]):
         attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"],
                           num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
-        kinds = [k for k in ("rest", "one") if k in meta]
-    elif "big" not in meta and "one" in meta:
-        kinds = ["rest", "one"]          # decoded tokens beside a few tokens of a prompt: a launch for each
+        kinds = ["rest"] if "rest" in meta else []
     for kind in kinds:
         tiles = meta[kind]
         rows = min(most_rows[kind], 64)

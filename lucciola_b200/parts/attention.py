@@ -19,8 +19,8 @@ import numpy as np
 import torch
 
 from .. import ops
-from .base import (BatchShape, KVCacheView, KVPages, Mixer, ParamSpec, Part, PositionEncoding, Runtime, StepContext,
-                   StepPlan)
+from .base import (BatchShape, KVCacheView, KVPages, Mixer, NormSink, ParamSpec, Part, PositionEncoding, RowScaled, Runtime,
+                   StepContext, StepPlan)
 from .linear import Linear
 
 # Entries with at least this many tokens in a step go to the tensor-memory attention kernel (128-row tiles).
@@ -44,32 +44,30 @@ def tiles_of(q_lens: Sequence[int], group: int, rows: int, take=None) -> list[tu
 
 
 def plan_tiles(batch: BatchShape, group: int) -> StepPlan:
-    """The tile lists of one step for query groups of `group` heads.  Kinds: "all" = every entry in tiles of up
-    to 64 query rows; when the step holds portions of prompts, also "big" = those portions in work items of up to
-    256 rows (two tiles of floor(128 / group) tokens, for the tensor-memory kernel) and "rest" = the other entries
-    in 64-row tiles; and when the entries that are not "big" mix tiles of at most 16 query rows (decoded tokens)
-    with larger ones (a few tokens of a prompt), "one" = the former and "rest" = the latter.  Each array is
-    int32 [n, 4]; host["rows"][kind] is the most query rows of a tile of that kind."""
+    """The tile lists of one step for query groups of `group` heads.  Kinds: "all" = every entry; when the step
+    holds portions of prompts of BIG_PORTION tokens or more, also "big" = those portions in work items of up to 256
+    rows (two tiles of floor(128 / group) tokens, for the tensor-memory kernel) and "rest" = the other entries.
+    Tiles of "all" and "rest" have up to 64 query rows; but where single tokens sit beside portions of a few tokens,
+    those lists are cut into tiles of at most 16 rows, so that one launch of the kernel for such tiles serves them all
+    (a portion of 8 tokens beside 32 decoded tokens then costs two more tiles, not a launch with key ranges split
+    through a workspace and a second kernel to combine them; its keys are read once per tile, which is little for a
+    few tokens).  Each array is int32 [n, 4]; host["rows"][kind] is the most query rows of a tile of that kind."""
     q_lens, starts, g = batch.q_lens, batch.start_positions, group
-    lists: dict[str, list] = {"all": tiles_of(q_lens, g, TILE_ROWS)}
-    if batch.max_q_len > 1:
-        has_big = batch.max_q_len >= BIG_PORTION
-        if has_big:
-            first_token = np.concatenate(([0], np.cumsum(q_lens)[:-1])).tolist()
-            big = tiles_of(q_lens, g, 2 * (128 // g) * g, lambda n: n >= BIG_PORTION)
-            # tiles that see the most keys first: the short ones then fill the end of the last wave
-            big.sort(key=lambda tl: -(starts[tl[2]] + (tl[0] - first_token[tl[2]]) + tl[1]))
-            lists["big"] = big
-        others = [n for n in q_lens if n < BIG_PORTION]
-        mixed = any(n * g <= DECODE_ROWS for n in others) and any(n * g > DECODE_ROWS for n in others)
-        if mixed:
-            lists["rest"] = tiles_of(q_lens, g, TILE_ROWS, lambda n: n < BIG_PORTION and n * g > DECODE_ROWS)
-            lists["one"] = tiles_of(q_lens, g, TILE_ROWS, lambda n: n * g <= DECODE_ROWS)
-        elif has_big and others:
-            lists["rest"] = tiles_of(q_lens, g, TILE_ROWS, lambda n: n < BIG_PORTION)
+    has_big = batch.max_q_len >= BIG_PORTION
+    small = [n for n in q_lens if n < BIG_PORTION]
+    fine = (g <= DECODE_ROWS and any(n * g <= DECODE_ROWS for n in small) and any(n * g > DECODE_ROWS for n in small))
+    rows_small = DECODE_ROWS if fine else TILE_ROWS
+    lists: dict[str, list] = {"all": tiles_of(q_lens, g, TILE_ROWS if has_big else rows_small)}
+    if has_big:
+        first_token = np.concatenate(([0], np.cumsum(q_lens)[:-1])).tolist()
+        big = tiles_of(q_lens, g, 2 * (128 // g) * g, lambda n: n >= BIG_PORTION)
+        # tiles that see the most keys first: the short ones then fill the end of the last wave
+        big.sort(key=lambda tl: -(starts[tl[2]] + (tl[0] - first_token[tl[2]]) + tl[1]))
+        lists["big"] = big
+        if small:
+            lists["rest"] = tiles_of(q_lens, g, rows_small, lambda n: n < BIG_PORTION)
     return StepPlan({k: np.asarray(tl, dtype=np.int32).reshape(len(tl), 4) for k, tl in lists.items()},
                     {"rows": {k: max(n for _, n, _, _ in tl) * g for k, tl in lists.items()}})
-
 
 
 class GQAttention(Mixer):
@@ -131,7 +129,25 @@ class GQAttention(Mixer):
     def cache_request(self) -> KVPages:
         return KVPages(self.num_kv_heads, self.head_dim, self.window)
 
-    def forward(self, h: torch.Tensor, step: StepContext, cache: KVCacheView, write_cache: bool = True) -> torch.Tensor:
+    accepts_sink = True
+
+    def _heads_in_epilogue(self, num_tokens: int, write_cache: bool) -> bool:
+        """Few tokens and heads of 128: the q|k|v product finishes the heads in its own epilogue."""
+        rotary = self.position_encoding.rotary_table() if self.position_encoding is not None else None
+        return (write_cache and self.rt.fast_kernels and (self.position_encoding is None or rotary is not None)
+                and (rotary is None or rotary[1] == self.head_dim)
+                and ops.gemm_tcgen05_heads_sizes_ok(num_tokens, self.qkv.out_features, self.hidden_size, self.head_dim))
+
+    def row_scaled_ok(self, num_tokens: int, write_cache: bool = True) -> bool:
+        """That epilogue also applies the factor that rows without their norm's factor lack."""
+        return self._heads_in_epilogue(num_tokens, write_cache)
+
+    def _project_out(self, out: torch.Tensor, sink: Optional[NormSink]):
+        if sink is not None and self.o.sink_ok(out):
+            return self.o.forward_into(out, sink)
+        return self.o.forward(out)
+
+    def forward(self, h, step: StepContext, cache: KVCacheView, write_cache: bool = True, sink: Optional[NormSink] = None):
         rt = self.rt
         T = h.shape[0]
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
@@ -139,17 +155,21 @@ class GQAttention(Mixer):
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         q = rt.empty((T, nq, d))
         rotary = self.position_encoding.rotary_table() if self.position_encoding is not None else None
-        if (write_cache and rt.fast_kernels and (self.position_encoding is None or rotary is not None)
-                and ops.gemm_tcgen05_heads_ok(h, self.qkv.weight, d, rotary[1] if rotary is not None else None)):
-            # Few tokens and heads of 128: the q|k|v product finishes the heads in its own epilogue (norm, rotation,
-            # queries into their layout, keys and values into the pages); its output never exists as a matrix.
-            ops.gemm_tcgen05_heads(h, self.qkv.weight, q, step.positions, step.token_seq, cache_table, cache.k, cache.v,
+        scaled = h if isinstance(h, RowScaled) else None
+        x = scaled.x if scaled is not None else h
+        if self._heads_in_epilogue(T, write_cache) and ops.gemm_tcgen05_heads_ok(x, self.qkv.weight, d, rotary[1] if rotary is not None else None):
+            # Norm, rotation, queries into their layout, keys and values into the pages: the product's output never
+            # exists as a matrix.
+            ops.gemm_tcgen05_heads(x, self.qkv.weight, q, step.positions, step.token_seq, cache_table, cache.k, cache.v,
                                    nq, nkv, cache.page_size, eps, rt.stream, q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w,
-                                   inv_freq=rotary[0] if rotary is not None else None)
+                                   inv_freq=rotary[0] if rotary is not None else None,
+                                   sumsq=scaled.sumsq if scaled is not None else None, row_eps=scaled.eps if scaled is not None else 0.0)
             out = rt.empty((T, nq, d))
             ops.attention(q, out, cache.k, cache.v, step, cache.group, nq, nkv, d, cache.page_size, self.window,
                           self.scale, rt.stream, plan=step.plans.get(self.plan_key()))
-            return self.o.forward(out.view(T, self.q_size))
+            return self._project_out(out.view(T, self.q_size), sink)
+        if scaled is not None:
+            raise ops.KernelError("this mixer was handed rows without their norm factor for a step it cannot take them in")
         if write_cache:
             qkv = self.qkv.forward(h)
             q_in, k_in, v_in = qkv[:, :self.q_size], qkv[:, self.q_size:self.q_size + self.kv_size], qkv[:, self.q_size + self.kv_size:]
@@ -179,4 +199,4 @@ class GQAttention(Mixer):
         out = rt.empty((T, nq, d))
         ops.attention(q, out, cache.k, cache.v, step, cache.group, nq, nkv, d, cache.page_size, self.window,
                       self.scale, rt.stream, plan=step.plans.get(self.plan_key()))
-        return self.o.forward(out.view(T, self.q_size))
+        return self._project_out(out.view(T, self.q_size), sink)

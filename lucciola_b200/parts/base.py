@@ -141,6 +141,31 @@ class StepContext:
     plans: dict[Hashable, PlanView] = field(default_factory=dict)
 
 
+@dataclass
+class RowScaled:
+    """Rows that still lack the factor of their RMSNorm: the normed row m is x[m] * rsqrt(sum(sumsq[m]) / width + eps).
+    A product whose epilogue adds to the residual stream hands its result on in this form (the row's sum of squares is
+    complete only when all of the product's tiles are), and the product that reads it applies the factor to its
+    32-bit sums: a factor per row commutes with a linear map."""
+    x: torch.Tensor                 # [T, width], residual * norm weight, in the activation type
+    sumsq: torch.Tensor             # [T, tiles] float32: sums of squares of the residual over blocks of the row
+    width: int
+    eps: float
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+
+@dataclass
+class NormSink:
+    """Where a part may put its output instead of returning it: added into `residual` (float32, in place), and the
+    sum handed on multiplied by `weight` as RowScaled, for the norm with these weights and eps that follows."""
+    residual: torch.Tensor
+    weight: torch.Tensor            # float32 [width]
+    eps: float
+
+
 class Part:
     # True when forward() only launches work on the step's stream and takes nothing from the host that changes
     # between steps of the same shape (see BatchShape): then a step through it may be recorded as a CUDA graph.
@@ -179,6 +204,11 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         raise NotImplementedError
 
+    def as_sink(self, residual: torch.Tensor) -> Optional[NormSink]:
+        """If this norm is y = x * rsqrt(mean(x^2) + eps) * w, what a product's epilogue needs to stand in for
+        add_forward(residual, its output); None for every other kind of norm."""
+        return None
+
     def add_forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
@@ -207,18 +237,40 @@ class Mixer(Part):
         `step.plans[self.plan_key()]` as a PlanView."""
         return None
 
+    # A mixer or feed-forward that sets `accepts_sink` takes a keyword `sink` (a NormSink or None) in forward() and may
+    # return RowScaled when it used it; one whose row_scaled_ok() says yes for a step takes RowScaled as `h`.  Parts
+    # that know neither are given plain tensors and asked for plain tensors.
+    accepts_sink = False
+
+    def row_scaled_ok(self, num_tokens: int, write_cache: bool = True) -> bool:
+        return False
+
     def forward(self, h: torch.Tensor, step: StepContext, cache, write_cache: bool = True) -> torch.Tensor:
         raise NotImplementedError
 
 
 class FeedForward(Part):
+    accepts_sink = False
+
+    def row_scaled_ok(self, num_tokens: int) -> bool:
+        return False
+
     def forward(self, h: torch.Tensor, step: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
 
 class Block(Part):
     mixer: Mixer
+    accepts_next_sink = False       # True: forward() takes the keyword `next_sink`
 
-    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], step: StepContext, cache,
-                write_cache: bool = True) -> tuple[torch.Tensor, Optional[torch.Tensor]]:
+    def entry_sink(self, residual: torch.Tensor, num_tokens: int, write_cache: bool) -> Optional[NormSink]:
+        """Not None: the block before this one may hand its output over already added to the residual stream and
+        multiplied by this block's first norm weight (RowScaled), through this sink."""
+        return None
+
+    def forward(self, residual: torch.Tensor, delta, step: StepContext, cache, write_cache: bool = True,
+                next_sink: Optional[NormSink] = None) -> tuple[torch.Tensor, object]:
+        """`delta`: what the block before left to be added (a tensor, or None for the first block), or RowScaled when
+        it went through this block's entry_sink.  Returns the residual stream and this block's own delta, RowScaled
+        if it used `next_sink`."""
         raise NotImplementedError

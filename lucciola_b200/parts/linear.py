@@ -11,7 +11,7 @@ from typing import Callable, Sequence
 import torch
 
 from .. import ops
-from .base import ParamSpec, Part, Runtime
+from .base import NormSink, ParamSpec, Part, RowScaled, Runtime
 
 
 class Linear(Part):
@@ -45,6 +45,18 @@ class Linear(Part):
     def bind_tensor(self, weight: torch.Tensor) -> None:
         """Use a tensor another part owns (a tied output head)."""
         self.weight = weight
+
+    def sink_ok(self, x: torch.Tensor) -> bool:
+        """Whether forward_into() takes this input: the bfloat16 path, and a product that is split over a cluster."""
+        return self.rt.fast_kernels and ops.gemm_tcgen05_addnorm_ok(x, self.weight)
+
+    def forward_into(self, x: torch.Tensor, sink: NormSink) -> RowScaled:
+        """sink.residual += x . W^T, and the sum times the sink's norm weight, without the row's factor, handed on."""
+        M, N = x.shape[0], self.weight.shape[0]
+        out = self.rt.empty((M, N))
+        sumsq = self.rt.empty((M, -(-N // 128)), torch.float32)
+        ops.gemm_tcgen05_addnorm(x, self.weight, sink.residual, sink.weight, out, sumsq, self.rt.stream)
+        return RowScaled(out, sumsq, N, sink.eps)
 
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, rows: int | None = None) -> torch.Tensor:
         """y = x . W^T; with `rows`, only the first `rows` output features."""

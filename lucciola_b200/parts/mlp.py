@@ -4,10 +4,12 @@ intermediate size is a multiple of 64, their rows are interleaved in blocks of 6
 formed in that product's epilogue, so the [T, 2 * intermediate] matrix is never written."""
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .. import ops
-from .base import FeedForward, Part, Runtime, StepContext
+from .base import FeedForward, NormSink, Part, RowScaled, Runtime, StepContext
 from .linear import Linear
 
 
@@ -34,15 +36,32 @@ class SwiGLUFeedForward(FeedForward):
             inter = self.intermediate_size
             self.gate_up.weight = ops.interleave_gate_up(w[:inter], w[inter:])
 
-    def forward(self, h: torch.Tensor, step: StepContext) -> torch.Tensor:
+    accepts_sink = True
+
+    def row_scaled_ok(self, num_tokens: int) -> bool:
+        """The few-token product with the activation in its epilogue also applies a row's norm factor there."""
+        return self.fused and num_tokens <= 256
+
+    def _down(self, act: torch.Tensor, sink: Optional[NormSink]):
+        if sink is not None and self.down.sink_ok(act):
+            return self.down.forward_into(act, sink)
+        return self.down.forward(act)
+
+    def forward(self, h, step: StepContext, sink: Optional[NormSink] = None):
         inter = self.intermediate_size
+        if isinstance(h, RowScaled):
+            if not self.row_scaled_ok(h.shape[0]):
+                raise ops.KernelError("this feed-forward was handed rows without their norm factor for a step it cannot take them in")
+            act = self.rt.empty((h.shape[0], inter))
+            ops.gemm_tcgen05(act, h.x, self.gate_up.weight, self.rt.stream, swiglu=True, sumsq=h.sumsq, eps=h.eps)
+            return self._down(act, sink)
         if self.fused and ops.gemm_tcgen05_ok(h, h, self.gate_up.weight):
             act = self.rt.empty((h.shape[0], inter))
             ops.gemm_tcgen05(act, h, self.gate_up.weight, self.rt.stream, swiglu=True)
-            return self.down.forward(act)
+            return self._down(act, sink)
         if self.fused:
             raise ops.KernelError("the interleaved gate|up weights need the tensor-core product (bfloat16, 16-byte aligned input)")
         gu = self.gate_up.forward(h)
         act = self.rt.empty((h.shape[0], inter))
         ops.swiglu(act, gu[:, :inter], gu[:, inter:], self.rt.stream)
-        return self.down.forward(act)
+        return self._down(act, sink)

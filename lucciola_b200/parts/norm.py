@@ -7,7 +7,7 @@ from typing import Callable, Optional
 import torch
 
 from .. import ops
-from .base import Norm, ParamSpec, Runtime
+from .base import Norm, NormSink, ParamSpec, Runtime
 
 
 class RMSNorm(Norm):
@@ -26,6 +26,9 @@ class RMSNorm(Norm):
 
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         return self.add_forward(x, None, out_dtype)
+
+    def as_sink(self, residual: torch.Tensor) -> Optional[NormSink]:
+        return NormSink(residual, self.weight, self.eps)
 
     def add_forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -51,11 +51,22 @@ TINY_C = {
     "layer_types": ["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
     "torch_dtype": "bfloat16",
 }
+# D is small but has the head size (128) and the widths (512: products long enough to be split) at which the engine
+# takes its fused paths: heads finished in the q|k|v product's epilogue, residual add and norm inside the o and down
+# products, the tensor-memory attention kernel, keys and values fetched by TMA.
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 512, "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 128,
+    "intermediate_size": 576, "vocab_size": 331, "rope_theta": 500000.0, "rms_norm_eps": 2e-6,
+    "tie_word_embeddings": False, "max_position_embeddings": 512, "hidden_act": "silu", "attention_bias": False,
+    "torch_dtype": "bfloat16",
+}
 # name -> (config, seed, std of linear weights, std of norm weights around 1, page size)
 TINY = {
     "A": (TINY_A, 0, 0.02, 0.1, 16),
     "B": (TINY_B, 1, 0.05, 0.2, 8),
     "C": (TINY_C, 2, 0.08, 0.15, 16),
+    "D": (TINY_D, 3, 0.04, 0.1, 16),
 }
 
 

@@ -1,8 +1,8 @@
 """Writes tests/golden/plain_tiny.json: a few numbers of the plain implementation on the tiny models.
 
-The plain implementation rests on lucciola's formulas alone (lucciola's model code is CUDA kernels
-and cannot be run on a CPU), so these are outputs of tests/plain_qwen3.py itself, kept to notice
-when that file changes its results.  Run from the repository root:  python tests/golden/make_golden.py
+lucciola's model code is CUDA kernels and cannot be run on a CPU, so these are outputs of
+tests/plain_qwen3.py itself, kept to notice when that file changes its results (what ties that file
+to lucciola's own code is tests/test_reference_kernels_gpu.py, on a GPU).  Run from the repository root:  python tests/golden/make_golden.py
 """
 import json
 import sys

@@ -3,10 +3,11 @@ function for each part, on the CPU.  It shares no code with lucciola_b200: it re
 with the json module and model.safetensors with its own few lines, and each function restates a
 formula of JunkuiZhang/lucciola, cited by file:line of that project.
 
-This file rests on the formulas only.  lucciola's model code cannot be imported or compiled on a
-CPU: all of its arithmetic is in __global__ kernels (src/kernels/*.cu) and src/qwen.cc needs
-<print> and network-fetched headers, so there is no output of lucciola's own to compare with, and
-tests/golden/ holds outputs of this file only.
+lucciola's model code cannot be imported or compiled on a CPU: all of its arithmetic is in
+__global__ kernels (src/kernels/*.cu) and src/qwen.cc needs <print> and network-fetched headers.
+So on the CPU this file rests on the formulas, and tests/golden/ holds outputs of this file only.
+On a GPU, tests/test_reference_kernels_gpu.py compiles lucciola's kernel files unchanged and checks
+each function of this file against the kernel it restates, to one rounding of the bfloat16 output.
 
 Arithmetic is float64 unless `dtype` says otherwise; the rotation angle is formed in float32 as
 lucciola forms it (pos * freq in float, src/kernels/rope.cu:34-37), because at positions in the

@@ -127,8 +127,10 @@ def test_rope_kv(env, act, nq, nkv, d, ps, theta):
     (6, 1, 32, 512, [(9, 30)], False, True), (2, 2, 64, 640, [(0, 20), (63, 2)], True, False),
     (3, 1, 16, 2048, [(0, 32)], True, True),                                           # the most tokens it takes
 ])
-def test_gemm_tcgen05_with_head_epilogue(env, nq, nkv, ps, K, seqs, norm, rotate):
-    """The q|k|v product that finishes the heads itself against product, norm, rotation and cache write done plainly."""
+@pytest.mark.parametrize("scaled", [False, True])
+def test_gemm_tcgen05_with_head_epilogue(env, nq, nkv, ps, K, seqs, norm, rotate, scaled):
+    """The q|k|v product that finishes the heads itself against product, norm, rotation and cache write done plainly;
+    `scaled`: its input rows lack a factor each, given as partial sums of squares, which the epilogue applies."""
     ops, dev, st = env
     d, theta, eps = 128, 1e6, 1e-6
     kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, torch.bfloat16)
@@ -140,10 +142,16 @@ def test_gemm_tcgen05_with_head_epilogue(env, nq, nkv, ps, K, seqs, norm, rotate
     inv = (1.0 / torch.pow(torch.tensor(theta), torch.arange(0, d, 2, dtype=torch.float32) / d)).to(dev) if rotate else None
     assert ops.gemm_tcgen05_heads_ok(x, w, d, d if rotate else None)
     q_out = torch.full((T, nq, d), float("nan"), device=dev, dtype=torch.bfloat16)
-    ops.gemm_tcgen05_heads(x, w, q_out, pos, seq, bt, kc, vc, nq, nkv, ps, eps, st, q_norm_w=qw, k_norm_w=kw, inv_freq=inv)
+    sumsq, row_eps, factor = None, 0.0, torch.ones(T, 1, dtype=torch.float64)
+    if scaled:
+        sumsq = (torch.rand(T, 5, device=dev) * K * 3).float()
+        row_eps = 1e-3
+        factor = torch.rsqrt(sumsq.double().sum(dim=1, keepdim=True) / K + row_eps).cpu()
+    ops.gemm_tcgen05_heads(x, w, q_out, pos, seq, bt, kc, vc, nq, nkv, ps, eps, st, q_norm_w=qw, k_norm_w=kw, inv_freq=inv,
+                           sumsq=sumsq, row_eps=row_eps)
     torch.cuda.synchronize()
     assert ops.device_error() == 0
-    y = (x.double() @ w.double().t()).cpu()
+    y = (x.double() @ w.double().t()).cpu() * factor
     a, b = nq * d, (nq + nkv) * d
     p = pos.cpu().tolist()
     q_ref, k_ref, v_ref = y[:, :a].reshape(T, nq, d), y[:, a:b].reshape(T, nkv, d), y[:, b:].reshape(T, nkv, d)
@@ -512,6 +520,66 @@ def test_gemm_tcgen05_with_swiglu_epilogue(env, M, I, K, bt, splits, ty):
     assert rel(y, want) < tol
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (1, 4096, 12288), (3, 1000, 2048), (32, 512, 1024), (20, 5120, 5120), (64, 1024, 2048)])
+def test_gemm_tcgen05_that_adds_to_the_residual_stream(env, M, N, K):
+    """residual += x . w^T; out = residual * norm weight (rounded, without the row's factor); partial sums of squares
+    whose total is the row's sum of squares: against the same done plainly, and the factor formed from the partial
+    sums against the norm's."""
+    ops, dev, st = env
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) / math.sqrt(K)).bfloat16()
+    assert ops.gemm_tcgen05_addnorm_ok(x, w)
+    residual = torch.randn(M, N, device=dev)
+    before = residual.double().cpu()
+    nw = 1 + 0.2 * torch.randn(N, device=dev)
+    tiles = -(-N // 128)
+    out = torch.full((M, N), float("nan"), device=dev, dtype=torch.bfloat16)
+    sumsq = torch.full((M, tiles), float("nan"), device=dev)
+    ops.gemm_tcgen05_addnorm(x, w, residual, nw, out, sumsq, st)
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
+    want = before + (x.double() @ w.double().t()).cpu()
+    assert rel(residual.cpu(), want) < 2e-6                              # a float32 sum of float32 partial sums
+    assert rel(out.cpu(), want * nw.double().cpu()) < 5e-3
+    assert torch.isfinite(sumsq).all()
+    blocks = torch.nn.functional.pad(want * want, (0, tiles * 128 - N)).reshape(M, tiles, 128).sum(dim=2)
+    assert rel(sumsq.cpu(), blocks) < 1e-5
+    eps = 1e-6
+    normed = plain.rms_norm(want, nw.double().cpu(), eps)
+    factor = torch.rsqrt(sumsq.double().sum(dim=1, keepdim=True) / N + eps).cpu()
+    assert rel(out.double().cpu() * factor, normed) < 5e-3
+    # what it does not take: products that are not split over a cluster (too many tiles, too short a k, many tokens)
+    assert not ops.gemm_tcgen05_addnorm_ok(x, torch.empty(24576, K, device=dev, dtype=torch.bfloat16))
+    assert not ops.gemm_tcgen05_addnorm_ok(x[:, :192], w[:, :192].contiguous())
+    assert not ops.gemm_tcgen05_addnorm_ok(torch.empty(300, K, device=dev, dtype=torch.bfloat16), w)
+
+
+@pytest.mark.parametrize("M,I,K", [(8, 12288, 4096), (1, 3072, 1024), (24, 512, 2048), (100, 1536, 512), (256, 12288, 1024)])
+def test_gemm_tcgen05_swiglu_of_rows_that_lack_their_factor(env, M, I, K):
+    """The gate|up product with the activation in its epilogue, given rows without their norm's factor: the factor is
+    applied to the 32-bit sums before the activation (products that are not split, and ones split over a cluster)."""
+    ops, dev, st = env
+    x = torch.randn(M, K, device=dev).bfloat16()
+    gate = (torch.randn(I, K, device=dev) / math.sqrt(K)).bfloat16()
+    up = (torch.randn(I, K, device=dev) / math.sqrt(K)).bfloat16()
+    w = ops.interleave_gate_up(gate, up)
+    sumsq = (torch.rand(M, 7, device=dev) * K * 2).float()
+    eps = 1e-5
+    factor = torch.rsqrt(sumsq.double().sum(dim=1, keepdim=True) / K + eps).cpu()
+    act = torch.full((M, I), float("nan"), device=dev, dtype=torch.bfloat16)
+    ops.gemm_tcgen05(act, x, w, st, swiglu=True, sumsq=sumsq, eps=eps)
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
+    g = (x.double() @ gate.double().t()).cpu() * factor
+    u = (x.double() @ up.double().t()).cpu() * factor
+    assert rel(act.cpu(), plain.swiglu(g, u)) < 6e-3
+    with pytest.raises(ops.KernelError, match="row scale"):                   # the many-token product does not take it
+        ops.gemm_tcgen05(torch.empty(300, I, device=dev, dtype=torch.bfloat16), torch.zeros(300, K, device=dev, dtype=torch.bfloat16),
+                         w, st, swiglu=True, sumsq=torch.ones(300, 7, device=dev), eps=eps)
+    with pytest.raises(ops.KernelError, match="row scale"):                   # nor a product without the activation
+        ops.gemm_tcgen05(torch.empty(M, 2 * I, device=dev, dtype=torch.bfloat16), x, w, st, sumsq=sumsq, eps=eps)
+
+
 def test_gemm_tcgen05_refuses_what_it_cannot_do(env):
     ops, dev, st = env
     from lucciola_b200.ops import KernelError
@@ -526,6 +594,38 @@ def test_gemm_tcgen05_refuses_what_it_cannot_do(env):
 
 
 # ---- samplers ------------------------------------------------------------------------------------------------------
+def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable(env):
+    """The give-up path of the bounded waits, made to happen without anything in flight: one CTA of the smallest
+    tensor-core product whose producer requests no tile, with a limit of 200 000 cycles (about 0.1 ms).  The kernel must
+    return, leave its code in the device error flag, store nothing, and an ordinary product right after must be right."""
+    import ctypes
+    import time
+    from lucciola_b200.csrc import library
+    ops, dev, st = env
+    fn = library().lb_gemm_tcgen05_wait_test
+    fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 3 + [ctypes.c_ulonglong, ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    M, N, K = 8, 100, 256
+    x, w = torch.randn(M, K, device=dev).bfloat16(), torch.randn(N, K, device=dev).bfloat16()
+    y = torch.full((M, N), 7.0, device=dev, dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    assert ops.device_error() == 0
+    t0 = time.perf_counter()
+    assert fn(y.data_ptr(), x.data_ptr(), w.data_ptr(), M, N, K, 200_000, st) == 0, library().lb_last_error().decode()
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0                     # it gave up after its limit, not after the ordinary two seconds
+    assert ops.device_error() == 101                          # ERR_FULL_WAIT of csrc/gemm_tcgen05.cu
+    assert ops.device_error() == 0                            # reading the flag clears it
+    assert (y == 7.0).all()
+    # sizes beyond one tile, and limits beyond the ordinary one, are refused
+    assert fn(y.data_ptr(), x.data_ptr(), w.data_ptr(), 17, N, K, 200_000, st) != 0
+    assert fn(y.data_ptr(), x.data_ptr(), w.data_ptr(), M, N, K, 1 << 40, st) != 0
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    ops.gemm_tcgen05(out, x, w, st)
+    torch.cuda.synchronize()
+    assert rel(out, x.double() @ w.double().t()) < 5e-3 and ops.device_error() == 0
+
+
 def test_greedy_takes_the_lowest_index_among_equals(env):
     ops, dev, st = env
     logits = torch.zeros(3, 70001, device=dev)

@@ -32,7 +32,7 @@ def requests_for(name):
     """Four requests per configuration (the prompt lengths of the tiny workloads among them), up to the
     configuration's longest sequence."""
     top = TINY[name][0]["max_position_embeddings"]
-    lengths = {"A": [5, 17, 33, 128], "B": [1, 9, 40, 100, 256], "C": [3, 64, 200, 333]}[name]
+    lengths = {"A": [5, 17, 33, 128], "B": [1, 9, 40, 100, 256], "C": [3, 64, 200, 333], "D": [2, 31, 150, 400]}[name]
     assert max(lengths) <= top
     return {f"{name}{n}": tokens_for(name, n) for n in lengths}
 
