@@ -150,6 +150,14 @@ class CacheManager:
             rc.length += 1
         return starts
 
+    def retract_by_one(self, rids: Sequence[Hashable]) -> None:
+        """Undo extend_by_one for a step that was prepared and will not run.  A page that was taken for the position
+        stays in the request's table (the position's next step finds it there; a request that ends gives it back)."""
+        for rid in rids:
+            rc = self._requests.get(rid)
+            if rc is not None and rc.length > 0:
+                rc.length -= 1
+
     def max_extension(self, rid: Hashable, upto: int) -> int:
         """The largest length <= upto that the free pages allow for this request."""
         rc = self._requests[rid]

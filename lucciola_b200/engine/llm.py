@@ -45,6 +45,7 @@ class Engine:
         self.sampler = Sampler(runner.device)
         self._next_id = 1
         self._live: dict[int, Request] = {}              # requests that have not finished, by id
+        self._prepared = None                            # the next step's host side, done while the GPU ran this one
         # What to do when a request's callback raises: None lets the exception through to whoever called step().
         self.on_callback_error: Optional[Callable[[Request, BaseException], None]] = None
 
@@ -76,7 +77,10 @@ class Engine:
         """Give a request up, wherever it is (waiting, in the middle of its prompt, decoding): its pages and its
         slot go back at once.  Returns the request, or None when no live request has this id."""
         req = self._live.get(rid)
-        if req is None or not self.scheduler.abort(rid):
+        if req is None:
+            return None
+        self._drop_prepared()
+        if not self.scheduler.abort(rid):
             return None
         del self._live[rid]
         return req
@@ -85,20 +89,49 @@ class Engine:
         return self.scheduler.has_unfinished()
 
     # ---- one step: schedule, run, sample, update ----------------------------------
+    def _drop_prepared(self) -> None:
+        if self._prepared is not None:
+            self.runner.drop_prepared(self._prepared)
+            self._prepared = None
+
+    def _goes_on_unchanged(self, plan: Sequence[Scheduled]) -> bool:
+        """True when the step after this one is known now: nobody waits, every request of the plan takes one token and
+        cannot end by its length with the token this step gives it (it may still end by an end-of-sequence token)."""
+        if self.scheduler.waiting or len(plan) != len(self.scheduler.running):
+            return False
+        top = self.runner.max_model_len
+        return all(s.num_tokens == 1 and s.sample and len(s.request.output) + 1 < s.request.params.max_new_tokens
+                   and s.request.length + 1 < top for s in plan)
+
     def step(self) -> list[tuple[Request, int, bool]]:
         plan = self.scheduler.schedule()
+        prep, self._prepared = self._prepared, None
+        if prep is not None and not (plan and prep.rids == [s.request.rid for s in plan]
+                                     and prep.starts == [s.start for s in plan] and all(s.num_tokens == 1 and s.sample for s in plan)):
+            self.runner.drop_prepared(prep)              # the plan is another than the one foreseen
+            prep = None
         if not plan:
             return []
-        entries = []
-        for s in plan:
-            toks = s.request.tokens[s.start:s.start + s.num_tokens]
-            entries.append(StepEntry(s.request.rid, toks, (s.num_tokens - 1,) if s.sample else ()))
-        logits = self.runner.step(entries)
+        if prep is not None:
+            logits = self.runner.finish_prepared(prep, [s.request.tokens[s.start] for s in plan])
+        else:
+            entries = []
+            for s in plan:
+                toks = s.request.tokens[s.start:s.start + s.num_tokens]
+                entries.append(StepEntry(s.request.rid, toks, (s.num_tokens - 1,) if s.sample else ()))
+            logits = self.runner.step(entries)
         sampled: list[int] = []
         if logits is not None:
             who = [s.request for s in plan if s.sample]
-            sampled = self.sampler.sample(logits, [r.params for r in who], [len(r.output) for r in who])
+            pending = self.sampler.launch(logits, [r.params for r in who], [len(r.output) for r in who])
+            # While the GPU works on this step, the host side of the next one, where it is known already: the
+            # scheduler's plan for it, its pages, its positions and tables; only the token ids are missing.
+            if self._goes_on_unchanged(plan):
+                self._prepared = self.runner.prepare_decode([s.request.rid for s in plan], [True] * len(plan))
+            sampled = self.sampler.collect(pending)
         events = self.scheduler.update(plan, sampled)
+        if self._prepared is not None and any(done for _, _, done in events):
+            self._drop_prepared()                        # somebody met an end-of-sequence token
         for req, tok, done in events:
             if done:
                 self._live.pop(req.rid, None)

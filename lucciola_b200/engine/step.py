@@ -90,6 +90,21 @@ class _Staging:
 
 
 @dataclass
+class PreparedStep:
+    """A step of single tokens whose host side is done (pages taken, the recording's input filled) but for the token
+    ids: see ModelRunner.prepare_decode."""
+    rids: list
+    starts: list[int]
+    shape: tuple
+    host_index: int
+    total: int
+    tokens_in_step: int
+    computed_rows: int
+    wanted_rows: list[int]
+    entries: list
+
+
+@dataclass
 class _Recording:
     graph: object                        # a torch.cuda.CUDAGraph: replay() runs the recorded step again
     logits: Optional[torch.Tensor]       # lives in the graph's memory; valid until the next step
@@ -257,10 +272,48 @@ class ModelRunner:
             self._staging = _Staging(self.device, max(n, 4096) * 2)
         return self._staging
 
+    def prepare_decode(self, rids: Sequence[Hashable], want: Sequence[bool]) -> Optional[PreparedStep]:
+        """The host side of a step that gives each of these running requests one more token, done before the tokens are
+        known (while the GPU still runs the step that produces them): pages are taken and the recording's input is filled.
+        finish_prepared() adds the token ids and replays the recording; drop_prepared() undoes it.  None when the step
+        cannot be prepared (pages are short, or no recording of this batch size exists yet); nothing is taken then.
+        No other step may run between prepare_decode and finish_prepared / drop_prepared."""
+        if not self._can_record or not rids or not all(self.manager.has_request(r) for r in rids):
+            return None
+        entries = [StepEntry(r, (0,), (0,) if w else ()) for r, w in zip(rids, want)]
+        try:
+            return self._step(entries, prepare=True)
+        except (OutOfPages, ValueError):
+            return None
+
+    def finish_prepared(self, prep: PreparedStep, tokens: Sequence[int]) -> Optional[torch.Tensor]:
+        vocab = self.model.vocab_size
+        if len(tokens) != len(prep.rids):
+            raise ValueError(f"{len(tokens)} tokens for {len(prep.rids)} prepared requests")
+        for rid, t in zip(prep.rids, tokens):
+            if not (0 <= int(t) < vocab):
+                raise ValueError(f"request {rid!r}: token id {t} is outside the vocabulary of {vocab}")
+        st = self._staging
+        st.host_np[prep.host_index][:len(tokens)] = tokens          # the token ids lead the buffer
+        st.upload(prep.host_index, prep.total, self._graph_inputs[prep.shape])
+        self.h2d_bytes += 4 * prep.total
+        rec = self._graphs[prep.shape]
+        self._graphs.move_to_end(prep.shape)
+        rec.graph.replay()
+        self._graph_launches += rec.kernels
+        self.graph_replays += 1
+        return self._after_step(prep.entries, prep.tokens_in_step, self._wanted(rec.logits, prep.wanted_rows, prep.computed_rows))
+
+    def drop_prepared(self, prep: PreparedStep) -> None:
+        self.manager.retract_by_one(prep.rids)
+
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run the entries as one batch.  Returns logits [wanted, vocab] (float32, on the device) in the
         order of the entries and of their `want`, or None when nothing is wanted.  The tensor is valid until
         the next step."""
+        return self._step(entries)
+
+    def _step(self, entries: Sequence[StepEntry], prepare: bool = False):
         if not entries:
             return None
         vocab = self.model.vocab_size
@@ -423,6 +476,11 @@ class ModelRunner:
                     elif kind == "all":
                         rows[r:r + n] = np.arange(t, t + n, dtype=np.int32)
                         r += n
+        if prepare:
+            if shape is None or shape not in self._graphs or batch.max_q_len != 1:
+                self.manager.retract_by_one([e.rid for e in entries])
+                return None
+            return PreparedStep([e.rid for e in entries], starts[:S_real], shape, hi, total, T, R, wanted_rows, list(entries))
         dev = self._graph_inputs.get(shape) if shape is not None else None
         if shape is not None and dev is None:
             dev = self._graph_inputs[shape] = torch.empty(total, dtype=torch.int32, device=self.device)

@@ -39,6 +39,11 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], generated: Sequence[int]) -> list[int]:
         """One token for each row; `generated[r]` is how many tokens request r has generated so far."""
+        return self.collect(self.launch(logits, params, generated))
+
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], generated: Sequence[int]):
+        """Start sampling and the copy of the ids to the host; collect() waits for them.  What the host does in
+        between overlaps the GPU's work on the step."""
         R = logits.shape[0]
         tokens = torch.empty(R, dtype=torch.int32, device=self.device)
         stream = torch.cuda.current_stream(self.device).cuda_stream
@@ -51,10 +56,15 @@ class Sampler:
             counters = torch.tensor(list(generated), dtype=torch.int32).to(self.device, non_blocking=True)
             ops.sample(tokens, logits, stream, temps, keys_t, counters)
         if self._done is None:
-            return tokens.cpu().tolist()
+            return tokens
         if self._host is None or self._host.shape[0] < R:
             self._host = torch.empty(max(R, 256), dtype=torch.int32, pin_memory=True)
         self._host[:R].copy_(tokens, non_blocking=True)
         self._done.record()
+        return R
+
+    def collect(self, handle) -> list[int]:
+        if self._done is None:
+            return handle.cpu().tolist()
         self._done.synchronize()
-        return self._host[:R].tolist()
+        return self._host[:handle].tolist()

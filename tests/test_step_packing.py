@@ -288,6 +288,41 @@ def test_state_slots_of_new_requests_are_cleared_inside_recordings_too(host_runn
     assert r.zeroed[-1] == [-1, r.manager.slot("c")]
 
 
+def test_a_step_prepared_ahead_equals_the_step_and_can_be_dropped(host_runner):
+    """prepare_decode does a step's host side before its tokens are known, finish_prepared adds them and replays the
+    recording; the result is that of step().  A prepared step that is dropped leaves the lengths as they were, and the
+    page it may have taken serves the position's real step."""
+    r = host_runner(record=True)
+    for rid, n in (("a", 15), ("b", 16), ("c", 40)):
+        r.step([StepEntry(rid, list(range(n)), [])])
+    assert r.prepare_decode(["a", "b", "c"], [True] * 3) is None               # no recording of this size yet: nothing taken
+    assert [r.length(x) for x in "abc"] == [15, 16, 40]
+    r.step([StepEntry("a", [7], [0]), StepEntry("b", [8], [0]), StepEntry("c", [9], [0])])     # records the step of 4
+    free = r.manager.pools[0].num_free
+    prep = r.prepare_decode(["a", "b", "c"], [True, False, True])
+    assert prep is not None and prep.starts == [16, 17, 41] and [r.length(x) for x in "abc"] == [17, 18, 42]
+    assert r.manager.pools[0].num_free == free - 1                             # a crossed a page boundary
+    got = r.finish_prepared(prep, [100, 200, 300])
+    page = lambda x: r.manager.block_table(x, 0)[0]
+    assert got.tolist() == [[100, 16, 17, page("a"), r.manager.slot("a")], [300, 41, 42, page("c"), r.manager.slot("c")]]
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        r.finish_prepared(r.prepare_decode(["a"], [True]) or r.prepare_decode(["a", "b", "c"], [True] * 3), [1, 2, VOCAB])
+    r.manager.retract_by_one(["a", "b", "c"])                                   # what the failed finish left prepared
+    # dropped: lengths return; the same positions then run as an ordinary step
+    prep = r.prepare_decode(["a", "b", "c"], [True] * 3)
+    assert [r.length(x) for x in "abc"] == [18, 19, 43]
+    r.drop_prepared(prep)
+    assert [r.length(x) for x in "abc"] == [17, 18, 42]
+    r.manager.check_invariants()
+    got = r.step([StepEntry("b", [5], [0]), StepEntry("c", [6], [0])])
+    assert got[:, :3].tolist() == [[5, 18, 19], [6, 42, 43]]
+    assert r.prepare_decode(["a", "zz"], [True, True]) is None                  # an unknown request
+    for x in "abc":
+        r.finish(x)
+    r.manager.check_invariants()
+    assert r.manager.pools[0].num_free == r.manager.pools[0].num_pages
+
+
 def test_a_part_that_cannot_be_recorded_keeps_the_model_from_recordings(monkeypatch):
     monkeypatch.setattr(step_mod, "_Staging", HostStaging)
     model = StandInModel()
