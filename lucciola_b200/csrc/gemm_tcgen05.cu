@@ -954,7 +954,90 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * PF_BN;
-      if (p.swiglu) {
+      // The factor this thread's token lacks (RowScale): its partial sums are asked for together, one round trip a tile.
+      float rf = 1.f;
+      if (p.rs.on) {
+        pdl_wait();
+        rf = m < p.M ? row_factor(p.rs, m) : 0.f;
+      }
+      if (p.an.on) {
+        // The residual add and the first half of the norm that follows (AddNormEpilogue): this thread holds one token's
+        // part of the tile; the residual values of the next 16 features are asked for while these 16 are finished.
+        pdl_wait();
+        const AddNormEpilogue& an = p.an;
+        const bool second = n0 >= plan.cols1 * plan.bn1 && plan.cols1 * plan.bn1 < p.N;
+        const int tile_col = second ? plan.cols1 + (n0 - plan.cols1 * plan.bn1) / plan.bn2 : n0 / plan.bn1;
+        const bool row_ok = m < p.M;
+        const bool vec = (p.N & 7) == 0;
+        float* res_row = an.residual + (size_t)(row_ok ? m : 0) * p.N;
+        bf16* out_row = an.out + (size_t)(row_ok ? m : 0) * p.N;
+        float ss = 0.f;
+        // Two chunks of 16 features are asked for while the two before them are finished: four in flight.
+        float4 nxt[8];
+        auto fetch = [&](int n, float4* dst) {
+          if (row_ok && vec && n + 16 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = *reinterpret_cast<const float4*>(res_row + n + 4 * j);
+          } else {
+            float* f = reinterpret_cast<float*>(dst);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) f[j] = (row_ok && n + j < p.N) ? res_row[n + j] : 0.f;
+          }
+        };
+        fetch(n0, nxt);
+        if (16 < bn) fetch(n0 + 16, nxt + 4);
+#pragma unroll 1
+        for (int c0 = 0; c0 < bn; c0 += 32) {
+          float4 cur[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+          if (c0 + 32 < bn) fetch(n0 + c0 + 32, nxt);
+          if (c0 + 48 < bn) fetch(n0 + c0 + 48, nxt + 4);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int c = c0 + 16 * h;
+            if (c >= bn) break;
+            uint32_t r[16];
+            tmem_ld16(taddr + c, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const int n = n0 + c;
+            if (row_ok && n < p.N) {
+              const float* before = reinterpret_cast<const float*>(cur + 4 * h);
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                v[j] = before[j] + __uint_as_float(r[j]);
+                if (n + j < p.N) ss += v[j] * v[j];
+              }
+              if (vec && n + 16 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  *reinterpret_cast<float4*>(res_row + n + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                uint32_t w[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float4 nw = *reinterpret_cast<const float4*>(an.norm_w + n + 4 * j);
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(v[4 * j] * nw.x, v[4 * j + 1] * nw.y);
+                  __nv_bfloat162 hi = __floats2bfloat162_rn(v[4 * j + 2] * nw.z, v[4 * j + 3] * nw.w);
+                  w[2 * j] = *reinterpret_cast<uint32_t*>(&lo); w[2 * j + 1] = *reinterpret_cast<uint32_t*>(&hi);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(out_row + n);
+                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  if (n + j < p.N) {
+                    res_row[n + j] = v[j];
+                    out_row[n + j] = __float2bfloat16_rn(v[j] * an.norm_w[n + j]);
+                  }
+                }
+              }
+            }
+          }
+        }
+        if (row_ok) an.sumsq[(size_t)m * an.tiles + tile_col] = ss;
+      } else if (p.swiglu) {
         // columns [128b, 128b+64) are gate rows, [128b+64, 128b+128) the up rows of the same 64 features
 #pragma unroll 1
         for (int cc = 0; cc < bn / 2; cc += 16) {
@@ -967,7 +1050,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
           if (m < p.M && feature < (p.N >> 1)) {
             float v[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+            for (int j = 0; j < 16; ++j) v[j] = silu_mul(__uint_as_float(g[j]) * rf, __uint_as_float(u[j]) * rf);
             if (vec_store && feature + 16 <= (p.N >> 1)) {
               if (p.out_dtype == LB_F32) {
                 float4* dst = reinterpret_cast<float4*>((float*)p.y + (size_t)m * p.ldy + feature);
@@ -1002,6 +1085,10 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
         tmem_ld16(taddr + c, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int n = n0 + c;
+        if (p.rs.on) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rf);
+        }
         if (m < p.M && n < p.N) {
           if (vec_store && n + 16 <= p.N) {
             if (p.out_dtype == LB_F32) {
@@ -1119,9 +1206,11 @@ static PrefillPlan prefill_plan_search(int m_tiles, int N, int step, int num_sms
 
 static int g_pair_slots_seen = -1;
 
-// force_bn: 0 choose, else the feature width of the tiles (tests).
-static int launch_prefill(const void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
-                          long long ldy, int swiglu, int force_bn, int pair, cudaStream_t stream) {
+// Which kind of tiles a many-token product uses: pairs of CTAs or single ones, how many token tiles, how many run at a
+// time, and the feature tiles.  force_bn: 0 choose, else the feature width of the tiles (tests); pair: 0 choose, 1 never,
+// 2 always.
+static void prefill_choose(int M, int N, int K, int swiglu, int force_bn, int pair, bool* use_pair_out, int* m_tiles_out,
+                           int* slots_out, PrefillPlan* plan_out) {
   static int num_sms = 0;
   if (num_sms == 0) {
     int dev = 0;
@@ -1172,6 +1261,20 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
     const int top = use_pair ? 8 : 16;
     plan.mb = (int)(mb < 2 ? 2 : mb > top ? top : mb);
   }
+  *use_pair_out = use_pair; *m_tiles_out = m_tiles; *slots_out = slots; *plan_out = plan;
+}
+
+// Feature tiles of a row in that plan: the columns of AddNormEpilogue::sumsq.
+static int prefill_feature_tiles(const PrefillPlan& plan, int N) {
+  const int rest = N - plan.cols1 * plan.bn1;
+  return plan.cols1 + (rest > 0 ? (rest + plan.bn2 - 1) / plan.bn2 : 0);
+}
+
+static int launch_prefill(const void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
+                          long long ldy, int swiglu, int force_bn, int pair, cudaStream_t stream,
+                          const AddNormEpilogue* an = nullptr, const RowScale* rs = nullptr) {
+  bool use_pair; int m_tiles, slots; PrefillPlan plan;
+  prefill_choose(M, N, K, swiglu, force_bn, pair, &use_pair, &m_tiles, &slots, &plan);
   if (use_pair && (plan.bn1 % 32 || plan.bn2 % 32)) { set_error("gemm_tcgen05: pairs of CTAs take tile widths that are multiples of 32"); return 1; }
   const int box1 = use_pair ? plan.bn1 / 2 : plan.bn1, box2 = use_pair ? plan.bn2 / 2 : plan.bn2;
   CUtensorMap mx, mw, mw2;
@@ -1182,6 +1285,11 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
   GemmParams p;
   p.y = const_cast<void*>(y); p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = ldy;
   p.out_dtype = y_dtype; p.cluster = 0; p.swiglu = swiglu;
+  if (an) {
+    p.an = *an; p.an.on = 1;
+    if (p.an.tiles != prefill_feature_tiles(plan, N)) { set_error("gemm_tcgen05: %d columns of partial sums, the plan has %d feature tiles", p.an.tiles, prefill_feature_tiles(plan, N)); return 1; }
+  }
+  if (rs) { p.rs = *rs; p.rs.on = 1; }
   const int rest = N - plan.cols1 * plan.bn1;
   const int num_tiles = m_tiles * (plan.cols1 + (rest > 0 ? (rest + plan.bn2 - 1) / plan.bn2 : 0));
   const int el = y_dtype == LB_F32 ? 4 : 2;
@@ -1270,8 +1378,9 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
                               long long ldy, float* workspace, long long workspace_elems, int* counters,
                               int counters_len, int force_bt, int force_splits, int swiglu, const lb::RowScale* row_scale,
                               cudaStream_t stream) {
-  LB_CHECK_ARG(!row_scale || (swiglu && M <= 256 && row_scale->sumsq && row_scale->tiles > 0),
-               "gemm_tcgen05: a row scale is taken by the few-token product with the fused SwiGLU only (M=%d)", M);
+  LB_CHECK_ARG(!row_scale || ((swiglu || M > 256) && force_bt <= 0 && row_scale->sumsq && row_scale->tiles > 0),
+               "gemm_tcgen05: a row scale is taken by the many-token product (M > 256) and by the few-token product with the "
+               "fused SwiGLU only (M=%d)", M);
   LB_CHECK_ARG(lb::valid_dtype(y_dtype), "gemm_tcgen05: bad output dtype %d", y_dtype);
   LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && ldx >= K && ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
   LB_CHECK_ARG(!swiglu || N % 128 == 0, "gemm_tcgen05: the fused SwiGLU needs gate and up rows in blocks of 64 (N=%d is no multiple of 128)", N);
@@ -1287,7 +1396,7 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
     LB_CHECK_ARG(force_splits == 0 || (fw >= 16 && fw <= lb::PF_BN && fw % 16 == 0 && (!swiglu || fw % 128 == 0)),
                  "gemm_tcgen05: tile width %d is no multiple of 16 (128 with SwiGLU) up to 256", fw);
     LB_CHECK_ARG(force_bt >= -2, "gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", force_bt);
-    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, force_splits, -force_bt, stream)) return rc;
+    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, force_splits, -force_bt, stream, nullptr, row_scale)) return rc;
     LB_CHECK_LAUNCH("gemm_tcgen05 (many tokens)");
     return 0;
   }
@@ -1328,10 +1437,19 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   return 0;
 }
 
-// The plan of a product whose epilogue adds to the residual stream (AddNormEpilogue): token tile and splits, or 0 when
-// the sizes do not allow it.  The epilogue lives in the reduction over a cluster, so the product has to be one that is
-// split over a cluster (few tokens, fewer tiles than SMs).
+// The plan of a product whose epilogue adds to the residual stream (AddNormEpilogue): token tile and splits with few
+// tokens, -1 for the many-token product, 0 when the sizes do not allow it or would not gain.  With few tokens the
+// epilogue lives in the reduction over a cluster, so the product has to be one that is split over a cluster (fewer
+// tiles than SMs).  With many tokens it runs under the main loop of the CTA's next tile; a product with no more tiles
+// than CTAs has no next tile, its epilogues are the end of the kernel, and there the add and the norm as a kernel of
+// their own, spread over all SMs, are the faster (measured at the 8B sizes: 512 tokens 9.2 ms a step against 9.8 with
+// the epilogue, 1024 tokens 14.9 against 15.3; 2048 tokens 27.1 against 26.9, 4096 tokens 56.7 against 55.4).
 static int addnorm_plan(int M, int N, int K, int* bt) {
+  if (M > 256 && K % 8 == 0) {
+    bool use_pair; int m_tiles, slots; lb::PrefillPlan pl;
+    lb::prefill_choose(M, N, K, 0, 0, 0, &use_pair, &m_tiles, &slots, &pl);
+    return (long long)m_tiles * lb::prefill_feature_tiles(pl, N) > slots ? -1 : 0;
+  }
   if (M <= 0 || M > 256 || K % 8) return 0;
   int t = 16;
   int splits = lb_gemm_tcgen05_plan(M, N, K, &t);
@@ -1342,18 +1460,40 @@ static int addnorm_plan(int M, int N, int K, int* bt) {
   return splits;
 }
 
-LB_EXPORT int lb_gemm_tcgen05_addnorm_ok(int M, int N, int K) { return addnorm_plan(M, N, K, nullptr) > 0; }
+LB_EXPORT int lb_gemm_tcgen05_addnorm_ok(int M, int N, int K) { return addnorm_plan(M, N, K, nullptr) != 0; }
+
+// Columns of the partial sums of squares that lb_gemm_tcgen05_addnorm writes for these sizes (0: sizes it does not
+// take): blocks of 128 features with few tokens, the feature tiles of the plan with many.
+LB_EXPORT int lb_gemm_tcgen05_addnorm_tiles(int M, int N, int K) {
+  const int plan = addnorm_plan(M, N, K, nullptr);
+  if (plan == 0) return 0;
+  if (plan > 0) return (N + lb::BM - 1) / lb::BM;
+  bool use_pair; int m_tiles, slots; lb::PrefillPlan pl;
+  lb::prefill_choose(M, N, K, 0, 0, 0, &use_pair, &m_tiles, &slots, &pl);
+  return lb::prefill_feature_tiles(pl, N);
+}
 
 // x[M,K] . w[N,K]^T added to residual [M,N] (float32, in place); out [M,N] (bfloat16) receives residual * norm_w
 // without the row's norm factor, sumsq [M, ceil(N/128)] the partial sums of squares of the new residual from which
 // the reader of `out` forms that factor (see AddNormEpilogue, RowScale).
 LB_EXPORT int lb_gemm_tcgen05_addnorm(const void* x, const void* w, int M, int N, int K, long long ldx, float* residual,
-                                      const float* norm_w, void* out, float* sumsq, cudaStream_t stream) {
+                                      const float* norm_w, void* out, float* sumsq, int sumsq_tiles, cudaStream_t stream) {
   int bt = 16;
   const int splits = addnorm_plan(M, N, K, &bt);
-  LB_CHECK_ARG(splits > 0, "gemm_tcgen05_addnorm: sizes M=%d N=%d K=%d are not taken (a product that is split over a cluster)", M, N, K);
+  LB_CHECK_ARG(splits != 0, "gemm_tcgen05_addnorm: sizes M=%d N=%d K=%d are not taken (many tokens, or a product that is split over a cluster)", M, N, K);
   LB_CHECK_ARG(residual && norm_w && out && sumsq, "gemm_tcgen05_addnorm: null argument");
   LB_CHECK_ARG(ldx >= K && ldx % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05_addnorm: operands must be 16-byte aligned");
+  LB_CHECK_ARG(sumsq_tiles == lb_gemm_tcgen05_addnorm_tiles(M, N, K), "gemm_tcgen05_addnorm: %d columns of partial sums, these sizes write %d",
+               sumsq_tiles, lb_gemm_tcgen05_addnorm_tiles(M, N, K));
+  if (splits < 0) {
+    LB_CHECK_ARG(((uintptr_t)residual % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)norm_w % 16 == 0),
+                 "gemm_tcgen05_addnorm: residual, output and norm weight must be 16-byte aligned");
+    lb::AddNormEpilogue an = {};
+    an.on = 1; an.tiles = sumsq_tiles; an.residual = residual; an.norm_w = norm_w; an.out = (lb::bf16*)out; an.sumsq = sumsq;
+    if (int rc = lb::launch_prefill(nullptr, LB_BF16, x, w, M, N, K, ldx, N, 0, 0, 0, stream, &an, nullptr)) return rc;
+    LB_CHECK_LAUNCH("gemm_tcgen05_addnorm (many tokens)");
+    return 0;
+  }
   CUtensorMap mw, mx;
   if (!lb::cached_map(&mw, w, N, K, K, lb::BM) || !lb::cached_map(&mx, x, M, K, ldx, bt)) {
     lb::set_error("gemm_tcgen05_addnorm: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);

@@ -43,7 +43,7 @@ _SIGNATURES = {
     "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
                         c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "lb_gemm_tcgen05_addnorm": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_void_p],
+                                c_int, c_void_p],
     "lb_upload": [c_void_p, c_void_p, c_longlong, c_void_p],
     "lb_zero_rows": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p],
     "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p],
@@ -294,20 +294,30 @@ def gemm_tcgen05_addnorm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and bool(lib.lb_gemm_tcgen05_addnorm_ok(M, w.shape[0], K)))
 
 
+def gemm_tcgen05_addnorm_tiles(M: int, N: int, K: int) -> int:
+    """Columns of the partial sums of squares that gemm_tcgen05_addnorm writes for these sizes: blocks of 128 features
+    with few tokens, the feature tiles the many-token product chooses otherwise (0: sizes it does not take)."""
+    lib = library()
+    lib.lb_gemm_tcgen05_addnorm_tiles.argtypes = [c_int, c_int, c_int]
+    lib.lb_gemm_tcgen05_addnorm_tiles.restype = c_int
+    return int(lib.lb_gemm_tcgen05_addnorm_tiles(M, N, K))
+
+
 def gemm_tcgen05_addnorm(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor, out: torch.Tensor,
                          sumsq: torch.Tensor, stream: int) -> None:
     """residual += x . w^T; out = (residual * norm_w) rounded to bfloat16, without the factor rsqrt(mean(residual^2) + eps)
-    of the RMSNorm; sumsq[m, t] = sum of residual[m]^2 over the t-th block of 128 features.  The product that reads
+    of the RMSNorm; sumsq[m, t] = sum of residual[m]^2 over the t-th block of features (gemm_tcgen05_addnorm_tiles says
+    how many blocks these sizes have).  The product that reads
     `out` is given `sumsq` and multiplies its sums by the row's factor (a row's factor commutes with a linear map), so
     the add, the copy and the norm between two products cost no kernel of their own."""
     M, K = x.shape
     N = w.shape[0]
     _check(w, "w", torch.bfloat16); _check(residual, "residual", torch.float32); _check(norm_w, "norm weight", torch.float32)
     _check(out, "normed output", torch.bfloat16); _check(sumsq, "partial sums of squares", torch.float32)
-    if tuple(residual.shape) != (M, N) or tuple(out.shape) != (M, N) or tuple(sumsq.shape) != (M, -(-N // 128)) or norm_w.shape[0] != N:
+    if tuple(residual.shape) != (M, N) or tuple(out.shape) != (M, N) or sumsq.shape[0] != M or norm_w.shape[0] != N:
         raise KernelError(f"gemm_tcgen05_addnorm shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, residual {tuple(residual.shape)}, sumsq {tuple(sumsq.shape)}")
     _call("lb_gemm_tcgen05_addnorm", x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0) if M > 1 else K, residual.data_ptr(),
-          norm_w.data_ptr(), out.data_ptr(), sumsq.data_ptr(), stream)
+          norm_w.data_ptr(), out.data_ptr(), sumsq.data_ptr(), sumsq.shape[1], stream)
 
 
 def gemm_tcgen05_heads(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,

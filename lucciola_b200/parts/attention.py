@@ -139,8 +139,9 @@ class GQAttention(Mixer):
                 and ops.gemm_tcgen05_heads_sizes_ok(num_tokens, self.qkv.out_features, self.hidden_size, self.head_dim))
 
     def row_scaled_ok(self, num_tokens: int, write_cache: bool = True) -> bool:
-        """That epilogue also applies the factor that rows without their norm's factor lack."""
-        return self._heads_in_epilogue(num_tokens, write_cache)
+        """That epilogue also applies the factor that rows without their norm's factor lack; so does the many-token
+        product."""
+        return self._heads_in_epilogue(num_tokens, write_cache) or self.qkv.row_scaled_ok(num_tokens)
 
     def _project_out(self, out: torch.Tensor, sink: Optional[NormSink]):
         if sink is not None and self.o.sink_ok(out):
@@ -168,7 +169,7 @@ class GQAttention(Mixer):
             ops.attention(q, out, cache.k, cache.v, step, cache.group, nq, nkv, d, cache.page_size, self.window,
                           self.scale, rt.stream, plan=step.plans.get(self.plan_key()))
             return self._project_out(out.view(T, self.q_size), sink)
-        if scaled is not None:
+        if scaled is not None and not self.qkv.row_scaled_ok(T):
             raise ops.KernelError("this mixer was handed rows without their norm factor for a step it cannot take them in")
         if write_cache:
             qkv = self.qkv.forward(h)

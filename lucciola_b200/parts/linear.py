@@ -54,14 +54,23 @@ class Linear(Part):
         """sink.residual += x . W^T, and the sum times the sink's norm weight, without the row's factor, handed on."""
         M, N = x.shape[0], self.weight.shape[0]
         out = self.rt.empty((M, N))
-        sumsq = self.rt.empty((M, -(-N // 128)), torch.float32)
+        sumsq = self.rt.empty((M, ops.gemm_tcgen05_addnorm_tiles(M, N, x.shape[1])), torch.float32)
         ops.gemm_tcgen05_addnorm(x, self.weight, sink.residual, sink.weight, out, sumsq, self.rt.stream)
         return RowScaled(out, sumsq, N, sink.eps)
 
-    def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, rows: int | None = None) -> torch.Tensor:
-        """y = x . W^T; with `rows`, only the first `rows` output features."""
+    def row_scaled_ok(self, num_tokens: int) -> bool:
+        """Whether forward() takes rows without their norm's factor: the many-token product applies it in its epilogue."""
+        return self.rt.fast_kernels and num_tokens > 256 and self.in_features % 8 == 0
+
+    def forward(self, x, out_dtype: torch.dtype | None = None, rows: int | None = None) -> torch.Tensor:
+        """y = x . W^T; with `rows`, only the first `rows` output features.  x: a tensor, or RowScaled."""
         M = x.shape[0]
         w = self.weight if rows is None else self.weight[:rows]
         y = self.rt.empty((M, w.shape[0]), out_dtype or self.rt.act_dtype)
+        if isinstance(x, RowScaled):
+            if not (self.row_scaled_ok(M) and ops.gemm_tcgen05_ok(y, x.x, w)):
+                raise ops.KernelError("this product was handed rows without their norm factor for sizes it cannot take them in")
+            ops.gemm_tcgen05(y, x.x, w, self.rt.stream, sumsq=x.sumsq, eps=x.eps)
+            return y
         ops.linear(y, x, w, self.rt.stream, fast=self.rt.fast_kernels)
         return y

@@ -39,8 +39,8 @@ class SwiGLUFeedForward(FeedForward):
     accepts_sink = True
 
     def row_scaled_ok(self, num_tokens: int) -> bool:
-        """The few-token product with the activation in its epilogue also applies a row's norm factor there."""
-        return self.fused and num_tokens <= 256
+        """The products with the activation in their epilogue also apply a row's norm factor there."""
+        return self.fused
 
     def _down(self, act: torch.Tensor, sink: Optional[NormSink]):
         if sink is not None and self.down.sink_ok(act):
