@@ -19,6 +19,8 @@ decode step of the whole batch.  The line printed at the end is one JSON object:
                 decode_bN_ctx768   the 8B shape, N = 1, 8, 64 requests, prompts of 512 tokens, 256 new tokens each
                 mixed14b           the 14B shape: every step 32 decoding requests and one 512-token portion of a
                                    2048-token prompt (compute-bound: FLOPs / time / peak)
+                mixed8b            the 8B shape: 32 requests decoding at the run's context, alone and beside a
+                                   portion of 8 and of 512 tokens of a new prompt (step function, device-timed)
                 pressure32b        the 32B shape: 64 requests with prompts of 4096 tokens and 256 new tokens each, in a
                                    pool with fewer pages than they need together, so that the scheduler preempts
               (--no-points skips them; --only-points runs nothing else)
@@ -190,6 +192,47 @@ def run_ctx768(engine, cfg, layers, rng, pk, batches=(64, 8, 1)) -> dict:
     return out
 
 
+def run_mixed8b(runner, cfg, rng, ctx, B=32, steps=10) -> dict:
+    """What a few tokens of a prompt cost beside decoding requests: B requests at the context, then steps of their
+    single tokens alone, with a portion of 8 tokens and with one of 512 tokens of a new request (lucciola's schedule
+    puts a portion beside the running requests in every step while a prompt waits, src/scheduler.cc:51-120)."""
+    import torch
+    from lucciola_b200.engine.step import StepEntry
+    V = cfg["vocab_size"]
+    for j in range(B):
+        left = ctx - 6 * (steps + 4) - 8
+        while left > 0:
+            n = min(left, 2048)
+            runner.step([StepEntry(("m", j), rng.integers(0, V, size=n).tolist(), [])])
+            left -= n
+    out, fresh = {}, [0]
+    for portion in (0, 8, 512):
+        def entries():
+            e = [StepEntry(("m", j), [int(rng.integers(0, V))], [0]) for j in range(B)]
+            if portion:
+                fresh[0] += 1
+                e.append(StepEntry(("mp", fresh[0]), rng.integers(0, V, size=portion).tolist(), []))
+            return e
+        def one():
+            runner.step(entries())
+            if portion:
+                runner.finish(("mp", fresh[0]))
+        for _ in range(4):
+            one()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            one()
+        b.record()
+        torch.cuda.synchronize()
+        out[f"mixed8b_b{B}_portion{portion}_ms"] = round(a.elapsed_time(b) / steps, 3)
+    for j in range(B):
+        runner.finish(("m", j))
+    out[f"mixed8b_b{B}_portion8_over_alone"] = round(out[f"mixed8b_b{B}_portion8_ms"] / out[f"mixed8b_b{B}_portion0_ms"], 4)
+    return out
+
+
 def run_mixed14b(rng, pk, layers=0, steps=40) -> dict:
     """32 requests decode while prompts of 2048 tokens are read in portions of 512: every timed step holds 32 single
     tokens and one portion (lucciola's schedule: all running requests, then one portion, src/scheduler.cc:51-120)."""
@@ -297,11 +340,16 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 and the other workloads")
-    ap.add_argument("--workloads", default="ctx768,mixed14b,pressure32b",
+    ap.add_argument("--workloads", default="ctx768,mixed8b,mixed14b,pressure32b",
                     help="which of the other workloads run (comma-separated; empty: none)")
     ap.add_argument("--workload-layers", type=int, default=0,
                     help="fewer layers for the 14B and 32B workloads than their configurations have (reported with them)")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps from CUDA graphs")
+    ap.add_argument("--fuse-norms", choices=["both", "entry", "middle", "none"], default="both",
+                    help="where the residual add and the norm between two products run inside those products' epilogues: "
+                         "between a block's feed-forward and the next block's mixer (entry), between mixer and feed-forward "
+                         "(middle), both (the default), or none: always as a kernel of their own (for comparisons)")
+    ap.add_argument("--no-fuse-norms", action="store_true", help="the same as --fuse-norms none")
     ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], default=None,
                     help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off); "
                          "mixed: --batch decoding requests at --context and one portion of --portion tokens of a new prompt")
@@ -328,6 +376,11 @@ def main() -> int:
     from lucciola_b200.engine.step import StepEntry
     from lucciola_b200.sampling.params import SamplingParams
 
+    if args.no_fuse_norms:
+        args.fuse_norms = "none"
+    if args.fuse_norms != "both":
+        from lucciola_b200.parts.block import PreNormBlock
+        PreNormBlock.fuse_norms = args.fuse_norms
     pk = peaks()
     shape_name, shape = SHAPES[args.shape]
     full_layers = shape["num_hidden_layers"]
@@ -473,6 +526,11 @@ def main() -> int:
             extra.update(run_ctx768(engine, cfg, args.layers, rng, pk))
         except Exception as e:                                       # noqa: BLE001
             extra["ctx768_error"] = f"{type(e).__name__}: {e}"[:200]
+    if "mixed8b" in workloads and max_b >= 32:
+        try:
+            extra.update(run_mixed8b(runner, cfg, rng, ctx))
+        except Exception as e:                                       # noqa: BLE001
+            extra["mixed8b_error"] = f"{type(e).__name__}: {e}"[:200]
     err = ops.device_error()
     if any(w in workloads for w in ("mixed14b", "pressure32b")):
         import gc
@@ -500,7 +558,7 @@ def main() -> int:
                    "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"], "global_batch": args.batch, "seq_len": ctx,
                    "context_len": main_r["final_context"], "page_size": page, "parallelism": "single GPU",
-                   "cuda_graph": bool(options.use_cuda_graph), "l2": "inputs larger than L2 (%.0f GB of weights a step)" % (weight_bytes / 1e9),
+                   "cuda_graph": bool(options.use_cuda_graph), "fused_norms": args.fuse_norms, "l2": "inputs larger than L2 (%.0f GB of weights a step)" % (weight_bytes / 1e9),
                    "prefill_tokens": T, "peaks": pk["source"]},
         "e2e": main_r.get("e2e"),
         "gpu_launches": int(main_r["launches"]),

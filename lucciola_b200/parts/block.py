@@ -14,7 +14,10 @@ from .base import Block, FeedForward, Mixer, Norm, NormSink, Part, RowScaled, St
 
 class PreNormBlock(Block):
     accepts_next_sink = True
-    fuse_norms = True           # False: the add and the norm between two products always run as a kernel of their own
+    # Where the add and the norm between two products may run inside those products (see forward): "both", or only at
+    # the block's "entry" (the block before -> this block's mixer), only in its "middle" (mixer -> feed-forward), or
+    # "none": always as a kernel of their own.  For comparisons.
+    fuse_norms = "both"
     recordable = True
 
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm, act_dtype: torch.dtype):
@@ -28,7 +31,7 @@ class PreNormBlock(Block):
     def entry_sink(self, residual: torch.Tensor, num_tokens: int, write_cache: bool) -> Optional[NormSink]:
         """The block before may add its output to the residual stream itself and hand it over without the first norm's
         factor, when this block's mixer can take rows in that form for this step."""
-        if self.fuse_norms and self.mixer.row_scaled_ok(num_tokens, write_cache):
+        if self.fuse_norms in ("both", "entry") and self.mixer.row_scaled_ok(num_tokens, write_cache):
             return self.mixer_norm.as_sink(residual)
         return None
 
@@ -38,7 +41,7 @@ class PreNormBlock(Block):
         # where the product before and the product after can, inside those two (NormSink, RowScaled).
         h = delta if isinstance(delta, RowScaled) else self.mixer_norm.add_forward(residual, delta, self.act_dtype)
         sink = None
-        if self.fuse_norms and self.mixer.accepts_sink and self.feed_forward.row_scaled_ok(step.num_tokens):
+        if self.fuse_norms in ("both", "middle") and self.mixer.accepts_sink and self.feed_forward.row_scaled_ok(step.num_tokens):
             sink = self.ffn_norm.as_sink(residual)
         a = self.mixer.forward(h, step, cache, write_cache, sink=sink) if sink is not None else self.mixer.forward(h, step, cache, write_cache)
         h = a if isinstance(a, RowScaled) else self.ffn_norm.add_forward(residual, a, self.act_dtype)
