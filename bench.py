@@ -23,7 +23,7 @@ decode step of the whole batch.  The line printed at the end is one JSON object:
                                    portion of 8 and of 512 tokens of a new prompt (step function, device-timed)
                 pressure32b        the 32B shape: 64 requests with prompts of 4096 tokens and 256 new tokens each, in a
                                    pool with fewer pages than they need together, so that the scheduler preempts
-              (--no-points skips them; --only-points runs nothing else)
+              (--no-points skips them; --workloads chooses among them)
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures 6650 GB/s and 1590 TFLOP/s.  The timed work reads far more than the 126 MB of L2
@@ -253,32 +253,37 @@ def run_mixed14b(rng, pk, layers=0, steps=40) -> dict:
     while any(not r.output for r in decoders):
         engine.step()
     one = SamplingParams(max_new_tokens=1, ignore_eos=True)          # a prompt leaves when it has been read
-    warm = 12
-    for _ in range((warm + steps) // 4 + 2):
-        engine.add_request(rng.integers(0, V, size=prompt).tolist(), one)
-    for _ in range(warm):
-        engine.step()
-    torch.cuda.synchronize()
-    tokens0, launches0 = engine.runner.tokens_run, engine.runner.kernel_launches()
-    replays0 = engine.runner.graph_replays
-    left = [steps]
-    def more():
-        left[0] -= 1
-        return left[0] >= 0
-    ms = timed_steps(engine, torch, more)
-    tokens = engine.runner.tokens_run - tokens0
     per_layer, _, _ = model_bytes_and_flops(cfg, layers)
     nq, d, H = cfg["num_attention_heads"], cfg["head_dim"], cfg["hidden_size"]
-    ctx_decode = sum(r.num_computed for r in decoders) / D
-    flops_step = (2.0 * (D + chunk) * per_layer * layers                                   # every product of the layers
-                  + layers * nq * 4.0 * d * (D * ctx_decode + chunk * (prompt / 2))       # attention: decoded rows, mean portion
-                  + 2.0 * (D + 1) * V * H)                                                # the output head on 33 rows
-    mean_ms = sum(ms) / len(ms)
-    out = {"mixed14b_tokens_per_s": round(tokens / sum(ms) * 1e3, 1), "mixed14b_tokens_per_step": round(tokens / len(ms), 1),
-           "mixed14b_frac": round(flops_step / (mean_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-           "mixed14b_layers": layers, "mixed14b_replayed_steps": engine.runner.graph_replays - replays0,
-           "mixed14b_launches_per_step": round((engine.runner.kernel_launches() - launches0) / len(ms), 1)}
-    out.update({f"mixed14b_{k}": v for k, v in percentiles(ms).items()})
+    out = {"mixed14b_layers": layers}
+    # as specified (portions of 512 tokens: 544 tokens a step), then with the scheduler's token_tile option (portions
+    # shortened so that a step's tokens fill whole tiles of 128: 512 tokens a step)
+    for key, tile in (("mixed14b", 0), ("mixed14b_tile128", 128)):
+        engine.scheduler.token_tile = tile
+        warm = 12
+        while len(engine.scheduler.waiting) < (warm + steps) // 4 + 3:
+            engine.add_request(rng.integers(0, V, size=prompt).tolist(), one)
+        for _ in range(warm):
+            engine.step()
+        torch.cuda.synchronize()
+        tokens0, launches0 = engine.runner.tokens_run, engine.runner.kernel_launches()
+        replays0 = engine.runner.graph_replays
+        left = [steps]
+        def more():
+            left[0] -= 1
+            return left[0] >= 0
+        ms = timed_steps(engine, torch, more)
+        tokens = engine.runner.tokens_run - tokens0
+        ctx_decode = sum(r.num_computed for r in decoders) / D
+        portion_tokens = tokens - D * len(ms)
+        flops = (2.0 * tokens * per_layer * layers                                              # every product of the layers
+                 + layers * nq * 4.0 * d * (D * ctx_decode * len(ms) + portion_tokens * (prompt / 2))   # attention
+                 + 2.0 * (D + 1) * V * H * len(ms))                                             # the output head on 33 rows
+        out.update({f"{key}_tokens_per_s": round(tokens / sum(ms) * 1e3, 1), f"{key}_tokens_per_step": round(tokens / len(ms), 1),
+                    f"{key}_frac": round(flops / (sum(ms) * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    f"{key}_replayed_steps": engine.runner.graph_replays - replays0,
+                    f"{key}_launches_per_step": round((engine.runner.kernel_launches() - launches0) / len(ms), 1)})
+        out.update({f"{key}_{k}": v for k, v in percentiles(ms).items()})
     return out
 
 

@@ -19,6 +19,7 @@ class EngineOptions:
     mem_fraction: float = 0.90         # share of free memory for pages when max_blocks == 0
     max_tokens_per_step: int = 576     # token budget of one step (decoded tokens count first)
     prefill_chunk: int = 0             # largest portion of one prompt in a step; 0 = the budget
+    token_tile: int = 0                # > 1: portions are shortened so that a step's tokens fill whole tiles of this many
     max_num_seqs: int = 256            # most requests that run at a time
     max_model_len: int = 0             # longest sequence; 0 = max_position_embeddings
     use_cuda_graph: bool = True        # record steps whose shape comes again as CUDA graphs and replay them
@@ -39,5 +40,5 @@ class EngineOptions:
             raise ValueError("max_tokens_per_step and max_num_seqs must be positive")
         if self.graph_after < 1 or self.max_shape_graphs < 1:
             raise ValueError("graph_after and max_shape_graphs must be at least 1")
-        if self.prefill_chunk < 0 or self.max_model_len < 0:
-            raise ValueError("prefill_chunk and max_model_len must not be negative")
+        if self.prefill_chunk < 0 or self.max_model_len < 0 or self.token_tile < 0:
+            raise ValueError("prefill_chunk, max_model_len and token_tile must not be negative")

@@ -41,7 +41,7 @@ class Engine:
         self.options = runner.options
         self.scheduler = Scheduler(runner.manager, self.options.max_tokens_per_step, self.options.max_num_seqs,
                                    runner.max_model_len, self.options.prefill_chunk, runner.model.eos_token_ids,
-                                   release=runner.finish)
+                                   release=runner.finish, token_tile=self.options.token_tile)
         self.sampler = Sampler(runner.device)
         self._next_id = 1
         self._live: dict[int, Request] = {}              # requests that have not finished, by id

@@ -16,6 +16,9 @@ What it decides differently:
     generated, so its output is the same as without the preemption.  (lucciola moves such a
     request to a queue that nothing reads again, src/scheduler.cc:33-40: the request is lost.)
   * A request that could never fit the pool on its own is refused when it is added.
+  * With `token_tile` set, a portion that is not its prompt's last is shortened so that the step's tokens up to and
+    including it are a multiple of the tile: the many-token products work on tiles of 128 tokens, and 32 decoded tokens
+    beside a portion of 512 make them compute five tiles for 4.25 tiles of tokens.
 """
 from __future__ import annotations
 
@@ -38,7 +41,7 @@ class Scheduled:
 class Scheduler:
     def __init__(self, manager: CacheManager, max_tokens_per_step: int, max_num_seqs: int, max_model_len: int,
                  prefill_chunk: int = 0, eos_token_ids: Iterable[int] = (),
-                 release: Optional[Callable[[Hashable], None]] = None):
+                 release: Optional[Callable[[Hashable], None]] = None, token_tile: int = 0):
         """`release(rid)` gives back all that a request holds; whoever keeps more per request than the cache
         manager does (the runner's converted block tables) passes its own."""
         self.manager = manager
@@ -47,6 +50,7 @@ class Scheduler:
         self.max_num_seqs = min(max_num_seqs, manager.num_slots)
         self.max_model_len = max_model_len
         self.prefill_chunk = prefill_chunk
+        self.token_tile = token_tile
         self.eos_token_ids = frozenset(eos_token_ids)
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
@@ -111,6 +115,16 @@ class Scheduler:
             self._release_fn(rid)
         elif self.manager.has_request(rid):
             self.manager.release(rid)
+
+    def _aligned(self, n: int, r: Request, budget: int) -> int:
+        """The portion of n tokens, shortened so that the step's tokens so far plus the portion fill whole token tiles;
+        unchanged when it is the prompt's last portion, or when less than half of it would be left."""
+        tile = self.token_tile
+        if tile <= 1 or n >= r.remaining:
+            return n
+        used = self.max_tokens_per_step - budget
+        shorter = (used + n) // tile * tile - used
+        return shorter if shorter >= max(1, n // 2) else n
 
     def _preempt(self, r: Request) -> None:
         self._release(r.rid)
@@ -183,12 +197,15 @@ class Scheduler:
         for r in sorted((r for r in self.running if r.remaining > 1), key=lambda r: r.admitted_at):
             if budget <= 0:
                 break
-            n = min(budget, self.prefill_chunk or budget, r.remaining)
+            most = min(budget, self.prefill_chunk or budget, r.remaining)
+            n = self._aligned(most, r, budget)
             n = min(n, self._largest_fit(r, r.num_computed + n, reserved) - r.num_computed)
             if n <= 0:
                 blocked = True
                 break
             take(r, n)
+            if n < most and self.token_tile > 1:
+                budget = 0                    # the step ends on a tile's edge: what is left of the budget stays unused
 
         # 3. New requests, first come first served, while there is budget and a slot.  A request is
         # admitted only when the pages for all it has to run (its prompt, and what it had generated
@@ -197,13 +214,16 @@ class Scheduler:
             r = self.waiting[0]
             if not self._fits(self._pages_needed(r, r.length), reserved):
                 break
-            n = min(budget, self.prefill_chunk or budget, r.remaining)
+            most = min(budget, self.prefill_chunk or budget, r.remaining)
+            n = self._aligned(most, r, budget)
             self.waiting.popleft()
             r.status = Status.RUNNING
             r.admitted_at = self._admissions
             self._admissions += 1
             self.running.append(r)
             take(r, n)
+            if n < most:
+                budget = 0
 
         self.num_steps += bool(plan)
         self.num_scheduled_tokens += sum(s.num_tokens for s in plan)

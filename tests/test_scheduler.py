@@ -22,10 +22,10 @@ def next_token(tokens):
     return h % VOCAB
 
 
-def make(pages=64, page=4, budget=16, seqs=8, max_len=256, chunk=0, eos=(), window=0):
+def make(pages=64, page=4, budget=16, seqs=8, max_len=256, chunk=0, eos=(), window=0, **kw):
     groups = [CacheGroup(2, 16, 0, (0,))] + ([CacheGroup(2, 16, window, (1,))] if window else [])
     m = CacheManager(groups, page, pages, seqs)
-    return m, Scheduler(m, budget, seqs, max_len, chunk, eos)
+    return m, Scheduler(m, budget, seqs, max_len, chunk, eos, **kw)
 
 
 def run_step(m, s, log=None):
@@ -85,6 +85,60 @@ def test_decodes_go_first_and_the_rest_of_the_budget_goes_to_prompts():
     assert log[-1] == [(1, 6, 1, True), (2, 4, 3, True), (3, 0, 6, False)]
     run_step(m, s, log)                       # a and b decode first, then c continues with 8
     assert log[-1] == [(1, 7, 1, True), (2, 7, 1, True), (3, 6, 8, False)]
+
+
+def test_portions_shortened_to_fill_whole_token_tiles():
+    """token_tile 8, budget 21, portions of up to 16: beside 3 decoding requests a portion of 16 makes a step of 19 (21 with
+    two tokens of the next prompt); it is shortened to 13 so that the step has 16 and ends there.  A prompt's last portion is left alone, and the output is
+    what it is without the option."""
+    outs = {}
+    for tile in (0, 8):
+        m, s = make(pages=200, budget=21, chunk=16, token_tile=tile)
+        rs = [req(i, 5, new=40) for i in range(3)] + [req(9, 70, new=3), req(10, 30, new=3)]
+        for r in rs[:3]:
+            s.add_request(r)
+        while any(not r.output for r in rs[:3]):
+            run_step(m, s)
+        s.add_request(rs[3])
+        s.add_request(rs[4])                       # a second prompt waits: it must not fill what the shortening left
+        log = []
+        while s.has_unfinished():
+            run_step(m, s, log)
+        outs[tile] = [r.output for r in rs]
+        portions = [[e for e in step if e[0] == 9 and e[2] > 1] for step in log]
+        sizes = [(sum(e[2] for e in step), p[0][2]) for step, p in zip(log, portions) if p]
+        if tile:
+            assert sizes[:-1] and all(total % 8 == 0 for total, _ in sizes[:-1]), sizes       # every step but the prompt's last
+            assert sizes[0] == (16, 13)
+            assert sum(n for _, n in sizes) == 70
+        else:
+            assert sizes[0] == (21, 16)                   # the second prompt takes what is left of the budget
+        assert all(r.output == expected_output(r) for r in rs)
+    assert outs[0] == outs[8]
+
+
+def test_the_release_callback_sees_every_request_that_gives_up_its_pages():
+    """Whoever keeps more per request than the cache manager (the runner's converted block tables) passes `release`:
+    it is called when a request finishes, is preempted or is aborted."""
+    seen = []
+    groups = [CacheGroup(2, 16, 0, (0,))]
+    m = CacheManager(groups, 4, 10, 8)
+    def release(rid):
+        seen.append(rid)
+        if m.has_request(rid):
+            m.release(rid)
+    s = Scheduler(m, 16, 8, 256, 0, (), release=release)
+    rs = [req(i, 9, new=16) for i in range(3)]
+    for r in rs:
+        s.add_request(r)
+    for _ in range(6):
+        run_step(m, s)
+    assert s.abort(rs[0].rid)
+    while s.has_unfinished():
+        run_step(m, s)
+    assert s.num_preemptions > 0 and rs[0].rid in seen and {r.rid for r in rs} <= set(seen)
+    assert len(seen) >= 3 + s.num_preemptions
+    assert m.num_requests() == 0 and m.pools[0].num_free == 10
 
 
 def test_prefill_chunk_option_and_several_prompts_in_one_step():
