@@ -411,7 +411,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (ok && p.an.on && p.cluster > 0) {
       // The residual values of the first tokens this CTA finishes, on their way while the tile goes to shared memory.
       pdl_wait();
-      const int per = BT / p.cluster, j0 = split * per, j1 = min((split + 1) * per, p.M - m0);
+      const int per = (BT + p.cluster - 1) / p.cluster, j0 = split * per, j1 = min(min((split + 1) * per, BT), p.M - m0);
 #pragma unroll
       for (int u = 0; u < 4; ++u)
         an_before[u] = (j0 + u < j1 && n < p.N) ? p.an.residual[(size_t)(m0 + j0 + u) * p.N + n] : 0.f;
@@ -527,13 +527,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int quarter = warp & 3;
       const int nl = quarter * 32 + lane;
       const int n = n0 + nl;
-      const int per = BT / p.cluster;                 // columns (tokens) of the tile this CTA adds up
+      const int per = (BT + p.cluster - 1) / p.cluster;   // columns (tokens) of the tile this CTA adds up
+      const int jend = min((split + 1) * per, BT);
       const uint32_t base = smem_base + (uint32_t)nl * 4u;
       if (p.swiglu) {
         if (p.rs.on) pdl_wait();
         const int f = nl & 63, feature = (n0 >> 1) + f;
         if (feature < (p.N >> 1)) {
-          for (int j = split * per + (nl >> 6); j < (split + 1) * per; j += 2) {
+          for (int j = split * per + (nl >> 6); j < jend; j += 2) {
             const int m = m0 + j;
             if (m >= p.M) break;
             const uint32_t a = smem_base + (uint32_t)j * (BM * 4u) + (uint32_t)f * 4u;
@@ -571,7 +572,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           if (lane == 0) tok_rf[t] = f;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        for (int j = split * per; j < (split + 1) * per; ++j) {
+        for (int j = split * per; j < jend; ++j) {
           const int m = m0 + j;
           if (m >= p.M) break;                                        // the same for every thread
           float v = cluster_sum_f32(base + (uint32_t)j * (BM * 4u), splits) * tok_rf[j - split * per];
@@ -611,7 +612,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const AddNormEpilogue& an = p.an;
         float* scratch = reinterpret_cast<float*>(smem) + BT * BM;      // behind the partial tile: 4 warp sums a token
         const float w_n = an_w;
-        const int j0 = split * per, j1 = min((split + 1) * per, p.M - m0);
+        const int j0 = split * per, j1 = min(jend, p.M - m0);
         for (int jb = j0; jb < j1; jb += 4) {
           float before[4], acc[4];
 #pragma unroll
@@ -640,7 +641,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           an.sumsq[(size_t)(m0 + j0 + nl) * an.tiles + blockIdx.x] = sl[0] + sl[1] + sl[2] + sl[3];
         }
       } else if (n < p.N) {
-        for (int j = split * per; j < (split + 1) * per; ++j) {
+        for (int j = split * per; j < jend; ++j) {
           const int m = m0 + j;
           if (m >= p.M) break;
           const float acc = cluster_sum_f32(base + (uint32_t)j * (BM * 4u), splits);
@@ -1360,10 +1361,18 @@ LB_EXPORT int lb_gemm_tcgen05_plan(int M, int N, int K, int* bt) {
   const int kb = (K + lb::BK - 1) / lb::BK;
   int splits = 1;
   if (tiles < 148 && M <= 256) {       // splitting pays only while the weights are what is streamed
-    splits = 296 / tiles;                // all CTAs in one wave of two per SM
-    if (splits > kb / 4) splits = kb / 4;
-    // A power of two up to 8: the splits of a tile then form a cluster and add up through shared memory.
-    splits = splits >= 8 ? 8 : splits >= 4 ? 4 : splits >= 2 ? 2 : 1;
+    // The splits of a tile form a thread-block cluster that adds up through shared memory: any count up to 8.  As many
+    // as keep the launch within 256 CTAs: clusters are placed inside a GPC (18 or 20 SMs, two CTAs an SM), and
+    // beyond about 240-256 CTAs some of them wait for a second round (measured at 8 tokens, back to back, us: q|k|v of the
+    // 8B shape, 48 tiles: 4 splits 13.1, 5 splits 11.8, 6 splits 17.3; o, 32 tiles: 4 splits 10.9, 7 splits 8.8, 8
+    // splits 8.9; o of the 14B shape, 40 tiles: 4 splits 13.2, 6 splits 11.9, 7 splits 17.6).
+    for (int s = 2; s <= 8; ++s)
+      if (tiles * s <= 256 && s <= kb / 4) splits = s;
+    if (splits == 1) {                   // more than 128 tiles: two splits where they still fit one round of two CTAs an SM
+      splits = 296 / tiles;
+      if (splits > kb / 4) splits = kb / 4;
+      splits = splits >= 2 ? 2 : 1;
+    }
   }
   return splits;
 }
@@ -1413,7 +1422,7 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   if (splits > kb) splits = kb;
   if (splits > 16) splits = 16;            // the reduction holds at most 16 partials of an element at a time
   const long long tiles = (long long)((N + lb::BM - 1) / lb::BM) * ((M + bt - 1) / bt);
-  const bool cluster_ok = !workspace_path && splits <= 8 && (splits & (splits - 1)) == 0 && bt % splits == 0;
+  const bool cluster_ok = !workspace_path && splits <= 8;
   if (swiglu && splits > 1 && !cluster_ok) splits = 1;       // the pairing of gate and up is done in shared memory
   if (splits > 1 && !cluster_ok && (workspace == nullptr || counters == nullptr || (long long)splits * M * N > workspace_elems ||
                                     tiles > counters_len))
@@ -1429,7 +1438,7 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   p.y = y; p.workspace = workspace; p.counters = counters; p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.out_dtype = y_dtype;
   // Clusters when the split count allows it and the caller did not ask for the workspace path
   // (force_splits < 0 asks for -force_splits splits through the workspace).
-  p.cluster = (!workspace_path && splits > 1 && splits <= 8 && (splits & (splits - 1)) == 0 && bt % splits == 0) ? splits : 0;
+  p.cluster = (!workspace_path && splits > 1 && splits <= 8) ? splits : 0;
   p.swiglu = swiglu;
   if (row_scale) { p.rs = *row_scale; p.rs.on = 1; }
   if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
@@ -1455,7 +1464,7 @@ static int addnorm_plan(int M, int N, int K, int* bt) {
   int splits = lb_gemm_tcgen05_plan(M, N, K, &t);
   const int kb = (K + lb::BK - 1) / lb::BK;
   if (splits > kb) splits = kb;
-  if (splits < 2 || splits > 8 || (splits & (splits - 1)) || t % splits) return 0;
+  if (splits < 2 || splits > 8) return 0;
   if (bt) *bt = t;
   return splits;
 }
@@ -1520,7 +1529,7 @@ static int heads_plan(int M, int N, int K, int head_dim, int* bt) {
   int splits = lb_gemm_tcgen05_plan(M, N, K, &t);
   const int kb = (K + lb::BK - 1) / lb::BK;
   if (splits > kb) splits = kb;
-  if (splits < 2 || splits > 8 || (splits & (splits - 1)) || t % splits) return 0;
+  if (splits < 2 || splits > 8) return 0;
   if (bt) *bt = t;
   return splits;
 }
