@@ -1,5 +1,5 @@
-from .base import (Block, FeedForward, KVCacheView, KVPages, Mixer, Norm, ParamSpec, Part, PositionEncoding, Runtime,
-                   StateCacheView, StateSlot, StepContext)
+from .base import (BatchShape, Block, FeedForward, KVCacheView, KVPages, Mixer, Norm, NormSink, ParamSpec, Part, PlanView,
+                   PositionEncoding, RowScaled, Runtime, StateCacheView, StateSlot, StepContext, StepPlan)
 from .attention import GQAttention
 from .block import PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
@@ -9,7 +9,7 @@ from .norm import RMSNorm
 from .rope import RotaryEmbedding
 
 __all__ = [
-    "Block", "FeedForward", "KVCacheView", "KVPages", "Mixer", "Norm", "ParamSpec", "Part", "PositionEncoding",
-    "Runtime", "StateCacheView", "StateSlot", "StepContext", "GQAttention", "PreNormBlock", "OutputHead",
+    "BatchShape", "Block", "FeedForward", "KVCacheView", "KVPages", "Mixer", "Norm", "NormSink", "ParamSpec", "Part", "PlanView",
+    "PositionEncoding", "RowScaled", "Runtime", "StateCacheView", "StateSlot", "StepContext", "StepPlan", "GQAttention", "PreNormBlock", "OutputHead",
     "TokenEmbedding", "Linear", "SwiGLUFeedForward", "RMSNorm", "RotaryEmbedding",
 ]

@@ -381,6 +381,121 @@ def test_toy_mixer_with_state_is_recorded_and_replayed(tmp_path):
     runner.manager.check_invariants()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_norm_and_toy_block_between_the_frameworks_blocks(tmp_path, dtype):
+    """A norm defined here (centred: subtract the mean, divide by the standard deviation, weight and bias) and a block
+    arrangement defined here (post-norm: r = norm(r + mixer(r)); r = norm(r + ffn(r)), no keyword for what follows it),
+    as the middle one of three layers whose outer two are the framework's pre-norm blocks at sizes where those hand their
+    output on inside the products' epilogues.  The model must take the plain path around the toy block and still be right,
+    whole, in portions and token by token (recorded in bfloat16: the toy parts only launch work)."""
+    from lucciola_b200.config import EngineOptions, register_architecture
+    from lucciola_b200.engine.load import build_runner
+    from lucciola_b200.engine.step import StepEntry
+    from lucciola_b200.models import DecoderModel, LayerCall
+    from lucciola_b200.parts import (Block, GQAttention, Norm, OutputHead, ParamSpec, PreNormBlock, RMSNorm, RotaryEmbedding,
+                                     Runtime, SwiGLUFeedForward, TokenEmbedding)
+    from lucciola_b200.weights import write_safetensors
+    from lucciola_b200.weights.random_init import RandomWeights
+
+    class CentredNorm(Norm):
+        recordable = True
+
+        def __init__(self, rt, prefix, size, eps):
+            self.rt, self.prefix, self.size, self.eps = rt, prefix, size, eps
+
+        def param_specs(self):
+            return [ParamSpec(f"{self.prefix}.weight", (self.size,), "norm"), ParamSpec(f"{self.prefix}.bias", (self.size,), "linear")]
+
+        def bind(self, get):
+            self.w, self.b = get(f"{self.prefix}.weight").float(), get(f"{self.prefix}.bias").float()
+
+        def forward(self, x, out_dtype):
+            x = x.float()
+            c = x - x.mean(dim=-1, keepdim=True)
+            return (c * torch.rsqrt((c * c).mean(dim=-1, keepdim=True) + self.eps) * self.w + self.b).to(out_dtype)
+
+        def add_forward(self, residual, delta, out_dtype, rows=None):
+            if delta is not None:
+                residual += delta.float()
+            return self.forward(residual if rows is None else residual[rows.long()], out_dtype)
+
+    class PostNormBlock(Block):
+        recordable = True
+
+        def __init__(self, mixer, ffn, norm1, norm2, act):
+            self.mixer, self.ffn, self.norm1, self.norm2, self.act = mixer, ffn, norm1, norm2, act
+
+        def children(self):
+            return [self.mixer, self.norm1, self.ffn, self.norm2]
+
+        def forward(self, residual, delta, step, cache, write_cache=True):
+            if delta is not None:
+                residual += delta.float()
+            a = self.mixer.forward(residual.to(self.act), step, cache, write_cache)
+            residual.copy_(self.norm1.add_forward(residual, a, torch.float32))
+            f = self.ffn.forward(residual.to(self.act), step)
+            residual.copy_(self.norm2.add_forward(residual, f, torch.float32))
+            return residual, None
+
+    def build(cfg, rt):
+        H, V, d, nq, nkv, inner, eps = (cfg[k] for k in ("hidden_size", "vocab_size", "head_dim", "heads", "kv_heads", "inner", "eps"))
+        rope = RotaryEmbedding(rt, d, cfg["theta"])
+        att = lambda i: GQAttention(rt, f"l{i}.attn", H, nq, nkv, d, rope, eps)
+        ffn = lambda i: SwiGLUFeedForward(rt, f"l{i}.mlp", H, inner)
+        pre = lambda i: PreNormBlock(att(i), ffn(i), RMSNorm(rt, f"l{i}.n1.weight", H, eps), RMSNorm(rt, f"l{i}.n2.weight", H, eps), rt.act_dtype)
+        blocks = [pre(0), PostNormBlock(att(1), ffn(1), CentredNorm(rt, "l1.n1", H, eps), CentredNorm(rt, "l1.n2", H, eps), rt.act_dtype), pre(2)]
+        return DecoderModel(rt, TokenEmbedding(rt, "emb.weight", V, H), blocks, [LayerCall(i, i) for i in range(3)],
+                            RMSNorm(rt, "norm.weight", H, eps), OutputHead(rt, "head.weight", V, H, None), V, cfg["max_len"])
+
+    register_architecture("ToyPostNormLM", dict, build, replace=True)
+    cfg = {"architectures": ["ToyPostNormLM"], "hidden_size": 512, "vocab_size": 211, "inner": 576, "heads": 4, "kv_heads": 1,
+           "head_dim": 128, "theta": 10000.0, "eps": 1e-5, "max_len": 128}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    specs = build(cfg, Runtime("cpu", torch.float32)).all_param_specs()
+    src = RandomWeights(specs, 11, std=0.05, norm_std=0.1)
+    weights = {n: src.get(n) for n in src.names()}
+    write_safetensors(tmp_path / "model.safetensors", weights)
+    w = {k: v.double() for k, v in weights.items()}
+    pcfg = {"num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 128, "hidden_size": 512, "rms_norm_eps": 1e-5, "rope_theta": 10000.0}
+
+    def centred(x, prefix):
+        c = x - x.mean(dim=-1, keepdim=True)
+        return c * torch.rsqrt((c * c).mean(dim=-1, keepdim=True) + cfg["eps"]) * w[f"{prefix}.weight"] + w[f"{prefix}.bias"]
+
+    def mlp(h, i):
+        return plain.feed_forward(h, {k.replace(f"l{i}.mlp.", "m."): v for k, v in w.items() if k.startswith(f"l{i}.mlp.")}, "m")
+
+    def plain_forward(ids):
+        x = w["emb.weight"][torch.tensor(ids)]
+        pos = torch.arange(len(ids))
+        for i in (0, 1, 2):
+            if i == 1:
+                x = centred(x + plain.attention_block(x, w, "l1.attn", pcfg, pos, 0)[0], "l1.n1")
+                x = centred(x + mlp(x, 1), "l1.n2")
+            else:
+                x = x + plain.attention_block(plain.rms_norm(x, w[f"l{i}.n1.weight"], cfg["eps"]), w, f"l{i}.attn", pcfg, pos, 0)[0]
+                x = x + mlp(plain.rms_norm(x, w[f"l{i}.n2.weight"], cfg["eps"]), i)
+        return plain.linear(plain.rms_norm(x, w["norm.weight"], cfg["eps"]), w["head.weight"])
+
+    runner = build_runner(tmp_path, EngineOptions(dtype=dtype, block_size=16, max_blocks=16, max_num_seqs=2, graph_after=1))
+    assert runner._can_record == (dtype == "bfloat16")
+    ids = [(13 * i * i + 7 * i + 3) % 211 for i in range(60)]
+    want = plain_forward(ids)
+    tol = 1e-5 if dtype == "float32" else 3e-2
+    for cuts in ([60], [25, 2, 20], [40]):
+        rows, pos = [], 0
+        for n in cuts:
+            rows.append(runner.step([StepEntry("r", ids[pos:pos + n], list(range(n)))]).double().cpu())
+            pos += n
+        while pos < 60:                                           # the rest token by token (recorded and replayed in bfloat16)
+            rows.append(runner.step([StepEntry("r", [ids[pos]], [0])]).double().cpu().clone())
+            pos += 1
+        runner.finish("r")
+        got = torch.cat(rows)
+        assert ((got - want).abs().max() / want.abs().max()) < tol, cuts
+    assert (runner.graph_replays > 0) == (dtype == "bfloat16")
+
+
 def test_toy_feed_forward_with_routing_chosen_layer_by_layer(tmp_path):
     """A feed-forward with a router and experts, defined here: top-2 of 3 small SwiGLU experts, router logits and
     the softmax over the chosen ones in 32-bit.  Layer 0 uses it, layer 1 the framework's dense feed-forward, both
