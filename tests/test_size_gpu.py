@@ -170,6 +170,26 @@ def test_decode_batches_that_are_no_bucket_through_recordings(runners):
         assert torch.isfinite(got).all() and err < BF16_TOL, (count, err)
 
 
+def test_a_decode_step_at_real_layer_sizes_is_five_kernels_a_layer(runners):
+    """The fused paths are what runs, not a fallback: a recorded decode step of 8 requests holds, per layer, the q|k|v
+    product (heads finished in its epilogue), attention, the o product, the gate|up product and the down product (the adds
+    and norms between them inside their epilogues), plus embedding, first norm, final norm and output head."""
+    from lucciola_b200.engine.step import StepEntry
+    r = runners["bfloat16"]
+    g = torch.Generator().manual_seed(19)
+    for i in range(8):
+        r.step([StepEntry(("k", i), torch.randint(0, CFG["vocab_size"], (50 + 7 * i,), generator=g).tolist(), [])])
+    one = lambda: r.step([StepEntry(("k", i), [int(torch.randint(0, CFG["vocab_size"], (1,), generator=g))], [0]) for i in range(8)])
+    one(); one()                                              # recorded at the first, replayed from then on
+    before, replays = r.kernel_launches(), r.graph_replays
+    one()
+    assert r.graph_replays == replays + 1
+    layers = CFG["num_hidden_layers"]
+    assert r.kernel_launches() - before == 5 * layers + 4
+    for i in range(8):
+        r.finish(("k", i))
+
+
 def test_generation_under_page_pressure_at_real_layer_sizes(runners):
     """Six prompts through Engine.generate with so few pages that requests are preempted and recomputed: every
     request finishes; the bfloat16 engine's tokens are the float32 engine's choice for the same prefix or within a
