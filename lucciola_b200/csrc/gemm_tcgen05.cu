@@ -422,6 +422,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const bool via_cluster = (!direct && p.cluster > 0) || (direct && p.swiglu);   // the tile goes to shared memory first
       float* part = (direct || via_cluster) ? nullptr : p.workspace + (size_t)split * p.M * p.N;
       float* part_smem = reinterpret_cast<float*>(smem);          // [BT][128]; the stages are drained by now
+      float* row_f = part_smem + BT * BM;                         // the rows' norm factors, when the input lacks them
+      if (p.rs.on && direct) {
+        // Eight threads a token, each adds every eighth block of the row (its loads are in flight together), then the
+        // eight add up in a fixed pattern: one round trip to the L2 for 16 tokens.  (Waiting for the kernel before this
+        // one any earlier, while the main loop runs, made the step slower, not faster: see the residual-add epilogue.)
+        pdl_wait();
+        const int t = threadIdx.x - 64, sub = t & 7;
+        for (int jb = 0; jb < BT && m0 + jb < p.M; jb += 16) {
+          const int j = jb + (t >> 3);
+          float part_sum = 0.f;
+          if (m0 + j < p.M) {
+            const float* src = p.rs.sumsq + (size_t)(m0 + j) * p.rs.tiles;
+            for (int i = sub; i < p.rs.tiles; i += 8) part_sum += __ldcg(src + i);
+          }
+          part_sum += __shfl_xor_sync(0xffffffffu, part_sum, 4);
+          part_sum += __shfl_xor_sync(0xffffffffu, part_sum, 2);
+          part_sum += __shfl_xor_sync(0xffffffffu, part_sum, 1);
+          if (sub == 0 && j < BT) row_f[j] = m0 + j < p.M ? rsqrtf(part_sum * p.rs.inv_width + p.rs.eps) : 0.f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
 #pragma unroll 1
       for (int c = 0; c < BT; c += 16) {
         uint32_t r[16];
@@ -435,7 +456,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           for (int j = 0; j < 16; ++j) {
             const int m = m0 + c + j;
             if (m < p.M) {
-              const float v = __uint_as_float(r[j]);
+              const float v = (p.rs.on && direct) ? __uint_as_float(r[j]) * row_f[c + j] : __uint_as_float(r[j]);
               if (!direct) part[(size_t)m * p.N + n] = v;
               else if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + n] = v;
               else ((bf16*)p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(v);
@@ -445,26 +466,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
       if (direct && p.swiglu) {
         // gate and up of a feature sit 64 lanes apart: pair them through shared memory
-        float* row_f = part_smem + BT * BM;                        // the rows' norm factors, when the input lacks them
-        if (p.rs.on) {
-          // Eight threads a token, each adds every eighth tile (its loads are in flight together), then the eight add up
-          // in a fixed pattern: one round trip to the L2 for 16 tokens.  (Waiting for the kernel before this one any
-          // earlier, while the main loop runs, made the step slower, not faster.)
-          pdl_wait();
-          const int t = threadIdx.x - 64, sub = t & 7;
-          for (int jb = 0; jb < BT && m0 + jb < p.M; jb += 16) {
-            const int j = jb + (t >> 3);
-            float part = 0.f;
-            if (m0 + j < p.M) {
-              const float* src = p.rs.sumsq + (size_t)(m0 + j) * p.rs.tiles;
-              for (int i = sub; i < p.rs.tiles; i += 8) part += __ldcg(src + i);
-            }
-            part += __shfl_xor_sync(0xffffffffu, part, 4);
-            part += __shfl_xor_sync(0xffffffffu, part, 2);
-            part += __shfl_xor_sync(0xffffffffu, part, 1);
-            if (sub == 0 && j < BT) row_f[j] = m0 + j < p.M ? rsqrtf(part * p.rs.inv_width + p.rs.eps) : 0.f;
-          }
-        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int t = threadIdx.x - 64, f = t & 63;
         const int feature = (n0 >> 1) + f;
@@ -640,11 +641,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           const float* sl = scratch + nl * 4;
           an.sumsq[(size_t)(m0 + j0 + nl) * an.tiles + blockIdx.x] = sl[0] + sl[1] + sl[2] + sl[3];
         }
-      } else if (n < p.N) {
+      } else {
+        float* tok_rf = reinterpret_cast<float*>(smem) + BT * BM;       // behind the partial tile
+        if (p.rs.on) {                                                  // the factors the input rows lack: a warp a token
+          pdl_wait();
+          for (int t = quarter; split * per + t < jend && m0 + split * per + t < p.M; t += 4) {
+            const float f = row_factor_warp(p.rs, m0 + split * per + t, lane);
+            if (lane == 0) tok_rf[t] = f;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        if (n < p.N)
         for (int j = split * per; j < jend; ++j) {
           const int m = m0 + j;
           if (m >= p.M) break;
-          const float acc = cluster_sum_f32(base + (uint32_t)j * (BM * 4u), splits);
+          float acc = cluster_sum_f32(base + (uint32_t)j * (BM * 4u), splits);
+          if (p.rs.on) acc *= tok_rf[j - split * per];
           if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + n] = acc;
           else ((bf16*)p.y)[(size_t)m * p.ldy + n] = __float2bfloat16_rn(acc);
         }
@@ -1387,9 +1399,7 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
                               long long ldy, float* workspace, long long workspace_elems, int* counters,
                               int counters_len, int force_bt, int force_splits, int swiglu, const lb::RowScale* row_scale,
                               cudaStream_t stream) {
-  LB_CHECK_ARG(!row_scale || ((swiglu || M > 256) && force_bt <= 0 && row_scale->sumsq && row_scale->tiles > 0),
-               "gemm_tcgen05: a row scale is taken by the many-token product (M > 256) and by the few-token product with the "
-               "fused SwiGLU only (M=%d)", M);
+  LB_CHECK_ARG(!row_scale || (row_scale->sumsq && row_scale->tiles > 0), "gemm_tcgen05: a row scale without partial sums");
   LB_CHECK_ARG(lb::valid_dtype(y_dtype), "gemm_tcgen05: bad output dtype %d", y_dtype);
   LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && ldx >= K && ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
   LB_CHECK_ARG(!swiglu || N % 128 == 0, "gemm_tcgen05: the fused SwiGLU needs gate and up rows in blocks of 64 (N=%d is no multiple of 128)", N);
@@ -1440,6 +1450,8 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   // (force_splits < 0 asks for -force_splits splits through the workspace).
   p.cluster = (!workspace_path && splits > 1 && splits <= 8) ? splits : 0;
   p.swiglu = swiglu;
+  LB_CHECK_ARG(!row_scale || splits == 1 || p.cluster > 0,
+               "gemm_tcgen05: a row scale is not taken by a product that is split through the workspace (M=%d, %d splits)", M, splits);
   if (row_scale) { p.rs = *row_scale; p.rs.on = 1; }
   if (int rc = lb::launch_for_tile(bt, mw, mx, p, splits, stream)) return rc;
   LB_CHECK_LAUNCH("gemm_tcgen05");

@@ -241,7 +241,7 @@ def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int,
     With `swiglu` the rows of w alternate in blocks of 64 between gate rows and up rows of the same 64
     features (see interleave_gate_up), and y[M, N/2] = silu(x . gate^T) * (x . up^T), formed in the epilogue.
     With `sumsq` [M, tiles] the rows of x lack the factor of an RMSNorm over K values: row m of the product is
-    multiplied by rsqrt(sum(sumsq[m]) / K + eps) before the activation (see gemm_tcgen05_addnorm)."""
+    multiplied by rsqrt(sum(sumsq[m]) / K + eps), before the activation if there is one (see gemm_tcgen05_addnorm)."""
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or tuple(y.shape) != (M, N // 2 if swiglu else N):

@@ -59,8 +59,8 @@ class Linear(Part):
         return RowScaled(out, sumsq, N, sink.eps)
 
     def row_scaled_ok(self, num_tokens: int) -> bool:
-        """Whether forward() takes rows without their norm's factor: the many-token product applies it in its epilogue."""
-        return self.rt.fast_kernels and num_tokens > 256 and self.in_features % 8 == 0
+        """Whether forward() takes rows without their norm's factor: the tensor-core products apply it in their epilogues."""
+        return self.rt.fast_kernels and self.in_features % 8 == 0
 
     def forward(self, x, out_dtype: torch.dtype | None = None, rows: int | None = None) -> torch.Tensor:
         """y = x . W^T; with `rows`, only the first `rows` output features.  x: a tensor, or RowScaled."""

@@ -583,14 +583,15 @@ def test_gemm_tcgen05_swiglu_of_rows_that_lack_their_factor(env, M, I, K):
     g = (x.double() @ gate.double().t()).cpu() * factor
     u = (x.double() @ up.double().t()).cpu() * factor
     assert rel(act.cpu(), plain.swiglu(g, u)) < 6e-3
-    if M <= 256:
-        with pytest.raises(ops.KernelError, match="row scale"):               # few tokens without the activation: not taken
-            ops.gemm_tcgen05(torch.empty(M, 2 * I, device=dev, dtype=torch.bfloat16), x, w, st, sumsq=sumsq, eps=eps)
-    else:                                                                     # many tokens: the plain product takes it too
-        y = torch.full((M, 2 * I), float("nan"), device=dev, dtype=torch.bfloat16)
+    # the product without the activation takes the factors too (few tokens: split over a cluster or not; many tokens)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        y = torch.full((M, 2 * I), float("nan"), device=dev, dtype=out_dtype)
         ops.gemm_tcgen05(y, x, w, st, sumsq=sumsq, eps=eps)
         torch.cuda.synchronize()
         assert rel(y.cpu(), (x.double() @ w.double().t()).cpu() * factor) < 5e-3
+    if M <= 256:
+        with pytest.raises(ops.KernelError, match="through the workspace"):   # but not a product split through the workspace
+            ops.gemm_tcgen05(torch.empty(M, 2 * I, device=dev, dtype=torch.bfloat16), x, w, st, force_splits=-2, sumsq=sumsq, eps=eps)
 
 
 def test_gemm_tcgen05_refuses_what_it_cannot_do(env):
