@@ -915,7 +915,7 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
                       (long long)num_pages * num_kv_heads * page_size < (1ll << 31);
   // Up to 8 splits (a power of two) of tiles of at most 16 rows combine inside a thread-block cluster; the TMA kernel
   // also takes clusters of 16 (a size the launch has to ask for: not every GPU schedules it).
-  const bool may_cluster = part_rows <= 16 && splits <= (by_tma ? 16 : 8) && (splits & (splits - 1)) == 0 && !force_workspace;
+  const bool may_cluster = part_rows <= 16 && splits <= (by_tma ? 16 : 8) && !force_workspace;
   LB_CHECK_ARG(splits == 1 || may_cluster || (workspace && workspace_elems >= lb_attention_flash_workspace(num_tiles, num_kv_heads, splits, part_rows, head_dim)),
                "attention_flash: the workspace is too small for %d splits", splits);
   lb::FlashParams p;

@@ -484,7 +484,7 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     n = tiles.shape[0]
     ws, ws_elems = None, 0
     by_tma = tma and max_rows <= 16 and page_size in (8, 16, 32, 64, 128)
-    in_cluster = max_rows <= 16 and not force_workspace and (splits in (2, 4, 8) or (splits == 16 and by_tma))
+    in_cluster = max_rows <= 16 and not force_workspace and (2 <= splits <= 8 or (splits <= 16 and by_tma))
     if splits > 1 and not in_cluster:
         ws_elems = n * num_kv_heads * splits * max_rows * (head_dim + 2)
         ws = _attention_workspace(q.device, ws_elems)
