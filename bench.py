@@ -307,7 +307,7 @@ def run_pressure32b(rng, pk, layers=0, B=64, prompt=4096, new=256) -> dict:
     reqs = [engine.add_request(rng.integers(0, V, size=prompt).tolist(), SamplingParams(max_new_tokens=new, ignore_eos=True))
             for _ in range(B)]
     torch.cuda.synchronize()
-    ms, decode_ms, decode_bytes = [], 0.0, 0.0
+    ms, decode_fracs = [], []
     t_all = time.perf_counter()
     while engine.has_unfinished():
         cached = sum(r.num_computed for r in engine.scheduler.running)
@@ -317,8 +317,7 @@ def run_pressure32b(rng, pk, layers=0, B=64, prompt=4096, new=256) -> dict:
         dt = (time.perf_counter() - t0) * 1e3
         ms.append(dt)
         if events and engine.runner.tokens_run - tokens0 == len(events):      # single tokens only: a decode step
-            decode_ms += dt
-            decode_bytes += weight_bytes + cached * kv_per_token
+            decode_fracs.append((weight_bytes + cached * kv_per_token) / (dt * 1e-3) / 1e9 / pk["hbm_gbs"])
     total_s = time.perf_counter() - t_all
     generated = sum(len(r.output) for r in reqs)
     st = engine.stats()
@@ -327,7 +326,9 @@ def run_pressure32b(rng, pk, layers=0, B=64, prompt=4096, new=256) -> dict:
            "pressure32b_preemptions": st["preemptions"],
            "pressure32b_finished": sum(len(r.output) == new for r in reqs), "pressure32b_requests": B,
            "pressure32b_pages": pages, "pressure32b_pages_for_all": B * -(-(prompt + new) // 16),
-           "pressure32b_decode_hbm_frac": round(decode_bytes / max(decode_ms, 1e-9) / 1e6 / pk["hbm_gbs"], 4),
+           # the median over the steps of single tokens (the steps that record a CUDA graph among them are far slower)
+           "pressure32b_decode_hbm_frac": round(statistics.median(decode_fracs), 4) if decode_fracs else None,
+           "pressure32b_decode_steps": len(decode_fracs),
            "pressure32b_layers": layers, "pressure32b_steps": len(ms), "pressure32b_seconds": round(total_s, 2)}
     out.update({f"pressure32b_{k}": v for k, v in percentiles(ms).items()})
     return out
