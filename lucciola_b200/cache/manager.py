@@ -14,7 +14,7 @@ device_cache.py.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional, Hashable, Sequence
 
 from ..parts.base import KVPages, StateSlot

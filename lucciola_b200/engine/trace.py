@@ -17,7 +17,6 @@ import json
 import sys
 from pathlib import Path
 
-import numpy as np
 
 
 def main(argv: list[str] | None = None) -> int:

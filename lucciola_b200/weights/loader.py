@@ -17,7 +17,7 @@ from typing import Iterable, Protocol
 import torch
 
 from ..parts.base import ParamSpec
-from .safetensors_io import SafetensorsError, SafetensorsFile
+from .safetensors_io import SafetensorsFile
 
 
 class WeightError(ValueError):

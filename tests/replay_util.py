@@ -3,9 +3,7 @@ returns for them with the plain implementation."""
 from __future__ import annotations
 
 import random
-from functools import lru_cache
 
-import numpy as np
 import torch
 
 import plain_qwen3 as plain

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from conftest import TINY, tokens_for
+from conftest import tokens_for
 
 pytestmark = pytest.mark.gpu
 ACTS = [torch.float32, torch.bfloat16]

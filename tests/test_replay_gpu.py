@@ -1,9 +1,7 @@
 """The engine against the plain implementation under every way of cutting the work (GPU)."""
 import json
-import os
 import subprocess
 import sys
-from pathlib import Path
 
 import numpy as np
 import pytest
