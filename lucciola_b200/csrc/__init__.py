@@ -29,7 +29,7 @@ from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 _HERE = Path(__file__).resolve().parent
-ABI_VERSION = 2
+ABI_VERSION = 3
 LIB_NAME = "liblucciola_b200.so"
 
 NVCC_FLAGS = [

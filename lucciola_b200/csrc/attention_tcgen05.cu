@@ -60,7 +60,12 @@ struct TcAttnParams {
   const int4* tiles;                        // {first token, tokens, request index, unused}
   int num_q_heads, num_kv_heads, group, page_size, page_shift, window;
   float scale_log2;
+  // With gridDim.z > 1 the keys of every work item are cut into gridDim.z ranges of whole blocks, one CTA each; a CTA
+  // then leaves its rows unnormalised, with their reference value and sum, for ta_combine_kernel:
+  float* part_o;                            // [(item * kv heads + kv head) * ranges + range][TA_PART_ROWS][d] float32
+  float* part_ml;                           // [...][TA_PART_ROWS][2]: reference value (log2 domain, -inf: no key seen), sum
 };
+constexpr int TA_PART_ROWS = 256;           // rows of a work item in the partial results: (token of the item, head of the group)
 
 __device__ __forceinline__ uint32_t ta_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ta_mbar_init(uint32_t bar, uint32_t count) {
@@ -280,9 +285,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
   const int pos0 = p.positions[t0];
   const int pos_last = pos0 + ntok - 1;
   const int lo_tile = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-  const int kbeg = (lo_tile / TA_KEYS) * TA_KEYS;
-  const int kend = pos_last + 1;                // exclusive
-  const int nblocks = (kend - kbeg + TA_KEYS - 1) / TA_KEYS;
+  const int kbeg_all = (lo_tile / TA_KEYS) * TA_KEYS;
+  const int kend_all = pos_last + 1;            // exclusive
+  const int nblocks_all = (kend_all - kbeg_all + TA_KEYS - 1) / TA_KEYS;
+  // This CTA's range of blocks (all of them unless the keys are split; a range may be empty when the item sees few keys).
+  const int nsplit = gridDim.z, isplit = blockIdx.z;
+  const int blk0 = (int)((long long)nblocks_all * isplit / nsplit), blk1 = (int)((long long)nblocks_all * (isplit + 1) / nsplit);
+  const int kbeg = kbeg_all + blk0 * TA_KEYS;
+  const int kend = min(kend_all, kbeg_all + blk1 * TA_KEYS);       // keys from here on belong to the next range, or are not there
+  const int nblocks = blk1 - blk0;
   const int* bt = p.block_table + (size_t)seq * p.max_pages;
   // The page ids of the keys this work item visits, copied once into shared memory for the producers.
   int* spages = reinterpret_cast<int*>(smem + TA_PAGES_OFF);
@@ -292,7 +303,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
   __syncthreads();
   pdl_wait();                                   // the queries, keys and values below are what earlier kernels wrote
 
-  if (warp == 0 || warp == 10) {
+  if (nblocks <= 0) {
+    // ---- an empty range of a split item: its rows weigh nothing in the combination -------------------------------
+    if (warp >= 2 && warp < 10) {
+      const int t = (warp - 2) >> 2, r = (warp & 3) * 32 + lane;
+      const int tok_in_item = t * per + r / G;
+      if (r < per * G && tok_in_item < ntok) {
+        const size_t prow = (((size_t)blockIdx.y * p.num_kv_heads + kvh) * nsplit + isplit) * TA_PART_ROWS + tok_in_item * G + r % G;
+        p.part_ml[prow * 2] = -INFINITY;
+        p.part_ml[prow * 2 + 1] = 0.f;
+      }
+    }
+  } else if (warp == 0 || warp == 10) {
     // ---- producers: warp 0 the queries (TMA) and the keys, warp 10 the values ---------------------------------
     const bool is_v = warp == 10;
     if (!is_v && lane == 0) {
@@ -488,11 +510,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const int token = t0 + tok_in_item, head = kvh * G + r % G;
       uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)token * p.num_q_heads + head) * TA_D);
+      const size_t prow = (((size_t)blockIdx.y * p.num_kv_heads + kvh) * nsplit + isplit) * TA_PART_ROWS + tok_in_item * G + r % G;
+      if (nsplit > 1 && row_valid) {
+        p.part_ml[prow * 2] = m_ref;
+        p.part_ml[prow * 2 + 1] = l_run;
+      }
 #pragma unroll 1
       for (int c = 0; c < TA_D; c += 32) {
         uint32_t v[32];
         ta_tmem_ld32(o_addr + (uint32_t)c, v);              // warp-wide: rows without a token take part and write nothing
-        if (row_valid) {
+        if (nsplit > 1) {
+          if (row_valid) {
+            uint4* pdst = reinterpret_cast<uint4*>(p.part_o + prow * TA_D + c);
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) pdst[q4] = make_uint4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+          }
+        } else if (row_valid) {
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             uint32_t w[4];
@@ -512,6 +545,45 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
+// The rows of work items whose keys were cut into ranges: out = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z with
+// M = max_z m_z.  One warp a row (a lane adds up four dimensions), the rows of an item spread over gridDim.z blocks.
+// A range without keys for a row (m_z = -inf) is left out: its o_z may never have been written.
+constexpr int TA_MAX_SPLITS = 8;
+__global__ void __launch_bounds__(256) ta_combine_kernel(TcAttnParams p, int nsplit) {
+  pdl_trigger();
+  pdl_wait();
+  const int4 tile = p.tiles[blockIdx.x];
+  const int kvh = blockIdx.y, G = p.group;
+  const int rows = tile.y * G;
+  const int lane = threadIdx.x, warp = threadIdx.y;
+  const size_t base = ((size_t)blockIdx.x * p.num_kv_heads + kvh) * nsplit;
+  for (int r = blockIdx.z * blockDim.y + warp; r < rows; r += blockDim.y * gridDim.z) {
+    float w[TA_MAX_SPLITS];
+    float M = -INFINITY;
+#pragma unroll
+    for (int z = 0; z < TA_MAX_SPLITS; ++z) {
+      w[z] = z < nsplit ? __ldcg(p.part_ml + ((base + z) * TA_PART_ROWS + r) * 2) : -INFINITY;
+      M = fmaxf(M, w[z]);
+    }
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int z = 0; z < TA_MAX_SPLITS; ++z) {
+      if (z < nsplit && w[z] != -INFINITY) {
+        const float wz = exp2f(w[z] - M);
+        L += __ldcg(p.part_ml + ((base + z) * TA_PART_ROWS + r) * 2 + 1) * wz;
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_o + ((base + z) * TA_PART_ROWS + r) * TA_D) + lane);
+        acc.x += a.x * wz; acc.y += a.y * wz; acc.z += a.z * wz; acc.w += a.w * wz;
+      }
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const int token = tile.x + r / G, head = kvh * G + r % G;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(p.out + ((size_t)token * p.num_q_heads + head) * TA_D + lane * 4) =
+        make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
   }
 }
 
@@ -578,13 +650,21 @@ LB_EXPORT int lb_attention_tcgen05_ok(int num_q_heads, int num_kv_heads, int hea
   return 1;
 }
 
+// Floats of workspace a launch with `key_splits` ranges needs (0 for one range).
+LB_EXPORT long long lb_attention_tcgen05_workspace(int num_tiles, int num_kv_heads, int key_splits) {
+  if (key_splits <= 1) return 0;
+  return (long long)num_tiles * num_kv_heads * key_splits * lb::TA_PART_ROWS * (lb::TA_D + 2);
+}
+
 // q, out: [T, nq, 128] bfloat16.  k_cache, v_cache: [pages, nkv, page_size, 128].  tiles: {first token,
 // tokens, request index, 0} with tokens <= 2 * floor(128 / (nq / nkv)); the tokens of a tile are consecutive tokens of one
-// request at consecutive positions.
+// request at consecutive positions.  key_splits > 1 (at most 8): the keys of every tile are cut into that many ranges, a CTA
+// each, whose results a second kernel combines through `workspace` (float32, lb_attention_tcgen05_workspace elements).
 LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache, const void* v_cache, const int* positions,
                                    const int* block_table, const void* tiles, int num_tiles, int num_tokens,
                                    int num_q_heads, int num_kv_heads, int head_dim, int page_size, int num_pages,
-                                   int max_pages, int window, float scale, cudaStream_t stream) {
+                                   int max_pages, int window, float scale, int key_splits, float* workspace,
+                                   long long workspace_elems, cudaStream_t stream) {
   LB_CHECK_ARG(lb_attention_tcgen05_ok(num_q_heads, num_kv_heads, head_dim, page_size),
                "attention_tcgen05: needs head_dim 128, at most 128 query heads per kv head and a page size among 8, 16, 32, 64, 128 "
                "(got head_dim %d, %d/%d heads, pages of %d)", head_dim, num_q_heads, num_kv_heads, page_size);
@@ -600,7 +680,14 @@ LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache
     lb::set_error("attention_tcgen05: cuTensorMapEncodeTiled failed");
     return 3;
   }
+  LB_CHECK_ARG(key_splits >= 1 && key_splits <= lb::TA_MAX_SPLITS, "attention_tcgen05: %d key ranges, at most %d", key_splits, lb::TA_MAX_SPLITS);
+  LB_CHECK_ARG(key_splits == 1 || (workspace && ((uintptr_t)workspace % 16 == 0) &&
+                                   workspace_elems >= lb_attention_tcgen05_workspace(num_tiles, num_kv_heads, key_splits)),
+               "attention_tcgen05: %d key ranges of %d tiles need a 16-byte aligned workspace of %lld floats (got %lld)", key_splits,
+               num_tiles, lb_attention_tcgen05_workspace(num_tiles, num_kv_heads, key_splits), workspace_elems);
   lb::TcAttnParams p;
+  p.part_o = workspace;
+  p.part_ml = key_splits > 1 ? workspace + (size_t)num_tiles * num_kv_heads * key_splits * lb::TA_PART_ROWS * lb::TA_D : nullptr;
   p.out = (lb::bf16*)out; p.k_cache = (const uint8_t*)k_cache; p.v_cache = (const uint8_t*)v_cache; p.positions = positions; p.block_table = block_table; p.max_pages = max_pages;
   p.tiles = (const int4*)tiles; p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.group = group;
   p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
@@ -613,8 +700,12 @@ LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache
     if (e != cudaSuccess) { lb::set_error("attention_tcgen05: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e)); return 2; }
     configured = true;
   }
-  lb::launch(lb::attention_tcgen05_kernel, dim3(num_kv_heads, num_tiles), dim3(lb::TA_THREADS), smem, stream, mq, p);
+  lb::launch(lb::attention_tcgen05_kernel, dim3(num_kv_heads, num_tiles, key_splits), dim3(lb::TA_THREADS), smem, stream, mq, p);
   LB_CHECK_LAUNCH("attention_tcgen05");
+  if (key_splits > 1) {
+    lb::launch(lb::ta_combine_kernel, dim3(num_tiles, num_kv_heads, lb::TA_PART_ROWS / 32), dim3(32, 8), 0, stream, p, key_splits);
+    LB_CHECK_LAUNCH("attention_tcgen05 combine");
+  }
   return 0;
 }
 

@@ -35,7 +35,7 @@ LB_EXPORT int lb_upload(void* dst, const void* src, long long bytes, cudaStream_
 LB_EXPORT const char* lb_last_error() { return lb::g_error; }
 
 // Interface version; the Python side refuses a library of another version.
-LB_EXPORT int lb_abi_version() { return 2; }
+LB_EXPORT int lb_abi_version() { return 3; }
 
 // Compute capability of the current device as major*10+minor, or a negative
 // CUDA error code.

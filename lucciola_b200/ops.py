@@ -50,7 +50,7 @@ _SIGNATURES = {
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -505,18 +505,46 @@ def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, h
             and bool(lib.lb_attention_tcgen05_ok(num_q_heads, num_kv_heads, head_dim, page_size)))
 
 
+def attention_tcgen05_splits(num_tiles: int, num_kv_heads: int, max_span: int, sms: int = 148) -> int:
+    """Into how many key ranges the work items of the tensor-memory kernel are cut.  A CTA takes a whole SM, so a launch
+    of fewer CTAs than SMs (one portion of a few hundred tokens behind a long context) leaves SMs idle for as long as
+    its longest item lasts, and one of a few more CTAs than SMs runs a second round for them.  By a model fitted to
+    measurements (8 kv heads, items of 64 tokens): a CTA takes 6 us plus 0.0177 us per key it visits (8 us when it
+    leaves partial results), the launch as many rounds of that as its CTAs need on the SMs, and the second kernel
+    6 us plus 0.06 us per CTA (266 KB of partial results written and read again).  A cut must promise 5 % at least.  64 CTAs behind 7680 keys: 140 us whole, 87 us in two ranges; 8 CTAs behind 16 K keys:
+    240 and 43 us in eight.  A range has four blocks of 64 keys at least.  The count depends on the launch's shape alone
+    (tiles, kv heads, the bound of the context), never on where the requests stand, so a recorded step keeps it; it
+    takes every item to see `max_span` keys, which overrates whole prompts, whose items see half of that on average,
+    but those either fill the SMs many times over or are short."""
+    ctas = max(num_tiles * num_kv_heads, 1)
+    per_key = 0.0177 * max_span
+    best, best_cost = 1, -(-ctas // sms) * (6.0 + per_key)
+    for s in range(2, min(8, max_span // 256) + 1):
+        cost = -(-ctas * s // sms) * (8.0 + per_key / s) + 6.0 + 0.06 * ctas * s
+        if cost < 0.95 * best_cost:
+            best, best_cost = s, cost
+    return best
+
+
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, num_q_heads: int,
-                      num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, stream: int) -> None:
+                      num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, stream: int,
+                      key_splits: int = 1) -> None:
     """Attention of portions of prompts on tcgen05 (S and O in tensor memory).  tiles: int32 [n, 4] of
-    (first token, tokens, request index, 0) with tokens <= 2 * (128 // (nq // nkv))."""
+    (first token, tokens, request index, 0) with tokens <= 2 * (128 // (nq // nkv)).  With key_splits > 1 the keys of
+    every tile are cut into that many ranges, a CTA each, combined by a second kernel."""
     _check(q, "q", torch.bfloat16); _check(out, "attention output", torch.bfloat16)
     _check(k_cache, "k pool", torch.bfloat16); _check(v_cache, "v pool", torch.bfloat16)
     _check(positions, "positions", torch.int32); _check(block_table, "block table", torch.int32)
     _check(tiles, "tiles", torch.int32)
+    ws, ws_elems = None, 0
+    if key_splits > 1:
+        ws = _attention_workspace(q.device, tiles.shape[0] * num_kv_heads * key_splits * 256 * (head_dim + 2))
+        ws_elems = ws.numel()
     _call("lb_attention_tcgen05", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
           positions.data_ptr(), block_table.data_ptr(), tiles.data_ptr(), tiles.shape[0], q.shape[0], num_q_heads,
-          num_kv_heads, head_dim, page_size, k_cache.shape[0], block_table.shape[1], window, scale, stream)
+          num_kv_heads, head_dim, page_size, k_cache.shape[0], block_table.shape[1], window, scale, key_splits,
+          _ptr(ws), ws_elems, stream)
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
@@ -537,7 +565,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     if "big" in meta and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size,
                                               step.block_tables[group].shape[1]):
         attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"],
-                          num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
+                          num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream,
+                          key_splits=attention_tcgen05_splits(meta["big"].shape[0], num_kv_heads, span))
         kinds = ["rest"] if "rest" in meta else []
     for kind in kinds:
         tiles = meta[kind]

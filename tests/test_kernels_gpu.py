@@ -282,9 +282,10 @@ def test_attention_flash(env, nq, nkv, d, ps, window, seqs, splits, tma):
     assert rel(out.cpu(), ref) < 8e-3
 
 
-def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None, rows=256):
+def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None, rows=256, splits=1):
     """The tensor-memory kernel for portions of prompts (head size 128) against the float64 statement; work items
-    of up to `rows` query rows (256: two tiles in a CTA, 128: one)."""
+    of up to `rows` query rows (256: two tiles in a CTA, 128: one), their keys cut into `splits` ranges (the workspace
+    of the partial results holds NaN before: what a range did not write must not be read)."""
     d = 128
     kc, vc, bt, pos, seq = paged_setup(dev, seqs, nkv, d, ps, torch.bfloat16)
     fill_pages(kc, vc, bt.cpu(), seqs, ps)
@@ -300,7 +301,9 @@ def run_tc(ops, dev, st, nq, nkv, ps, window, seqs, hook=None, q=None, rows=256)
         t += n
     tl = torch.tensor(tiles, dtype=torch.int32, device=dev)
     out = torch.full_like(q, float("nan"))
-    ops.attention_tcgen05(q, out, kc, vc, pos, bt, tl, nq, nkv, d, ps, window, 1 / math.sqrt(d), st)
+    if splits > 1:
+        ops._attention_workspace(dev, len(tiles) * nkv * splits * 256 * (d + 2)).fill_(float("nan"))
+    ops.attention_tcgen05(q, out, kc, vc, pos, bt, tl, nq, nkv, d, ps, window, 1 / math.sqrt(d), st, key_splits=splits)
     torch.cuda.synchronize()
     assert ops.device_error() == 0
     ref = attention_reference(q, kc, vc, bt, pos.cpu(), seq.cpu(), nq, nkv, ps, window, 1 / math.sqrt(d))
@@ -325,6 +328,54 @@ def test_attention_tcgen05(env, nq, nkv, ps, window, seqs, rows):
     out, ref = run_tc(ops, dev, st, nq, nkv, ps, window, seqs, rows=rows)
     assert torch.isfinite(out).all()                # unused slots and freed pages hold NaN and must not reach a sum
     assert rel(out.cpu(), ref) < 8e-3
+
+
+@pytest.mark.parametrize("nq,nkv,ps,window,seqs", [
+    (4, 1, 16, 0, [(0, 32)]),                       # one block: all ranges but one are empty
+    (32, 8, 16, 0, [(0, 300), (100, 17), (0, 1)]),  # items of five, two and one blocks
+    (32, 8, 16, 0, [(3000, 64), (1500, 40)]),       # portions behind long contexts, what the split is for
+    (40, 8, 16, 0, [(2000, 100), (77, 30)]),        # five heads per kv head: rows of a tile unused
+    (4, 2, 32, 64, [(500, 100)]),                   # a window: the ranges begin at its first block
+    (2, 2, 128, 0, [(1000, 130)]),                  # a page of two blocks that a range's edge cuts
+    (8, 2, 16, 200, [(0, 700)]),                    # rows that see no key of the later ranges
+])
+@pytest.mark.parametrize("splits", [2, 3, 8])
+def test_attention_tcgen05_key_ranges(env, nq, nkv, ps, window, seqs, splits):
+    ops, dev, st = env
+    out, ref = run_tc(ops, dev, st, nq, nkv, ps, window, seqs, splits=splits)
+    assert torch.isfinite(out).all()
+    assert rel(out.cpu(), ref) < 8e-3
+
+
+def test_attention_tcgen05_key_ranges_far_key_and_spike(env):
+    """One key in the first range carries nearly all the weight of the last query, whose other ranges hold ordinary
+    keys: the combination must weigh the ranges by their reference values, not add them up."""
+    ops, dev, st = env
+    nq, nkv, ps = 8, 2, 16
+    q = torch.randn(1200, nq, 128, device=dev).bfloat16()
+
+    def far(kc, vc, bt):
+        for kvh in range(nkv):
+            kc[int(bt[0, 1]), kvh, 3] = (q[-1, kvh * 4].float() * 3).bfloat16()      # key 19
+            vc[int(bt[0, 1]), kvh, 3] = 7.0
+
+    for splits in (2, 5):
+        out, ref = run_tc(ops, dev, st, nq, nkv, ps, 0, [(0, 1200)], hook=far, q=q, splits=splits)
+        assert rel(out.cpu(), ref) < 8e-3 and (out[-1, 0].float() - 7.0).abs().max() < 0.2
+
+
+def test_attention_tcgen05_splits_rule():
+    from lucciola_b200 import ops
+    assert ops.attention_tcgen05_splits(32, 8, 2048) == 1           # a whole prompt: the launch fills the SMs
+    assert ops.attention_tcgen05_splits(128, 8, 8192) == 1
+    assert ops.attention_tcgen05_splits(8, 8, 8192) == 2            # 64 CTAs behind a long context: two ranges make 128
+    assert ops.attention_tcgen05_splits(8, 8, 1024) == 1            # too few keys to pay for the partial results
+    assert ops.attention_tcgen05_splits(16, 8, 8192) == 1           # 128 CTAs: any cut adds a round
+    assert ops.attention_tcgen05_splits(1, 8, 65536) == 8           # one item of a few tokens behind a very long context
+    assert ops.attention_tcgen05_splits(1, 8, 512) == 1
+    for tiles in range(1, 40):
+        for span in (256, 1024, 4096, 32768, 262144):
+            assert 1 <= ops.attention_tcgen05_splits(tiles, 8, span) <= min(8, max(1, span // 256))
 
 
 @pytest.mark.parametrize("order", ["growing", "shrinking", "late spike"])

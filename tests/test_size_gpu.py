@@ -245,7 +245,9 @@ def test_a_recording_survives_growth_of_the_attention_workspace(runners):
     r.step([StepEntry(("big", i), ids[i][3000:3008], [7]) for i in range(3)])
     for i in range(3):
         r.finish(("big", i))
-    assert ops._attn_ws[r.device.index].numel() > before and ops._attn_ws_retired, "the step did not make the workspace grow"
+    if ops._attn_ws[r.device.index].numel() == before:        # an earlier test has made it large enough for that step already
+        ops._attention_workspace(r.device, 2 * before + 1)
+    assert ops._attn_ws[r.device.index].numel() > before and ops._attn_ws_retired, "the workspace did not grow"
     r.step([StepEntry("w", ids[2][:600], [])])
     replays = r.graph_replays
     got2 = r.step([StepEntry("w", ids[2][600:608], list(range(8)))]).float().cpu().clone()     # the old recording, replayed
@@ -254,6 +256,34 @@ def test_a_recording_survives_growth_of_the_attention_workspace(runners):
     for got, ref in zip((got0, got1, got2), want):
         err = ((got - ref).abs().max() / ref.abs().max()).item()
         assert torch.isfinite(got).all() and err < BF16_TOL, err
+
+
+def test_portions_behind_a_long_context_cut_their_keys_into_ranges(runners, monkeypatch):
+    """A portion of a few dozen tokens behind thousands of cached ones makes fewer work items than the GPU has SMs; the
+    tensor-memory kernel then cuts every item's keys into ranges and a second kernel combines them.  Eagerly, recorded,
+    and replayed, against the float32 engine fed the prompt whole."""
+    from lucciola_b200 import ops
+    g = torch.Generator().manual_seed(23)
+    ids = torch.randint(0, CFG["vocab_size"], (3500,), generator=g).tolist()
+    ref = logits_of(runners["float32"], ids, [3500])
+    scale = ref.abs().max().item()
+    seen = []
+    plain = ops.attention_tcgen05
+
+    def spy(*args, key_splits=1, **kw):
+        seen.append((args[6].shape[0], key_splits))
+        return plain(*args, key_splits=key_splits, **kw)
+
+    monkeypatch.setattr(ops, "attention_tcgen05", spy)
+    r = runners["bfloat16"]
+    replays = r.graph_replays
+    for _ in range(3):
+        got = logits_of(r, ids, [3000, 64, 128, 200, 108])
+        err = ((got - ref).abs().max() / scale).item()
+        assert torch.isfinite(got).all() and err < BF16_TOL, err
+    assert (1, 8) in seen and all(k > 1 for n, k in seen if n <= 4), sorted(set(seen))      # 64 tokens: one item a kv head
+    assert r.graph_replays > replays
+    assert ops.device_error() == 0
 
 
 def test_sliding_window_at_the_real_head_size():
