@@ -286,6 +286,51 @@ def run_mixed14b(rng, pk, layers=0, steps=40) -> dict:
     return out
 
 
+def run_longprompt8b(rng, pk, layers=0, prompt=32768, new=4) -> dict:
+    """One request with a prompt of 32768 tokens through the engine with its default token budget of a step (576, as
+    lucciola's scheduler: src/scheduler.cc:48): 57 portions, each behind a longer cached context than the one before.
+    Time to the first generated token, prompt tokens a second and their share of the tensor peak."""
+    import torch
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.llm import Engine
+    from lucciola_b200.sampling.params import SamplingParams
+    name, shape = SHAPES["8b"]
+    layers = layers or shape["num_hidden_layers"]
+    cfg = dict(shape, num_hidden_layers=layers)
+    options = EngineOptions(dtype="bfloat16", block_size=16, max_blocks=(prompt + new) // 16 + 64, max_num_seqs=2,
+                            max_model_len=prompt + new + 16)
+    engine = Engine.from_random(cfg, seed=0, options=options)
+    per_layer, _, _ = model_bytes_and_flops(cfg, layers)
+    nq, d = cfg["num_attention_heads"], cfg["head_dim"]
+    flops = 2.0 * prompt * per_layer * layers + layers * nq * 4.0 * d * prompt * (prompt / 2)
+    ids = rng.integers(0, cfg["vocab_size"], size=prompt).tolist()
+    best, steps, at = None, 0, {}
+    for _ in range(3):                               # the first pass records the steps' shapes; the passes after replay them
+        req = engine.add_request(ids, SamplingParams(max_new_tokens=new, ignore_eos=True))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        marks = [torch.cuda.Event(enable_timing=True)]
+        marks[0].record()
+        while not req.output:
+            engine.step()
+            marks.append(torch.cuda.Event(enable_timing=True))
+            marks[-1].record()
+        ttft = time.perf_counter() - t0
+        while engine.has_unfinished():
+            engine.step()
+        steps = len(marks) - 1
+        if best is None or ttft < best:
+            best = ttft
+            budget = options.max_tokens_per_step
+            # the step that ends nearest below each context length, on the device's clock
+            at = {k: round(marks[k // budget - 1].elapsed_time(marks[k // budget]), 3) for k in (2048, 8192, 16384, 32768)}
+    return {"longprompt8b_layers": layers, "longprompt8b_prompt": prompt, "longprompt8b_budget": options.max_tokens_per_step,
+            "longprompt8b_steps": steps, "longprompt8b_first_token_ms": round(best * 1e3, 1),
+            "longprompt8b_tokens_per_s": round(prompt / best, 1),
+            "longprompt8b_frac": round(flops / best / (pk["bf16_tflops"] * 1e12), 4),
+            **{f"longprompt8b_step_ms_behind_{k // 1024}k": v for k, v in at.items()}}
+
+
 def run_pressure32b(rng, pk, layers=0, B=64, prompt=4096, new=256) -> dict:
     """64 requests with prompts of 4096 tokens generate 256 tokens each from a pool that holds fewer pages than they
     need together (64 x 272): the scheduler preempts the request admitted last and recomputes it later; every request
@@ -345,8 +390,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64 and the other workloads")
-    ap.add_argument("--workloads", default="ctx768,mixed8b,mixed14b,pressure32b",
+    ap.add_argument("--workloads", default="ctx768,mixed8b,mixed14b,longprompt8b,pressure32b",
                     help="which of the other workloads run (comma-separated; empty: none)")
+    ap.add_argument("--no-key-ranges", action="store_true",
+                    help="for comparison: the prompt-attention kernel never cuts the keys of its work items into ranges")
     ap.add_argument("--workload-layers", type=int, default=0,
                     help="fewer layers for the 14B and 32B workloads than their configurations have (reported with them)")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps from CUDA graphs")
@@ -381,6 +428,8 @@ def main() -> int:
     from lucciola_b200.engine.step import StepEntry
     from lucciola_b200.sampling.params import SamplingParams
 
+    if args.no_key_ranges:
+        ops.attention_tcgen05_splits = lambda *a, **k: 1
     if args.no_fuse_norms:
         args.fuse_norms = "none"
     if args.fuse_norms != "both":
@@ -537,12 +586,12 @@ def main() -> int:
         except Exception as e:                                       # noqa: BLE001
             extra["mixed8b_error"] = f"{type(e).__name__}: {e}"[:200]
     err = ops.device_error()
-    if any(w in workloads for w in ("mixed14b", "pressure32b")):
+    if any(w in workloads for w in ("mixed14b", "longprompt8b", "pressure32b")):
         import gc
         del engine, runner, logits
         gc.collect()
         torch.cuda.empty_cache()
-        for w, fn in (("mixed14b", run_mixed14b), ("pressure32b", run_pressure32b)):
+        for w, fn in (("mixed14b", run_mixed14b), ("longprompt8b", run_longprompt8b), ("pressure32b", run_pressure32b)):
             if w not in workloads:
                 continue
             try:
