@@ -364,20 +364,6 @@ def test_attention_tcgen05_key_ranges_far_key_and_spike(env):
         assert rel(out.cpu(), ref) < 8e-3 and (out[-1, 0].float() - 7.0).abs().max() < 0.2
 
 
-def test_attention_tcgen05_splits_rule():
-    from lucciola_b200 import ops
-    assert ops.attention_tcgen05_splits(32, 8, 2048) == 1           # a whole prompt: the launch fills the SMs
-    assert ops.attention_tcgen05_splits(128, 8, 8192) == 1
-    assert ops.attention_tcgen05_splits(8, 8, 8192) == 2            # 64 CTAs behind a long context: two ranges make 128
-    assert ops.attention_tcgen05_splits(8, 8, 1024) == 1            # too few keys to pay for the partial results
-    assert ops.attention_tcgen05_splits(16, 8, 8192) == 1           # 128 CTAs: any cut adds a round
-    assert ops.attention_tcgen05_splits(1, 8, 65536) == 8           # one item of a few tokens behind a very long context
-    assert ops.attention_tcgen05_splits(1, 8, 512) == 1
-    for tiles in range(1, 40):
-        for span in (256, 1024, 4096, 32768, 262144):
-            assert 1 <= ops.attention_tcgen05_splits(tiles, 8, span) <= min(8, max(1, span // 256))
-
-
 @pytest.mark.parametrize("order", ["growing", "shrinking", "late spike"])
 def test_attention_tcgen05_moving_maximum(env, order):
     """The row's reference value moves only when the maximum has grown by 2^8: keys whose scores grow from block to

@@ -334,3 +334,21 @@ def test_attention_split_counts_are_valid_and_hit_the_measured_points():
     assert attention_splits(1, 8, 8192, 4, wide_clusters=14) == 16      # one request: 16 ranges in clusters of 16
     assert attention_splits(1, 8, 32768, 4, wide_clusters=14) > 16      # very long: more ranges through the workspace
     assert attention_splits(2, 8, 8192, 4, wide_clusters=14) == 18      # 16 clusters of 16 would not fit at once
+
+
+def test_key_ranges_of_prompt_attention_are_valid_and_hit_the_measured_points():
+    """Into how many key ranges the work items of the tensor-memory prompt kernel are cut is a plan made on the host too: at
+    most 8, a range of 256 keys at least, none where the launch fills the SMs by itself; the measured points keep their answers."""
+    from lucciola_b200.ops import attention_tcgen05_splits
+    assert attention_tcgen05_splits(32, 8, 2048) == 1           # a whole prompt: the launch fills the SMs
+    assert attention_tcgen05_splits(128, 8, 8192) == 1
+    assert attention_tcgen05_splits(8, 8, 8192) == 2            # 64 CTAs behind a long context: two ranges make 128
+    assert attention_tcgen05_splits(8, 8, 1024) == 1            # too few keys to pay for the partial results
+    assert attention_tcgen05_splits(16, 8, 8192) == 1           # 128 CTAs: any cut adds a round
+    assert attention_tcgen05_splits(1, 8, 65536) == 8           # one item of a few tokens behind a very long context
+    assert attention_tcgen05_splits(1, 8, 512) == 1
+    for tiles in range(1, 40):
+        for heads in (1, 2, 8, 16):
+            for span in (1, 256, 1024, 4096, 32768, 262144):
+                s = attention_tcgen05_splits(tiles, heads, span)
+                assert 1 <= s <= min(8, max(1, span // 256)), (tiles, heads, span, s)
