@@ -98,6 +98,21 @@ class SafetensorsFile:
         t = torch.from_numpy(buf.copy() if n < (1 << 16) else np.array(buf, copy=True))
         return t.view(info.torch_dtype).reshape(info.shape)
 
+    def read_into(self, name: str, dst: torch.Tensor, start: int, n: int) -> None:
+        """Bytes [start, start + n) of the tensor's data into `dst` (uint8, contiguous, on the host), read from the
+        file itself: no page of a mapping is touched, and several threads may read at a time."""
+        import os
+        info = self.tensors[name]
+        if start < 0 or n < 0 or start + n > info.end - info.begin or dst.numel() < n:
+            raise SafetensorsError(f"{self.path}: bytes [{start}, {start + n}) do not lie in tensor {name!r} or in the buffer")
+        view = memoryview(dst.numpy())[:n]
+        at, done = self.data_offset + info.begin + start, 0
+        while done < n:
+            got = os.preadv(self._f.fileno(), [view[done:]], at + done)
+            if got <= 0:
+                raise SafetensorsError(f"{self.path}: the file ends inside tensor {name!r}")
+            done += got
+
     def close(self) -> None:
         if self._mm is not None:
             self._mm.close()

@@ -171,3 +171,20 @@ def test_random_model_program_writes_a_loadable_folder(tmp_path):
     from lucciola_b200.weights.loader import CheckpointFolder
     folder = CheckpointFolder(tmp_path / "m1")
     assert "model.embed_tokens.weight" in folder.names()
+
+
+def test_ranges_of_a_tensors_bytes_can_be_read_from_the_file(tmp_path):
+    """What the loader's pinned buffers are filled with: any range of a tensor's bytes, and nothing outside it."""
+    from lucciola_b200.weights.safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
+    t = torch.randn(301, 37)
+    write_safetensors(tmp_path / "a.safetensors", {"first": torch.arange(7, dtype=torch.int32), "x": t, "last": torch.ones(3)})
+    raw = t.view(torch.uint8).reshape(-1)
+    with SafetensorsFile(tmp_path / "a.safetensors") as f:
+        for start, n in ((0, raw.numel()), (5, 1), (1000, 4096), (raw.numel() - 3, 3), (17, 0)):
+            buf = torch.full((n + 8,), 255, dtype=torch.uint8)
+            f.read_into("x", buf, start, n)
+            assert torch.equal(buf[:n], raw[start:start + n]) and bool((buf[n:] == 255).all())
+        with pytest.raises(SafetensorsError):
+            f.read_into("x", torch.empty(64, dtype=torch.uint8), raw.numel() - 10, 11)
+        with pytest.raises(SafetensorsError):
+            f.read_into("x", torch.empty(4, dtype=torch.uint8), 0, 5)
