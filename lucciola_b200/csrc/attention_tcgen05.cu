@@ -35,6 +35,13 @@
 // Key and value rows outside the range a work item may see (past the last key, before the window, pages
 // that were given back) are filled with zeros instead of being read, so that whatever a reused page holds
 // cannot reach a sum; scores there are set to -inf by assignment.
+//
+// A CTA takes a whole SM, and a work item walks all the keys its tokens see: a portion of a few hundred tokens
+// behind a long context makes fewer items than the GPU has SMs, each as long as the context.  Such a launch cuts
+// the blocks of every item into gridDim.z ranges, one CTA each; a CTA then leaves its rows unnormalised, with
+// their reference value and sum, in a float32 workspace, and ta_combine_kernel weighs the ranges of a row by
+// 2^(m - M) in the ranges' order.  A range may be empty (an item that sees few keys): it leaves (-inf, 0) and no
+// rows, and the combining kernel does not read what it did not write.
 #include "common.cuh"
 
 #include <cuda.h>
