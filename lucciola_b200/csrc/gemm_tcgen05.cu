@@ -21,7 +21,8 @@
 // to) the partials go through a workspace in global memory and the CTA that finishes last for a
 // tile adds them, again in the order of the splits.  Either way the result does not depend on timing.
 //
-// With more than 256 tokens a second kernel takes over (gemm_tcgen05_prefill_kernel): tokens on the lanes, features on
+// With more than 256 tokens (and from 65 or 129 tokens on for products with many features, see lb_gemm_tcgen05) a second
+// kernel takes over (gemm_tcgen05_prefill_kernel): tokens on the lanes, features on
 // the columns, persistent CTAs over tiles of 128 tokens x up to 256 features with two accumulators, so that the epilogue
 // of a tile runs under the MMAs of the next; from 1024 tokens on as pairs of CTAs on tiles of 256 x 256 (tcgen05
 // cta_group::2: each CTA stages its 128 tokens and half of the weight rows, the first CTA issues the MMAs for both).
@@ -758,7 +759,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
 }
 
 // ---- many tokens: persistent CTAs, tokens on the lanes, two accumulators -----------------------------------
-// For more than 256 tokens the product is bound by the tensor cores, and the kernel is arranged for that:
+// With many tokens the product is bound by the tensor cores, and the kernel is arranged for that:
 // one CTA per SM walks over output tiles of 128 tokens x 256 features; tokens sit on the 128 lanes of the
 // accumulator, so an epilogue thread holds one token's row and stores 16 consecutive features as whole
 // 16-byte words; tensor memory holds two accumulators (2 x 256 columns), so the epilogue of one tile runs
@@ -1406,7 +1407,16 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   LB_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0, "gemm_tcgen05: K=%d and the row stride %lld must be multiples of 8 (TMA strides are multiples of 16 bytes)", K, ldx);
   LB_CHECK_ARG(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
   if (M == 0) return 0;
-  if (M > 256 && force_bt <= 0) {
+  // Which kernel: above 256 tokens the one with tokens on the lanes.  Below, it still wins where the product has many
+  // features for its inner size, so that its tiles fill the SMs without any cut along K: the gate|up product from 65
+  // tokens on (8B sizes, 128 tokens: 39 us against 46; 256 tokens: 58 against 92), other products with more features
+  // than inner size (q|k|v) from 129 tokens on (256 tokens: 26 us against 37).  The o and down products, few features
+  // and a long inner size, stay with the kernel that cuts K over a cluster (256 tokens, down: 37 us against 64).  The
+  // same at the sizes of every model of the family from 0.6B to 32B.  force_bt < 0 asks for the kernel with tokens on the
+  // lanes at any size; force_bt > 0 or a given split count for the other one.
+  const bool many = M > 256 ? force_bt <= 0
+                            : force_bt < 0 || (force_bt == 0 && force_splits == 0 && (swiglu ? M > 64 : (M > 128 && N > K)));
+  if (many) {
     // force_bt: 0 chooses between one CTA a tile of 128 tokens and a pair of CTAs a tile of 256, -1 asks for the former,
     // -2 for the latter
     // with many tokens force_splits stands for the feature width of the tiles (0: choose; -(c * 1024 + w): c columns of

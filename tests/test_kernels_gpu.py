@@ -516,6 +516,10 @@ def test_gemm_plain_is_true_32_bit(env):
     # CTA of the last pair without tokens, partial tiles in both directions, given widths, the sizes that choose pairs themselves
     (512, 256, 64, -2, 0), (300, 1000, 136, -2, 0), (1000, 300, 520, -2, 64), (640, 1030, 1024, -2, 224),
     (2048, 4096, 256, -2, -(9 * 1024 + 192)), (1300, 520, 4096, -2, 0), (1024, 6144, 512, 0, 0), (1024, 6144, 512, -1, 0),
+    # 129 to 256 tokens: tokens on the lanes when the product has more features than inner size, else the kernel that may cut K;
+    # either asked for by name at a size where the other would be chosen
+    (129, 1024, 512, 0, 0), (256, 2048, 1000, 0, 0), (200, 512, 1024, 0, 0), (200, 512, 1024, -1, 0), (65, 640, 256, -1, 0),
+    (256, 2048, 1024, 256, 0), (40, 4096, 64, -1, 0),
 ])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
@@ -538,7 +542,10 @@ def test_gemm_tcgen05(env, M, N, K, bt, splits, ty):
                                              (64, 192, 2048, 0, 0), (300, 320, 264, 0, 0), (2048, 1024, 256, 0, 0), (700, 64, 4096, 0, 0),
                                              (700, 1024, 2048, 0, 128), (512, 2048, 512, 0, 0),
                                              (1024, 1536, 512, 0, -(8 * 1024 + 128)), (2048, 12288, 64, 0, 0),
-                                             (1024, 1536, 512, -2, 0), (700, 512, 2048, -2, 128), (1100, 640, 256, -1, 0)])
+                                             (1024, 1536, 512, -2, 0), (700, 512, 2048, -2, 128), (1100, 640, 256, -1, 0),
+                                             # from 65 tokens on the kernel with tokens on the lanes; 64 stay with the other
+                                             (65, 256, 512, 0, 0), (128, 384, 1024, 0, 0), (200, 1024, 2048, 0, 0), (200, 1024, 2048, 256, 0),
+                                             (64, 384, 1024, -1, 0)])
 @pytest.mark.parametrize("ty", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05_with_swiglu_epilogue(env, M, I, K, bt, splits, ty):
     """gate and up rows interleaved in blocks of 64; the product's epilogue forms silu(gate) * up."""
