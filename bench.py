@@ -404,9 +404,10 @@ def main() -> int:
                          "between a block's feed-forward and the next block's mixer (entry), between mixer and feed-forward "
                          "(middle), both (the default), or none: always as a kernel of their own (for comparisons)")
     ap.add_argument("--no-fuse-norms", action="store_true", help="the same as --fuse-norms none")
-    ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], default=None,
+    ap.add_argument("--profile", choices=["decode", "prefill", "mixed", "chunk"], default=None,
                     help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off); "
-                         "mixed: --batch decoding requests at --context and one portion of --portion tokens of a new prompt")
+                         "mixed: --batch decoding requests at --context and one portion of --portion tokens of a new prompt; "
+                         "chunk: a portion of --portion tokens of one request behind --context tokens of its prompt")
     ap.add_argument("--portion", type=int, default=512, help="tokens of the portion of a --profile mixed step")
     args = ap.parse_args()
 
@@ -446,9 +447,10 @@ def main() -> int:
     batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
     page = 16
     max_b = max(batches)
-    pages = max_b * (-(-ctx // page)) + 64
+    longest = ctx + args.portion if args.profile == "chunk" else max(ctx, args.prefill_tokens)
+    pages = max_b * (-(-longest // page)) + 64
     options = EngineOptions(dtype="bfloat16", block_size=page, max_blocks=pages, max_num_seqs=max(64, max_b),
-                            max_tokens_per_step=max(args.prefill_tokens, 2048) + max_b, max_model_len=max(ctx, args.prefill_tokens),
+                            max_tokens_per_step=max(args.prefill_tokens, 2048) + max_b, max_model_len=longest,
                             use_cuda_graph=not (args.no_graph or args.profile))
     t_build = time.time()
     engine = Engine.from_random(cfg, seed=0, options=options)
@@ -466,6 +468,15 @@ def main() -> int:
         B, T = args.batch, args.prefill_tokens
         if args.profile == "prefill":
             entries = lambda i: [StepEntry(("p", i), rng.integers(0, V, size=T).tolist(), [T - 1])]
+        elif args.profile == "chunk":
+            # one request's next portion of --portion tokens behind --context tokens of its prompt (each call a new request)
+            def entries(i):
+                left = ctx
+                while left > 0:
+                    n = min(left, 2048)
+                    runner.step([StepEntry(("p", i), rng.integers(0, V, size=n).tolist(), [])])
+                    left -= n
+                return [StepEntry(("p", i), rng.integers(0, V, size=args.portion).tolist(), [])]
         else:
             for j in range(B):                                        # bring B requests to the context, untimed
                 left = ctx - 8
@@ -481,9 +492,10 @@ def main() -> int:
             runner.step(entries(i))
             if args.profile != "decode":
                 runner.finish(("p", i))
+        last = entries(3)
         torch.cuda.synchronize()
         torch.cuda.profiler.start()
-        runner.step(entries(3))
+        runner.step(last)
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
         print(json.dumps({"profiled": args.profile, "layers": args.layers, "batch": B, "context": ctx, "tokens": T}))
