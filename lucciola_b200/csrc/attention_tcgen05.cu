@@ -710,7 +710,7 @@ LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache
   lb::launch(lb::attention_tcgen05_kernel, dim3(num_kv_heads, num_tiles, key_splits), dim3(lb::TA_THREADS), smem, stream, mq, p);
   LB_CHECK_LAUNCH("attention_tcgen05");
   if (key_splits > 1) {
-    lb::launch(lb::ta_combine_kernel, dim3(num_tiles, num_kv_heads, lb::TA_PART_ROWS / 32), dim3(32, 8), 0, stream, p, key_splits);
+    lb::launch(lb::ta_combine_kernel, dim3(num_tiles, num_kv_heads, lb::TA_PART_ROWS / 8), dim3(32, 8), 0, stream, p, key_splits);   // a row a warp: one round of loads
     LB_CHECK_LAUNCH("attention_tcgen05 combine");
   }
   return 0;
