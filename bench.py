@@ -380,6 +380,48 @@ def run_pressure32b(rng, pk, layers=0, B=64, prompt=4096, new=256) -> dict:
     return out
 
 
+def time_attention_key_ranges() -> int:
+    """The prompt-attention kernel alone (CUDA events, 20 launches back to back after 3): one request's portion behind a
+    cached context, its work items' keys whole and cut into 2 to 8 ranges, at 8B and 14B head counts; the last column
+    is what `ops.attention_tcgen05_splits` takes.  Prints one line of JSON per case."""
+    import math
+
+    import torch
+
+    from lucciola_b200 import ops
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    nkv, d, page = 8, 128, 16
+    for nq in (32, 40):
+        for ctx, n in ((0, 512), (1536, 512), (7680, 512), (32256, 512), (7680, 128), (16384, 32), (7680, 1024)):
+            pages = -(-(ctx + n) // page)
+            kc = torch.randn(pages, nkv, page, d, device=dev).bfloat16()
+            vc = torch.randn(pages, nkv, page, d, device=dev).bfloat16()
+            table = torch.randperm(pages, dtype=torch.int32).view(1, pages).to(dev)
+            pos = torch.arange(ctx, ctx + n, dtype=torch.int32, device=dev)
+            q = torch.randn(n, nq, d, device=dev).bfloat16()
+            out = torch.empty_like(q)
+            per = 2 * (128 // (nq // nkv))
+            tiles = sorted(((off, min(per, n - off), 0, 0) for off in range(0, n, per)), key=lambda t: -t[0])
+            tl = torch.tensor(tiles, dtype=torch.int32, device=dev)
+            us = {}
+            for s in (1, 2, 3, 4, 8):
+                run = lambda: ops.attention_tcgen05(q, out, kc, vc, pos, table, tl, nq, nkv, d, page, 0, 1 / math.sqrt(d), st, key_splits=s)
+                for _ in range(3):
+                    run()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                for _ in range(20):
+                    run()
+                b.record()
+                torch.cuda.synchronize()
+                us[s] = round(a.elapsed_time(b) / 20 * 1e3, 1)
+            print(json.dumps({"query_heads": nq, "portion": n, "cached_context": ctx, "ctas": len(tiles) * nkv, "us_by_ranges": us,
+                              "rule": ops.attention_tcgen05_splits(len(tiles), nkv, ctx + n), "device_error": ops.device_error()}), flush=True)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -409,7 +451,11 @@ def main() -> int:
                          "mixed: --batch decoding requests at --context and one portion of --portion tokens of a new prompt; "
                          "chunk: a portion of --portion tokens of one request behind --context tokens of its prompt")
     ap.add_argument("--portion", type=int, default=512, help="tokens of the portion of a --profile mixed step")
+    ap.add_argument("--time-kernel", choices=["attention_key_ranges"], default=None,
+                    help="time one kernel alone over a grid of sizes, print a line of JSON a case, and exit")
     args = ap.parse_args()
+    if args.time_kernel == "attention_key_ranges":
+        return time_attention_key_ranges()
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
